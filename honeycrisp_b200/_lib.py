@@ -1,0 +1,92 @@
+"""ctypes binding of libhccuda.so, symbol for symbol as declared in include/hc_cuda.h.
+
+There is no fallback: if the library is missing and cannot be built, importing raises.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+
+from . import build as _build
+
+_i64 = ctypes.c_int64
+_vp = ctypes.c_void_p
+_int = ctypes.c_int
+_sz = ctypes.c_size_t
+
+HC_OK = 0
+HC_ERR_ALLOCATION_FAILED = 1
+HC_ERR_KERNEL_FAILED = 2
+HC_ERR_NOT_IMPLEMENTED = 3
+HC_ERR_INVALID_ARGUMENT = 4
+HC_ERR_TIMEOUT = 5
+HC_ERR_CUDA = 6
+
+HC_F16 = 0
+HC_F32 = 1
+
+HC_KERNEL_AUTO = 0
+HC_KERNEL_SIMT = 1
+HC_KERNEL_SIMT_EXACT = 2
+HC_KERNEL_TENSOR = 3
+
+
+class LaunchInfo(ctypes.Structure):
+    _fields_ = [
+        ("kernel", _int), ("tile_m", _int), ("tile_n", _int), ("tile_k", _int),
+        ("stages", _int), ("grid", _int), ("block", _int),
+        ("tiles", _i64), ("flops", _i64), ("scratch_bytes", _sz),
+    ]
+
+
+# name -> (restype, argtypes); the complete export list of include/hc_cuda.h
+SIGNATURES = {
+    "hc_init": (_int, [_int, ctypes.POINTER(_vp)]),
+    "hc_destroy": (None, [_vp]),
+    "hc_set_stream": (_int, [_vp, _vp]),
+    "hc_get_stream": (_vp, [_vp]),
+    "hc_get_device": (_int, [_vp]),
+    "hc_alloc": (_int, [_vp, _sz, ctypes.POINTER(_vp)]),
+    "hc_free": (_int, [_vp, _vp]),
+    "hc_h2d": (_int, [_vp, _vp, _vp, _sz]),
+    "hc_d2h": (_int, [_vp, _vp, _vp, _sz]),
+    "hc_sync": (_int, [_vp]),
+    "hc_event_record": (_int, [_vp, ctypes.POINTER(_vp)]),
+    "hc_event_wait": (_int, [_vp]),
+    "hc_event_elapsed_ms": (_int, [_vp, _vp, ctypes.POINTER(ctypes.c_float)]),
+    "hc_event_destroy": (None, [_vp]),
+    "hc_matmul": (_int, [_vp, _int, _vp, _int, _vp, _int, _int, _i64, _i64, _i64, _vp]),
+    "hc_batched_matmul": (_int, [_vp, _int, _i64, _vp, _int, _vp, _int, _int, _i64, _i64, _i64, _vp]),
+    "hc_batched_matmul_ex": (_int, [_vp, _int, _int, _i64, _vp, _int, _vp, _int, _int, _i64, _i64, _i64, _vp]),
+    "hc_batched_matmul_host": (_int, [_vp, _int, _i64, _vp, _int, _vp, _int, _int, _i64, _i64, _i64, _vp]),
+    "hc_matmul_colblock": (_int, [_vp, _int, _int, _vp, _int, _vp, _int, _int, _i64, _i64, _i64, _i64, _i64, _vp]),
+    "hc_status_string": (ctypes.c_char_p, [_int]),
+    "hc_last_error": (ctypes.c_char_p, [_vp]),
+    "hc_last_launch_info": (_int, [_vp, ctypes.POINTER(LaunchInfo)]),
+    "hc_launch_count": (_i64, [_vp]),
+    "hc_check_device_status": (_int, [_vp]),
+    "hc_version": (ctypes.c_char_p, []),
+}
+
+_lib = None
+
+
+def lib_path() -> str:
+    return _build.LIB_PATH
+
+
+def load() -> ctypes.CDLL:
+    """Load libhccuda.so (building it first if the sources are newer). Raises on failure."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    path = _build.LIB_PATH
+    if not os.path.exists(path) or os.environ.get("HC_CUDA_REBUILD") == "1":
+        path = _build.build()
+    L = ctypes.CDLL(path)
+    for name, (res, args) in SIGNATURES.items():
+        fn = getattr(L, name)  # AttributeError if the library lacks a declared symbol
+        fn.restype = res
+        fn.argtypes = args
+    _lib = L
+    return L

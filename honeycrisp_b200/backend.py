@@ -1,0 +1,302 @@
+"""Host-side mirror of the part of Honeycrisp's `Backend` interface that libhccuda serves.
+
+The reference's host language is Swift, for which this image has no toolchain; this module is
+the same surface in Python over the same C ABI, so the tests can read like the reference's own
+(Sources/HCTestUtils/BackendTests.swift:684-783).  Names and argument meaning follow
+
+* `Backend.matmul(a:transA:b:transB:transOut:rows:inner:cols:dtype:)`
+  (Sources/Honeycrisp/Backend.swift:650-658),
+* `Backend.batchedMatmul(matrixCount:a:transA:b:transB:transOut:rows:inner:cols:dtype:)`
+  (Backend.swift:661-669),
+* `Tensor.Data` (Sources/Honeycrisp/Tensor.swift:69-85): `byteCount`, `wait()`, `onCPU`,
+* `BackendError` (Backend.swift:6-16): allocationFailed / kernelFailed / notImplemented.
+
+Everything is computed by the CUDA library; nothing here has a CPU path.
+"""
+from __future__ import annotations
+
+import ctypes
+import enum
+from typing import Optional
+
+import numpy as np
+
+from . import _lib as L
+
+
+class BackendError(Exception):
+    """Base of the errors a backend call can throw (Backend.swift:6-16)."""
+
+
+class AllocationFailed(BackendError):
+    pass
+
+
+class KernelFailed(BackendError):
+    pass
+
+
+class NotImplementedByBackend(BackendError):
+    pass
+
+
+class DeviceTimeout(KernelFailed):
+    """A bounded device-side wait expired; the context is still usable."""
+
+
+class DType(enum.Enum):
+    float16 = "float16"
+    float32 = "float32"
+    int64 = "int64"  # legal in the reference's CPU backend; this backend throws notImplemented
+
+    @property
+    def byteSize(self) -> int:
+        return {"float16": 2, "float32": 4, "int64": 8}[self.value]
+
+    @property
+    def numpy(self):
+        return {"float16": np.float16, "float32": np.float32, "int64": np.int64}[self.value]
+
+
+def _as_dtype(dtype) -> DType:
+    if isinstance(dtype, DType):
+        return dtype
+    return DType(np.dtype(dtype).name)
+
+
+_HC_DTYPE = {DType.float16: L.HC_F16, DType.float32: L.HC_F32}
+
+
+class CUDAData:
+    """Device buffer handle: the `Tensor.Data` of this backend.
+
+    Either owns stream-ordered memory from the library's allocator, or borrows a device
+    pointer (for example a torch tensor's) and keeps `owner` alive for as long as it lives.
+    """
+
+    def __init__(self, backend: "CUDABackend", ptr: int, byteCount: int, owns: bool, owner=None):
+        self.backend = backend
+        self.ptr = int(ptr) if ptr else 0
+        self.byteCount = int(byteCount)
+        self._owns = owns
+        self._owner = owner
+        self._event: Optional[int] = None
+
+    def _mark(self):
+        """Record a completion marker after the work that produces this buffer."""
+        lib = L.load()
+        if self._event:
+            lib.hc_event_destroy(self._event)
+            self._event = None
+        ev = ctypes.c_void_p()
+        self.backend._check(lib.hc_event_record(self.backend._ctx, ctypes.byref(ev)))
+        self._event = ev.value
+
+    def wait(self) -> None:
+        """Tensor.Data.wait(): block until the buffer's producer has run; rethrow its failure."""
+        if self._event:
+            self.backend._check(L.load().hc_event_wait(self._event))
+        else:
+            self.backend.sync()
+
+    def onCPU(self, dtype=np.uint8) -> np.ndarray:
+        """Tensor.Data.onCPU: the buffer's bytes on the host, viewed as `dtype`."""
+        out = np.empty(self.byteCount, dtype=np.uint8)
+        if self.byteCount:
+            lib = L.load()
+            self.backend._check(lib.hc_d2h(self.backend._ctx, out.ctypes.data, self.ptr, self.byteCount))
+        self.backend.sync()
+        if self._event:
+            self.backend._check(L.load().hc_event_wait(self._event))
+        return out.view(dtype)
+
+    def free(self) -> None:
+        if self._event:
+            L.load().hc_event_destroy(self._event)
+            self._event = None
+        if self._owns and self.ptr and self.backend._ctx:
+            L.load().hc_free(self.backend._ctx, self.ptr)
+        self.ptr = 0
+        self._owner = None
+
+    def __del__(self):
+        try:
+            self.free()
+        except Exception:
+            pass
+
+
+class CUDABackend:
+    """`Backend` subclass counterpart: one CUDA device, one stream, matmul and batchedMatmul.
+
+    Methods of `Backend` outside the matrix-product path are not provided; asking for them
+    raises NotImplementedByBackend, the reference's convention for partial backends
+    (Backend.swift: every primitive defaults to `throw BackendError.notImplemented`).
+    """
+
+    def __init__(self, device: int = 0):
+        lib = L.load()
+        ctx = ctypes.c_void_p()
+        st = lib.hc_init(int(device), ctypes.byref(ctx))
+        if st != L.HC_OK:
+            raise KernelFailed(f"hc_init(device={device}) failed: {lib.hc_status_string(st).decode()}")
+        self._ctx = ctx.value
+        self.device = int(device)
+
+    # -- plumbing ------------------------------------------------------------------------
+
+    def close(self):
+        if getattr(self, "_ctx", None):
+            L.load().hc_destroy(self._ctx)
+            self._ctx = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def _check(self, status: int):
+        if status == L.HC_OK:
+            return
+        lib = L.load()
+        msg = lib.hc_last_error(self._ctx).decode() or lib.hc_status_string(status).decode()
+        if status == L.HC_ERR_ALLOCATION_FAILED:
+            raise AllocationFailed(msg)
+        if status == L.HC_ERR_NOT_IMPLEMENTED:
+            raise NotImplementedByBackend(msg)
+        if status == L.HC_ERR_TIMEOUT:
+            raise DeviceTimeout(msg)
+        if status == L.HC_ERR_INVALID_ARGUMENT:
+            # The reference traps these with #alwaysAssert before the backend is reached.
+            raise ValueError(msg)
+        raise KernelFailed(msg)
+
+    def useStream(self, cuda_stream_ptr: Optional[int]):
+        """Enqueue this backend's work on a stream owned by the caller (None: its own)."""
+        self._check(L.load().hc_set_stream(self._ctx, cuda_stream_ptr or None))
+
+    def sync(self):
+        self._check(L.load().hc_sync(self._ctx))
+
+    def checkDeviceStatus(self):
+        self._check(L.load().hc_check_device_status(self._ctx))
+
+    def launchCount(self) -> int:
+        return int(L.load().hc_launch_count(self._ctx))
+
+    def lastLaunchInfo(self) -> dict:
+        info = L.LaunchInfo()
+        self._check(L.load().hc_last_launch_info(self._ctx, ctypes.byref(info)))
+        return {name: getattr(info, name) for name, _ in L.LaunchInfo._fields_}
+
+    # -- buffers -------------------------------------------------------------------------
+
+    def allocate(self, byteCount: int) -> CUDAData:
+        ptr = ctypes.c_void_p()
+        self._check(L.load().hc_alloc(self._ctx, int(byteCount), ctypes.byref(ptr)))
+        return CUDAData(self, ptr.value, int(byteCount), owns=True)
+
+    def collection(self, values, dtype) -> CUDAData:
+        """Backend.collection (Backend.swift:794-800): host values -> device buffer."""
+        dt = _as_dtype(dtype)
+        arr = np.ascontiguousarray(np.asarray(values).astype(dt.numpy, copy=False)).reshape(-1)
+        data = self.allocate(arr.nbytes)
+        if arr.nbytes:
+            self._check(L.load().hc_h2d(self._ctx, data.ptr, arr.ctypes.data, arr.nbytes))
+            self.sync()  # the host array may be a temporary
+        return data
+
+    def wrap(self, device_ptr: int, byteCount: int, owner=None) -> CUDAData:
+        """Borrow device memory allocated elsewhere (e.g. `t.data_ptr()` of a CUDA torch tensor)."""
+        return CUDAData(self, device_ptr, byteCount, owns=False, owner=owner)
+
+    def _device_operand(self, x, dt: DType):
+        """Operands of a foreign Data type are staged to the device, as the reference's GPU
+        backend does through onCPU (Sources/Honeycrisp/BackendMPS.swift:585-620)."""
+        if isinstance(x, CUDAData):
+            return x
+        if isinstance(x, np.ndarray):
+            return self.collection(x, dt)
+        if hasattr(x, "data_ptr") and hasattr(x, "element_size"):  # a CUDA torch tensor
+            if not x.is_cuda or not x.is_contiguous():
+                raise ValueError("torch operands must be contiguous CUDA tensors")
+            return self.wrap(x.data_ptr(), x.numel() * x.element_size(), owner=x)
+        raise TypeError(f"unsupported operand type {type(x)!r}")
+
+    # -- the hot path --------------------------------------------------------------------
+
+    def matmul(self, a, transA: bool, b, transB: bool, transOut: bool, rows: int, inner: int, cols: int,
+               dtype, kernel: int = L.HC_KERNEL_AUTO, out: Optional[CUDAData] = None) -> CUDAData:
+        """`transOut(op(a) * op(b))`; rows x cols is the shape of op(a)*op(b) (Backend.swift:650-658)."""
+        return self.batchedMatmul(1, a, transA, b, transB, transOut, rows, inner, cols, dtype, kernel=kernel,
+                                  out=out)
+
+    def batchedMatmul(self, matrixCount: int, a, transA: bool, b, transB: bool, transOut: bool, rows: int,
+                      inner: int, cols: int, dtype, kernel: int = L.HC_KERNEL_AUTO,
+                      out: Optional[CUDAData] = None) -> CUDAData:
+        """matrixCount independent products, operands packed back to back (Backend.swift:661-669)."""
+        dt = _as_dtype(dtype)
+        if dt not in _HC_DTYPE:
+            raise NotImplementedByBackend(f"matmul for dtype {dt.value}")
+        a_d = self._device_operand(a, dt)
+        b_d = self._device_operand(b, dt)
+        n_out = matrixCount * rows * cols * dt.byteSize
+        # Same size checks the reference's GPU backend makes before encoding
+        # (Sources/Honeycrisp/BackendMPS.swift:2221-2230).
+        if a_d.byteCount < matrixCount * rows * inner * dt.byteSize:
+            raise ValueError("matmul: operand a is smaller than matrixCount*rows*inner elements")
+        if b_d.byteCount < matrixCount * inner * cols * dt.byteSize:
+            raise ValueError("matmul: operand b is smaller than matrixCount*inner*cols elements")
+        if out is None:
+            out = self.allocate(n_out)
+        elif out.byteCount < n_out:
+            raise ValueError("matmul: output buffer too small")
+        st = L.load().hc_batched_matmul_ex(self._ctx, int(kernel), _HC_DTYPE[dt], int(matrixCount), a_d.ptr,
+                                           int(bool(transA)), b_d.ptr, int(bool(transB)), int(bool(transOut)),
+                                           int(rows), int(inner), int(cols), out.ptr)
+        self._check(st)
+        out._mark()
+        out._inputs = (a_d, b_d)  # keep operands alive until the result is collected
+        return out
+
+    def matmulColumnBlock(self, a, transA: bool, b, transB: bool, transOut: bool, rows: int, inner: int,
+                          cols: int, colBegin: int, colCount: int, dtype, out: CUDAData,
+                          kernel: int = L.HC_KERNEL_AUTO) -> CUDAData:
+        """Columns [colBegin, colBegin+colCount) of op(a)*op(b), written in place into the
+        full-size `out`.  One device's share of a product split over devices."""
+        dt = _as_dtype(dtype)
+        if dt not in _HC_DTYPE:
+            raise NotImplementedByBackend(f"matmul for dtype {dt.value}")
+        a_d = self._device_operand(a, dt)
+        b_d = self._device_operand(b, dt)
+        if out.byteCount < rows * cols * dt.byteSize:
+            raise ValueError("matmulColumnBlock: output must be the full rows x cols buffer")
+        st = L.load().hc_matmul_colblock(self._ctx, int(kernel), _HC_DTYPE[dt], a_d.ptr, int(bool(transA)), b_d.ptr,
+                                         int(bool(transB)), int(bool(transOut)), int(rows), int(inner), int(cols),
+                                         int(colBegin), int(colCount), out.ptr)
+        self._check(st)
+        out._mark()
+        out._inputs = (a_d, b_d)
+        return out
+
+    def batchedMatmulHost(self, matrixCount: int, a: np.ndarray, transA: bool, b: np.ndarray, transB: bool,
+                          transOut: bool, rows: int, inner: int, cols: int, dtype,
+                          out: Optional[np.ndarray] = None) -> np.ndarray:
+        """Host arrays in, host array out: stage, multiply, read back, in one library call."""
+        dt = _as_dtype(dtype)
+        if dt not in _HC_DTYPE:
+            raise NotImplementedByBackend(f"matmul for dtype {dt.value}")
+        if a.dtype != dt.numpy or b.dtype != dt.numpy or not a.flags.c_contiguous or not b.flags.c_contiguous:
+            raise ValueError("host operands must be contiguous arrays of the stated dtype")
+        if a.size < matrixCount * rows * inner or b.size < matrixCount * inner * cols:
+            raise ValueError("host operand smaller than its stated shape")
+        if out is None:
+            out = np.empty(matrixCount * rows * cols, dtype=dt.numpy)
+        elif out.dtype != dt.numpy or out.size < matrixCount * rows * cols or not out.flags.c_contiguous:
+            raise ValueError("bad host output array")
+        st = L.load().hc_batched_matmul_host(self._ctx, _HC_DTYPE[dt], int(matrixCount), a.ctypes.data,
+                                             int(bool(transA)), b.ctypes.data, int(bool(transB)),
+                                             int(bool(transOut)), int(rows), int(inner), int(cols), out.ctypes.data)
+        self._check(st)
+        return out

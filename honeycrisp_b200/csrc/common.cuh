@@ -1,0 +1,59 @@
+// Shared declarations of libhccuda's translation units.
+#pragma once
+#include <cuda_runtime.h>
+#include <cuda_fp16.h>
+#include <stdint.h>
+#include <stddef.h>
+
+#include "../../include/hc_cuda.h"
+
+namespace hc {
+
+// A matrix product after the reference's three flags have been folded away.
+//
+// Backend.matmul computes transOut(op(a)*op(b)) (Sources/Honeycrisp/Backend.swift:650-658).
+// transOut(X*Y) = Y^T * X^T, so a transposed output is the plain product of the swapped
+// operands with their flags negated; the reference's GPU backend folds it the same way
+// (Sources/Honeycrisp/BackendMPS.swift:2200-2205).  What is left is C[M,N] = A[M,K] * B[K,N]
+// with C row-major and each operand either "K-major" (the contracted index is the
+// contiguous one) or "MN-major" (the row/column index of the product is contiguous).
+struct GemmProblem {
+  hc_dtype dtype;
+  int64_t batch;
+  int64_t M, N, K;
+  const void* A;   // K-major: stored [M][lda>=K];  MN-major: stored [K][lda>=M]
+  const void* B;   // K-major: stored [N][ldb>=K];  MN-major: stored [K][ldb>=N]
+  void* C;         // stored [M][ldc>=N]
+  int a_mn_major, b_mn_major;
+  int64_t lda, ldb, ldc;              // leading dimensions, elements
+  int64_t strideA, strideB, strideC;  // distance between consecutive matrices, elements
+};
+
+// Word in device memory that kernels set when a bounded wait gives up.
+enum DeviceStatusBits : unsigned int {
+  kDevTimeoutProducer = 1u,
+  kDevTimeoutMma = 2u,
+  kDevTimeoutEpilogue = 4u,
+};
+
+struct LaunchRecord {
+  int kernel = 0;
+  int tile_m = 0, tile_n = 0, tile_k = 0, stages = 0, grid = 0, block = 0;
+  int64_t tiles = 0;
+  size_t scratch_bytes = 0;
+  int launches = 0;
+};
+
+// CUDA-core kernel: any shape, any alignment.  exact = separate multiply and add.
+cudaError_t launch_simt(const GemmProblem& p, bool exact, cudaStream_t stream, LaunchRecord* rec);
+
+// tcgen05 kernel.  Returns cudaErrorNotSupported when TMA cannot describe the operands
+// (misaligned base or leading dimension); the caller then uses the CUDA-core kernel.
+// `status_word` is the device status word of the context; `scratch`/`scratch_bytes` is a
+// caller-provided work area for the float32 split operands (see tc_scratch_bytes).
+cudaError_t launch_tc(const GemmProblem& p, cudaStream_t stream, unsigned int* status_word,
+                      void* scratch, size_t scratch_bytes, int sm_count, LaunchRecord* rec);
+bool tc_supported(const GemmProblem& p);
+size_t tc_scratch_bytes(const GemmProblem& p);
+
+}  // namespace hc

@@ -1,0 +1,708 @@
+// Tensor-core matrix product for sm_100a: tcgen05.mma with the accumulator in tensor memory,
+// operands brought into shared memory by TMA through an mbarrier ring.
+//
+// One persistent CTA per SM walks a list of 128 x BN output tiles.  Inside a CTA:
+//   warp 0, one lane : TMA producer.  Fills a ring of kStages shared-memory slots with one
+//                      128-byte-wide k-slab of A and of B per slot (128B-swizzled).
+//   warp 1, one lane : MMA issuer.  For every filled slot issues the tcgen05.mma instructions
+//                      of that slab into one of two accumulator buffers in tensor memory, then
+//                      commits the slot back to the producer.
+//   warps 2..        : epilogue.  Drain a finished accumulator buffer (tcgen05.ld), round and
+//                      store it, and hand the buffer back, while the issuer already works on
+//                      the other buffer.
+//
+// Transposed operands are never moved: a "K-major" operand (contracted index contiguous) and
+// an "MN-major" one (row/column index contiguous) differ only in the TMA box shape and in one
+// bit of the instruction descriptor.
+//
+// float32 runs as 3xTF32: x = hi + lo with hi, lo representable in TF32, and
+// A*B ~= A_lo*B_hi + A_hi*B_lo + A_hi*B_hi.  The split operands live in a scratch area; the
+// producer alternates between the hi and lo tensor maps so the three products of each k-slab
+// land in the same accumulator.  Tensor-core accumulation does not round to nearest, so a long
+// contraction is cut into windows: every window accumulates in tensor memory, and the
+// epilogue warps add the windows together in registers with ordinary float32 adds.
+//
+// Every wait in this file is bounded: after a time limit the waiting thread records a bit in
+// the context's status word, raises a CTA-wide abort flag and the CTA leaves through the
+// normal teardown (tensor memory is freed).  The host reports HC_ERR_TIMEOUT.
+#include <cuda.h>
+#include <cstdlib>
+#include <mutex>
+
+#include "common.cuh"
+
+namespace hc {
+namespace {
+
+constexpr int BM = 128;
+constexpr unsigned long long kWaitLimitNs = 4000000000ull;  // 4 s
+
+struct TcParams {
+  int64_t M, N;
+  int num_k_blocks;   // slabs per tile, counting the three passes of a split product
+  int k_phases;       // 1, or 3 for split float32 operands
+  int chunk_kb;       // slabs per accumulation window (== num_k_blocks when not windowed)
+  int tiles_m, tiles_n;
+  int64_t total_tiles;
+  int group_m;
+  int a_mn_major, b_mn_major;
+  void* C;
+  int64_t ldc, strideC;
+  unsigned int* status;
+  int vec_ok;         // C base and ldc allow 16-byte stores
+  int debug;
+};
+
+// ---- PTX wrappers ---------------------------------------------------------------------------
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+  return (uint32_t)__cvta_generic_to_shared(p);
+}
+__device__ __forceinline__ unsigned long long globaltimer_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes)
+               : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+      "selp.u32 %0, 1, 0, p;\n"
+      "}\n"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+// Bounded wait.  False means: gave up (time limit, or another role of this CTA already did).
+__device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+  const unsigned long long t0 = globaltimer_ns();
+#pragma unroll 1
+  for (;;) {
+#pragma unroll 1
+    for (int i = 0; i < 64; i++)
+      if (mbar_try_wait(bar, parity)) return true;
+    if (*abort_flag) return false;
+    if (globaltimer_ns() - t0 > kWaitLimitNs) return false;
+  }
+}
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+#pragma unroll 1
+  for (int i = 0; i < 16; i++)
+    if (mbar_try_wait(bar, parity)) return true;
+  return mbar_wait_slow(bar, parity, abort_flag);
+}
+
+__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map, uint32_t bar,
+                                            int c0, int c1, int c2) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes "
+      "[%0], [%1, {%3, %4, %5}], [%2];"
+      ::"r"(dst), "l"((unsigned long long)map), "r"(bar), "r"(c0), "r"(c1), "r"(c2)
+      : "memory");
+}
+
+__device__ __forceinline__ void tc_fence_before() {
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+}
+__device__ __forceinline__ void tc_fence_after() {
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+}
+__device__ __forceinline__ void tc_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar)
+               : "memory");
+}
+template <bool kTf32>
+__device__ __forceinline__ void tc_mma(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc,
+                                       uint32_t idesc, uint32_t accumulate) {
+  if (kTf32) {
+    asm volatile(
+        "{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\n"
+        "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n}\n"
+        ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+        : "memory");
+  } else {
+    asm volatile(
+        "{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\n"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}\n"
+        ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+        : "memory");
+  }
+}
+// 32 lanes x 32 consecutive 32-bit columns: thread i of the warp gets lane (base+i).
+__device__ __forceinline__ void tmem_ld_x32(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
+        "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]),
+        "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]),
+        "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]),
+        "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() {
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+// Shared-memory matrix descriptor of tcgen05.mma, 128-byte swizzle.
+//   bits  0-13 start address >> 4      bits 16-29 leading-dimension byte offset >> 4
+//   bits 32-45 stride byte offset >> 4 bits 46-47 descriptor version (1 on sm_100)
+//   bits 61-63 swizzle mode (2 = 128 bytes)
+// K-major operand : rows are 128-byte k-slabs; 8-row groups are 1024 bytes apart (stride offset).
+// MN-major operand: each 128-byte row holds consecutive M (or N) indices for one k; 8 k-rows
+//                   form a 1024-byte group (stride offset); the next run of M/N indices starts
+//                   one whole box later (leading offset).
+__device__ __forceinline__ uint64_t make_smem_desc(uint32_t addr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+  uint64_t d = 0;
+  d |= (uint64_t)((addr >> 4) & 0x3FFF);
+  d |= (uint64_t)((lbo_bytes >> 4) & 0x3FFF) << 16;
+  d |= (uint64_t)((sbo_bytes >> 4) & 0x3FFF) << 32;
+  d |= (uint64_t)1 << 46;
+  d |= (uint64_t)2 << 61;
+  return d;
+}
+
+// Instruction descriptor of tcgen05.mma kind::f16 / kind::tf32 (dense, fp32 accumulate).
+//   bits 4-5 D format (1 = f32)   bits 7-9 A format   bits 10-12 B format (0 = f16, 2 = tf32)
+//   bit 15 A is MN-major          bit 16 B is MN-major
+//   bits 17-22 N >> 3             bits 24-28 M >> 4
+__host__ __device__ constexpr uint32_t make_idesc(bool tf32, int a_mn, int b_mn, int m, int n) {
+  return (1u << 4) | ((tf32 ? 2u : 0u) << 7) | ((tf32 ? 2u : 0u) << 10) | ((uint32_t)(a_mn & 1) << 15) |
+         ((uint32_t)(b_mn & 1) << 16) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
+}
+
+template <bool kHalf>
+__device__ __forceinline__ void store_row32(void* cbase, int64_t row_off, int64_t gn, int64_t N,
+                                            const float (&v)[32], bool vec_ok) {
+  if (kHalf) {
+    __half* dst = (__half*)cbase + row_off + gn;
+    if (vec_ok && gn + 32 <= N) {
+#pragma unroll
+      for (int q = 0; q < 4; q++) {
+        uint4 u;
+        __half2 h0 = __floats2half2_rn(v[q * 8 + 0], v[q * 8 + 1]);
+        __half2 h1 = __floats2half2_rn(v[q * 8 + 2], v[q * 8 + 3]);
+        __half2 h2 = __floats2half2_rn(v[q * 8 + 4], v[q * 8 + 5]);
+        __half2 h3 = __floats2half2_rn(v[q * 8 + 6], v[q * 8 + 7]);
+        u.x = *(uint32_t*)&h0; u.y = *(uint32_t*)&h1; u.z = *(uint32_t*)&h2; u.w = *(uint32_t*)&h3;
+        *(uint4*)(dst + q * 8) = u;
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < 32; j++)
+        if (gn + j < N) dst[j] = __float2half_rn(v[j]);
+    }
+  } else {
+    float* dst = (float*)cbase + row_off + gn;
+    if (vec_ok && gn + 32 <= N) {
+#pragma unroll
+      for (int q = 0; q < 8; q++)
+        *(float4*)(dst + q * 4) = make_float4(v[q * 4], v[q * 4 + 1], v[q * 4 + 2], v[q * 4 + 3]);
+    } else {
+#pragma unroll
+      for (int j = 0; j < 32; j++)
+        if (gn + j < N) dst[j] = v[j];
+    }
+  }
+}
+
+struct TileCoord { int64_t mat; int tm, tn; };
+__device__ __forceinline__ TileCoord decode_tile(int64_t tile, const TcParams& p) {
+  const int64_t per_mat = (int64_t)p.tiles_m * p.tiles_n;
+  TileCoord t;
+  t.mat = tile / per_mat;
+  const int r = (int)(tile % per_mat);
+  const int per_group = p.group_m * p.tiles_n;
+  const int g = r / per_group;
+  const int first_m = g * p.group_m;
+  const int gsize = min(p.group_m, p.tiles_m - first_m);
+  const int rr = r % per_group;
+  t.tm = first_m + rr % gsize;
+  t.tn = rr / gsize;
+  return t;
+}
+
+// kElemBytes: 2 (float16 operands) or 4 (float32 operands consumed as TF32).
+// kWindowed : epilogue sums accumulation windows in registers (float32 output only).
+template <int kElemBytes, int kBN, int kStages, int kEpiWarps, bool kWindowed>
+__global__ void __launch_bounds__(64 + 32 * kEpiWarps, 1)
+tc_gemm_kernel(const __grid_constant__ CUtensorMap mapA_hi, const __grid_constant__ CUtensorMap mapA_lo,
+               const __grid_constant__ CUtensorMap mapB_hi, const __grid_constant__ CUtensorMap mapB_lo,
+               const TcParams p) {
+  constexpr bool kTf32 = (kElemBytes == 4);
+  constexpr bool kOutHalf = (kElemBytes == 2);
+  constexpr int BK = 128 / kElemBytes;       // elements in one 128-byte slab row
+  constexpr int UMMA_K = 32 / kElemBytes;    // k per tcgen05.mma
+  constexpr int KGROUPS = UMMA_K / 8;        // 8-row k groups one MMA consumes of an MN-major operand
+  constexpr int CH = 128 / kElemBytes;       // M/N indices in one 128-byte row of an MN-major box
+  constexpr uint32_t A_BYTES = BM * 128, B_BYTES = kBN * 128, STAGE_BYTES = A_BYTES + B_BYTES;
+  constexpr int TMEM_COLS = (2 * kBN <= 32) ? 32 : 2 * kBN;
+  constexpr int COL_SPLIT = kEpiWarps / 4;   // epilogue warps sharing one lane quarter
+  constexpr int COLS_PER_THREAD = kBN / COL_SPLIT;
+  static_assert(kEpiWarps == 4 || kEpiWarps == 8, "epilogue warps come in groups of four");
+  static_assert(TMEM_COLS == 64 || TMEM_COLS == 128 || TMEM_COLS == 256 || TMEM_COLS == 512, "power of two");
+
+  extern __shared__ uint8_t smem_raw[];
+  __shared__ __align__(8) uint64_t bars[2 * kStages + 4];
+  __shared__ uint32_t tmem_base_slot;
+  __shared__ int abort_flag;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  const uint32_t bar_full = smem_u32(&bars[0]);
+  const uint32_t bar_empty = smem_u32(&bars[kStages]);
+  const uint32_t bar_tfull = smem_u32(&bars[2 * kStages]);
+  const uint32_t bar_tempty = smem_u32(&bars[2 * kStages + 2]);
+
+  if (threadIdx.x == 0) {
+    abort_flag = 0;
+    for (int s = 0; s < kStages; s++) {
+      mbar_init(bar_full + 8 * s, 1);
+      mbar_init(bar_empty + 8 * s, 1);
+    }
+    for (int s = 0; s < 2; s++) {
+      mbar_init(bar_tfull + 8 * s, 1);
+      mbar_init(bar_tempty + 8 * s, 32 * kEpiWarps);
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_slot)),
+                 "r"((uint32_t)TMEM_COLS)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = tmem_base_slot;
+  volatile int* abortp = &abort_flag;
+
+  const int nkb = p.num_k_blocks;
+  const int chunk_kb = p.chunk_kb;
+
+  if (warp == 0) {
+    // ---------------------------------------------------------------- TMA producer
+    if (lane == 0) {
+      asm volatile("prefetch.tensormap [%0];" ::"l"((unsigned long long)&mapA_hi) : "memory");
+      asm volatile("prefetch.tensormap [%0];" ::"l"((unsigned long long)&mapB_hi) : "memory");
+      uint32_t s = 0, ph = 0;
+      bool ok = true;
+      for (int64_t tile = blockIdx.x; ok && tile < p.total_tiles; tile += gridDim.x) {
+        const TileCoord t = decode_tile(tile, p);
+        const int m0 = t.tm * BM, n0 = t.tn * kBN, mat = (int)t.mat;
+        for (int kb = 0; kb < nkb; kb++) {
+          if (!mbar_wait(bar_empty + 8 * s, ph ^ 1, abortp)) {
+            atomicOr(p.status, kDevTimeoutProducer);
+            abort_flag = 1;
+            ok = false;
+            break;
+          }
+          const int phase = (p.k_phases == 3) ? kb % 3 : 2;
+          const int kc = ((p.k_phases == 3) ? kb / 3 : kb) * BK;
+          // pass 0: A_lo*B_hi, pass 1: A_hi*B_lo, pass 2: A_hi*B_hi
+          const CUtensorMap* ma = (phase == 0) ? &mapA_lo : &mapA_hi;
+          const CUtensorMap* mb = (phase == 1) ? &mapB_lo : &mapB_hi;
+          const uint32_t full = bar_full + 8 * s;
+          const uint32_t sa = smem_base + s * STAGE_BYTES, sb = sa + A_BYTES;
+          mbar_expect_tx(full, STAGE_BYTES);
+          if (!p.a_mn_major) {
+            tma_load_3d(sa, ma, full, kc, m0, mat);
+          } else {
+#pragma unroll
+            for (int c = 0; c < BM / CH; c++) tma_load_3d(sa + c * (BK * 128), ma, full, m0 + c * CH, kc, mat);
+          }
+          if (!p.b_mn_major) {
+            tma_load_3d(sb, mb, full, kc, n0, mat);
+          } else {
+#pragma unroll
+            for (int c = 0; c < kBN / CH; c++) tma_load_3d(sb + c * (BK * 128), mb, full, n0 + c * CH, kc, mat);
+          }
+          if (++s == kStages) { s = 0; ph ^= 1; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------------------------------------------------------- MMA issuer
+    if (lane == 0) {
+      const uint32_t idesc = make_idesc(kTf32, p.a_mn_major, p.b_mn_major, BM, kBN);
+      const bool swap = (p.debug & 1) != 0;
+      // K-major: leading offset unused (1), stride offset = 8 rows * 128 B.
+      // MN-major: leading offset = one box (BK rows * 128 B), stride offset = 8 k-rows * 128 B.
+      const uint32_t mn_lbo = swap ? 1024u : (uint32_t)(BK * 128), mn_sbo = swap ? (uint32_t)(BK * 128) : 1024u;
+      const uint32_t a_lbo = p.a_mn_major ? mn_lbo : 16u, a_sbo = p.a_mn_major ? mn_sbo : 1024u;
+      const uint32_t b_lbo = p.b_mn_major ? mn_lbo : 16u, b_sbo = p.b_mn_major ? mn_sbo : 1024u;
+      const uint32_t a_kstep = p.a_mn_major ? (uint32_t)(KGROUPS * 1024) : 32u;
+      const uint32_t b_kstep = p.b_mn_major ? (uint32_t)(KGROUPS * 1024) : 32u;
+      uint32_t s = 0, ph = 0, win = 0, slot = 0;
+      bool ok = true;
+      for (int64_t tile = blockIdx.x; ok && tile < p.total_tiles; tile += gridDim.x) {
+        for (int kb = 0; kb < nkb; kb++) {
+          const int in_win = kb % chunk_kb;
+          if (in_win == 0) {
+            slot = win & 1;
+            if (!mbar_wait(bar_tempty + 8 * slot, ((win >> 1) & 1) ^ 1, abortp)) {
+              atomicOr(p.status, kDevTimeoutMma);
+              abort_flag = 1;
+              ok = false;
+              break;
+            }
+            tc_fence_after();
+          }
+          if (!mbar_wait(bar_full + 8 * s, ph, abortp)) {
+            atomicOr(p.status, kDevTimeoutMma);
+            abort_flag = 1;
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t sa = smem_base + s * STAGE_BYTES, sb = sa + A_BYTES;
+          const uint64_t adesc = make_smem_desc(sa, a_lbo, a_sbo);
+          const uint64_t bdesc = make_smem_desc(sb, b_lbo, b_sbo);
+          const uint32_t d = tmem_base + slot * kBN;
+#pragma unroll
+          for (int k = 0; k < BK / UMMA_K; k++) {
+            tc_mma<kTf32>(d, adesc + (uint64_t)((k * a_kstep) >> 4), bdesc + (uint64_t)((k * b_kstep) >> 4), idesc,
+                          (in_win | k) ? 1u : 0u);
+          }
+          tc_commit(bar_empty + 8 * s);
+          if (in_win == chunk_kb - 1 || kb == nkb - 1) {
+            tc_commit(bar_tfull + 8 * slot);
+            win++;
+          }
+          if (++s == kStages) { s = 0; ph ^= 1; }
+        }
+      }
+    }
+  } else {
+    // ---------------------------------------------------------------- epilogue
+    const int ew = warp - 2;
+    const int quarter = warp & 3;            // tensor-memory lanes this warp may read
+    const int col_part = ew / 4;             // which share of the columns
+    const int col0 = col_part * COLS_PER_THREAD;
+    const uint32_t lane_base = (uint32_t)(quarter * 32) << 16;
+    uint32_t win = 0;
+    bool ok = true;
+    for (int64_t tile = blockIdx.x; ok && tile < p.total_tiles; tile += gridDim.x) {
+      const TileCoord t = decode_tile(tile, p);
+      const int64_t gm = (int64_t)t.tm * BM + quarter * 32 + lane;
+      const int64_t n0 = (int64_t)t.tn * kBN + col0;
+      void* cmat = kOutHalf ? (void*)((__half*)p.C + t.mat * p.strideC) : (void*)((float*)p.C + t.mat * p.strideC);
+      const int64_t row_off = gm * p.ldc;
+      const int nwin = (nkb + chunk_kb - 1) / chunk_kb;
+      if (!kWindowed) {
+        const uint32_t slot = win & 1;
+        bool got = mbar_wait(bar_tfull + 8 * slot, (win >> 1) & 1, abortp);
+        got = __all_sync(0xffffffffu, got);
+        if (!got) {
+          if (lane == 0) { atomicOr(p.status, kDevTimeoutEpilogue); abort_flag = 1; }
+          ok = false;
+          break;
+        }
+        tc_fence_after();
+        const uint32_t tbase = tmem_base + lane_base + slot * kBN + col0;
+#pragma unroll 1
+        for (int c = 0; c < COLS_PER_THREAD; c += 32) {
+          uint32_t r[32];
+          tmem_ld_x32(tbase + c, r);
+          tmem_ld_wait();
+          float v[32];
+#pragma unroll
+          for (int j = 0; j < 32; j++) v[j] = __uint_as_float(r[j]);
+          if (gm < p.M && n0 + c < p.N) store_row32<kOutHalf>(cmat, row_off, n0 + c, p.N, v, p.vec_ok != 0);
+        }
+        tc_fence_before();
+        mbar_arrive(bar_tempty + 8 * slot);
+        win++;
+      } else {
+        float acc[COLS_PER_THREAD];
+        for (int w = 0; w < nwin && ok; w++) {
+          const uint32_t slot = win & 1;
+          bool got = mbar_wait(bar_tfull + 8 * slot, (win >> 1) & 1, abortp);
+          got = __all_sync(0xffffffffu, got);
+          if (!got) {
+            if (lane == 0) { atomicOr(p.status, kDevTimeoutEpilogue); abort_flag = 1; }
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t tbase = tmem_base + lane_base + slot * kBN + col0;
+#pragma unroll
+          for (int c = 0; c < COLS_PER_THREAD; c += 32) {
+            uint32_t r[32];
+            tmem_ld_x32(tbase + c, r);
+            tmem_ld_wait();
+            if (w == 0) {
+#pragma unroll
+              for (int j = 0; j < 32; j++) acc[c + j] = __uint_as_float(r[j]);
+            } else {
+#pragma unroll
+              for (int j = 0; j < 32; j++) acc[c + j] = __fadd_rn(acc[c + j], __uint_as_float(r[j]));
+            }
+          }
+          tc_fence_before();
+          mbar_arrive(bar_tempty + 8 * slot);
+          win++;
+        }
+        if (ok && gm < p.M) {
+#pragma unroll
+          for (int c = 0; c < COLS_PER_THREAD; c += 32) {
+            float v[32];
+#pragma unroll
+            for (int j = 0; j < 32; j++) v[j] = acc[c + j];
+            if (n0 + c < p.N) store_row32<kOutHalf>(cmat, row_off, n0 + c, p.N, v, p.vec_ok != 0);
+          }
+        }
+      }
+    }
+  }
+
+  // ---------------------------------------------------------------- teardown
+  __syncwarp();
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  if (abort_flag) {
+    // Give copies and MMAs that were already issued time to land before the CTA's
+    // shared and tensor memory are handed to another CTA.
+    const unsigned long long t0 = globaltimer_ns();
+    while (globaltimer_ns() - t0 < 200000ull) { __nanosleep(1000); }
+    __syncthreads();
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)TMEM_COLS)
+                 : "memory");
+  }
+}
+
+// Splits float32 into two TF32-representable parts: hi = nearest TF32 of x, lo = nearest TF32
+// of (x - hi).  x - hi is exact in float32.  Non-finite x: hi = x, lo = 0, so infinities and
+// NaNs propagate through the hi*hi product only.
+__global__ void split_tf32_kernel(const float* __restrict__ src, float* __restrict__ hi, float* __restrict__ lo,
+                                  int64_t rows, int64_t width, int64_t ld_src, int64_t ld_dst, int64_t stride_src,
+                                  int64_t stride_dst, int64_t batch) {
+  const int64_t total = batch * rows * width;
+  for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t c = i % width, r = (i / width) % rows, b = i / (width * rows);
+    const float x = src[b * stride_src + r * ld_src + c];
+    uint32_t hbits;
+    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(hbits) : "f"(x));
+    float h = __uint_as_float(hbits & 0xFFFFE000u);
+    float l = 0.0f;
+    if (isfinite(x)) {
+      if (!isfinite(h)) h = __uint_as_float(__float_as_uint(x) & 0xFFFFE000u);
+      const float d = x - h;
+      uint32_t lbits;
+      asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(lbits) : "f"(d));
+      l = __uint_as_float(lbits & 0xFFFFE000u);
+    } else {
+      h = x;
+    }
+    hi[b * stride_dst + r * ld_dst + c] = h;
+    lo[b * stride_dst + r * ld_dst + c] = l;
+  }
+}
+
+// ---- host side ------------------------------------------------------------------------------
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = (EncodeTiledFn)p;
+  });
+  return fn;
+}
+
+// One operand as a rank-3 tensor {contiguous index, other index, matrix}.
+bool make_operand_map(CUtensorMap* map, const void* base, int elem_bytes, bool mn_major, int64_t mn, int64_t k,
+                      int64_t ld, int64_t stride_mat, int64_t batch, int tile_mn) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return false;
+  const int per_row = 128 / elem_bytes;
+  cuuint64_t dims[3] = {(cuuint64_t)(mn_major ? mn : k), (cuuint64_t)(mn_major ? k : mn), (cuuint64_t)batch};
+  cuuint64_t mat_bytes = (cuuint64_t)stride_mat * elem_bytes;
+  if (batch == 1) mat_bytes = (cuuint64_t)ld * elem_bytes * dims[1];
+  cuuint64_t strides[2] = {(cuuint64_t)ld * elem_bytes, mat_bytes};
+  cuuint32_t box[3] = {(cuuint32_t)per_row, (cuuint32_t)(mn_major ? per_row : tile_mn), 1};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = fn(map, elem_bytes == 2 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3,
+                  const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                  CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS;
+}
+
+bool operand_ok(const void* base, int elem_bytes, int64_t ld, int64_t stride_mat, int64_t batch, int64_t d0,
+                int64_t d1) {
+  if (((uintptr_t)base & 15) != 0) return false;
+  if ((ld * elem_bytes) % 16 != 0) return false;
+  if (batch > 1 && (stride_mat * elem_bytes) % 16 != 0) return false;
+  if (d0 >= (1ll << 31) || d1 >= (1ll << 31) || batch >= (1ll << 31)) return false;
+  if (ld * elem_bytes >= (1ll << 40) || stride_mat * elem_bytes >= (1ll << 40)) return false;
+  return true;
+}
+
+int debug_flags() {
+  static int v = -1;
+  if (v < 0) {
+    const char* e = getenv("HC_TC_DEBUG");
+    v = e ? atoi(e) : 0;
+  }
+  return v;
+}
+
+template <int kElemBytes, int kBN, int kStages, int kEpiWarps, bool kWindowed>
+cudaError_t launch_cfg(const CUtensorMap maps[4], const TcParams& p, int grid, cudaStream_t stream,
+                       LaunchRecord* rec) {
+  auto kern = tc_gemm_kernel<kElemBytes, kBN, kStages, kEpiWarps, kWindowed>;
+  constexpr size_t smem = (size_t)kStages * (BM * 128 + kBN * 128) + 1024;
+  static bool configured[64] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 64 && !configured[dev]) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return e;
+    configured[dev] = true;
+  }
+  const int block = 64 + 32 * kEpiWarps;
+  kern<<<grid, block, smem, stream>>>(maps[0], maps[1], maps[2], maps[3], p);
+  if (rec) {
+    rec->tile_m = BM; rec->tile_n = kBN; rec->tile_k = 128 / kElemBytes; rec->stages = kStages;
+    rec->grid = grid; rec->block = block; rec->launches++;
+  }
+  return cudaGetLastError();
+}
+
+}  // namespace
+
+bool tc_supported(const GemmProblem& p) {
+  if (p.M <= 0 || p.N <= 0 || p.K <= 0 || p.batch <= 0) return false;
+  const int eb = p.dtype == HC_F16 ? 2 : 4;
+  if (!operand_ok(p.A, eb, p.lda, p.strideA, p.batch, p.M, p.K)) return false;
+  if (!operand_ok(p.B, eb, p.ldb, p.strideB, p.batch, p.N, p.K)) return false;
+  if (p.M >= (1ll << 31) - 256 || p.N >= (1ll << 31) - 256 || p.K >= (1ll << 31) - 256) return false;
+  return encode_fn() != nullptr;
+}
+
+// float32 products split both operands into hi and lo copies, stored compactly with the
+// leading dimension rounded up to four elements so TMA can address them.
+static inline int64_t round4(int64_t x) { return (x + 3) & ~3ll; }
+struct SplitLayout {
+  int64_t a_rows, a_width, a_ld, a_mat, b_rows, b_width, b_ld, b_mat;
+  size_t a_bytes, b_bytes;
+};
+static SplitLayout split_layout(const GemmProblem& p) {
+  SplitLayout s;
+  s.a_rows = p.a_mn_major ? p.K : p.M; s.a_width = p.a_mn_major ? p.M : p.K;
+  s.b_rows = p.b_mn_major ? p.K : p.N; s.b_width = p.b_mn_major ? p.N : p.K;
+  s.a_ld = round4(s.a_width); s.b_ld = round4(s.b_width);
+  s.a_mat = s.a_rows * s.a_ld; s.b_mat = s.b_rows * s.b_ld;
+  s.a_bytes = ((size_t)(s.a_mat * p.batch) * 4 + 255) & ~(size_t)255;
+  s.b_bytes = ((size_t)(s.b_mat * p.batch) * 4 + 255) & ~(size_t)255;
+  return s;
+}
+
+size_t tc_scratch_bytes(const GemmProblem& p) {
+  if (p.dtype != HC_F32) return 0;
+  const SplitLayout s = split_layout(p);
+  return 2 * s.a_bytes + 2 * s.b_bytes;
+}
+
+cudaError_t launch_tc(const GemmProblem& p, cudaStream_t stream, unsigned int* status_word, void* scratch,
+                      size_t scratch_bytes, int sm_count, LaunchRecord* rec) {
+  if (!tc_supported(p)) return cudaErrorNotSupported;
+  const bool f32 = p.dtype == HC_F32;
+  const int eb = f32 ? 4 : 2;
+  const int BK = 128 / eb;
+  if (rec) { *rec = LaunchRecord(); rec->kernel = HC_KERNEL_TENSOR; }
+
+  const void *a_hi = p.A, *a_lo = p.A, *b_hi = p.B, *b_lo = p.B;
+  int64_t lda = p.lda, ldb = p.ldb, sa = p.strideA, sb = p.strideB;
+  if (f32) {
+    const SplitLayout s = split_layout(p);
+    if (!scratch || scratch_bytes < 2 * s.a_bytes + 2 * s.b_bytes) return cudaErrorInvalidValue;
+    float* base = (float*)scratch;
+    float* ah = base; float* al = (float*)((char*)ah + s.a_bytes);
+    float* bh = (float*)((char*)al + s.a_bytes); float* bl = (float*)((char*)bh + s.b_bytes);
+    const int threads = 256;
+    auto blocks = [&](int64_t n) { int64_t b = (n + threads - 1) / threads; return (int)(b > 148 * 16 ? 148 * 16 : (b < 1 ? 1 : b)); };
+    split_tf32_kernel<<<blocks(p.batch * s.a_rows * s.a_width), threads, 0, stream>>>(
+        (const float*)p.A, ah, al, s.a_rows, s.a_width, p.lda, s.a_ld, p.strideA, s.a_mat, p.batch);
+    split_tf32_kernel<<<blocks(p.batch * s.b_rows * s.b_width), threads, 0, stream>>>(
+        (const float*)p.B, bh, bl, s.b_rows, s.b_width, p.ldb, s.b_ld, p.strideB, s.b_mat, p.batch);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return e;
+    if (rec) { rec->launches += 2; rec->scratch_bytes = 2 * s.a_bytes + 2 * s.b_bytes; }
+    a_hi = ah; a_lo = al; b_hi = bh; b_lo = bl;
+    lda = s.a_ld; ldb = s.b_ld; sa = s.a_mat; sb = s.b_mat;
+  }
+
+  // Tile width: 256 columns unless the product is narrow.
+  const int bn = (p.N > 128) ? 256 : 128;
+  CUtensorMap maps[4];
+  if (!make_operand_map(&maps[0], a_hi, eb, p.a_mn_major, p.M, p.K, lda, sa, p.batch, BM) ||
+      !make_operand_map(&maps[1], a_lo, eb, p.a_mn_major, p.M, p.K, lda, sa, p.batch, BM) ||
+      !make_operand_map(&maps[2], b_hi, eb, p.b_mn_major, p.N, p.K, ldb, sb, p.batch, bn) ||
+      !make_operand_map(&maps[3], b_lo, eb, p.b_mn_major, p.N, p.K, ldb, sb, p.batch, bn))
+    return cudaErrorNotSupported;
+
+  TcParams tp;
+  tp.M = p.M; tp.N = p.N;
+  const int kslabs = (int)((p.K + BK - 1) / BK);
+  tp.k_phases = f32 ? 3 : 1;
+  tp.num_k_blocks = kslabs * tp.k_phases;
+  // float32: windows of 8 slabs (256 k, 24 MMA passes of 4 instructions) bound the number of
+  // non-rounding tensor-core accumulations that feed one rounded float32 add.
+  tp.chunk_kb = f32 ? 24 : tp.num_k_blocks;
+  if (tp.chunk_kb > tp.num_k_blocks) tp.chunk_kb = tp.num_k_blocks;
+  tp.tiles_m = (int)((p.M + BM - 1) / BM);
+  tp.tiles_n = (int)((p.N + bn - 1) / bn);
+  tp.total_tiles = (int64_t)tp.tiles_m * tp.tiles_n * p.batch;
+  tp.group_m = 16;
+  tp.a_mn_major = p.a_mn_major; tp.b_mn_major = p.b_mn_major;
+  tp.C = p.C; tp.ldc = p.ldc; tp.strideC = p.strideC;
+  tp.status = status_word;
+  tp.vec_ok = (((uintptr_t)p.C & 15) == 0 && (p.ldc * eb) % 16 == 0 && (p.strideC * eb) % 16 == 0) ? 1 : 0;
+  tp.debug = debug_flags();
+  const int grid = (int)(tp.total_tiles < sm_count ? tp.total_tiles : sm_count);
+  if (rec) rec->tiles = tp.total_tiles;
+
+  const bool windowed = f32 && !(tp.debug & 2);
+  if (!windowed) tp.chunk_kb = tp.num_k_blocks;
+  if (!f32) {
+    if (bn == 256) return launch_cfg<2, 256, 4, 4, false>(maps, tp, grid, stream, rec);
+    return launch_cfg<2, 128, 6, 4, false>(maps, tp, grid, stream, rec);
+  }
+  if (windowed) {
+    if (bn == 256) return launch_cfg<4, 256, 4, 8, true>(maps, tp, grid, stream, rec);
+    return launch_cfg<4, 128, 6, 4, true>(maps, tp, grid, stream, rec);
+  }
+  if (bn == 256) return launch_cfg<4, 256, 4, 4, false>(maps, tp, grid, stream, rec);
+  return launch_cfg<4, 128, 6, 4, false>(maps, tp, grid, stream, rec);
+}
+
+}  // namespace hc

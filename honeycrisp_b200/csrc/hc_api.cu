@@ -1,0 +1,479 @@
+// C ABI of libhccuda: context, memory, ordering, and dispatch of the matrix products.
+// Declarations and the reference interfaces they replace are in include/hc_cuda.h.
+#include <cstdio>
+#include <cstring>
+#include <mutex>
+#include <new>
+#include <string>
+
+#include "common.cuh"
+
+struct hc_ctx {
+  int device = 0;
+  cudaStream_t own_stream = nullptr;
+  cudaStream_t stream = nullptr;
+  std::mutex mu;
+  unsigned int* status_word = nullptr;  // device memory
+  std::string last_error;
+  hc::LaunchRecord last;
+  int64_t last_flops = 0;
+  int64_t launch_count = 0;
+  int sm_count = 0;
+  // Work area of the float32 split operands; grown on demand, freed with the context.
+  void* scratch = nullptr;
+  size_t scratch_bytes = 0;
+  // Device staging buffers of the host-buffer entry point.
+  void* stage[3] = {nullptr, nullptr, nullptr};
+  size_t stage_bytes[3] = {0, 0, 0};
+};
+
+struct hc_event {
+  hc_ctx* ctx;
+  cudaEvent_t ev;
+};
+
+namespace {
+
+struct DeviceGuard {
+  int prev = -1;
+  bool ok = true;
+  explicit DeviceGuard(int dev) {
+    if (cudaGetDevice(&prev) != cudaSuccess) prev = -1;
+    if (prev != dev) ok = (cudaSetDevice(dev) == cudaSuccess);
+  }
+  ~DeviceGuard() {
+    int cur = -1;
+    if (prev >= 0 && cudaGetDevice(&cur) == cudaSuccess && cur != prev) cudaSetDevice(prev);
+  }
+};
+
+hc_status fail(hc_ctx* ctx, hc_status s, const std::string& msg) {
+  if (ctx) ctx->last_error = msg;
+  return s;
+}
+
+hc_status cuda_fail(hc_ctx* ctx, cudaError_t e, const char* what) {
+  hc_status s = HC_ERR_CUDA;
+  if (e == cudaErrorMemoryAllocation) s = HC_ERR_ALLOCATION_FAILED;
+  std::string msg = std::string(what) + ": " + cudaGetErrorString(e);
+  cudaGetLastError();  // clear the sticky-less error state
+  return fail(ctx, s, msg);
+}
+
+#define HC_CUDA_TRY(ctx, expr)                                   \
+  do {                                                           \
+    cudaError_t e__ = (expr);                                    \
+    if (e__ != cudaSuccess) return cuda_fail(ctx, e__, #expr);   \
+  } while (0)
+
+// Grow-only device buffer owned by the context.
+hc_status ensure_buffer(hc_ctx* ctx, void** buf, size_t* have, size_t need) {
+  if (need <= *have && *buf) return HC_OK;
+  if (*buf) {
+    // Earlier work on the stream may still read the old buffer.
+    HC_CUDA_TRY(ctx, cudaStreamSynchronize(ctx->stream));
+    HC_CUDA_TRY(ctx, cudaFree(*buf));
+    *buf = nullptr;
+    *have = 0;
+  }
+  size_t bytes = need ? need : 1;
+  cudaError_t e = cudaMalloc(buf, bytes);
+  if (e != cudaSuccess) {
+    *buf = nullptr;
+    cudaGetLastError();
+    char msg[96];
+    snprintf(msg, sizeof msg, "allocation of %zu bytes failed", bytes);
+    return fail(ctx, HC_ERR_ALLOCATION_FAILED, msg);
+  }
+  *have = bytes;
+  return HC_OK;
+}
+
+bool mul_overflows(int64_t a, int64_t b, int64_t* out) { return __builtin_mul_overflow(a, b, out); }
+
+// Folds (trans_a, trans_b, trans_out) into operand major-ness; optionally narrows to a
+// column block of op(a)*op(b).
+hc_status build_problem(hc_ctx* ctx, hc_dtype dtype, int64_t count, const void* a, int trans_a, const void* b,
+                        int trans_b, int trans_out, int64_t rows, int64_t inner, int64_t cols, int64_t col_begin,
+                        int64_t col_count, void* out, hc::GemmProblem* p) {
+  if (dtype != HC_F16 && dtype != HC_F32)
+    return fail(ctx, HC_ERR_NOT_IMPLEMENTED, "matmul: only float16 and float32 are implemented");
+  if (count < 0 || rows < 0 || inner < 0 || cols < 0) return fail(ctx, HC_ERR_INVALID_ARGUMENT, "negative dimension");
+  if (col_begin < 0 || col_count < 0 || col_begin + col_count > cols)
+    return fail(ctx, HC_ERR_INVALID_ARGUMENT, "column block outside the product");
+  int64_t t;
+  if (mul_overflows(rows, inner, &t) || mul_overflows(t, count, &t) || mul_overflows(inner, cols, &t) ||
+      mul_overflows(t, count, &t) || mul_overflows(rows, cols, &t) || mul_overflows(t, count, &t) ||
+      mul_overflows(t, 4, &t))
+    return fail(ctx, HC_ERR_INVALID_ARGUMENT, "operand size overflows int64");
+  const bool empty = (count == 0 || rows == 0 || cols == 0 || col_count == 0);
+  if (!empty && (!out || (inner > 0 && (!a || !b)))) return fail(ctx, HC_ERR_INVALID_ARGUMENT, "null operand");
+  const int64_t eb = dtype == HC_F16 ? 2 : 4;
+  const char* ap = (const char*)a;
+  const char* bp = (const char*)b;
+  char* cp = (char*)out;
+  p->dtype = dtype;
+  p->batch = count;
+  p->K = inner;
+  p->strideC = rows * cols;
+  if (!trans_out) {
+    // C[rows, cols] = op(a) * op(b); block = columns of C and of op(b).
+    p->M = rows; p->N = col_count;
+    p->A = ap; p->a_mn_major = trans_a ? 1 : 0; p->lda = trans_a ? rows : inner; p->strideA = rows * inner;
+    p->b_mn_major = trans_b ? 0 : 1; p->ldb = trans_b ? inner : cols; p->strideB = inner * cols;
+    p->B = bp + (trans_b ? col_begin * inner : col_begin) * eb;
+    p->C = cp + col_begin * eb; p->ldc = cols;
+  } else {
+    // out[cols, rows] = op(b)^T * op(a)^T; block = rows of out.
+    p->M = col_count; p->N = rows;
+    p->a_mn_major = trans_b ? 0 : 1; p->lda = trans_b ? inner : cols; p->strideA = inner * cols;
+    p->A = bp + (trans_b ? col_begin * inner : col_begin) * eb;
+    p->B = ap; p->b_mn_major = trans_a ? 1 : 0; p->ldb = trans_a ? rows : inner; p->strideB = rows * inner;
+    p->C = cp + col_begin * rows * eb; p->ldc = rows;
+  }
+  return HC_OK;
+}
+
+// Shapes below this many multiply-adds are served by the CUDA-core kernel under AUTO: a
+// 128 x 128 tensor-core tile would be mostly padding.
+constexpr int64_t kAutoTensorMinWork = 64ll * 64 * 64;
+
+hc_status run_problem(hc_ctx* ctx, hc_kernel kernel, const hc::GemmProblem& p, int64_t flops) {
+  ctx->last_flops = flops;
+  if (p.batch == 0 || p.M == 0 || p.N == 0) {
+    ctx->last = hc::LaunchRecord();
+    return HC_OK;
+  }
+  const int64_t eb = p.dtype == HC_F16 ? 2 : 4;
+  if (p.K == 0) {
+    // Empty contraction: every output is the empty sum, +0 (BackendCPU.swift:1293 starts at 0).
+    for (int64_t m = 0; m < p.batch; m++) {
+      HC_CUDA_TRY(ctx, cudaMemset2DAsync((char*)p.C + m * p.strideC * eb, p.ldc * eb, 0, p.N * eb, p.M, ctx->stream));
+    }
+    ctx->last = hc::LaunchRecord();
+    return HC_OK;
+  }
+  hc_kernel chosen = kernel;
+  if (kernel == HC_KERNEL_AUTO) {
+    const bool big = (p.M * p.N >= 64 * 64) && (p.M * p.N * p.K >= kAutoTensorMinWork) && p.K >= 32;
+    chosen = (big && hc::tc_supported(p)) ? HC_KERNEL_TENSOR : HC_KERNEL_SIMT;
+  }
+  cudaError_t e;
+  if (chosen == HC_KERNEL_TENSOR) {
+    if (!hc::tc_supported(p))
+      return fail(ctx, HC_ERR_NOT_IMPLEMENTED,
+                  "tensor-core kernel needs 16-byte aligned operands and leading dimensions");
+    const size_t need = hc::tc_scratch_bytes(p);
+    if (need) {
+      hc_status s = ensure_buffer(ctx, &ctx->scratch, &ctx->scratch_bytes, need);
+      if (s != HC_OK) return s;
+    }
+    e = hc::launch_tc(p, ctx->stream, ctx->status_word, ctx->scratch, ctx->scratch_bytes, ctx->sm_count, &ctx->last);
+  } else if (chosen == HC_KERNEL_SIMT || chosen == HC_KERNEL_SIMT_EXACT) {
+    e = hc::launch_simt(p, chosen == HC_KERNEL_SIMT_EXACT, ctx->stream, &ctx->last);
+  } else {
+    return fail(ctx, HC_ERR_INVALID_ARGUMENT, "unknown kernel selector");
+  }
+  ctx->launch_count += ctx->last.launches;
+  if (e != cudaSuccess) {
+    cudaGetLastError();
+    return fail(ctx, HC_ERR_KERNEL_FAILED, std::string("kernel launch failed: ") + cudaGetErrorString(e));
+  }
+  return HC_OK;
+}
+
+int64_t flop_count(int64_t count, int64_t rows, int64_t inner, int64_t cols) {
+  return 2 * count * rows * inner * cols;
+}
+
+}  // namespace
+
+extern "C" {
+
+hc_status hc_init(int device, hc_ctx** out) {
+  if (!out) return HC_ERR_INVALID_ARGUMENT;
+  *out = nullptr;
+  int n = 0;
+  if (cudaGetDeviceCount(&n) != cudaSuccess || device < 0 || device >= n) {
+    cudaGetLastError();
+    return HC_ERR_INVALID_ARGUMENT;
+  }
+  hc_ctx* ctx = new (std::nothrow) hc_ctx();
+  if (!ctx) return HC_ERR_ALLOCATION_FAILED;
+  ctx->device = device;
+  DeviceGuard g(device);
+  cudaDeviceProp prop;
+  if (!g.ok || cudaGetDeviceProperties(&prop, device) != cudaSuccess) {
+    delete ctx;
+    return HC_ERR_CUDA;
+  }
+  if (prop.major != 10) {
+    // The kernels in this library are built for sm_100a only.
+    delete ctx;
+    return HC_ERR_NOT_IMPLEMENTED;
+  }
+  ctx->sm_count = prop.multiProcessorCount;
+  if (cudaStreamCreateWithFlags(&ctx->own_stream, cudaStreamNonBlocking) != cudaSuccess ||
+      cudaMalloc((void**)&ctx->status_word, sizeof(unsigned int)) != cudaSuccess ||
+      cudaMemset(ctx->status_word, 0, sizeof(unsigned int)) != cudaSuccess) {
+    if (ctx->own_stream) cudaStreamDestroy(ctx->own_stream);
+    if (ctx->status_word) cudaFree(ctx->status_word);
+    delete ctx;
+    cudaGetLastError();
+    return HC_ERR_CUDA;
+  }
+  ctx->stream = ctx->own_stream;
+  *out = ctx;
+  return HC_OK;
+}
+
+void hc_destroy(hc_ctx* ctx) {
+  if (!ctx) return;
+  DeviceGuard g(ctx->device);
+  cudaStreamSynchronize(ctx->stream);
+  if (ctx->stream != ctx->own_stream) cudaStreamSynchronize(ctx->own_stream);
+  if (ctx->scratch) cudaFree(ctx->scratch);
+  for (int i = 0; i < 3; i++)
+    if (ctx->stage[i]) cudaFree(ctx->stage[i]);
+  cudaFree(ctx->status_word);
+  cudaStreamDestroy(ctx->own_stream);
+  cudaGetLastError();
+  delete ctx;
+}
+
+hc_status hc_set_stream(hc_ctx* ctx, void* cuda_stream) {
+  if (!ctx) return HC_ERR_INVALID_ARGUMENT;
+  std::lock_guard<std::mutex> lock(ctx->mu);
+  ctx->stream = cuda_stream ? (cudaStream_t)cuda_stream : ctx->own_stream;
+  return HC_OK;
+}
+
+void* hc_get_stream(hc_ctx* ctx) { return ctx ? (void*)ctx->stream : nullptr; }
+int hc_get_device(hc_ctx* ctx) { return ctx ? ctx->device : -1; }
+
+hc_status hc_alloc(hc_ctx* ctx, size_t bytes, void** dptr) {
+  if (!ctx || !dptr) return HC_ERR_INVALID_ARGUMENT;
+  std::lock_guard<std::mutex> lock(ctx->mu);
+  DeviceGuard g(ctx->device);
+  *dptr = nullptr;
+  const size_t n = bytes ? bytes : 1;
+  cudaError_t e = cudaMallocAsync(dptr, n, ctx->stream);
+  if (e != cudaSuccess) {
+    *dptr = nullptr;
+    cudaGetLastError();
+    char msg[96];
+    snprintf(msg, sizeof msg, "allocation of %zu bytes failed", n);
+    return fail(ctx, HC_ERR_ALLOCATION_FAILED, msg);
+  }
+  return HC_OK;
+}
+
+hc_status hc_free(hc_ctx* ctx, void* dptr) {
+  if (!ctx) return HC_ERR_INVALID_ARGUMENT;
+  if (!dptr) return HC_OK;
+  std::lock_guard<std::mutex> lock(ctx->mu);
+  DeviceGuard g(ctx->device);
+  HC_CUDA_TRY(ctx, cudaFreeAsync(dptr, ctx->stream));
+  return HC_OK;
+}
+
+hc_status hc_h2d(hc_ctx* ctx, void* dst, const void* src, size_t bytes) {
+  if (!ctx || (bytes && (!dst || !src))) return HC_ERR_INVALID_ARGUMENT;
+  if (!bytes) return HC_OK;
+  std::lock_guard<std::mutex> lock(ctx->mu);
+  DeviceGuard g(ctx->device);
+  HC_CUDA_TRY(ctx, cudaMemcpyAsync(dst, src, bytes, cudaMemcpyHostToDevice, ctx->stream));
+  return HC_OK;
+}
+
+hc_status hc_d2h(hc_ctx* ctx, void* dst, const void* src, size_t bytes) {
+  if (!ctx || (bytes && (!dst || !src))) return HC_ERR_INVALID_ARGUMENT;
+  if (!bytes) return HC_OK;
+  std::lock_guard<std::mutex> lock(ctx->mu);
+  DeviceGuard g(ctx->device);
+  HC_CUDA_TRY(ctx, cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDeviceToHost, ctx->stream));
+  return HC_OK;
+}
+
+hc_status hc_sync(hc_ctx* ctx) {
+  if (!ctx) return HC_ERR_INVALID_ARGUMENT;
+  std::lock_guard<std::mutex> lock(ctx->mu);
+  DeviceGuard g(ctx->device);
+  HC_CUDA_TRY(ctx, cudaStreamSynchronize(ctx->stream));
+  return HC_OK;
+}
+
+hc_status hc_event_record(hc_ctx* ctx, hc_event** out) {
+  if (!ctx || !out) return HC_ERR_INVALID_ARGUMENT;
+  *out = nullptr;
+  std::lock_guard<std::mutex> lock(ctx->mu);
+  DeviceGuard g(ctx->device);
+  hc_event* ev = new (std::nothrow) hc_event();
+  if (!ev) return HC_ERR_ALLOCATION_FAILED;
+  ev->ctx = ctx;
+  cudaError_t e = cudaEventCreate(&ev->ev);
+  if (e == cudaSuccess) e = cudaEventRecord(ev->ev, ctx->stream);
+  if (e != cudaSuccess) {
+    delete ev;
+    return cuda_fail(ctx, e, "event record");
+  }
+  *out = ev;
+  return HC_OK;
+}
+
+hc_status hc_event_wait(hc_event* ev) {
+  if (!ev) return HC_ERR_INVALID_ARGUMENT;
+  hc_ctx* ctx = ev->ctx;
+  DeviceGuard g(ctx->device);
+  cudaError_t e = cudaEventSynchronize(ev->ev);
+  std::lock_guard<std::mutex> lock(ctx->mu);
+  if (e != cudaSuccess) return cuda_fail(ctx, e, "event wait");
+  unsigned int word = 0;
+  // The status word is only written by kernels; reading it after the event is race-free for
+  // everything enqueued before the event.
+  e = cudaMemcpy(&word, ctx->status_word, sizeof word, cudaMemcpyDeviceToHost);
+  if (e != cudaSuccess) return cuda_fail(ctx, e, "status read");
+  if (word) {
+    char msg[96];
+    snprintf(msg, sizeof msg, "a bounded device-side wait expired (status bits 0x%x)", word);
+    return fail(ctx, HC_ERR_TIMEOUT, msg);
+  }
+  return HC_OK;
+}
+
+hc_status hc_event_elapsed_ms(hc_event* start, hc_event* stop, float* ms) {
+  if (!start || !stop || !ms) return HC_ERR_INVALID_ARGUMENT;
+  DeviceGuard g(start->ctx->device);
+  cudaError_t e = cudaEventElapsedTime(ms, start->ev, stop->ev);
+  if (e != cudaSuccess) return cuda_fail(start->ctx, e, "event elapsed");
+  return HC_OK;
+}
+
+void hc_event_destroy(hc_event* ev) {
+  if (!ev) return;
+  DeviceGuard g(ev->ctx->device);
+  cudaEventDestroy(ev->ev);
+  delete ev;
+}
+
+hc_status hc_batched_matmul_ex(hc_ctx* ctx, hc_kernel kernel, hc_dtype dtype, int64_t matrix_count, const void* a,
+                               int trans_a, const void* b, int trans_b, int trans_out, int64_t rows, int64_t inner,
+                               int64_t cols, void* out) {
+  if (!ctx) return HC_ERR_INVALID_ARGUMENT;
+  std::lock_guard<std::mutex> lock(ctx->mu);
+  DeviceGuard g(ctx->device);
+  hc::GemmProblem p;
+  hc_status s = build_problem(ctx, dtype, matrix_count, a, trans_a, b, trans_b, trans_out, rows, inner, cols, 0, cols,
+                              out, &p);
+  if (s != HC_OK) return s;
+  return run_problem(ctx, kernel, p, flop_count(matrix_count, rows, inner, cols));
+}
+
+hc_status hc_batched_matmul(hc_ctx* ctx, hc_dtype dtype, int64_t matrix_count, const void* a, int trans_a,
+                            const void* b, int trans_b, int trans_out, int64_t rows, int64_t inner, int64_t cols,
+                            void* out) {
+  return hc_batched_matmul_ex(ctx, HC_KERNEL_AUTO, dtype, matrix_count, a, trans_a, b, trans_b, trans_out, rows,
+                              inner, cols, out);
+}
+
+hc_status hc_matmul(hc_ctx* ctx, hc_dtype dtype, const void* a, int trans_a, const void* b, int trans_b,
+                    int trans_out, int64_t rows, int64_t inner, int64_t cols, void* out) {
+  return hc_batched_matmul_ex(ctx, HC_KERNEL_AUTO, dtype, 1, a, trans_a, b, trans_b, trans_out, rows, inner, cols,
+                              out);
+}
+
+hc_status hc_matmul_colblock(hc_ctx* ctx, hc_kernel kernel, hc_dtype dtype, const void* a, int trans_a, const void* b,
+                             int trans_b, int trans_out, int64_t rows, int64_t inner, int64_t cols,
+                             int64_t col_begin, int64_t col_count, void* out) {
+  if (!ctx) return HC_ERR_INVALID_ARGUMENT;
+  std::lock_guard<std::mutex> lock(ctx->mu);
+  DeviceGuard g(ctx->device);
+  hc::GemmProblem p;
+  hc_status s = build_problem(ctx, dtype, 1, a, trans_a, b, trans_b, trans_out, rows, inner, cols, col_begin,
+                              col_count, out, &p);
+  if (s != HC_OK) return s;
+  return run_problem(ctx, kernel, p, flop_count(1, rows, inner, col_count));
+}
+
+hc_status hc_batched_matmul_host(hc_ctx* ctx, hc_dtype dtype, int64_t matrix_count, const void* a_host, int trans_a,
+                                 const void* b_host, int trans_b, int trans_out, int64_t rows, int64_t inner,
+                                 int64_t cols, void* out_host) {
+  if (!ctx) return HC_ERR_INVALID_ARGUMENT;
+  std::lock_guard<std::mutex> lock(ctx->mu);
+  DeviceGuard g(ctx->device);
+  if (dtype != HC_F16 && dtype != HC_F32)
+    return fail(ctx, HC_ERR_NOT_IMPLEMENTED, "matmul: only float16 and float32 are implemented");
+  if (matrix_count < 0 || rows < 0 || inner < 0 || cols < 0)
+    return fail(ctx, HC_ERR_INVALID_ARGUMENT, "negative dimension");
+  const size_t eb = dtype == HC_F16 ? 2 : 4;
+  const size_t bytes[3] = {(size_t)(matrix_count * rows * inner) * eb, (size_t)(matrix_count * inner * cols) * eb,
+                           (size_t)(matrix_count * rows * cols) * eb};
+  if ((bytes[0] && !a_host) || (bytes[1] && !b_host) || (bytes[2] && !out_host))
+    return fail(ctx, HC_ERR_INVALID_ARGUMENT, "null operand");
+  for (int i = 0; i < 3; i++) {
+    hc_status s = ensure_buffer(ctx, &ctx->stage[i], &ctx->stage_bytes[i], bytes[i]);
+    if (s != HC_OK) return s;
+  }
+  if (bytes[0]) HC_CUDA_TRY(ctx, cudaMemcpyAsync(ctx->stage[0], a_host, bytes[0], cudaMemcpyHostToDevice, ctx->stream));
+  if (bytes[1]) HC_CUDA_TRY(ctx, cudaMemcpyAsync(ctx->stage[1], b_host, bytes[1], cudaMemcpyHostToDevice, ctx->stream));
+  hc::GemmProblem p;
+  hc_status s = build_problem(ctx, dtype, matrix_count, ctx->stage[0], trans_a, ctx->stage[1], trans_b, trans_out,
+                              rows, inner, cols, 0, cols, ctx->stage[2], &p);
+  if (s != HC_OK) return s;
+  s = run_problem(ctx, HC_KERNEL_AUTO, p, flop_count(matrix_count, rows, inner, cols));
+  if (s != HC_OK) return s;
+  if (bytes[2]) HC_CUDA_TRY(ctx, cudaMemcpyAsync(out_host, ctx->stage[2], bytes[2], cudaMemcpyDeviceToHost, ctx->stream));
+  HC_CUDA_TRY(ctx, cudaStreamSynchronize(ctx->stream));
+  return HC_OK;
+}
+
+const char* hc_status_string(hc_status s) {
+  switch (s) {
+    case HC_OK: return "ok";
+    case HC_ERR_ALLOCATION_FAILED: return "allocation failed";
+    case HC_ERR_KERNEL_FAILED: return "kernel failed";
+    case HC_ERR_NOT_IMPLEMENTED: return "not implemented";
+    case HC_ERR_INVALID_ARGUMENT: return "invalid argument";
+    case HC_ERR_TIMEOUT: return "device-side wait timed out";
+    case HC_ERR_CUDA: return "CUDA error";
+  }
+  return "unknown status";
+}
+
+const char* hc_last_error(hc_ctx* ctx) { return ctx ? ctx->last_error.c_str() : ""; }
+
+hc_status hc_last_launch_info(hc_ctx* ctx, hc_launch_info* out) {
+  if (!ctx || !out) return HC_ERR_INVALID_ARGUMENT;
+  std::lock_guard<std::mutex> lock(ctx->mu);
+  out->kernel = ctx->last.kernel;
+  out->tile_m = ctx->last.tile_m; out->tile_n = ctx->last.tile_n; out->tile_k = ctx->last.tile_k;
+  out->stages = ctx->last.stages; out->grid = ctx->last.grid; out->block = ctx->last.block;
+  out->tiles = ctx->last.tiles; out->flops = ctx->last_flops; out->scratch_bytes = ctx->last.scratch_bytes;
+  return HC_OK;
+}
+
+int64_t hc_launch_count(hc_ctx* ctx) {
+  if (!ctx) return 0;
+  std::lock_guard<std::mutex> lock(ctx->mu);
+  return ctx->launch_count;
+}
+
+hc_status hc_check_device_status(hc_ctx* ctx) {
+  if (!ctx) return HC_ERR_INVALID_ARGUMENT;
+  std::lock_guard<std::mutex> lock(ctx->mu);
+  DeviceGuard g(ctx->device);
+  HC_CUDA_TRY(ctx, cudaStreamSynchronize(ctx->stream));
+  unsigned int word = 0;
+  HC_CUDA_TRY(ctx, cudaMemcpy(&word, ctx->status_word, sizeof word, cudaMemcpyDeviceToHost));
+  if (word) {
+    HC_CUDA_TRY(ctx, cudaMemset(ctx->status_word, 0, sizeof word));
+    char msg[96];
+    snprintf(msg, sizeof msg, "a bounded device-side wait expired (status bits 0x%x)", word);
+    return fail(ctx, HC_ERR_TIMEOUT, msg);
+  }
+  return HC_OK;
+}
+
+const char* hc_version(void) { return "0.1"; }
+
+}  // extern "C"

@@ -1,0 +1,179 @@
+/*
+ * hc_cuda.h - C ABI of libhccuda, the sm_100a implementation of Honeycrisp's dense
+ * matrix-product hot path (Backend.matmul / Backend.batchedMatmul, float32 and float16).
+ *
+ * This is the surface a Swift `CUDABackend: Backend` binds through a module map
+ * (`module CHCCuda { header "hc_cuda.h" link "hccuda" export * }`), and the surface the
+ * ctypes host mirror and the tests call.  Plain C: pointers, sizes, int status codes.
+ * No exceptions or aborts cross it, there is no CPU fallback behind it, and nothing in it
+ * depends on PyTorch.
+ *
+ * Conventions shared by all matrix entry points (they are the reference's):
+ *   - every operand is dense, row-major and contiguous;
+ *   - `rows` x `cols` is the shape of op(a)*op(b), `inner` the contracted length;
+ *   - `a` is stored [rows,inner], or [inner,rows] when trans_a; `b` is stored [inner,cols],
+ *     or [cols,inner] when trans_b; `out` is [rows,cols], or [cols,rows] when trans_out;
+ *   - batched calls hold `matrix_count` such matrices back to back, no padding, equal counts;
+ *   - float16 accumulates in float32 and rounds once (nearest-even, overflow -> +-inf).
+ * Pointers are device pointers on the context's device unless a function says "host".
+ * Work is enqueued on the context's stream and the call returns without waiting; inputs must
+ * stay alive until the stream has passed the call (hc_sync / hc_event_wait).
+ * All functions are thread-safe; calls on one context are ordered by a mutex, which is the
+ * same discipline as the reference backends' single worker thread
+ * (Sources/Honeycrisp/BackendCPU.swift:235-248).
+ */
+#ifndef HC_CUDA_H_
+#define HC_CUDA_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct hc_ctx hc_ctx;     /* one device, one stream, one allocator pool */
+typedef struct hc_event hc_event; /* completion marker on the context's stream */
+
+/* Status codes.  The first three after OK map one-to-one onto the reference's BackendError
+ * cases (Sources/Honeycrisp/Backend.swift:6-16): allocationFailed, kernelFailed,
+ * notImplemented. */
+typedef enum hc_status {
+  HC_OK = 0,
+  HC_ERR_ALLOCATION_FAILED = 1,
+  HC_ERR_KERNEL_FAILED = 2,
+  HC_ERR_NOT_IMPLEMENTED = 3,
+  HC_ERR_INVALID_ARGUMENT = 4, /* the reference traps these earlier with #alwaysAssert
+                                  (Sources/Honeycrisp/Linalg.swift:52-59,90-104) */
+  HC_ERR_TIMEOUT = 5,          /* a bounded device-side wait gave up; context stays usable */
+  HC_ERR_CUDA = 6              /* any other CUDA runtime/driver error; see hc_last_error */
+} hc_status;
+
+/* Tensor.DType subset in scope (Sources/Honeycrisp/Tensor.swift: DType). int64 products are
+ * legal on the reference's CPU backend but outside this library: HC_ERR_NOT_IMPLEMENTED. */
+typedef enum hc_dtype { HC_F16 = 0, HC_F32 = 1 } hc_dtype;
+
+/* Which kernel serves a product.  AUTO is what a backend uses; the rest exist for tests,
+ * benchmarks and as the GPU-side cross-check of the tensor-core paths. */
+typedef enum hc_kernel {
+  HC_KERNEL_AUTO = 0,
+  HC_KERNEL_SIMT = 1,       /* CUDA-core kernel, fused multiply-add, any shape/alignment */
+  HC_KERNEL_SIMT_EXACT = 2, /* same, separate multiply and add in k order: bit-identical to
+                               the reference CPU loop (BackendCPU.swift:1290-1300) */
+  HC_KERNEL_TENSOR = 3      /* tcgen05 path: fp16 direct; fp32 as 3xTF32 split operands.
+                               HC_ERR_NOT_IMPLEMENTED if the shape cannot be described to TMA */
+} hc_kernel;
+
+typedef struct hc_launch_info {
+  int kernel;          /* hc_kernel actually used (never AUTO) */
+  int tile_m, tile_n, tile_k;
+  int stages;
+  int grid, block;
+  int64_t tiles;       /* output tiles over all matrices */
+  int64_t flops;       /* 2*matrix_count*rows*inner*cols, the reference's own convention
+                          (Sources/Honeycrisp/BackendWrapper.swift:485,499) */
+  size_t scratch_bytes;/* global memory used beyond inputs and outputs */
+} hc_launch_info;
+
+/* ---- context, memory, ordering ---------------------------------------------------------- */
+
+/* Create a context on CUDA device `device` with its own non-blocking stream.
+ * Replaces: `try CUDABackend()` taking the place of MPSBackend.init
+ * (Sources/Honeycrisp/BackendMPS.swift:352-375). */
+hc_status hc_init(int device, hc_ctx** out);
+void hc_destroy(hc_ctx* ctx);
+
+/* Run this context's work on a stream the caller owns (a `cudaStream_t` passed as void*);
+ * NULL returns to the context's own stream.  The caller keeps the stream alive. */
+hc_status hc_set_stream(hc_ctx* ctx, void* cuda_stream);
+void* hc_get_stream(hc_ctx* ctx);
+int hc_get_device(hc_ctx* ctx);
+
+/* Stream-ordered allocation; `bytes == 0` allocates one byte, as the reference's GPU backend
+ * does (Sources/Honeycrisp/BackendMPS.swift:538-540).
+ * Replaces: MPSBackend.allocateBuf (BackendMPS.swift:500-527), CPUBackend.allocate
+ * (BackendCPU.swift:250-253). */
+hc_status hc_alloc(hc_ctx* ctx, size_t bytes, void** dptr);
+hc_status hc_free(hc_ctx* ctx, void* dptr);
+
+/* Copies between host and device, ordered on the stream; both return after the copy has
+ * been enqueued (h2d from pageable memory has been staged).  hc_d2h needs hc_sync or an
+ * event wait before the host reads `dst`.
+ * Replaces: Tensor.Data.onCPU / MPSBackend.gpuBuffer staging (BackendMPS.swift:585-620). */
+hc_status hc_h2d(hc_ctx* ctx, void* dst_device, const void* src_host, size_t bytes);
+hc_status hc_d2h(hc_ctx* ctx, void* dst_host, const void* src_device, size_t bytes);
+hc_status hc_sync(hc_ctx* ctx);
+
+/* Completion markers; they back Tensor.Data.wait() (Sources/Honeycrisp/Tensor.swift:69-85,
+ * 618-621), like the command-buffer completion Task of the reference's GPU backend
+ * (BackendMPS.swift:2694-2720).  hc_event_wait also reports a device-side timeout or kernel
+ * failure recorded before the event. */
+hc_status hc_event_record(hc_ctx* ctx, hc_event** out);
+hc_status hc_event_wait(hc_event* ev);
+/* Milliseconds between two completed events of the same context. */
+hc_status hc_event_elapsed_ms(hc_event* start, hc_event* stop, float* ms);
+void hc_event_destroy(hc_event* ev);
+
+/* ---- the hot path ------------------------------------------------------------------------ */
+
+/* out = trans_out(op(a) * op(b)).
+ * Replaces: Backend.matmul(a:transA:b:transB:transOut:rows:inner:cols:dtype:)
+ * (Sources/Honeycrisp/Backend.swift:650-658; CPU body BackendCPU.swift:1222-1232). */
+hc_status hc_matmul(hc_ctx* ctx, hc_dtype dtype, const void* a, int trans_a, const void* b,
+                    int trans_b, int trans_out, int64_t rows, int64_t inner, int64_t cols,
+                    void* out);
+
+/* The same for `matrix_count` independent products.
+ * Replaces: Backend.batchedMatmul(matrixCount:a:transA:b:transB:transOut:rows:inner:cols:dtype:)
+ * (Sources/Honeycrisp/Backend.swift:661-669; CPU body BackendCPU.swift:1234-1313). */
+hc_status hc_batched_matmul(hc_ctx* ctx, hc_dtype dtype, int64_t matrix_count, const void* a,
+                            int trans_a, const void* b, int trans_b, int trans_out,
+                            int64_t rows, int64_t inner, int64_t cols, void* out);
+
+/* As hc_batched_matmul with the kernel chosen by the caller. */
+hc_status hc_batched_matmul_ex(hc_ctx* ctx, hc_kernel kernel, hc_dtype dtype,
+                               int64_t matrix_count, const void* a, int trans_a, const void* b,
+                               int trans_b, int trans_out, int64_t rows, int64_t inner,
+                               int64_t cols, void* out);
+
+/* Host-buffer form of the batched product: operands and result live in HOST memory; the call
+ * stages them to the device, runs the product and copies the result back before returning.
+ * This is what a backend does for operands of a foreign Tensor.Data type, which the reference
+ * wraps through onCPU (Sources/Honeycrisp/BackendMPS.swift:585-620), followed by the caller
+ * reading the result (Tensor.floats()).  Pinned host memory makes the copies asynchronous
+ * DMA; pageable memory works but is slower. */
+hc_status hc_batched_matmul_host(hc_ctx* ctx, hc_dtype dtype, int64_t matrix_count,
+                                 const void* a_host, int trans_a, const void* b_host,
+                                 int trans_b, int trans_out, int64_t rows, int64_t inner,
+                                 int64_t cols, void* out_host);
+
+/* One column block of a product, for splitting a large GEMM over devices: computes columns
+ * [col_begin, col_begin+col_count) of op(a)*op(b) (of its transpose's rows when trans_out) and
+ * writes them in place into the FULL-size `out`.  `b` is the full operand; only the block's
+ * part of it is read.  Each device of a group calls this with its own block; the blocks are
+ * then exchanged (all-gather) by the caller.  No counterpart in the reference, which has no
+ * multi-device code; the contract is "equals the same columns of hc_matmul". */
+hc_status hc_matmul_colblock(hc_ctx* ctx, hc_kernel kernel, hc_dtype dtype, const void* a,
+                             int trans_a, const void* b, int trans_b, int trans_out,
+                             int64_t rows, int64_t inner, int64_t cols, int64_t col_begin,
+                             int64_t col_count, void* out);
+
+/* ---- diagnostics ------------------------------------------------------------------------- */
+
+const char* hc_status_string(hc_status s);
+/* Text of the last failure on this context (thread-unsafe snapshot; empty if none). */
+const char* hc_last_error(hc_ctx* ctx);
+/* Geometry of the most recent product launched on this context. */
+hc_status hc_last_launch_info(hc_ctx* ctx, hc_launch_info* out);
+/* Kernels launched on this context since creation (each matrix product may launch several). */
+int64_t hc_launch_count(hc_ctx* ctx);
+/* Reads and clears the device-side status word; HC_ERR_TIMEOUT if a bounded wait expired in
+ * a kernel that has completed.  Synchronises the stream. */
+hc_status hc_check_device_status(hc_ctx* ctx);
+/* Library version, "major.minor". */
+const char* hc_version(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* HC_CUDA_H_ */

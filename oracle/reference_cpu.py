@@ -1,0 +1,195 @@
+"""numpy/ctypes front end of the CPU oracle.  TEST INFRASTRUCTURE ONLY.
+
+Only tests, the smoke check and the CPU-baseline leg of the benchmark import this module;
+the shipped package never does.  The arithmetic lives in oracle/hc_oracle.c (a restatement of
+Honeycrisp's CPUBackend.batchedMatmul, Sources/Honeycrisp/BackendCPU.swift:1234-1313); this
+file adds
+
+* the host sgemm that stands in for Accelerate's vDSP_mmul (BackendCPU.swift:1256), found in
+  the OpenBLAS builds that ship inside the Python wheels on this image,
+* a float64 product with the same flag semantics (for the float16 tolerance, which is quoted
+  against a float64 product),
+* the relative Frobenius error,
+* the autodiff flag algebra of Tensor.matmul (Sources/Honeycrisp/Linalg.swift:73-80) so the
+  reference's gradient known-answer vectors can be replayed.
+"""
+from __future__ import annotations
+
+import ctypes
+import glob
+import os
+import sys
+
+import numpy as np
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+if _HERE not in sys.path:
+    sys.path.insert(0, _HERE)
+import build as _oracle_build  # noqa: E402  (oracle/build.py)
+
+_lib = None
+_sgemm = None  # (kind, address, owner, set_threads)
+
+
+def lib() -> ctypes.CDLL:
+    global _lib
+    if _lib is None:
+        path = _oracle_build.build()
+        L = ctypes.CDLL(path)
+        i64, vp, ci = ctypes.c_int64, ctypes.c_void_p, ctypes.c_int
+        L.hc_oracle_batched_matmul_f32.argtypes = [i64, vp, ci, vp, ci, ci, i64, i64, i64, vp, vp, vp, ci]
+        L.hc_oracle_batched_matmul_f32.restype = ci
+        L.hc_oracle_batched_matmul_f16.argtypes = [i64, vp, ci, vp, ci, ci, i64, i64, i64, vp]
+        L.hc_oracle_batched_matmul_f16.restype = ci
+        L.hc_oracle_loop_rows_f32.argtypes = [i64, vp, ci, vp, ci, ci, i64, i64, i64, vp, i64, i64, ci]
+        L.hc_oracle_loop_rows_f32.restype = None
+        L.hc_oracle_half_to_float.argtypes = [vp, vp, i64]
+        L.hc_oracle_float_to_half.argtypes = [vp, vp, i64]
+        _lib = L
+    return _lib
+
+
+def find_sgemm():
+    """Locate a row-major cblas sgemm.  Returns (kind, address, description) with kind in
+    {"lp64", "ilp64"} or (None, None, reason)."""
+    global _sgemm
+    if _sgemm is not None:
+        return _sgemm[:3]
+    roots = [p for p in sys.path if p.endswith("site-packages")]
+    candidates = []
+    for r in roots:
+        candidates += [(p, "cblas_sgemm", "lp64", "openblas_set_num_threads")
+                       for p in sorted(glob.glob(os.path.join(r, "opencv_python_headless.libs", "libopenblas*.so*")))]
+        candidates += [(p, "scipy_cblas_sgemm", "lp64", "scipy_openblas_set_num_threads")
+                       for p in sorted(glob.glob(os.path.join(r, "scipy.libs", "libscipy_openblas-*.so*")))]
+        candidates += [(p, "scipy_cblas_sgemm64_", "ilp64", "scipy_openblas_set_num_threads64_")
+                       for p in sorted(glob.glob(os.path.join(r, "numpy.libs", "libscipy_openblas64_*.so*")))]
+    for path, sym, kind, thr in candidates:
+        try:
+            L = ctypes.CDLL(path)
+            fn = getattr(L, sym)
+        except (OSError, AttributeError):
+            continue
+        setter = getattr(L, thr, None)
+        _sgemm = (kind, ctypes.cast(fn, ctypes.c_void_p).value, f"{os.path.basename(path)}:{sym}", L, setter)
+        return _sgemm[:3]
+    _sgemm = (None, None, "no OpenBLAS with a cblas sgemm found", None, None)
+    return _sgemm[:3]
+
+
+def set_sgemm_threads(n: int) -> bool:
+    find_sgemm()
+    setter = _sgemm[4]
+    if setter is None:
+        return False
+    setter.argtypes = [ctypes.c_int]
+    setter(int(n))
+    return True
+
+
+def _ptr(x: np.ndarray):
+    return ctypes.c_void_p(x.ctypes.data)
+
+
+def batched_matmul(matrix_count, a, trans_a, b, trans_b, trans_out, rows, inner, cols,
+                   library_fast_path=True):
+    """CPUBackend.batchedMatmul on flat numpy operands (float32 or float16).
+
+    `a` holds matrix_count dense matrices of shape [rows,inner] ([inner,rows] if trans_a), `b`
+    likewise [inner,cols] ([cols,inner] if trans_b); the result is flat, [rows,cols] per matrix
+    ([cols,rows] if trans_out).  float32 with no flags goes to the host sgemm unless
+    library_fast_path is False, everything else through the literal loop.
+    """
+    a = np.ascontiguousarray(a).reshape(-1)
+    b = np.ascontiguousarray(b).reshape(-1)
+    assert a.dtype == b.dtype and a.dtype in (np.float32, np.float16)
+    assert a.size == matrix_count * rows * inner and b.size == matrix_count * inner * cols
+    out = np.empty(matrix_count * rows * cols, dtype=a.dtype)
+    L = lib()
+    if a.dtype == np.float32:
+        kind, addr, _ = find_sgemm()
+        use_fast = bool(library_fast_path) and not (trans_a or trans_b or trans_out)
+        if use_fast and addr is None:
+            # numpy's own float32 matmul is the same OpenBLAS sgemm behind another door.
+            A = a.reshape(matrix_count, rows, inner)
+            B = b.reshape(matrix_count, inner, cols)
+            return np.matmul(A, B).reshape(-1)
+        rc = L.hc_oracle_batched_matmul_f32(
+            matrix_count, _ptr(a), int(trans_a), _ptr(b), int(trans_b), int(trans_out), rows, inner,
+            cols, _ptr(out), addr if kind == "lp64" else None, addr if kind == "ilp64" else None,
+            int(use_fast))
+    else:
+        rc = L.hc_oracle_batched_matmul_f16(
+            matrix_count, _ptr(a.view(np.uint16)), int(trans_a), _ptr(b.view(np.uint16)), int(trans_b),
+            int(trans_out), rows, inner, cols, _ptr(out.view(np.uint16)))
+    if rc != 0:
+        raise RuntimeError(f"oracle failed with code {rc}")
+    return out
+
+
+def matmul(a, trans_a, b, trans_b, trans_out, rows, inner, cols, library_fast_path=True):
+    """CPUBackend.matmul (BackendCPU.swift:1222-1232)."""
+    return batched_matmul(1, a, trans_a, b, trans_b, trans_out, rows, inner, cols, library_fast_path)
+
+
+def loop_rows(matrix_count, a32, trans_a, b32, trans_b, trans_out, rows, inner, cols, row_begin,
+              row_end, threads=1, out=None):
+    """The literal loop on float32 operands for rows [row_begin,row_end) of each matrix.
+    Returns the full-size float32 output buffer with only those rows filled."""
+    a32 = np.ascontiguousarray(a32, dtype=np.float32).reshape(-1)
+    b32 = np.ascontiguousarray(b32, dtype=np.float32).reshape(-1)
+    if out is None:
+        out = np.zeros(matrix_count * rows * cols, dtype=np.float32)
+    lib().hc_oracle_loop_rows_f32(matrix_count, _ptr(a32), int(trans_a), _ptr(b32), int(trans_b),
+                                  int(trans_out), rows, inner, cols, _ptr(out), row_begin, row_end,
+                                  int(threads))
+    return out
+
+
+def float_to_half(x32):
+    x32 = np.ascontiguousarray(x32, dtype=np.float32).reshape(-1)
+    out = np.empty(x32.size, dtype=np.float16)
+    lib().hc_oracle_float_to_half(_ptr(x32), _ptr(out.view(np.uint16)), x32.size)
+    return out
+
+
+def half_to_float(x16):
+    x16 = np.ascontiguousarray(x16, dtype=np.float16).reshape(-1)
+    out = np.empty(x16.size, dtype=np.float32)
+    lib().hc_oracle_half_to_float(_ptr(x16.view(np.uint16)), _ptr(out), x16.size)
+    return out
+
+
+def logical_operands(matrix_count, a, trans_a, b, trans_b, rows, inner, cols):
+    """Views of the stored operands as [matrix_count, rows, inner] and [matrix_count, inner, cols]."""
+    a = np.asarray(a).reshape(-1)
+    b = np.asarray(b).reshape(-1)
+    A = a.reshape(matrix_count, inner, rows).transpose(0, 2, 1) if trans_a else a.reshape(matrix_count, rows, inner)
+    B = b.reshape(matrix_count, cols, inner).transpose(0, 2, 1) if trans_b else b.reshape(matrix_count, inner, cols)
+    return A, B
+
+
+def batched_matmul_f64(matrix_count, a, trans_a, b, trans_b, trans_out, rows, inner, cols):
+    """float64 product with the same storage conventions; flat float64 result."""
+    A, B = logical_operands(matrix_count, a, trans_a, b, trans_b, rows, inner, cols)
+    C = np.matmul(A.astype(np.float64), B.astype(np.float64))
+    if trans_out:
+        C = C.transpose(0, 2, 1)
+    return np.ascontiguousarray(C).reshape(-1)
+
+
+def rel_frobenius(x, ref) -> float:
+    x = np.asarray(x, dtype=np.float64).reshape(-1)
+    ref = np.asarray(ref, dtype=np.float64).reshape(-1)
+    den = np.linalg.norm(ref)
+    num = np.linalg.norm(x - ref)
+    if den == 0.0:
+        return 0.0 if num == 0.0 else float("inf")
+    return float(num / den)
+
+
+def matmul_grad_calls(trans_a, trans_b, trans_out):
+    """Flag triples of the two backward products of Tensor.matmul (Linalg.swift:73-80):
+    dA = matmul(a: grad, transA: transOut, b: B, transB: !transB, transOut: transA)
+    dB = matmul(a: A, transA: !transA, b: grad, transB: transOut, transOut: transB)."""
+    return ((bool(trans_out), not trans_b, bool(trans_a)), (not trans_a, bool(trans_out), bool(trans_b)))
