@@ -1,0 +1,412 @@
+#!/usr/bin/env python
+"""Benchmark of the dense matrix-product hot path.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--all-configs]
+
+One step = one pass of the headline workload: float16 GEMM M=N=K=8192, fp32 accumulate, over
+all four transA/transB combinations (four products, 4.398 TFLOP).  With N > 1 (launched by
+torchrun, one rank per GPU) every rank runs that step on its own operands - independent
+products, nothing exchanged - and the value is the aggregate over the box.
+
+Prints ONE JSON line on stdout (rank 0).  `value` is timed with operands resident in HBM;
+`e2e` is the same step through the host-buffer C-ABI call, copies inside the timed region.
+`--impl reference` times the reference's CPU path (the oracle port of CPUBackend's loop) on the
+host cores instead.  `--all-configs` adds quick numbers for the other four configurations
+under "extra".
+"""
+from __future__ import annotations
+
+import argparse
+import ctypes
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+METRIC = "GEMM TFLOP/s (box aggregate; per GPU = value / n_gpus)"
+UNIT = "TFLOP/s"
+N_DIM = 8192
+COMBOS = [(False, False), (False, True), (True, False), (True, True)]  # (transA, transB)
+WORKLOAD = "float16 GEMM M=N=K=8192, fp32 accumulate, float16 out, all four transA/transB, N(0,1)/sqrt(K), seed 1"
+FLOPS_PER_GEMM = 2.0 * N_DIM ** 3
+# DRAM bytes (read + write) of one 8192^3 launch of the tensor-core kernel, from the ncu capture
+# summarised in profiles/tc_gemm_f16_8192.md.  None until that capture exists.
+NCU_DRAM_BYTES_PER_LAUNCH = None
+
+
+def load_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            p = json.load(f)
+        return {"burst": float(p["bf16_tflops"]), "sustained": float(p.get("bf16_tflops_sustained", p["bf16_tflops"])),
+                "hbm_gbs": float(p["hbm_gbs"]), "source": "measured"}
+    return {"burst": 1590.0, "sustained": 1400.0, "hbm_gbs": 6650.0, "source": "fallback"}
+
+
+class ClockSampler:
+    """Samples nvidia-smi clocks and throttle reasons of one GPU while the timed region runs."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index = index
+        self.proc = None
+        self.lines = []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", str(self.index), f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
+                 "-lms", "50"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if not self.proc:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, mx, power, reasons = [], [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in self.lines:
+            parts = [x.strip() for x in line.split(",")]
+            if len(parts) < 7:
+                continue
+            try:
+                sm.append(float(parts[0])); mx.append(float(parts[1])); power.append(float(parts[2]))
+            except ValueError:
+                continue
+            for name, val in zip(names, parts[3:7]):
+                if val == "Active":
+                    reasons.add(name)
+        if not sm:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["no samples"]}
+        # "under load" = samples in the upper half of the power range seen
+        cut = (max(power) + min(power)) / 2
+        loaded = [s for s, p in zip(sm, power) if p >= cut] or sm
+        return {"sm_mhz": statistics.median(loaded), "sm_max_mhz": max(mx), "power_w_max": max(power),
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+def dist_env():
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    return rank, world, local
+
+
+# ------------------------------------------------------------------------------------------------
+# reference arm: the reference's CPU path on the host cores
+# ------------------------------------------------------------------------------------------------
+
+def cpu_sample(rows_per_combo: int, threads: int, a32, b32, out32):
+    """One bounded sample of the workload on the CPU: `rows_per_combo` output rows of each of
+    the four products through the oracle's loop.  Returns (seconds, flops)."""
+    from oracle import reference_cpu as ref
+    t0 = time.perf_counter()
+    for ta, tb in COMBOS:
+        ref.loop_rows(1, a32, ta, b32, tb, False, N_DIM, N_DIM, N_DIM, 0, rows_per_combo, threads=threads, out=out32)
+    dt = time.perf_counter() - t0
+    return dt, 4 * 2.0 * rows_per_combo * N_DIM * N_DIM
+
+
+def cpu_operands():
+    import numpy as np
+    rng = np.random.default_rng(1)
+    scale = 1.0 / np.sqrt(N_DIM)
+    # float16 operands widened once, as CPUBackend does before its loop (BackendCPU.swift:2018-2030);
+    # the widening is outside the timed sample, which favours the CPU number.
+    a32 = (rng.standard_normal((N_DIM, N_DIM), dtype=np.float32) * scale).astype(np.float16).astype(np.float32)
+    b32 = (rng.standard_normal((N_DIM, N_DIM), dtype=np.float32) * scale).astype(np.float16).astype(np.float32)
+    out32 = np.zeros(N_DIM * N_DIM, dtype=np.float32)
+    return a32, b32, out32
+
+
+def calibrate_rows(threads, a32, b32, out32, target_s):
+    dt, _ = cpu_sample(threads, threads, a32, b32, out32)   # one row per thread
+    per_row = dt / threads
+    rows = int(max(threads, min(N_DIM, target_s / max(per_row, 1e-9))))
+    return (rows // threads) * threads or threads
+
+
+def run_reference(args):
+    rank, world, _ = dist_env()
+    if rank != 0:
+        return
+    threads = os.cpu_count() or 1
+    a32, b32, out32 = cpu_operands()
+    rows = calibrate_rows(threads, a32, b32, out32, target_s=2.0)
+    for _ in range(args.warmup):
+        cpu_sample(rows, threads, a32, b32, out32)
+    t_total, f_total = 0.0, 0.0
+    for _ in range(args.steps):
+        dt, fl = cpu_sample(rows, threads, a32, b32, out32)
+        t_total += dt
+        f_total += fl
+    value = f_total / t_total / 1e12
+    sample = (f"{rows} of {N_DIM} output rows of each of the four products per step through the port of "
+              f"CPUBackend's loop (float16 operands widened to float32 beforehand, fp32 accumulate), "
+              f"OpenMP over rows on {threads} threads; the reference itself runs this loop on one thread")
+    line = {
+        "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * t_total / args.steps,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f16 in, f32 accumulate",
+        "data": "synthetic", "config": {"workload": WORKLOAD, "sampled": True},
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": threads, "kind": "port", "sample": sample},
+        "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+# ------------------------------------------------------------------------------------------------
+# our arm
+# ------------------------------------------------------------------------------------------------
+
+def run_ours(args):
+    import numpy as np
+    import torch
+
+    from honeycrisp_b200 import CUDABackend
+
+    rank, world, local = dist_env()
+    if world != args.gpus and world > 1:
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}")
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device; there is no CPU fallback")
+    torch.cuda.set_device(local)
+    use_dist = world > 1
+    if use_dist:
+        import torch.distributed as dist
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+
+    be = CUDABackend(local)
+    stream = torch.cuda.Stream()
+    torch.cuda.set_stream(stream)
+    be.useStream(stream.cuda_stream)
+
+    n = N_DIM
+    gen = torch.Generator(device="cuda").manual_seed(1 + rank)
+    a = (torch.randn((n, n), generator=gen, device="cuda") / n ** 0.5).half()
+    b = (torch.randn((n, n), generator=gen, device="cuda") / n ** 0.5).half()
+    out = torch.empty((n, n), device="cuda", dtype=torch.float16)
+    out_d = be.wrap(out.data_ptr(), out.numel() * 2, out)
+    torch.cuda.synchronize()
+
+    def step():
+        for ta, tb in COMBOS:
+            be.matmul(a, ta, b, tb, False, n, n, n, np.float16, out=out_d)
+
+    def barrier():
+        if use_dist:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    be.checkDeviceStatus()
+
+    sampler = ClockSampler(local)
+    launches0 = be.launchCount()
+    barrier()
+    if rank == 0:
+        sampler.start()
+    e0 = torch.cuda.Event(enable_timing=True)
+    e1 = torch.cuda.Event(enable_timing=True)
+    e0.record(stream)
+    for _ in range(args.steps):
+        step()
+    e1.record(stream)
+    barrier()
+    clocks = sampler.stop() if rank == 0 else None
+    ms = e0.elapsed_time(e1)
+    launches = be.launchCount() - launches0
+    be.checkDeviceStatus()
+    if use_dist:
+        t = torch.tensor([ms], device="cuda", dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+        lt = torch.tensor([launches], device="cuda", dtype=torch.int64)
+        dist.all_reduce(lt, op=dist.ReduceOp.SUM)
+        launches = int(lt.item())
+    total_flops = FLOPS_PER_GEMM * 4 * args.steps * world
+    value = total_flops / (ms * 1e-3) / 1e12
+
+    # ---- end to end: host buffers through hc_batched_matmul_host, copies in the timed region
+    e2e_steps = max(1, min(args.steps, 3))
+    ha = a.cpu().pin_memory()
+    hb = b.cpu().pin_memory()
+    hout = torch.empty((n, n), dtype=torch.float16).pin_memory()
+    ha_np, hb_np, hout_np = ha.numpy(), hb.numpy(), hout.numpy().reshape(-1)
+
+    def e2e_step():
+        for ta, tb in COMBOS:
+            be.batchedMatmulHost(1, ha_np, ta, hb_np, tb, False, n, n, n, np.float16, out=hout_np)
+
+    e2e_step()
+    barrier()
+    t0 = time.perf_counter()
+    for _ in range(e2e_steps):
+        e2e_step()
+    barrier()
+    e2e_s = time.perf_counter() - t0
+    if use_dist:
+        t = torch.tensor([e2e_s], device="cuda", dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e_s = float(t.item())
+    e2e_value = FLOPS_PER_GEMM * 4 * e2e_steps * world / e2e_s / 1e12
+    h2d = 4 * 2 * n * n * 2
+    d2h = 4 * n * n * 2
+
+    # ---- per-launch timing of the dominant kernel for the roofline (events around each launch)
+    evs = []
+    for ta, tb in COMBOS * 2:
+        s0 = torch.cuda.Event(enable_timing=True); s1 = torch.cuda.Event(enable_timing=True)
+        s0.record(stream)
+        be.matmul(a, ta, b, tb, False, n, n, n, np.float16, out=out_d)
+        s1.record(stream)
+        evs.append((s0, s1))
+    torch.cuda.synchronize()
+    launch_ms = statistics.mean(x.elapsed_time(y) for x, y in evs)
+    info = be.lastLaunchInfo()
+
+    if rank != 0:
+        if use_dist:
+            dist.destroy_process_group()
+        return
+
+    peaks = load_peaks()
+    timed_s = ms * 1e-3
+    # The sustained figure is the denominator for a timed region long enough for the power cap
+    # to settle (hundreds of milliseconds); the burst figure otherwise.
+    use_sustained = timed_s > 0.25
+    peak = peaks["sustained"] if use_sustained else peaks["burst"]
+    achieved = value / world
+    roofline = {
+        "bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
+        "peak_kind": ("sustained" if use_sustained else "burst") + " bf16 cuBLAS, of " + peaks["source"],
+        "frac_of_burst": achieved / peaks["burst"], "frac_of_sustained": achieved / peaks["sustained"],
+        "frac_of_nominal_2250": achieved / 2250.0,
+        "single_launch_tflops": FLOPS_PER_GEMM / (launch_ms * 1e-3) / 1e12,
+        "traffic": NCU_DRAM_BYTES_PER_LAUNCH,
+        "algorithmic_flops_per_launch": FLOPS_PER_GEMM,
+    }
+
+    threads = os.cpu_count() or 1
+    a32, b32, out32 = cpu_operands()
+    rows = calibrate_rows(threads, a32, b32, out32, target_s=12.0)
+    dt, fl = cpu_sample(rows, threads, a32, b32, out32)
+    cpu_baseline = {
+        "value": fl / dt / 1e12, "unit": UNIT, "cores": threads, "kind": "port",
+        "sample": (f"{rows} of {N_DIM} output rows of each of the four products ({dt:.1f} s) through the port of "
+                   f"CPUBackend's loop, OpenMP over rows; the reference runs it on one thread"),
+    }
+
+    line = {
+        "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+        "warmup": max(args.warmup, 3), "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f16 in, f32 accumulate", "data": "synthetic",
+        "config": {"workload": WORKLOAD, "products_per_step": 4, "l2": "inputs larger than L2 (384 MB per product)",
+                   "kernel": info, "per_rank": "each rank runs the step on its own operands; no collective"},
+        "clocks": clocks,
+        "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                "steps": e2e_steps},
+        "gpu_launches": launches,
+        "roofline": roofline,
+        "cpu_baseline": cpu_baseline,
+    }
+    if args.all_configs:
+        line["extra"] = other_configs(be, stream, rank, world)
+    print(json.dumps(line), flush=True)
+    if use_dist:
+        dist.destroy_process_group()
+
+
+def other_configs(be, stream, rank, world):
+    """Quick device-resident numbers for configurations 1, 3, 4 and 5 (single GPU)."""
+    import numpy as np
+    import torch
+
+    def timed(fn, iters):
+        for _ in range(3):
+            fn()
+        e0 = torch.cuda.Event(enable_timing=True); e1 = torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        for _ in range(iters):
+            fn()
+        e1.record(stream)
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / iters
+
+    res = {}
+    g = torch.Generator(device="cuda").manual_seed(0)
+    a = torch.rand((1024, 1024), generator=g, device="cuda"); b = torch.rand((1024, 1024), generator=g, device="cuda")
+    o = torch.empty((1024, 1024), device="cuda"); od = be.wrap(o.data_ptr(), o.numel() * 4, o)
+    ms = timed(lambda: be.matmul(a, False, b, False, False, 1024, 1024, 1024, np.float32, out=od), 20)
+    res["c1_f32_1024"] = {"ms": ms, "tflops": 2 * 1024 ** 3 / ms / 1e9}
+    q = torch.randn((64, 2048, 128), generator=g, device="cuda").half(); k = torch.randn((64, 2048, 128), generator=g, device="cuda").half()
+    o = torch.empty((64, 2048, 2048), device="cuda", dtype=torch.float16); od = be.wrap(o.data_ptr(), o.numel() * 2, o)
+    ms = timed(lambda: be.batchedMatmul(64, q, False, k, True, False, 2048, 128, 2048, np.float16, out=od), 20)
+    res["c3_f16_batched_qkT"] = {"ms": ms, "tflops": 2 * 64 * 2048 * 2048 * 128 / ms / 1e9,
+                                 "hbm_gbs": (2 * 64 * 2048 * 128 * 2 + 64 * 2048 * 2048 * 2) / ms / 1e6}
+    del q, k, o
+    x = torch.randn((16384, 4096), generator=g, device="cuda").half()
+    w = ((torch.rand((16384, 4096), generator=g, device="cuda") - 0.5) / 32).half()
+    dy = torch.randn((16384, 16384), generator=g, device="cuda").half()
+    y = torch.empty((16384, 16384), device="cuda", dtype=torch.float16); yd = be.wrap(y.data_ptr(), y.numel() * 2, y)
+    dx = torch.empty((16384, 4096), device="cuda", dtype=torch.float16); dxd = be.wrap(dx.data_ptr(), dx.numel() * 2, dx)
+    dw = torch.empty((16384, 4096), device="cuda", dtype=torch.float16); dwd = be.wrap(dw.data_ptr(), dw.numel() * 2, dw)
+
+    def triple():
+        be.matmul(x, False, w, True, False, 16384, 4096, 16384, np.float16, out=yd)       # Y = X W^T
+        be.matmul(dy, False, w, False, False, 16384, 16384, 4096, np.float16, out=dxd)    # dX = dY W
+        be.matmul(x, True, dy, False, True, 4096, 16384, 16384, np.float16, out=dwd)      # dW = (X^T dY)^T = dY^T X
+
+    ms = timed(triple, 5)
+    res["c4_f16_linear_triple"] = {"ms": ms, "tflops": 3 * 2 * 16384 * 16384 * 4096 / ms / 1e9}
+    del x, w, dy, y, dx, dw
+    a = torch.rand((16384, 16384), generator=g, device="cuda") * 2 - 1
+    b = torch.rand((16384, 16384), generator=g, device="cuda") * 2 - 1
+    o = torch.empty((16384, 16384), device="cuda"); od = be.wrap(o.data_ptr(), o.numel() * 4, o)
+    ms = timed(lambda: be.matmul(a, False, b, False, False, 16384, 16384, 16384, np.float32, out=od), 2)
+    res["c5_f32_16384_3xtf32"] = {"ms": ms, "tflops_effective": 2 * 16384 ** 3 / ms / 1e9}
+    be.checkDeviceStatus()
+    return res
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=100)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
+    ap.add_argument("--all-configs", action="store_true")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

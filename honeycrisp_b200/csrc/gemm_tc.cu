@@ -11,6 +11,12 @@
 //                      store it, and hand the buffer back, while the issuer already works on
 //                      the other buffer.
 //
+// Large products run the same roles on CTA pairs (cta_group::2): the two CTAs of a cluster own
+// the upper and lower 128 rows of a 256-row tile, each loads its own rows of A and its own half
+// of the B columns, and the leader CTA issues one MMA that spans both SMs.  That halves the
+// shared-memory traffic per flop, which is what bounds the single-CTA form.  Every copy is an
+// ordinary per-CTA TMA load into the CTA's own shared memory.
+//
 // Transposed operands are never moved: a "K-major" operand (contracted index contiguous) and
 // an "MN-major" one (row/column index contiguous) differ only in the TMA box shape and in one
 // bit of the instruction descriptor.
@@ -50,6 +56,7 @@ struct TcParams {
   int64_t ldc, strideC;
   unsigned int* status;
   int vec_ok;         // C base and ldc allow 16-byte stores
+  int tile_rows;      // 128 per CTA of the group
   int debug;
 };
 
@@ -63,6 +70,20 @@ __device__ __forceinline__ unsigned long long globaltimer_ns() {
   asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
   return t;
 }
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+// Address of the same shared-memory location in CTA `rank` of this cluster.
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t addr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\nbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
   asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
 }
@@ -70,8 +91,9 @@ __device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
   asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes)
                : "memory");
 }
-__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
-  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+// Arrive on a barrier given by its cluster-wide address (this CTA's or the partner's).
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t bar) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(bar) : "memory");
 }
 __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
   uint32_t ok;
@@ -105,13 +127,24 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
   return mbar_wait_slow(bar, parity, abort_flag);
 }
 
+// Tiled TMA load of one box into this CTA's shared memory.  With kCta == 2 the completion
+// bytes are counted on a barrier that may live in the partner CTA (the leader's).
+template <int kCta>
 __device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map, uint32_t bar,
                                             int c0, int c1, int c2) {
-  asm volatile(
-      "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes "
-      "[%0], [%1, {%3, %4, %5}], [%2];"
-      ::"r"(dst), "l"((unsigned long long)map), "r"(bar), "r"(c0), "r"(c1), "r"(c2)
-      : "memory");
+  if (kCta == 2) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes "
+        "[%0], [%1, {%3, %4, %5}], [%2];"
+        ::"r"(dst), "l"((unsigned long long)map), "r"(bar), "r"(c0), "r"(c1), "r"(c2)
+        : "memory");
+  } else {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes "
+        "[%0], [%1, {%3, %4, %5}], [%2];"
+        ::"r"(dst), "l"((unsigned long long)map), "r"(bar), "r"(c0), "r"(c1), "r"(c2)
+        : "memory");
+  }
 }
 
 __device__ __forceinline__ void tc_fence_before() {
@@ -120,23 +153,42 @@ __device__ __forceinline__ void tc_fence_before() {
 __device__ __forceinline__ void tc_fence_after() {
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 }
+// Arrive on `bar` (cluster-wide address) once every MMA issued so far by this thread is done.
+template <int kCta>
 __device__ __forceinline__ void tc_commit(uint32_t bar) {
-  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar)
-               : "memory");
+  if (kCta == 2) {
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar)
+                 : "memory");
+  } else {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar)
+                 : "memory");
+  }
 }
-template <bool kTf32>
+template <bool kTf32, int kCta>
 __device__ __forceinline__ void tc_mma(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc,
                                        uint32_t idesc, uint32_t accumulate) {
-  if (kTf32) {
+  if (kTf32 && kCta == 1) {
     asm volatile(
         "{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\n"
         "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n}\n"
         ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
         : "memory");
-  } else {
+  } else if (kTf32 && kCta == 2) {
+    asm volatile(
+        "{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\n"
+        "tcgen05.mma.cta_group::2.kind::tf32 [%0], %1, %2, %3, p;\n}\n"
+        ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+        : "memory");
+  } else if (kCta == 1) {
     asm volatile(
         "{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\n"
         "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}\n"
+        ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+        : "memory");
+  } else {
+    asm volatile(
+        "{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\n"
+        "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n}\n"
         ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
         : "memory");
   }
@@ -159,21 +211,24 @@ __device__ __forceinline__ void tmem_ld_wait() {
   asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
 
-// Shared-memory matrix descriptor of tcgen05.mma, 128-byte swizzle.
+// Shared-memory matrix descriptor of tcgen05.mma.
 //   bits  0-13 start address >> 4      bits 16-29 leading-dimension byte offset >> 4
 //   bits 32-45 stride byte offset >> 4 bits 46-47 descriptor version (1 on sm_100)
-//   bits 61-63 swizzle mode (2 = 128 bytes)
+//   bits 61-63 swizzle mode: 2 = 128-byte rows permuted in 16-byte units,
+//                            1 = 128-byte rows permuted in 32-byte units
 // K-major operand : rows are 128-byte k-slabs; 8-row groups are 1024 bytes apart (stride offset).
-// MN-major operand: each 128-byte row holds consecutive M (or N) indices for one k; 8 k-rows
-//                   form a 1024-byte group (stride offset); the next run of M/N indices starts
-//                   one whole box later (leading offset).
-__device__ __forceinline__ uint64_t make_smem_desc(uint32_t addr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+// MN-major operand: each 128-byte row holds consecutive M (or N) indices for one k; a group of
+//                   k-rows (8 rows for 16-bit data; 4 rows for 32-bit data, which only supports
+//                   the 32-byte-unit swizzle in this orientation) is one stride offset; the
+//                   next run of M/N indices starts one whole box later (leading offset).
+__device__ __forceinline__ uint64_t make_smem_desc(uint32_t addr, uint32_t lbo_bytes, uint32_t sbo_bytes,
+                                                   uint32_t swizzle_mode) {
   uint64_t d = 0;
   d |= (uint64_t)((addr >> 4) & 0x3FFF);
   d |= (uint64_t)((lbo_bytes >> 4) & 0x3FFF) << 16;
   d |= (uint64_t)((sbo_bytes >> 4) & 0x3FFF) << 32;
   d |= (uint64_t)1 << 46;
-  d |= (uint64_t)2 << 61;
+  d |= (uint64_t)swizzle_mode << 61;
   return d;
 }
 
@@ -238,8 +293,10 @@ __device__ __forceinline__ TileCoord decode_tile(int64_t tile, const TcParams& p
 }
 
 // kElemBytes: 2 (float16 operands) or 4 (float32 operands consumed as TF32).
+// kBN       : tile width in output columns.
 // kWindowed : epilogue sums accumulation windows in registers (float32 output only).
-template <int kElemBytes, int kBN, int kStages, int kEpiWarps, bool kWindowed>
+// kCta      : 1, or 2 for CTA pairs (cluster of two, 256-row tiles, one MMA over both SMs).
+template <int kElemBytes, int kBN, int kStages, int kEpiWarps, bool kWindowed, int kCta>
 __global__ void __launch_bounds__(64 + 32 * kEpiWarps, 1)
 tc_gemm_kernel(const __grid_constant__ CUtensorMap mapA_hi, const __grid_constant__ CUtensorMap mapA_lo,
                const __grid_constant__ CUtensorMap mapB_hi, const __grid_constant__ CUtensorMap mapB_lo,
@@ -248,14 +305,19 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap mapA_hi, const __grid_constan
   constexpr bool kOutHalf = (kElemBytes == 2);
   constexpr int BK = 128 / kElemBytes;       // elements in one 128-byte slab row
   constexpr int UMMA_K = 32 / kElemBytes;    // k per tcgen05.mma
-  constexpr int KGROUPS = UMMA_K / 8;        // 8-row k groups one MMA consumes of an MN-major operand
   constexpr int CH = 128 / kElemBytes;       // M/N indices in one 128-byte row of an MN-major box
-  constexpr uint32_t A_BYTES = BM * 128, B_BYTES = kBN * 128, STAGE_BYTES = A_BYTES + B_BYTES;
+  constexpr int BN_LOCAL = kBN / kCta;       // B columns this CTA loads
+  // MN-major geometry: 16-bit data uses the 16-byte-unit swizzle with 8-row k groups, 32-bit
+  // data the 32-byte-unit swizzle with 4-row k groups.  One MMA consumes UMMA_K 128-byte k-rows.
+  constexpr uint32_t MN_SBO = kTf32 ? 512u : 1024u;
+  constexpr uint32_t MN_MODE = kTf32 ? 1u : 2u;
+  constexpr uint32_t A_BYTES = BM * 128, B_BYTES = BN_LOCAL * 128, STAGE_BYTES = A_BYTES + B_BYTES;
   constexpr int TMEM_COLS = (2 * kBN <= 32) ? 32 : 2 * kBN;
   constexpr int COL_SPLIT = kEpiWarps / 4;   // epilogue warps sharing one lane quarter
   constexpr int COLS_PER_THREAD = kBN / COL_SPLIT;
   static_assert(kEpiWarps == 4 || kEpiWarps == 8, "epilogue warps come in groups of four");
   static_assert(TMEM_COLS == 64 || TMEM_COLS == 128 || TMEM_COLS == 256 || TMEM_COLS == 512, "power of two");
+  static_assert(kCta == 1 || kCta == 2, "one CTA or a pair");
 
   extern __shared__ uint8_t smem_raw[];
   __shared__ __align__(8) uint64_t bars[2 * kStages + 4];
@@ -263,6 +325,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap mapA_hi, const __grid_constan
   __shared__ int abort_flag;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t rank = (kCta == 2) ? cluster_ctarank() : 0u;
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   const uint32_t bar_full = smem_u32(&bars[0]);
   const uint32_t bar_empty = smem_u32(&bars[kStages]);
@@ -277,36 +340,50 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap mapA_hi, const __grid_constan
     }
     for (int s = 0; s < 2; s++) {
       mbar_init(bar_tfull + 8 * s, 1);
-      mbar_init(bar_tempty + 8 * s, 32 * kEpiWarps);
+      mbar_init(bar_tempty + 8 * s, 32 * kEpiWarps * kCta);
     }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   }
   if (warp == 1) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_slot)),
-                 "r"((uint32_t)TMEM_COLS)
-                 : "memory");
-    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    if (kCta == 2) {
+      asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_slot)),
+                   "r"((uint32_t)TMEM_COLS)
+                   : "memory");
+      asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+    } else {
+      asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_slot)),
+                   "r"((uint32_t)TMEM_COLS)
+                   : "memory");
+      asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
   }
   tc_fence_before();
   __syncthreads();
+  if (kCta == 2) cluster_sync_all();   // the partner's barriers are initialised before anyone signals them
   tc_fence_after();
   const uint32_t tmem_base = tmem_base_slot;
   volatile int* abortp = &abort_flag;
 
   const int nkb = p.num_k_blocks;
   const int chunk_kb = p.chunk_kb;
+  const int64_t tile_first = blockIdx.x / kCta, tile_step = gridDim.x / kCta;
 
   if (warp == 0) {
     // ---------------------------------------------------------------- TMA producer
     if (lane == 0) {
       asm volatile("prefetch.tensormap [%0];" ::"l"((unsigned long long)&mapA_hi) : "memory");
       asm volatile("prefetch.tensormap [%0];" ::"l"((unsigned long long)&mapB_hi) : "memory");
+      // Completion bytes of both CTAs of a pair are counted on the leader's barrier.
+      const uint32_t full_leader = (kCta == 2) ? map_to_cta(bar_full, 0) : bar_full;
       uint32_t s = 0, ph = 0;
       bool ok = true;
-      for (int64_t tile = blockIdx.x; ok && tile < p.total_tiles; tile += gridDim.x) {
+      if (p.debug & 32) ok = false;  // timing experiment: the issuer runs without a producer
+      for (int64_t tile = tile_first; ok && tile < p.total_tiles; tile += tile_step) {
         const TileCoord t = decode_tile(tile, p);
-        const int m0 = t.tm * BM, n0 = t.tn * kBN, mat = (int)t.mat;
+        const int m0 = t.tm * (BM * kCta) + (int)rank * BM;
+        const int n0 = t.tn * kBN + (int)rank * BN_LOCAL;
+        const int mat = (int)t.mat;
         for (int kb = 0; kb < nkb; kb++) {
           if (!mbar_wait(bar_empty + 8 * s, ph ^ 1, abortp)) {
             atomicOr(p.status, kDevTimeoutProducer);
@@ -319,40 +396,59 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap mapA_hi, const __grid_constan
           // pass 0: A_lo*B_hi, pass 1: A_hi*B_lo, pass 2: A_hi*B_hi
           const CUtensorMap* ma = (phase == 0) ? &mapA_lo : &mapA_hi;
           const CUtensorMap* mb = (phase == 1) ? &mapB_lo : &mapB_hi;
-          const uint32_t full = bar_full + 8 * s;
+          const uint32_t full = full_leader + 8 * s;
           const uint32_t sa = smem_base + s * STAGE_BYTES, sb = sa + A_BYTES;
-          mbar_expect_tx(full, STAGE_BYTES);
+          if (p.debug & 8) {  // timing experiment: no copies
+            if (rank == 0) mbar_expect_tx(bar_full + 8 * s, 0);
+            if (++s == kStages) { s = 0; ph ^= 1; }
+            continue;
+          }
+          if (rank == 0) mbar_expect_tx(bar_full + 8 * s, STAGE_BYTES * kCta);
           if (!p.a_mn_major) {
-            tma_load_3d(sa, ma, full, kc, m0, mat);
+            tma_load_3d<kCta>(sa, ma, full, kc, m0, mat);
           } else {
 #pragma unroll
-            for (int c = 0; c < BM / CH; c++) tma_load_3d(sa + c * (BK * 128), ma, full, m0 + c * CH, kc, mat);
+            for (int c = 0; c < BM / CH; c++) tma_load_3d<kCta>(sa + c * (BK * 128), ma, full, m0 + c * CH, kc, mat);
           }
           if (!p.b_mn_major) {
-            tma_load_3d(sb, mb, full, kc, n0, mat);
+            tma_load_3d<kCta>(sb, mb, full, kc, n0, mat);
           } else {
 #pragma unroll
-            for (int c = 0; c < kBN / CH; c++) tma_load_3d(sb + c * (BK * 128), mb, full, n0 + c * CH, kc, mat);
+            for (int c = 0; c < BN_LOCAL / CH; c++)
+              tma_load_3d<kCta>(sb + c * (BK * 128), mb, full, n0 + c * CH, kc, mat);
+          }
+          if (++s == kStages) { s = 0; ph ^= 1; }
+        }
+      }
+      if (kCta == 2 && ok && !(p.debug & 32)) {
+        // Drain: every slot's release (an asynchronous arrive from the leader's MMA commits)
+        // must have landed in this CTA's barriers before the CTA may exit.
+        for (int i = 0; i < kStages; i++) {
+          if (!mbar_wait(bar_empty + 8 * s, ph ^ 1, abortp)) {
+            atomicOr(p.status, kDevTimeoutProducer);
+            abort_flag = 1;
+            break;
           }
           if (++s == kStages) { s = 0; ph ^= 1; }
         }
       }
     }
   } else if (warp == 1) {
-    // ---------------------------------------------------------------- MMA issuer
-    if (lane == 0) {
-      const uint32_t idesc = make_idesc(kTf32, p.a_mn_major, p.b_mn_major, BM, kBN);
-      const bool swap = (p.debug & 1) != 0;
-      // K-major: leading offset unused (1), stride offset = 8 rows * 128 B.
-      // MN-major: leading offset = one box (BK rows * 128 B), stride offset = 8 k-rows * 128 B.
-      const uint32_t mn_lbo = swap ? 1024u : (uint32_t)(BK * 128), mn_sbo = swap ? (uint32_t)(BK * 128) : 1024u;
-      const uint32_t a_lbo = p.a_mn_major ? mn_lbo : 16u, a_sbo = p.a_mn_major ? mn_sbo : 1024u;
-      const uint32_t b_lbo = p.b_mn_major ? mn_lbo : 16u, b_sbo = p.b_mn_major ? mn_sbo : 1024u;
-      const uint32_t a_kstep = p.a_mn_major ? (uint32_t)(KGROUPS * 1024) : 32u;
-      const uint32_t b_kstep = p.b_mn_major ? (uint32_t)(KGROUPS * 1024) : 32u;
+    // ---------------------------------------------------------------- MMA issuer (leader CTA)
+    if (lane == 0 && rank == 0) {
+      const uint32_t idesc = make_idesc(kTf32, p.a_mn_major, p.b_mn_major, BM * kCta, kBN);
+      // K-major: leading offset unused (1 unit), stride offset = 8 rows * 128 B.
+      // MN-major: leading offset = one box (BK rows * 128 B), stride offset = one k-row group.
+      const uint32_t a_lbo = p.a_mn_major ? (uint32_t)(BK * 128) : 16u, a_sbo = p.a_mn_major ? MN_SBO : 1024u;
+      const uint32_t b_lbo = p.b_mn_major ? (uint32_t)(BK * 128) : 16u, b_sbo = p.b_mn_major ? MN_SBO : 1024u;
+      const uint32_t a_mode = p.a_mn_major ? MN_MODE : 2u, b_mode = p.b_mn_major ? MN_MODE : 2u;
+      const uint32_t a_kstep = p.a_mn_major ? (uint32_t)(UMMA_K * 128) : 32u;
+      const uint32_t b_kstep = p.b_mn_major ? (uint32_t)(UMMA_K * 128) : 32u;
+      const uint32_t empty_peer = (kCta == 2) ? map_to_cta(bar_empty, 1) : 0u;
+      const uint32_t tfull_peer = (kCta == 2) ? map_to_cta(bar_tfull, 1) : 0u;
       uint32_t s = 0, ph = 0, win = 0, slot = 0;
       bool ok = true;
-      for (int64_t tile = blockIdx.x; ok && tile < p.total_tiles; tile += gridDim.x) {
+      for (int64_t tile = tile_first; ok && tile < p.total_tiles; tile += tile_step) {
         for (int kb = 0; kb < nkb; kb++) {
           const int in_win = kb % chunk_kb;
           if (in_win == 0) {
@@ -365,7 +461,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap mapA_hi, const __grid_constan
             }
             tc_fence_after();
           }
-          if (!mbar_wait(bar_full + 8 * s, ph, abortp)) {
+          if (!(p.debug & 32) && !mbar_wait(bar_full + 8 * s, ph, abortp)) {
             atomicOr(p.status, kDevTimeoutMma);
             abort_flag = 1;
             ok = false;
@@ -373,17 +469,22 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap mapA_hi, const __grid_constan
           }
           tc_fence_after();
           const uint32_t sa = smem_base + s * STAGE_BYTES, sb = sa + A_BYTES;
-          const uint64_t adesc = make_smem_desc(sa, a_lbo, a_sbo);
-          const uint64_t bdesc = make_smem_desc(sb, b_lbo, b_sbo);
+          const uint64_t adesc = make_smem_desc(sa, a_lbo, a_sbo, a_mode);
+          const uint64_t bdesc = make_smem_desc(sb, b_lbo, b_sbo, b_mode);
           const uint32_t d = tmem_base + slot * kBN;
 #pragma unroll
           for (int k = 0; k < BK / UMMA_K; k++) {
-            tc_mma<kTf32>(d, adesc + (uint64_t)((k * a_kstep) >> 4), bdesc + (uint64_t)((k * b_kstep) >> 4), idesc,
-                          (in_win | k) ? 1u : 0u);
+            if (p.debug & 16) break;  // timing experiment: no MMAs
+            tc_mma<kTf32, kCta>(d, adesc + (uint64_t)((k * a_kstep) >> 4), bdesc + (uint64_t)((k * b_kstep) >> 4),
+                                idesc, (in_win | k) ? 1u : 0u);
           }
-          tc_commit(bar_empty + 8 * s);
+          if (!(p.debug & 32)) {
+            tc_commit<kCta>(bar_empty + 8 * s);
+            if (kCta == 2) tc_commit<kCta>(empty_peer + 8 * s);
+          }
           if (in_win == chunk_kb - 1 || kb == nkb - 1) {
-            tc_commit(bar_tfull + 8 * slot);
+            tc_commit<kCta>(bar_tfull + 8 * slot);
+            if (kCta == 2) tc_commit<kCta>(tfull_peer + 8 * slot);
             win++;
           }
           if (++s == kStages) { s = 0; ph ^= 1; }
@@ -397,11 +498,13 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap mapA_hi, const __grid_constan
     const int col_part = ew / 4;             // which share of the columns
     const int col0 = col_part * COLS_PER_THREAD;
     const uint32_t lane_base = (uint32_t)(quarter * 32) << 16;
+    // Buffers are handed back to the leader's MMA issuer.
+    const uint32_t tempty_leader = (kCta == 2) ? map_to_cta(bar_tempty, 0) : bar_tempty;
     uint32_t win = 0;
     bool ok = true;
-    for (int64_t tile = blockIdx.x; ok && tile < p.total_tiles; tile += gridDim.x) {
+    for (int64_t tile = tile_first; ok && tile < p.total_tiles; tile += tile_step) {
       const TileCoord t = decode_tile(tile, p);
-      const int64_t gm = (int64_t)t.tm * BM + quarter * 32 + lane;
+      const int64_t gm = (int64_t)t.tm * (BM * kCta) + rank * BM + quarter * 32 + lane;
       const int64_t n0 = (int64_t)t.tn * kBN + col0;
       void* cmat = kOutHalf ? (void*)((__half*)p.C + t.mat * p.strideC) : (void*)((float*)p.C + t.mat * p.strideC);
       const int64_t row_off = gm * p.ldc;
@@ -428,7 +531,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap mapA_hi, const __grid_constan
           if (gm < p.M && n0 + c < p.N) store_row32<kOutHalf>(cmat, row_off, n0 + c, p.N, v, p.vec_ok != 0);
         }
         tc_fence_before();
-        mbar_arrive(bar_tempty + 8 * slot);
+        mbar_arrive_cluster(tempty_leader + 8 * slot);
         win++;
       } else {
         float acc[COLS_PER_THREAD];
@@ -457,7 +560,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap mapA_hi, const __grid_constan
             }
           }
           tc_fence_before();
-          mbar_arrive(bar_tempty + 8 * slot);
+          mbar_arrive_cluster(tempty_leader + 8 * slot);
           win++;
         }
         if (ok && gm < p.M) {
@@ -477,6 +580,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap mapA_hi, const __grid_constan
   __syncwarp();
   tc_fence_before();
   __syncthreads();
+  if (kCta == 2) cluster_sync_all();   // neither CTA leaves while the other may still signal it
   tc_fence_after();
   if (abort_flag) {
     // Give copies and MMAs that were already issued time to land before the CTA's
@@ -486,8 +590,13 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap mapA_hi, const __grid_constan
     __syncthreads();
   }
   if (warp == 1) {
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)TMEM_COLS)
-                 : "memory");
+    if (kCta == 2) {
+      asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)TMEM_COLS)
+                   : "memory");
+    } else {
+      asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)TMEM_COLS)
+                   : "memory");
+    }
   }
 }
 
@@ -539,8 +648,10 @@ EncodeTiledFn encode_fn() {
 }
 
 // One operand as a rank-3 tensor {contiguous index, other index, matrix}.
+// `box_rows` is the number of M (or N) indices one load brings in for a K-major operand; an
+// MN-major operand is always loaded in boxes of one 128-byte row of indices by one k-slab.
 bool make_operand_map(CUtensorMap* map, const void* base, int elem_bytes, bool mn_major, int64_t mn, int64_t k,
-                      int64_t ld, int64_t stride_mat, int64_t batch, int tile_mn) {
+                      int64_t ld, int64_t stride_mat, int64_t batch, int box_rows) {
   EncodeTiledFn fn = encode_fn();
   if (!fn) return false;
   const int per_row = 128 / elem_bytes;
@@ -548,11 +659,15 @@ bool make_operand_map(CUtensorMap* map, const void* base, int elem_bytes, bool m
   cuuint64_t mat_bytes = (cuuint64_t)stride_mat * elem_bytes;
   if (batch == 1) mat_bytes = (cuuint64_t)ld * elem_bytes * dims[1];
   cuuint64_t strides[2] = {(cuuint64_t)ld * elem_bytes, mat_bytes};
-  cuuint32_t box[3] = {(cuuint32_t)per_row, (cuuint32_t)(mn_major ? per_row : tile_mn), 1};
+  cuuint32_t box[3] = {(cuuint32_t)per_row, (cuuint32_t)(mn_major ? per_row : box_rows), 1};
   cuuint32_t estr[3] = {1, 1, 1};
+  // 32-bit MN-major operands must use the swizzle that permutes 32-byte units (the only one
+  // tcgen05.mma accepts for them); everything else the usual 16-byte-unit 128B swizzle.
+  const CUtensorMapSwizzle swz =
+      (mn_major && elem_bytes == 4) ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_128B;
   CUresult r = fn(map, elem_bytes == 2 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3,
-                  const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                  CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+                  const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, swz,
+                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return r == CUDA_SUCCESS;
 }
 
@@ -566,36 +681,95 @@ bool operand_ok(const void* base, int elem_bytes, int64_t ld, int64_t stride_mat
   return true;
 }
 
+int env_int(const char* name, int fallback) {
+  const char* e = getenv(name);
+  return e ? atoi(e) : fallback;
+}
+// Development switches (not part of the interface): bit 1 = no accumulation windows,
+// bit 2 = never pair CTAs.
 int debug_flags() {
-  static int v = -1;
-  if (v < 0) {
-    const char* e = getenv("HC_TC_DEBUG");
-    v = e ? atoi(e) : 0;
-  }
+  static int v = env_int("HC_TC_DEBUG", 0);
   return v;
 }
-
-template <int kElemBytes, int kBN, int kStages, int kEpiWarps, bool kWindowed>
-cudaError_t launch_cfg(const CUtensorMap maps[4], const TcParams& p, int grid, cudaStream_t stream,
-                       LaunchRecord* rec) {
-  auto kern = tc_gemm_kernel<kElemBytes, kBN, kStages, kEpiWarps, kWindowed>;
-  constexpr size_t smem = (size_t)kStages * (BM * 128 + kBN * 128) + 1024;
-  static bool configured[64] = {};
-  int dev = 0;
-  cudaGetDevice(&dev);
-  if (dev < 64 && !configured[dev]) {
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e != cudaSuccess) return e;
-    configured[dev] = true;
-  }
-  const int block = 64 + 32 * kEpiWarps;
-  kern<<<grid, block, smem, stream>>>(maps[0], maps[1], maps[2], maps[3], p);
-  if (rec) {
-    rec->tile_m = BM; rec->tile_n = kBN; rec->tile_k = 128 / kElemBytes; rec->stages = kStages;
-    rec->grid = grid; rec->block = block; rec->launches++;
-  }
-  return cudaGetLastError();
+// Slabs of the original contraction per accumulation window of a float32 product.
+int window_slabs() {
+  static int v = env_int("HC_TC_WINDOW_SLABS", 4);
+  return v < 1 ? 1 : v;
 }
+
+template <int kElemBytes, int kBN, int kStages, int kEpiWarps, bool kWindowed, int kCta>
+struct TcConfig {
+  static constexpr size_t smem = (size_t)kStages * (BM * 128 + (kBN / kCta) * 128) + 1024;
+  static constexpr int block = 64 + 32 * kEpiWarps;
+  static auto kernel() { return tc_gemm_kernel<kElemBytes, kBN, kStages, kEpiWarps, kWindowed, kCta>; }
+
+  static cudaError_t configure() {
+    static bool configured[64] = {};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev < 64 && !configured[dev]) {
+      cudaError_t e = cudaFuncSetAttribute(kernel(), cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+      if (e != cudaSuccess) return e;
+      if (kCta == 2) {
+        e = cudaFuncSetAttribute(kernel(), cudaFuncAttributeNonPortableClusterSizeAllowed, 0);
+        if (e != cudaSuccess) cudaGetLastError();
+      }
+      configured[dev] = true;
+    }
+    return cudaSuccess;
+  }
+
+  // CTA pairs that can be resident at once (pairs need two free SMs of one cluster-capable
+  // group; on some parts that leaves a few SMs unpaired).
+  static int max_pairs(int sm_count) {
+    static int cached[64] = {};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev < 64 && cached[dev]) return cached[dev];
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)(sm_count / 2 * 2));
+    cfg.blockDim = dim3(block);
+    cfg.dynamicSmemBytes = smem;
+    cudaLaunchAttribute attr;
+    attr.id = cudaLaunchAttributeClusterDimension;
+    attr.val.clusterDim.x = 2; attr.val.clusterDim.y = 1; attr.val.clusterDim.z = 1;
+    cfg.attrs = &attr;
+    cfg.numAttrs = 1;
+    int n = 0;
+    if (cudaOccupancyMaxActiveClusters(&n, kernel(), &cfg) != cudaSuccess || n <= 0) {
+      cudaGetLastError();
+      n = sm_count / 2;
+    }
+    if (dev < 64) cached[dev] = n;
+    return n;
+  }
+
+  static cudaError_t launch(const CUtensorMap maps[4], const TcParams& p, int sm_count, cudaStream_t stream,
+                            LaunchRecord* rec) {
+    cudaError_t e = configure();
+    if (e != cudaSuccess) return e;
+    int64_t groups = (kCta == 2) ? max_pairs(sm_count) : sm_count;
+    if (p.total_tiles < groups) groups = p.total_tiles;
+    const int grid = (int)groups * kCta;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)grid);
+    cfg.blockDim = dim3(block);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr;
+    attr.id = cudaLaunchAttributeClusterDimension;
+    attr.val.clusterDim.x = kCta; attr.val.clusterDim.y = 1; attr.val.clusterDim.z = 1;
+    cfg.attrs = &attr;
+    cfg.numAttrs = 1;
+    e = cudaLaunchKernelEx(&cfg, kernel(), maps[0], maps[1], maps[2], maps[3], p);
+    if (rec) {
+      rec->tile_m = BM * kCta; rec->tile_n = kBN; rec->tile_k = 128 / kElemBytes; rec->stages = kStages;
+      rec->grid = grid; rec->block = block; rec->launches++;
+    }
+    if (e != cudaSuccess) return e;
+    return cudaGetLastError();
+  }
+};
 
 }  // namespace
 
@@ -661,13 +835,17 @@ cudaError_t launch_tc(const GemmProblem& p, cudaStream_t stream, unsigned int* s
     lda = s.a_ld; ldb = s.b_ld; sa = s.a_mat; sb = s.b_mat;
   }
 
-  // Tile width: 256 columns unless the product is narrow.
+  // Tile shape: 256 columns unless the product is narrow; CTA pairs (256 rows) when there is
+  // more than one 128-row block of output.
+  const int dbg = debug_flags();
   const int bn = (p.N > 128) ? 256 : 128;
+  const int cta = (p.M > BM && bn == 256 && !(dbg & 4)) ? 2 : 1;
+  const int b_box = bn / cta;
   CUtensorMap maps[4];
   if (!make_operand_map(&maps[0], a_hi, eb, p.a_mn_major, p.M, p.K, lda, sa, p.batch, BM) ||
       !make_operand_map(&maps[1], a_lo, eb, p.a_mn_major, p.M, p.K, lda, sa, p.batch, BM) ||
-      !make_operand_map(&maps[2], b_hi, eb, p.b_mn_major, p.N, p.K, ldb, sb, p.batch, bn) ||
-      !make_operand_map(&maps[3], b_lo, eb, p.b_mn_major, p.N, p.K, ldb, sb, p.batch, bn))
+      !make_operand_map(&maps[2], b_hi, eb, p.b_mn_major, p.N, p.K, ldb, sb, p.batch, b_box) ||
+      !make_operand_map(&maps[3], b_lo, eb, p.b_mn_major, p.N, p.K, ldb, sb, p.batch, b_box))
     return cudaErrorNotSupported;
 
   TcParams tp;
@@ -675,34 +853,36 @@ cudaError_t launch_tc(const GemmProblem& p, cudaStream_t stream, unsigned int* s
   const int kslabs = (int)((p.K + BK - 1) / BK);
   tp.k_phases = f32 ? 3 : 1;
   tp.num_k_blocks = kslabs * tp.k_phases;
-  // float32: windows of 8 slabs (256 k, 24 MMA passes of 4 instructions) bound the number of
-  // non-rounding tensor-core accumulations that feed one rounded float32 add.
-  tp.chunk_kb = f32 ? 24 : tp.num_k_blocks;
+  // float32: a window bounds the number of truncating tensor-core accumulations that feed one
+  // correctly rounded float32 add in the epilogue.
+  const bool windowed = f32 && !(dbg & 2);
+  tp.chunk_kb = windowed ? 3 * window_slabs() : tp.num_k_blocks;
   if (tp.chunk_kb > tp.num_k_blocks) tp.chunk_kb = tp.num_k_blocks;
-  tp.tiles_m = (int)((p.M + BM - 1) / BM);
+  tp.tile_rows = BM * cta;
+  tp.tiles_m = (int)((p.M + tp.tile_rows - 1) / tp.tile_rows);
   tp.tiles_n = (int)((p.N + bn - 1) / bn);
   tp.total_tiles = (int64_t)tp.tiles_m * tp.tiles_n * p.batch;
-  tp.group_m = 16;
+  tp.group_m = 16 / cta;
   tp.a_mn_major = p.a_mn_major; tp.b_mn_major = p.b_mn_major;
   tp.C = p.C; tp.ldc = p.ldc; tp.strideC = p.strideC;
   tp.status = status_word;
   tp.vec_ok = (((uintptr_t)p.C & 15) == 0 && (p.ldc * eb) % 16 == 0 && (p.strideC * eb) % 16 == 0) ? 1 : 0;
-  tp.debug = debug_flags();
-  const int grid = (int)(tp.total_tiles < sm_count ? tp.total_tiles : sm_count);
+  tp.debug = dbg;
   if (rec) rec->tiles = tp.total_tiles;
 
-  const bool windowed = f32 && !(tp.debug & 2);
-  if (!windowed) tp.chunk_kb = tp.num_k_blocks;
   if (!f32) {
-    if (bn == 256) return launch_cfg<2, 256, 4, 4, false>(maps, tp, grid, stream, rec);
-    return launch_cfg<2, 128, 6, 4, false>(maps, tp, grid, stream, rec);
+    if (cta == 2) return TcConfig<2, 256, 6, 4, false, 2>::launch(maps, tp, sm_count, stream, rec);
+    if (bn == 256) return TcConfig<2, 256, 4, 4, false, 1>::launch(maps, tp, sm_count, stream, rec);
+    return TcConfig<2, 128, 6, 4, false, 1>::launch(maps, tp, sm_count, stream, rec);
   }
   if (windowed) {
-    if (bn == 256) return launch_cfg<4, 256, 4, 8, true>(maps, tp, grid, stream, rec);
-    return launch_cfg<4, 128, 6, 4, true>(maps, tp, grid, stream, rec);
+    if (cta == 2) return TcConfig<4, 256, 6, 8, true, 2>::launch(maps, tp, sm_count, stream, rec);
+    if (bn == 256) return TcConfig<4, 256, 4, 8, true, 1>::launch(maps, tp, sm_count, stream, rec);
+    return TcConfig<4, 128, 6, 4, true, 1>::launch(maps, tp, sm_count, stream, rec);
   }
-  if (bn == 256) return launch_cfg<4, 256, 4, 4, false>(maps, tp, grid, stream, rec);
-  return launch_cfg<4, 128, 6, 4, false>(maps, tp, grid, stream, rec);
+  if (cta == 2) return TcConfig<4, 256, 6, 4, false, 2>::launch(maps, tp, sm_count, stream, rec);
+  if (bn == 256) return TcConfig<4, 256, 4, 4, false, 1>::launch(maps, tp, sm_count, stream, rec);
+  return TcConfig<4, 128, 6, 4, false, 1>::launch(maps, tp, sm_count, stream, rec);
 }
 
 }  // namespace hc

@@ -1,0 +1,235 @@
+"""Parity of the CUDA path with the CPU oracle, through the C ABI (needs a B200)."""
+import threading
+
+import numpy as np
+import pytest
+
+from helpers import FLAG_COMBOS, golden, logical_out, random_operands, stored
+from oracle import reference_cpu as ref
+
+pytestmark = pytest.mark.gpu
+
+G = golden()
+
+
+@pytest.fixture(scope="module")
+def be():
+    from honeycrisp_b200 import CUDABackend
+    b = CUDABackend(0)
+    yield b
+    b.checkDeviceStatus()
+    b.close()
+
+
+def K():
+    from honeycrisp_b200 import _lib
+    return _lib
+
+
+def run(be, count, A, B, ta, tb, to, dtype, kernel=0):
+    rows, inner, cols = A.shape[-2], A.shape[-1], B.shape[-1]
+    a_st, b_st = stored(A, ta), stored(B, tb)
+    out = be.batchedMatmul(count, a_st, ta, b_st, tb, to, rows, inner, cols, dtype, kernel=kernel)
+    res = out.onCPU(dtype)[: count * rows * cols]
+    be.checkDeviceStatus()
+    return res, a_st, b_st
+
+
+# ---- the reference's own tests, replayed through the Tensor-level mirror --------------------
+
+@pytest.mark.parametrize("dtype", [np.float32, np.float16])
+@pytest.mark.parametrize("ta,tb,to", FLAG_COMBOS)
+def test_matrix_matrix_product(be, ta, tb, to, dtype):
+    """BackendTests.swift:684-712: exact output and both gradients for all eight flag triples."""
+    from honeycrisp_b200 import Tensor, matmul
+    v = G["matrix_matrix_product"]
+    x = np.array(v["x"], dtype=dtype).reshape(v["x_shape"])
+    y = np.array(v["y_before_t"], dtype=dtype).reshape(v["y_before_t_shape"]).T
+    g = np.array(v["out_grad"], dtype=dtype).reshape(v["out_shape"])
+    a = Tensor.fromHost(be, stored(x, ta), stored(x, ta).shape, dtype).onGrad()
+    b = Tensor.fromHost(be, stored(y, tb), stored(y, tb).shape, dtype).onGrad()
+    sub = matmul(a, ta, b, tb, to)
+    out = sub.numpy().T if to else sub.numpy()
+    assert list(out.shape) == [2, 4]
+    np.testing.assert_array_equal(out.reshape(-1).astype(np.float64), v["out"])
+    sub.backward(Tensor.fromHost(be, stored(g, to), stored(g, to).shape, dtype))
+    a_grad = a.grad.numpy().T if ta else a.grad.numpy()
+    b_grad = b.grad.numpy().T if tb else b.grad.numpy()
+    np.testing.assert_array_equal(a_grad.reshape(-1).astype(np.float64), v["a_grad"])
+    np.testing.assert_array_equal(b_grad.reshape(-1).astype(np.float64), v["b_grad"])
+
+
+@pytest.mark.parametrize("kernel", [0, 1, 2, 3])
+def test_ones_product_and_half_overflow(be, kernel):
+    """BackendTests.swift:713-725; every kernel, including the 3xTF32 path (small integers
+    split exactly, so 128 must come out exactly)."""
+    v = G["ones_product"]
+    a = np.ones(v["a_shape"], dtype=np.float32)
+    b = np.ones(v["b_shape"], dtype=np.float32)
+    z = be.matmul(a, False, b, False, False, 64, 128, 32, np.float32, kernel=kernel).onCPU(np.float32)
+    np.testing.assert_array_equal(z, np.full(64 * 32, v["value"], dtype=np.float32))
+    small = be.matmul(a.astype(np.float16), False, b.astype(np.float16), False, False, 64, 128, 32, np.float16,
+                      kernel=kernel).onCPU(np.float16)
+    assert np.isfinite(small.astype(np.float32).sum())
+    s = v["overflow_scale"]
+    big = be.matmul((a * s).astype(np.float16), False, (b * s).astype(np.float16), False, False, 64, 128, 32,
+                    np.float16, kernel=kernel).onCPU(np.float16)
+    assert not np.isfinite(big.astype(np.float32).sum())
+    assert np.all(np.isposinf(big.astype(np.float32)))
+
+
+def test_matrix_vector_product(be):
+    """BackendTests.swift:769-783."""
+    from honeycrisp_b200 import Tensor, matmul
+    v = G["matrix_vector_product"]
+    x = Tensor.fromHost(be, v["x"], v["x_shape"], np.float32).onGrad()
+    y = Tensor.fromHost(be, v["y"], v["y_shape"], np.float32).onGrad()
+    product = matmul(x, False, y, False, False)
+    np.testing.assert_array_equal(product.numpy().reshape(-1), np.array(v["out"], dtype=np.float32))
+    product.backward(Tensor.fromHost(be, np.ones((2, 1)), [2, 1], np.float32))
+    np.testing.assert_array_equal(x.grad.numpy().reshape(-1), np.array(v["x_grad"], dtype=np.float32))
+    assert x.grad.shape == v["x_shape"]
+    np.testing.assert_array_equal(y.grad.numpy().reshape(-1), np.array(v["y_grad"], dtype=np.float32))
+    assert y.grad.shape == v["y_shape"]
+
+
+@pytest.mark.parametrize("dtype,eps", [(np.float32, 1e-4), (np.float16, 1e-2)])
+@pytest.mark.parametrize("ta,tb,to", FLAG_COMBOS)
+def test_batched_matmul_matches_single(be, ta, tb, to, dtype, eps):
+    """BackendTests.swift:728-767: batched output and both gradients against per-matrix products."""
+    from honeycrisp_b200 import Tensor, batchedMatmul, matmul
+    A, B = random_operands(7, 3, 2, 3, 4, dtype, dist="uniform01")
+    Gr = np.random.default_rng(8).random((3, 2, 4)).astype(dtype)
+    a = Tensor.fromHost(be, stored(A, ta), stored(A, ta).shape, dtype).onGrad()
+    b = Tensor.fromHost(be, stored(B, tb), stored(B, tb).shape, dtype).onGrad()
+    pre = batchedMatmul(a, ta, b, tb, to)
+    pre.backward(Tensor.fromHost(be, stored(Gr, to), stored(Gr, to).shape, dtype))
+    out = pre.numpy()
+    for i in range(3):
+        ai = Tensor.fromHost(be, stored(A[i], ta), stored(A[i], ta).shape, dtype).onGrad()
+        bi = Tensor.fromHost(be, stored(B[i], tb), stored(B[i], tb).shape, dtype).onGrad()
+        single = matmul(ai, ta, bi, tb, to)
+        single.backward(Tensor.fromHost(be, stored(Gr[i], to), stored(Gr[i], to).shape, dtype))
+        np.testing.assert_allclose(single.numpy().astype(np.float32), out[i].astype(np.float32), atol=eps, rtol=eps)
+        np.testing.assert_allclose(ai.grad.numpy().astype(np.float32), a.grad.numpy()[i].astype(np.float32), atol=eps, rtol=eps)
+        np.testing.assert_allclose(bi.grad.numpy().astype(np.float32), b.grad.numpy()[i].astype(np.float32), atol=eps, rtol=eps)
+
+
+def test_concurrent_products_from_many_threads(be):
+    """HoneycrispTests.swift:847-871: 100 concurrent [128,16]x[16,1] products + backward passes."""
+    from honeycrisp_b200 import Tensor, matmul
+    v = G["concurrent_backward"]
+    rng = np.random.default_rng(3)
+    A = rng.standard_normal(v["a_shape"]).astype(np.float32)
+    Bv = rng.standard_normal(v["b_shape"]).astype(np.float32)
+    expect = ref.matmul(A, False, Bv, False, False, 128, 16, 1, library_fast_path=False)
+    results, errors = [None] * v["count"], []
+
+    def work(i):
+        try:
+            a = Tensor.fromHost(be, A, A.shape, np.float32).onGrad()
+            b = Tensor.fromHost(be, Bv, Bv.shape, np.float32).onGrad()
+            out = matmul(a, False, b, False, False, kernel=K().HC_KERNEL_SIMT_EXACT)
+            out.backward(Tensor.fromHost(be, np.ones((128, 1)), [128, 1], np.float32))
+            results[i] = (out.numpy().reshape(-1), a.grad.numpy(), b.grad.numpy())
+        except Exception as e:  # pragma: no cover
+            errors.append(e)
+
+    threads = [threading.Thread(target=work, args=(i,)) for i in range(v["count"])]
+    for t in threads:
+        t.start()
+    for t in threads:
+        t.join()
+    assert not errors
+    for out, ga, gb in results:
+        assert np.array_equal(out, expect)
+        assert np.array_equal(ga, results[0][1]) and np.array_equal(gb, results[0][2])
+
+
+# ---- bit-exact parity of the CUDA-core kernel with the reference CPU loop ------------------
+
+SHAPES_SMALL = [(1, 1, 1, 1), (2, 3, 4, 1), (7, 5, 3, 2), (64, 128, 32, 1), (129, 65, 130, 3), (300, 17, 7, 2),
+                (33, 257, 31, 1), (128, 16, 1, 4), (1, 40, 200, 1)]
+
+
+@pytest.mark.parametrize("dtype", [np.float32, np.float16])
+@pytest.mark.parametrize("shape", SHAPES_SMALL)
+def test_exact_kernel_is_bit_identical_to_cpu_loop(be, shape, dtype):
+    M, Kd, N, cnt = shape
+    for (ta, tb, to) in FLAG_COMBOS:
+        A, B = random_operands(M * 131 + N, cnt, M, Kd, N, dtype)
+        res, a_st, b_st = run(be, cnt, A, B, ta, tb, to, dtype, kernel=K().HC_KERNEL_SIMT_EXACT)
+        orc = ref.batched_matmul(cnt, a_st, ta, b_st, tb, to, M, Kd, N, library_fast_path=False)
+        assert np.array_equal(res.view(np.uint8), orc.view(np.uint8)), (shape, ta, tb, to)
+
+
+@pytest.mark.parametrize("shape", SHAPES_SMALL)
+def test_fused_kernel_is_bit_identical_for_half(be, shape):
+    """Products of two halves are exact in float32, so fusing the multiply-add changes nothing."""
+    M, Kd, N, cnt = shape
+    for (ta, tb, to) in [(False, False, False), (True, True, True), (False, True, False)]:
+        A, B = random_operands(M + N, cnt, M, Kd, N, np.float16)
+        res, a_st, b_st = run(be, cnt, A, B, ta, tb, to, np.float16, kernel=K().HC_KERNEL_SIMT)
+        orc = ref.batched_matmul(cnt, a_st, ta, b_st, tb, to, M, Kd, N)
+        assert np.array_equal(res.view(np.uint16), orc.view(np.uint16))
+
+
+def test_float32_plain_product_against_host_sgemm(be):
+    """The one case the reference sends to a library GEMM (BackendCPU.swift:1256): agreement
+    with the host sgemm stand-in within 1e-5 relative Frobenius error, all kernels."""
+    A, B = random_operands(0, 1, 256, 512, 384, np.float32, dist="uniform01")
+    host = ref.matmul(A, False, B, False, False, 256, 512, 384, library_fast_path=True)
+    for kernel in (0, 1, 2, 3):
+        res, _, _ = run(be, 1, A, B, False, False, False, np.float32, kernel=kernel)
+        assert ref.rel_frobenius(res, host) < 1e-5, kernel
+
+
+# ---- edge cases -----------------------------------------------------------------------------
+
+def test_empty_dimensions(be):
+    for dtype in (np.float32, np.float16):
+        z = be.matmul(np.zeros((3, 0), dtype), False, np.zeros((0, 4), dtype), False, False, 3, 0, 4, dtype)
+        assert np.all(z.onCPU(dtype)[:12] == 0)           # empty contraction sums to +0
+        z = be.matmul(np.zeros((0, 5), dtype), False, np.zeros((5, 4), dtype), False, False, 0, 5, 4, dtype)
+        assert z.byteCount == 0 and z.ptr != 0            # max(1, byteCount) allocation, no launch
+        z = be.batchedMatmul(0, np.zeros((0,), dtype), False, np.zeros((0,), dtype), False, False, 4, 5, 6, dtype)
+        assert z.byteCount == 0
+
+
+def test_int64_is_not_implemented(be):
+    from honeycrisp_b200 import DType, NotImplementedByBackend
+    with pytest.raises(NotImplementedByBackend):
+        be.matmul(np.zeros(4, np.int64), False, np.zeros(4, np.int64), False, False, 2, 2, 2, DType.int64)
+
+
+def test_undersized_operand_is_rejected(be):
+    with pytest.raises(ValueError):
+        be.matmul(np.zeros(5, np.float32), False, np.zeros(6, np.float32), False, False, 2, 3, 2, np.float32)
+
+
+def test_tensor_kernel_refuses_misaligned_shapes_and_auto_falls_back(be):
+    from honeycrisp_b200 import NotImplementedByBackend
+    A, B = random_operands(2, 1, 130, 67, 129, np.float16)   # leading dimensions not 16-byte multiples
+    with pytest.raises(NotImplementedByBackend):
+        run(be, 1, A, B, False, False, False, np.float16, kernel=K().HC_KERNEL_TENSOR)
+    res, a_st, b_st = run(be, 1, A, B, False, False, False, np.float16, kernel=0)
+    assert be.lastLaunchInfo()["kernel"] == K().HC_KERNEL_SIMT
+    orc = ref.matmul(a_st, False, b_st, False, False, 130, 67, 129)
+    assert np.array_equal(res.view(np.uint16), orc.view(np.uint16))
+
+
+def test_host_buffer_entry_point(be):
+    A, B = random_operands(9, 2, 96, 160, 72, np.float16)
+    out = be.batchedMatmulHost(2, stored(A, False), False, stored(B, True), True, False, 96, 160, 72, np.float16)
+    f64 = ref.batched_matmul_f64(2, stored(A, False), False, stored(B, True), True, False, 96, 160, 72)
+    assert ref.rel_frobenius(out, f64) < 2e-3
+    orc = ref.batched_matmul(2, stored(A, False), False, stored(B, True), True, False, 96, 160, 72)
+    assert ref.rel_frobenius(out, orc) < 1e-3
+
+
+def test_run_to_run_determinism(be):
+    A, B = random_operands(4, 2, 384, 512, 640, np.float16)
+    first, _, _ = run(be, 2, A, B, False, True, False, np.float16)
+    for _ in range(3):
+        again, _, _ = run(be, 2, A, B, False, True, False, np.float16)
+        assert np.array_equal(first.view(np.uint16), again.view(np.uint16))
