@@ -75,6 +75,20 @@ __device__ __forceinline__ uint32_t cluster_ctarank() {
   asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
   return r;
 }
+// True in exactly one lane of a fully active warp.  Choosing the issuing lane with elect.sync
+// (rather than comparing the lane index) tells the compiler that a single thread runs the
+// guarded code, so descriptors and barrier addresses can live in uniform registers.
+__device__ __forceinline__ bool elect_one() {
+  uint32_t pred;
+  asm volatile(
+      "{\n"
+      ".reg .pred P;\n"
+      "elect.sync _|P, 0xffffffff;\n"
+      "selp.u32 %0, 1, 0, P;\n"
+      "}\n"
+      : "=r"(pred));
+  return pred != 0;
+}
 // Address of the same shared-memory location in CTA `rank` of this cluster.
 __device__ __forceinline__ uint32_t map_to_cta(uint32_t addr, uint32_t rank) {
   uint32_t r;
@@ -371,7 +385,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap mapA_hi, const __grid_constan
 
   if (warp == 0) {
     // ---------------------------------------------------------------- TMA producer
-    if (lane == 0) {
+    if (elect_one()) {
       asm volatile("prefetch.tensormap [%0];" ::"l"((unsigned long long)&mapA_hi) : "memory");
       asm volatile("prefetch.tensormap [%0];" ::"l"((unsigned long long)&mapB_hi) : "memory");
       // Completion bytes of both CTAs of a pair are counted on the leader's barrier.
@@ -435,7 +449,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap mapA_hi, const __grid_constan
     }
   } else if (warp == 1) {
     // ---------------------------------------------------------------- MMA issuer (leader CTA)
-    if (lane == 0 && rank == 0) {
+    if (elect_one() && rank == 0) {
       const uint32_t idesc = make_idesc(kTf32, p.a_mn_major, p.b_mn_major, BM * kCta, kBN);
       // K-major: leading offset unused (1 unit), stride offset = 8 rows * 128 B.
       // MN-major: leading offset = one box (BK rows * 128 B), stride offset = one k-row group.
@@ -475,7 +489,9 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap mapA_hi, const __grid_constan
 #pragma unroll
           for (int k = 0; k < BK / UMMA_K; k++) {
             if (p.debug & 16) break;  // timing experiment: no MMAs
-            tc_mma<kTf32, kCta>(d, adesc + (uint64_t)((k * a_kstep) >> 4), bdesc + (uint64_t)((k * b_kstep) >> 4),
+            // timing experiment (bit 6): consecutive MMAs alternate between the two accumulators
+            const uint32_t dd = (p.debug & 64) ? tmem_base + (uint32_t)((k & 1) * kBN) : d;
+            tc_mma<kTf32, kCta>(dd, adesc + (uint64_t)((k * a_kstep) >> 4), bdesc + (uint64_t)((k * b_kstep) >> 4),
                                 idesc, (in_win | k) ? 1u : 0u);
           }
           if (!(p.debug & 32)) {

