@@ -1,0 +1,175 @@
+// CUDABackend: a Honeycrisp `Backend` whose matrix products run in libhccuda on a B200.
+//
+// Written against the reference's interfaces as read from its sources; it has NOT been
+// compiled (no Swift toolchain exists where this repository is built).  It subclasses the open
+// class `Backend` (Sources/Honeycrisp/Backend.swift:28) and overrides the two hot-path
+// primitives, `matmul` (:650-658) and `batchedMatmul` (:661-669); every other primitive keeps
+// the base class behaviour, `throw BackendError.notImplemented`, which is the reference's own
+// convention for partial backends.  Install with `Backend.defaultBackend = try CUDABackend()`.
+//
+// CHCCuda is the module map over include/hc_cuda.h (Sources/CHCCuda/module.modulemap; copy or
+// symlink the header next to it and put libhccuda.so on the linker path).
+
+import CHCCuda
+import Foundation
+import HCBacktrace
+import Honeycrisp
+
+/// Device buffer: the `Tensor.Data` conformer of this backend (Tensor.swift:69-85).
+public final class CUDAData: Tensor.Data, @unchecked Sendable {
+  public let backend: CUDABackend
+  public let pointer: UnsafeMutableRawPointer
+  public let byteCount: Int
+  /// Completion marker recorded after the work that fills this buffer.
+  var event: OpaquePointer?
+  /// Operands of that work; kept until the work is known to have run.
+  var inputs: [any Tensor.Data] = []
+
+  init(backend: CUDABackend, byteCount: Int) throws {
+    self.backend = backend
+    self.byteCount = byteCount
+    var ptr: UnsafeMutableRawPointer? = nil
+    // bytes == 0 allocates one byte, as MPSBackend does (BackendMPS.swift:538-540).
+    let st = hc_alloc(backend.ctx, byteCount, &ptr)
+    guard st == HC_OK, let p = ptr else { throw BackendError.allocationFailed(byteCount) }
+    self.pointer = p
+  }
+
+  deinit {
+    if let ev = event { hc_event_destroy(ev) }
+    // Stream-ordered free: runs after everything already enqueued that uses the buffer.
+    _ = hc_free(backend.ctx, pointer)
+  }
+
+  func mark() throws {
+    if let ev = event { hc_event_destroy(ev) }
+    var ev: OpaquePointer? = nil
+    try backend.check(hc_event_record(backend.ctx, &ev))
+    event = ev
+  }
+
+  public func wait() async throws {
+    let ev = event
+    let backend = self.backend
+    try await backend.offload {
+      if let ev = ev { try backend.check(hc_event_wait(ev)) } else { try backend.check(hc_sync(backend.ctx)) }
+    }
+    inputs = []
+  }
+
+  public func onCPU<T>(_ fn: (_: UnsafeRawPointer) async throws -> T) async throws -> T {
+    let host = UnsafeMutableRawPointer.allocate(byteCount: max(1, byteCount), alignment: 16)
+    defer { host.deallocate() }
+    let (ctx, src, n) = (backend.ctx, pointer, byteCount)
+    let backend = self.backend
+    try await backend.offload {
+      try backend.check(hc_d2h(ctx, host, src, n))
+      try backend.check(hc_sync(ctx))
+    }
+    return try await fn(UnsafeRawPointer(host))
+  }
+
+  public func mutateOnCPU<T>(_ fn: (_: UnsafeMutableRawPointer) async throws -> T) async throws -> T {
+    let host = UnsafeMutableRawPointer.allocate(byteCount: max(1, byteCount), alignment: 16)
+    defer { host.deallocate() }
+    let (ctx, dev, n) = (backend.ctx, pointer, byteCount)
+    let backend = self.backend
+    try await backend.offload {
+      try backend.check(hc_d2h(ctx, host, dev, n))
+      try backend.check(hc_sync(ctx))
+    }
+    let result = try await fn(host)
+    try await backend.offload {
+      try backend.check(hc_h2d(ctx, dev, host, n))
+      try backend.check(hc_sync(ctx))
+    }
+    return result
+  }
+}
+
+open class CUDABackend: Backend, @unchecked Sendable {
+  let ctx: OpaquePointer
+  /// Calls that may block (syncs, copies) leave the cooperative pool, as the reference backends
+  /// do with their WorkerThread (Backend.swift:135-163, BackendCPU.swift:235-248).
+  private let worker = Backend.WorkerThread()
+
+  public init(device: Int = 0) throws {
+    var c: OpaquePointer? = nil
+    let st = hc_init(Int32(device), &c)
+    guard st == HC_OK, let ctx = c else {
+      throw BackendError.kernelFailed("hc_init(device: \(device)): \(String(cString: hc_status_string(st)))")
+    }
+    self.ctx = ctx
+    super.init()
+  }
+
+  deinit { hc_destroy(ctx) }
+
+  func offload<T>(_ fn: @escaping () throws -> T) async throws -> T {
+    try await worker.schedule(fn)
+  }
+
+  func check(_ st: hc_status) throws {
+    if st == HC_OK { return }
+    let msg = String(cString: hc_last_error(ctx))
+    switch st {
+    case HC_ERR_ALLOCATION_FAILED: throw BackendError.allocationFailed(0)
+    case HC_ERR_NOT_IMPLEMENTED: throw BackendError.notImplemented(msg)
+    default: throw BackendError.kernelFailed(msg.isEmpty ? String(cString: hc_status_string(st)) : msg)
+    }
+  }
+
+  /// Operands of another backend's Data type are staged through onCPU, as
+  /// MPSBackend.gpuBuffer does (BackendMPS.swift:585-620).
+  func deviceOperand(_ x: Tensor.Data, byteCount n: Int) async throws -> CUDAData {
+    if let d = x as? CUDAData, d.backend === self { return d }
+    let out = try CUDAData(backend: self, byteCount: n)
+    try await x.onCPU { host in
+      try await self.offload {
+        try self.check(hc_h2d(self.ctx, out.pointer, host, n))
+        try self.check(hc_sync(self.ctx))
+      }
+    }
+    return out
+  }
+
+  func hcDType(_ dtype: Tensor.DType, _ op: String) throws -> hc_dtype {
+    switch dtype {
+    case .float16: return HC_F16
+    case .float32: return HC_F32
+    default: throw BackendError.notImplemented("\(op) for \(dtype)")
+    }
+  }
+
+  override open func matmul(
+    a: Tensor.Data, transA: Bool, b: Tensor.Data, transB: Bool, transOut: Bool, rows: Int,
+    inner: Int, cols: Int, dtype: Tensor.DType
+  ) async throws -> Tensor.Data {
+    try await batchedMatmul(
+      matrixCount: 1, a: a, transA: transA, b: b, transB: transB, transOut: transOut, rows: rows,
+      inner: inner, cols: cols, dtype: dtype)
+  }
+
+  override open func batchedMatmul(
+    matrixCount: Int, a: Tensor.Data, transA: Bool, b: Tensor.Data, transB: Bool, transOut: Bool,
+    rows: Int, inner: Int, cols: Int, dtype: Tensor.DType
+  ) async throws -> Tensor.Data {
+    let dt = try hcDType(dtype, "matmul")
+    let aCount = matrixCount * rows * inner * dtype.byteSize
+    let bCount = matrixCount * inner * cols * dtype.byteSize
+    // Same size checks MPSBackend makes before encoding (BackendMPS.swift:2221-2230).
+    alwaysAssert(a.byteCount >= aCount, "matmul: operand a is too small")
+    alwaysAssert(b.byteCount >= bCount, "matmul: operand b is too small")
+    let aBuf = try await deviceOperand(a, byteCount: aCount)
+    let bBuf = try await deviceOperand(b, byteCount: bCount)
+    let out = try CUDAData(backend: self, byteCount: matrixCount * rows * cols * dtype.byteSize)
+    // Enqueue only; the product runs asynchronously and `out.wait()` is the sync point.
+    try check(
+      hc_batched_matmul(
+        ctx, dt, Int64(matrixCount), aBuf.pointer, transA ? 1 : 0, bBuf.pointer, transB ? 1 : 0,
+        transOut ? 1 : 0, Int64(rows), Int64(inner), Int64(cols), out.pointer))
+    try out.mark()
+    out.inputs = [aBuf, bBuf]
+    return out
+  }
+}
