@@ -60,6 +60,8 @@ SIGNATURES = {
     "hc_batched_matmul_ex": (_int, [_vp, _int, _int, _i64, _vp, _int, _vp, _int, _int, _i64, _i64, _i64, _vp]),
     "hc_batched_matmul_host": (_int, [_vp, _int, _i64, _vp, _int, _vp, _int, _int, _i64, _i64, _i64, _vp]),
     "hc_matmul_colblock": (_int, [_vp, _int, _int, _vp, _int, _vp, _int, _int, _i64, _i64, _i64, _i64, _i64, _vp]),
+    "hc_matmul_f32_static_scratch": (_int, [_vp, _vp, _int, _vp, _int, _int, _i64, _i64, _i64, _vp]),
+    "hc_static_scratch_capacity": (_sz, []),
     "hc_status_string": (ctypes.c_char_p, [_int]),
     "hc_last_error": (ctypes.c_char_p, [_vp]),
     "hc_last_launch_info": (_int, [_vp, ctypes.POINTER(LaunchInfo)]),

@@ -57,3 +57,18 @@ bool tc_supported(const GemmProblem& p);
 size_t tc_scratch_bytes(const GemmProblem& p);
 
 }  // namespace hc
+
+// Context internals shared between translation units (defined in hc_api.cu).
+#include <mutex>
+namespace hc {
+std::mutex& ctx_mutex(hc_ctx* ctx);
+cudaStream_t ctx_stream(hc_ctx* ctx);
+unsigned int* ctx_status_word(hc_ctx* ctx);
+int ctx_sm_count(hc_ctx* ctx);
+int ctx_device(hc_ctx* ctx);
+hc_status ctx_fail(hc_ctx* ctx, hc_status s, const char* msg);
+void ctx_note_launch(hc_ctx* ctx, const LaunchRecord& rec, int64_t flops);
+hc_status ctx_build_problem(hc_ctx* ctx, hc_dtype dtype, int64_t count, const void* a, int trans_a, const void* b,
+                            int trans_b, int trans_out, int64_t rows, int64_t inner, int64_t cols, void* out,
+                            GemmProblem* p);
+}  // namespace hc

@@ -188,6 +188,26 @@ int64_t flop_count(int64_t count, int64_t rows, int64_t inner, int64_t cols) {
 
 }  // namespace
 
+// Accessors for the library's other translation units (hc_ctx is private to this file).
+namespace hc {
+std::mutex& ctx_mutex(hc_ctx* ctx) { return ctx->mu; }
+cudaStream_t ctx_stream(hc_ctx* ctx) { return ctx->stream; }
+unsigned int* ctx_status_word(hc_ctx* ctx) { return ctx->status_word; }
+int ctx_sm_count(hc_ctx* ctx) { return ctx->sm_count; }
+int ctx_device(hc_ctx* ctx) { return ctx->device; }
+hc_status ctx_fail(hc_ctx* ctx, hc_status s, const char* msg) { return fail(ctx, s, msg); }
+void ctx_note_launch(hc_ctx* ctx, const LaunchRecord& rec, int64_t flops) {
+  ctx->last = rec;
+  ctx->last_flops = flops;
+  ctx->launch_count += rec.launches;
+}
+hc_status ctx_build_problem(hc_ctx* ctx, hc_dtype dtype, int64_t count, const void* a, int trans_a, const void* b,
+                            int trans_b, int trans_out, int64_t rows, int64_t inner, int64_t cols, void* out,
+                            GemmProblem* p) {
+  return build_problem(ctx, dtype, count, a, trans_a, b, trans_b, trans_out, rows, inner, cols, 0, cols, out, p);
+}
+}  // namespace hc
+
 extern "C" {
 
 hc_status hc_init(int device, hc_ctx** out) {

@@ -158,6 +158,23 @@ hc_status hc_matmul_colblock(hc_ctx* ctx, hc_kernel kernel, hc_dtype dtype, cons
                              int64_t rows, int64_t inner, int64_t cols, int64_t col_begin,
                              int64_t col_count, void* out);
 
+/* float32 `transOut(op(a) * op(b))` on the tensor cores WITHOUT allocating: no counterpart in
+ * the reference.  It exists for hosts that must not allocate device memory from inside a
+ * library call - a framework whose caching allocator already owns the device, or a loop that
+ * cannot afford the device-wide synchronisation cudaMalloc implies.  The work area of the
+ * 3xTF32 split operands is a fixed array inside the library (hc_static_scratch_capacity()
+ * bytes, held by every GPU that loads the library); a product needs about
+ * 8 * (rows*inner + inner*cols) bytes of it, and a larger one is refused with
+ * HC_ERR_INVALID_ARGUMENT (hc_last_error says how much was needed).  Same result, bit for
+ * bit, as hc_batched_matmul_ex(ctx, HC_KERNEL_TENSOR, HC_F32, 1, ...).
+ * The first call on each device looks up the array's device address; make that call outside
+ * stream capture.  All calls in the process share the one array: calls that can overlap on
+ * the GPU (other streams or contexts on the same device) must be ordered by the caller. */
+hc_status hc_matmul_f32_static_scratch(hc_ctx* ctx, const void* a, int trans_a, const void* b,
+                                       int trans_b, int trans_out, int64_t rows, int64_t inner,
+                                       int64_t cols, void* out);
+size_t hc_static_scratch_capacity(void);
+
 /* ---- diagnostics ------------------------------------------------------------------------- */
 
 const char* hc_status_string(hc_status s);
