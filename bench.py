@@ -394,6 +394,41 @@ def other_configs(be, stream, rank, world):
     return res
 
 
+def run_probe(args):
+    """A few launches of ONE product, for profiler captures:
+    `--probe M,K,N[,count] --dtype f16|f32 --flags tA,tB --steps K`."""
+    import numpy as np
+    import torch
+
+    from honeycrisp_b200 import CUDABackend
+
+    dims = [int(x) for x in args.probe.split(",")]
+    M, K, N = dims[:3]
+    cnt = dims[3] if len(dims) > 3 else 1
+    ta, tb = (bool(int(x)) for x in args.flags.split(","))
+    npdt, tdt = (np.float16, torch.float16) if args.dtype == "f16" else (np.float32, torch.float32)
+    be = CUDABackend(0)
+    stream = torch.cuda.Stream()
+    torch.cuda.set_stream(stream)
+    be.useStream(stream.cuda_stream)
+    g = torch.Generator(device="cuda").manual_seed(1)
+    a = (torch.randn((cnt, K, M) if ta else (cnt, M, K), generator=g, device="cuda") / K ** 0.25).to(tdt)
+    b = (torch.randn((cnt, N, K) if tb else (cnt, K, N), generator=g, device="cuda") / K ** 0.25).to(tdt)
+    out = torch.empty((cnt, M, N), device="cuda", dtype=tdt)
+    od = be.wrap(out.data_ptr(), out.numel() * out.element_size(), out)
+    be.batchedMatmul(cnt, a, ta, b, tb, False, M, K, N, npdt, out=od)
+    e0 = torch.cuda.Event(enable_timing=True); e1 = torch.cuda.Event(enable_timing=True)
+    e0.record(stream)
+    for _ in range(args.steps):
+        be.batchedMatmul(cnt, a, ta, b, tb, False, M, K, N, npdt, out=od)
+    e1.record(stream)
+    torch.cuda.synchronize()
+    be.checkDeviceStatus()
+    ms = e0.elapsed_time(e1) / args.steps
+    print(json.dumps({"probe": [M, K, N, cnt], "dtype": args.dtype, "flags": [ta, tb], "ms": ms,
+                      "tflops": 2.0 * cnt * M * N * K / ms / 1e9, "kernel": be.lastLaunchInfo()}), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -401,8 +436,13 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--all-configs", action="store_true")
+    ap.add_argument("--probe", default=None, help="M,K,N[,count]: run one product a few times (profiler target)")
+    ap.add_argument("--dtype", choices=["f16", "f32"], default="f16")
+    ap.add_argument("--flags", default="0,1", help="transA,transB for --probe")
     args = ap.parse_args()
-    if args.impl == "reference":
+    if args.probe:
+        run_probe(args)
+    elif args.impl == "reference":
         run_reference(args)
     else:
         run_ours(args)

@@ -33,6 +33,7 @@
 // normal teardown (tensor memory is freed).  The host reports HC_ERR_TIMEOUT.
 #include <cuda.h>
 #include <cstdlib>
+#include <cstring>
 #include <mutex>
 
 #include "common.cuh"
@@ -57,6 +58,7 @@ struct TcParams {
   unsigned int* status;
   int vec_ok;         // C base and ldc allow 16-byte stores
   int tile_rows;      // 128 per CTA of the group
+  int tma_store;      // results leave through shared memory and TMA stores (else direct stores)
   int debug;
 };
 
@@ -159,6 +161,27 @@ __device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map
         ::"r"(dst), "l"((unsigned long long)map), "r"(bar), "r"(c0), "r"(c1), "r"(c2)
         : "memory");
   }
+}
+
+// Tiled TMA store of one box from this CTA's shared memory; out-of-range parts are clipped.
+__device__ __forceinline__ void tma_store_3d(const CUtensorMap* map, uint32_t src, int c0, int c1, int c2) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.global.shared::cta.tile.bulk_group [%0, {%2, %3, %4}], [%1];"
+      ::"l"((unsigned long long)map), "r"(src), "r"(c0), "r"(c1), "r"(c2)
+      : "memory");
+}
+__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+// Wait until at most kPending of this thread's bulk groups have not finished reading shared memory.
+template <int kPending>
+__device__ __forceinline__ void bulk_wait_read() {
+  asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(kPending) : "memory");
+}
+__device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+__device__ __forceinline__ void fence_proxy_async_smem() {
+  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
+__device__ __forceinline__ void st_shared_v4(uint32_t addr, uint32_t x, uint32_t y, uint32_t z, uint32_t w) {
+  asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(x), "r"(y), "r"(z), "r"(w) : "memory");
 }
 
 __device__ __forceinline__ void tc_fence_before() {
@@ -314,7 +337,7 @@ template <int kElemBytes, int kBN, int kStages, int kEpiWarps, bool kWindowed, i
 __global__ void __launch_bounds__(64 + 32 * kEpiWarps, 1)
 tc_gemm_kernel(const __grid_constant__ CUtensorMap mapA_hi, const __grid_constant__ CUtensorMap mapA_lo,
                const __grid_constant__ CUtensorMap mapB_hi, const __grid_constant__ CUtensorMap mapB_lo,
-               const TcParams p) {
+               const __grid_constant__ CUtensorMap mapC, const TcParams p) {
   constexpr bool kTf32 = (kElemBytes == 4);
   constexpr bool kOutHalf = (kElemBytes == 2);
   constexpr int BK = 128 / kElemBytes;       // elements in one 128-byte slab row
@@ -392,7 +415,6 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap mapA_hi, const __grid_constan
       const uint32_t full_leader = (kCta == 2) ? map_to_cta(bar_full, 0) : bar_full;
       uint32_t s = 0, ph = 0;
       bool ok = true;
-      if (p.debug & 32) ok = false;  // timing experiment: the issuer runs without a producer
       for (int64_t tile = tile_first; ok && tile < p.total_tiles; tile += tile_step) {
         const TileCoord t = decode_tile(tile, p);
         const int m0 = t.tm * (BM * kCta) + (int)rank * BM;
@@ -434,7 +456,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap mapA_hi, const __grid_constan
           if (++s == kStages) { s = 0; ph ^= 1; }
         }
       }
-      if (kCta == 2 && ok && !(p.debug & 32)) {
+      if (kCta == 2 && ok) {
         // Drain: every slot's release (an asynchronous arrive from the leader's MMA commits)
         // must have landed in this CTA's barriers before the CTA may exit.
         for (int i = 0; i < kStages; i++) {
@@ -475,7 +497,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap mapA_hi, const __grid_constan
             }
             tc_fence_after();
           }
-          if (!(p.debug & 32) && !mbar_wait(bar_full + 8 * s, ph, abortp)) {
+          if (!mbar_wait(bar_full + 8 * s, ph, abortp)) {
             atomicOr(p.status, kDevTimeoutMma);
             abort_flag = 1;
             ok = false;
@@ -489,15 +511,11 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap mapA_hi, const __grid_constan
 #pragma unroll
           for (int k = 0; k < BK / UMMA_K; k++) {
             if (p.debug & 16) break;  // timing experiment: no MMAs
-            // timing experiment (bit 6): consecutive MMAs alternate between the two accumulators
-            const uint32_t dd = (p.debug & 64) ? tmem_base + (uint32_t)((k & 1) * kBN) : d;
-            tc_mma<kTf32, kCta>(dd, adesc + (uint64_t)((k * a_kstep) >> 4), bdesc + (uint64_t)((k * b_kstep) >> 4),
+            tc_mma<kTf32, kCta>(d, adesc + (uint64_t)((k * a_kstep) >> 4), bdesc + (uint64_t)((k * b_kstep) >> 4),
                                 idesc, (in_win | k) ? 1u : 0u);
           }
-          if (!(p.debug & 32)) {
-            tc_commit<kCta>(bar_empty + 8 * s);
-            if (kCta == 2) tc_commit<kCta>(empty_peer + 8 * s);
-          }
+          tc_commit<kCta>(bar_empty + 8 * s);
+          if (kCta == 2) tc_commit<kCta>(empty_peer + 8 * s);
           if (in_win == chunk_kb - 1 || kb == nkb - 1) {
             tc_commit<kCta>(bar_tfull + 8 * slot);
             if (kCta == 2) tc_commit<kCta>(tfull_peer + 8 * slot);
@@ -516,6 +534,9 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap mapA_hi, const __grid_constan
     const uint32_t lane_base = (uint32_t)(quarter * 32) << 16;
     // Buffers are handed back to the leader's MMA issuer.
     const uint32_t tempty_leader = (kCta == 2) ? map_to_cta(bar_tempty, 0) : bar_tempty;
+    // Staging for TMA stores: two 4 KB buffers per epilogue warp behind the operand ring.
+    const uint32_t stg_base = smem_base + kStages * STAGE_BYTES + (uint32_t)ew * 8192u;
+    const bool store_leader = elect_one();
     uint32_t win = 0;
     bool ok = true;
     for (int64_t tile = tile_first; ok && tile < p.total_tiles; tile += tile_step) {
@@ -536,15 +557,71 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap mapA_hi, const __grid_constan
         }
         tc_fence_after();
         const uint32_t tbase = tmem_base + lane_base + slot * kBN + col0;
+        if (p.tma_store) {
+          // Each warp rounds its 32 rows x 128 bytes into a swizzled staging buffer and one lane
+          // sends it with a TMA store (full 128-byte lines); two buffers per warp alternate.
+          constexpr int COLS_PER_BUF = kOutHalf ? 64 : 32;   // columns in one 128-byte staging row
+          constexpr int LOADS = kOutHalf ? 4 : 2;            // tcgen05.ld.x32 per pass (two buffers)
+          static_assert(COLS_PER_THREAD % (2 * COLS_PER_BUF) == 0, "a pass fills both staging buffers");
+          const int m_warp = t.tm * (BM * kCta) + (int)rank * BM + quarter * 32;
+          const uint32_t row_addr = stg_base + (uint32_t)lane * 128u;
+          const uint32_t sw = (uint32_t)(lane & 7);
 #pragma unroll 1
-        for (int c = 0; c < COLS_PER_THREAD; c += 32) {
-          uint32_t r[32];
-          tmem_ld_x32(tbase + c, r);
-          tmem_ld_wait();
-          float v[32];
+          for (int c = 0; c < COLS_PER_THREAD; c += 2 * COLS_PER_BUF) {
+            uint32_t r[LOADS][32];
 #pragma unroll
-          for (int j = 0; j < 32; j++) v[j] = __uint_as_float(r[j]);
-          if (gm < p.M && n0 + c < p.N) store_row32<kOutHalf>(cmat, row_off, n0 + c, p.N, v, p.vec_ok != 0);
+            for (int l = 0; l < LOADS; l++) tmem_ld_x32(tbase + c + 32 * l, r[l]);
+            tmem_ld_wait();
+            // The previous pass's stores must have finished reading the buffers; they had the
+            // whole tensor-memory load above to do so.
+            if (store_leader) bulk_wait_read<0>();
+            __syncwarp();
+#pragma unroll
+            for (int l = 0; l < LOADS; l++) {
+              if (kOutHalf) {
+                // load l covers columns 32l..32l+31 = 16-byte chunks 4(l&1)..4(l&1)+3 of buffer l>>1
+                const uint32_t buf = row_addr + (uint32_t)(l >> 1) * 4096u;
+#pragma unroll
+                for (int q = 0; q < 4; q++) {
+                  uint32_t h[4];
+#pragma unroll
+                  for (int e = 0; e < 4; e++) {
+                    __half2 v2 = __floats2half2_rn(__uint_as_float(r[l][q * 8 + 2 * e]),
+                                                   __uint_as_float(r[l][q * 8 + 2 * e + 1]));
+                    h[e] = *(uint32_t*)&v2;
+                  }
+                  st_shared_v4(buf + (((uint32_t)(q + 4 * (l & 1)) ^ sw) << 4), h[0], h[1], h[2], h[3]);
+                }
+              } else {
+                const uint32_t buf = row_addr + (uint32_t)l * 4096u;
+#pragma unroll
+                for (int q = 0; q < 8; q++)
+                  st_shared_v4(buf + (((uint32_t)q ^ sw) << 4), r[l][q * 4], r[l][q * 4 + 1], r[l][q * 4 + 2],
+                               r[l][q * 4 + 3]);
+              }
+            }
+            fence_proxy_async_smem();
+            __syncwarp();
+            if (store_leader && m_warp < p.M) {
+#pragma unroll
+              for (int b2 = 0; b2 < 2; b2++) {
+                const int64_t col = n0 + c + b2 * COLS_PER_BUF;
+                if (col < p.N) tma_store_3d(&mapC, stg_base + (uint32_t)b2 * 4096u, (int)col, m_warp, (int)t.mat);
+              }
+              bulk_commit();
+            }
+          }
+        } else {
+#pragma unroll 1
+          for (int c = 0; c < COLS_PER_THREAD; c += 32) {
+            uint32_t r[32];
+            tmem_ld_x32(tbase + c, r);
+            tmem_ld_wait();
+            float v[32];
+#pragma unroll
+            for (int j = 0; j < 32; j++) v[j] = __uint_as_float(r[j]);
+            if (gm < p.M && n0 + c < p.N) store_row32<kOutHalf>(cmat, row_off, n0 + c, p.N, v, p.vec_ok != 0);
+          }
         }
         tc_fence_before();
         mbar_arrive_cluster(tempty_leader + 8 * slot);
@@ -592,6 +669,11 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap mapA_hi, const __grid_constan
     }
   }
 
+  if (warp >= 2 && !kWindowed) {
+    // Shared memory must outlive the TMA stores that read it.
+    __syncwarp();
+    if (elect_one()) bulk_wait_all();
+  }
   // ---------------------------------------------------------------- teardown
   __syncwarp();
   tc_fence_before();
@@ -687,6 +769,23 @@ bool make_operand_map(CUtensorMap* map, const void* base, int elem_bytes, bool m
   return r == CUDA_SUCCESS;
 }
 
+// The result as a rank-3 tensor {column, row, matrix}; one store moves 32 rows x 128 bytes.
+bool make_output_map(CUtensorMap* map, void* base, int elem_bytes, int64_t n, int64_t m, int64_t ldc,
+                     int64_t stride_mat, int64_t batch) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return false;
+  cuuint64_t dims[3] = {(cuuint64_t)n, (cuuint64_t)m, (cuuint64_t)batch};
+  cuuint64_t mat_bytes = (cuuint64_t)stride_mat * elem_bytes;
+  if (batch == 1) mat_bytes = (cuuint64_t)ldc * elem_bytes * dims[1];
+  cuuint64_t strides[2] = {(cuuint64_t)ldc * elem_bytes, mat_bytes};
+  cuuint32_t box[3] = {(cuuint32_t)(128 / elem_bytes), 32, 1};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = fn(map, elem_bytes == 2 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, base,
+                  dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                  CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS;
+}
+
 bool operand_ok(const void* base, int elem_bytes, int64_t ld, int64_t stride_mat, int64_t batch, int64_t d0,
                 int64_t d1) {
   if (((uintptr_t)base & 15) != 0) return false;
@@ -701,8 +800,9 @@ int env_int(const char* name, int fallback) {
   const char* e = getenv(name);
   return e ? atoi(e) : fallback;
 }
-// Development switches (not part of the interface): bit 1 = no accumulation windows,
-// bit 2 = never pair CTAs.
+// Diagnostic switches (HC_TC_DEBUG, not part of the interface): 2 = no accumulation windows,
+// 4 = never pair CTAs, 8 = skip the copies, 16 = skip the MMAs (8 and 16 give wrong results and
+// exist to time the load path and the MMA stream separately), 128 = direct stores, no TMA store.
 int debug_flags() {
   static int v = env_int("HC_TC_DEBUG", 0);
   return v;
@@ -715,7 +815,9 @@ int window_slabs() {
 
 template <int kElemBytes, int kBN, int kStages, int kEpiWarps, bool kWindowed, int kCta>
 struct TcConfig {
-  static constexpr size_t smem = (size_t)kStages * (BM * 128 + (kBN / kCta) * 128) + 1024;
+  // operand ring + (non-windowed kernels) two 4 KB store-staging buffers per epilogue warp + alignment slack
+  static constexpr size_t smem =
+      (size_t)kStages * (BM * 128 + (kBN / kCta) * 128) + (kWindowed ? 0 : (size_t)kEpiWarps * 8192) + 1024;
   static constexpr int block = 64 + 32 * kEpiWarps;
   static auto kernel() { return tc_gemm_kernel<kElemBytes, kBN, kStages, kEpiWarps, kWindowed, kCta>; }
 
@@ -760,7 +862,7 @@ struct TcConfig {
     return n;
   }
 
-  static cudaError_t launch(const CUtensorMap maps[4], const TcParams& p, int sm_count, cudaStream_t stream,
+  static cudaError_t launch(const CUtensorMap maps[5], const TcParams& p, int sm_count, cudaStream_t stream,
                             LaunchRecord* rec) {
     cudaError_t e = configure();
     if (e != cudaSuccess) return e;
@@ -777,7 +879,7 @@ struct TcConfig {
     attr.val.clusterDim.x = kCta; attr.val.clusterDim.y = 1; attr.val.clusterDim.z = 1;
     cfg.attrs = &attr;
     cfg.numAttrs = 1;
-    e = cudaLaunchKernelEx(&cfg, kernel(), maps[0], maps[1], maps[2], maps[3], p);
+    e = cudaLaunchKernelEx(&cfg, kernel(), maps[0], maps[1], maps[2], maps[3], maps[4], p);
     if (rec) {
       rec->tile_m = BM * kCta; rec->tile_n = kBN; rec->tile_k = 128 / kElemBytes; rec->stages = kStages;
       rec->grid = grid; rec->block = block; rec->launches++;
@@ -857,7 +959,8 @@ cudaError_t launch_tc(const GemmProblem& p, cudaStream_t stream, unsigned int* s
   const int bn = (p.N > 128) ? 256 : 128;
   const int cta = (p.M > BM && bn == 256 && !(dbg & 4)) ? 2 : 1;
   const int b_box = bn / cta;
-  CUtensorMap maps[4];
+  CUtensorMap maps[5];
+  memset(maps, 0, sizeof maps);
   if (!make_operand_map(&maps[0], a_hi, eb, p.a_mn_major, p.M, p.K, lda, sa, p.batch, BM) ||
       !make_operand_map(&maps[1], a_lo, eb, p.a_mn_major, p.M, p.K, lda, sa, p.batch, BM) ||
       !make_operand_map(&maps[2], b_hi, eb, p.b_mn_major, p.N, p.K, ldb, sb, p.batch, b_box) ||
@@ -884,9 +987,19 @@ cudaError_t launch_tc(const GemmProblem& p, cudaStream_t stream, unsigned int* s
   tp.status = status_word;
   tp.vec_ok = (((uintptr_t)p.C & 15) == 0 && (p.ldc * eb) % 16 == 0 && (p.strideC * eb) % 16 == 0) ? 1 : 0;
   tp.debug = dbg;
+  // Results leave through TMA stores when the result can be described to TMA (16-byte aligned
+  // base and pitches); the windowed float32 epilogue stores from registers.
+  tp.tma_store = 0;
+  if (!windowed && tp.vec_ok && !(dbg & 128) && p.M < (1ll << 31) && p.N < (1ll << 31) &&
+      p.ldc * eb < (1ll << 40) && make_output_map(&maps[4], p.C, eb, p.N, p.M, p.ldc, p.strideC, p.batch))
+    tp.tma_store = 1;
   if (rec) rec->tiles = tp.total_tiles;
 
   if (!f32) {
+    // Short contractions are bound by draining results, not by the MMA: more epilogue warps,
+    // fewer operand stages.
+    const bool short_k = tp.num_k_blocks <= env_int("HC_TC_SHORT_K", 8);
+    if (cta == 2 && short_k) return TcConfig<2, 256, 4, 8, false, 2>::launch(maps, tp, sm_count, stream, rec);
     if (cta == 2) return TcConfig<2, 256, 6, 4, false, 2>::launch(maps, tp, sm_count, stream, rec);
     if (bn == 256) return TcConfig<2, 256, 4, 4, false, 1>::launch(maps, tp, sm_count, stream, rec);
     return TcConfig<2, 128, 6, 4, false, 1>::launch(maps, tp, sm_count, stream, rec);
