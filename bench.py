@@ -291,6 +291,10 @@ def run_ours(args):
     launch_ms = statistics.mean(x.elapsed_time(y) for x, y in evs)
     info = be.lastLaunchInfo()
 
+    multi_extra = None
+    if args.all_configs and use_dist:
+        multi_extra = sharded_configs(be, stream, rank, world)   # collective: every rank takes part
+
     if rank != 0:
         if use_dist:
             dist.destroy_process_group()
@@ -337,7 +341,7 @@ def run_ours(args):
         "cpu_baseline": cpu_baseline,
     }
     if args.all_configs:
-        line["extra"] = other_configs(be, stream, rank, world)
+        line["extra"] = other_configs(be, stream, rank, world) if world == 1 else multi_extra
     print(json.dumps(line), flush=True)
     if use_dist:
         dist.destroy_process_group()
@@ -428,6 +432,65 @@ def run_probe(args):
     ms = e0.elapsed_time(e1) / args.steps
     print(json.dumps({"probe": [M, K, N, cnt], "dtype": args.dtype, "flags": [ta, tb], "ms": ms,
                       "tflops": 2.0 * cnt * M * N * K / ms / 1e9, "kernel": be.lastLaunchInfo()}), flush=True)
+
+
+def sharded_configs(be, stream, rank, world):
+    """Configurations 3 and 5 split over the ranks (strong scaling): batch-sharded Q.K^T with no
+    collective; float32 16384^3 split over columns, exchanged by NCCL all-gather and by the fused
+    epilogue push.  Device-timed, max over ranks."""
+    import numpy as np
+    import torch
+    import torch.distributed as dist
+
+    from honeycrisp_b200.sharding import FusedColumnSplit, batchedMatmulSharded, matmulColumnSplit, shardBatch
+
+    def max_ms(ms):
+        t = torch.tensor([ms], device="cuda", dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    def timed(fn, iters):
+        fn()
+        torch.cuda.synchronize(); dist.barrier()
+        e0 = torch.cuda.Event(enable_timing=True); e1 = torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        for _ in range(iters):
+            fn()
+        e1.record(stream)
+        torch.cuda.synchronize(); dist.barrier()
+        return max_ms(e0.elapsed_time(e1) / iters)
+
+    res = {}
+    g = torch.Generator(device="cuda").manual_seed(2)
+    begin, count = shardBatch(64, rank, world)
+    q = torch.randn((64, 2048, 128), generator=g, device="cuda").half()
+    k = torch.randn((64, 2048, 128), generator=g, device="cuda").half()
+    o = torch.empty(count * 2048 * 2048, device="cuda", dtype=torch.float16)
+    ms = timed(lambda: batchedMatmulSharded(be, rank, world, 64, q, False, k, True, False, 2048, 128, 2048,
+                                            np.float16, out=o), 20)
+    res["c3_batch_sharded"] = {"ms": ms, "box_tflops": 2 * 64 * 2048 * 2048 * 128 / ms / 1e9, "collective": "none"}
+    del q, k, o
+    n = 16384
+    g = torch.Generator(device="cuda").manual_seed(4)
+    a = torch.rand((n, n), generator=g, device="cuda") * 2 - 1
+    b = torch.rand((n, n), generator=g, device="cuda") * 2 - 1
+    holder = {}
+
+    def nccl_path():
+        holder["c"] = matmulColumnSplit(be, rank, world, a, False, b, False, n, n, n, np.float32, gather=True)
+
+    ms = timed(nccl_path, 2)
+    res["c5_colsplit_nccl_allgather"] = {"ms": ms, "box_tflops_effective": 2 * n ** 3 / ms / 1e9}
+    fused = FusedColumnSplit(be, rank, world, n, n, np.float32)
+    ms = timed(lambda: fused.matmul(a, False, b, False, n, wait=False), 2)
+    fused.finish()
+    same = bool(torch.equal(fused.out.asTorch((n, n), torch.float32), holder["c"]))
+    res["c5_colsplit_fused_push"] = {"ms": ms, "box_tflops_effective": 2 * n ** 3 / ms / 1e9,
+                                     "equals_nccl_result": same}
+    holder.clear()
+    fused.close()
+    be.checkDeviceStatus()
+    return res
 
 
 def main():

@@ -60,6 +60,13 @@ SIGNATURES = {
     "hc_batched_matmul_ex": (_int, [_vp, _int, _int, _i64, _vp, _int, _vp, _int, _int, _i64, _i64, _i64, _vp]),
     "hc_batched_matmul_host": (_int, [_vp, _int, _i64, _vp, _int, _vp, _int, _int, _i64, _i64, _i64, _vp]),
     "hc_matmul_colblock": (_int, [_vp, _int, _int, _vp, _int, _vp, _int, _int, _i64, _i64, _i64, _i64, _i64, _vp]),
+    "hc_matmul_colblock_push": (_int, [_vp, _int, _vp, _int, _vp, _int, _int, _i64, _i64, _i64, _i64, _i64, _vp,
+                                      ctypes.POINTER(_vp), _int]),
+    "hc_shared_alloc": (_int, [_vp, _sz, ctypes.POINTER(_vp)]),
+    "hc_shared_free": (_int, [_vp, _vp]),
+    "hc_ipc_export": (_int, [_vp, _vp, _vp]),
+    "hc_ipc_open": (_int, [_vp, _vp, ctypes.POINTER(_vp)]),
+    "hc_ipc_close": (_int, [_vp, _vp]),
     "hc_matmul_f32_static_scratch": (_int, [_vp, _vp, _int, _vp, _int, _int, _i64, _i64, _i64, _vp]),
     "hc_static_scratch_capacity": (_sz, []),
     "hc_status_string": (ctypes.c_char_p, [_int]),

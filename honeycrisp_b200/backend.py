@@ -110,12 +110,34 @@ class CUDAData:
             self.backend._check(L.load().hc_event_wait(self._event))
         return out.view(dtype)
 
+    def asTorch(self, shape, torch_dtype):
+        """The buffer as a torch tensor that aliases it (no copy); the tensor keeps this handle alive."""
+        import torch
+        typestr = {torch.float16: "<f2", torch.float32: "<f4"}[torch_dtype]
+
+        class _View:
+            pass
+
+        v = _View()
+        v.__cuda_array_interface__ = {"shape": tuple(int(x) for x in shape), "typestr": typestr,
+                                      "data": (self.ptr, False), "version": 3}
+        v._keep = self
+        t = torch.as_tensor(v, device=torch.device("cuda", self.backend.device))
+        t._hc_owner = self
+        return t
+
     def free(self) -> None:
         if self._event:
             L.load().hc_event_destroy(self._event)
             self._event = None
-        if self._owns and self.ptr and self.backend._ctx:
-            L.load().hc_free(self.backend._ctx, self.ptr)
+        if self.ptr and self.backend._ctx:
+            kind = getattr(self, "_kind", None)
+            if kind == "shared":
+                L.load().hc_shared_free(self.backend._ctx, self.ptr)
+            elif kind == "ipc":
+                L.load().hc_ipc_close(self.backend._ctx, self.ptr)
+            elif self._owns:
+                L.load().hc_free(self.backend._ctx, self.ptr)
         self.ptr = 0
         self._owner = None
 
@@ -206,6 +228,48 @@ class CUDABackend:
             self._check(L.load().hc_h2d(self._ctx, data.ptr, arr.ctypes.data, arr.nbytes))
             self.sync()  # the host array may be a temporary
         return data
+
+    def sharedAllocate(self, byteCount: int) -> CUDAData:
+        """Memory that the other processes of the box (one per GPU) can map with ipcOpen."""
+        ptr = ctypes.c_void_p()
+        self._check(L.load().hc_shared_alloc(self._ctx, int(byteCount), ctypes.byref(ptr)))
+        d = CUDAData(self, ptr.value, int(byteCount), owns=False)
+        d._kind = "shared"
+        return d
+
+    def ipcExport(self, data: CUDAData) -> bytes:
+        """Opaque 64-byte handle of a sharedAllocate buffer, to send to the other processes."""
+        buf = ctypes.create_string_buffer(64)
+        self._check(L.load().hc_ipc_export(self._ctx, data.ptr, buf))
+        return bytes(buf.raw)
+
+    def ipcOpen(self, handle: bytes, byteCount: int) -> CUDAData:
+        """Map another process's sharedAllocate buffer into this one (peer access over NVLink)."""
+        ptr = ctypes.c_void_p()
+        self._check(L.load().hc_ipc_open(self._ctx, ctypes.c_char_p(handle), ctypes.byref(ptr)))
+        d = CUDAData(self, ptr.value, int(byteCount), owns=False)
+        d._kind = "ipc"
+        return d
+
+    def matmulColumnBlockPush(self, a, transA: bool, b, transB: bool, transOut: bool, rows: int, inner: int,
+                              cols: int, colBegin: int, colCount: int, dtype, out: CUDAData, peerOuts) -> CUDAData:
+        """matmulColumnBlock whose epilogue also stores every tile into the peers' results."""
+        dt = _as_dtype(dtype)
+        if dt not in _HC_DTYPE:
+            raise NotImplementedByBackend(f"matmul for dtype {dt.value}")
+        a_d = self._device_operand(a, dt)
+        b_d = self._device_operand(b, dt)
+        need = rows * cols * dt.byteSize
+        if out.byteCount < need or any(p.byteCount < need for p in peerOuts):
+            raise ValueError("matmulColumnBlockPush: every result must be the full rows x cols buffer")
+        arr = (ctypes.c_void_p * max(1, len(peerOuts)))(*[p.ptr for p in peerOuts])
+        st = L.load().hc_matmul_colblock_push(self._ctx, _HC_DTYPE[dt], a_d.ptr, int(bool(transA)), b_d.ptr,
+                                              int(bool(transB)), int(bool(transOut)), int(rows), int(inner),
+                                              int(cols), int(colBegin), int(colCount), out.ptr, arr, len(peerOuts))
+        self._check(st)
+        out._mark()
+        out._inputs = (a_d, b_d)
+        return out
 
     def wrap(self, device_ptr: int, byteCount: int, owner=None) -> CUDAData:
         """Borrow device memory allocated elsewhere (e.g. `t.data_ptr()` of a CUDA torch tensor)."""

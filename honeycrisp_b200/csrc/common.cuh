@@ -51,8 +51,11 @@ cudaError_t launch_simt(const GemmProblem& p, bool exact, cudaStream_t stream, L
 // (misaligned base or leading dimension); the caller then uses the CUDA-core kernel.
 // `status_word` is the device status word of the context; `scratch`/`scratch_bytes` is a
 // caller-provided work area for the float32 split operands (see tc_scratch_bytes).
+// `extra_out`: up to 7 more result buffers of the same shape and pitch as p.C (other devices'
+// copies, mapped into this process); every result tile is stored to each of them as well.
 cudaError_t launch_tc(const GemmProblem& p, cudaStream_t stream, unsigned int* status_word,
-                      void* scratch, size_t scratch_bytes, int sm_count, LaunchRecord* rec);
+                      void* scratch, size_t scratch_bytes, int sm_count, LaunchRecord* rec,
+                      void* const* extra_out = nullptr, int n_extra = 0);
 bool tc_supported(const GemmProblem& p);
 size_t tc_scratch_bytes(const GemmProblem& p);
 

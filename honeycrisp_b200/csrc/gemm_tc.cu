@@ -59,6 +59,7 @@ struct TcParams {
   int vec_ok;         // C base and ldc allow 16-byte stores
   int tile_rows;      // 128 per CTA of the group
   int tma_store;      // results leave through shared memory and TMA stores (else direct stores)
+  int n_out;          // destinations of every result tile: this device's result, then peers' copies
   int debug;
 };
 
@@ -313,6 +314,12 @@ __device__ __forceinline__ void store_row32(void* cbase, int64_t row_off, int64_
   }
 }
 
+// One tensor map per destination of the result: [0] is this device's buffer, the rest are the
+// same-shaped buffers of other devices of the box, mapped into this process (plain peer
+// stores over NVLink; never a load).
+constexpr int kMaxOut = 8;
+struct OutMaps { CUtensorMap m[kMaxOut]; };
+
 struct TileCoord { int64_t mat; int tm, tn; };
 __device__ __forceinline__ TileCoord decode_tile(int64_t tile, const TcParams& p) {
   const int64_t per_mat = (int64_t)p.tiles_m * p.tiles_n;
@@ -337,7 +344,7 @@ template <int kElemBytes, int kBN, int kStages, int kEpiWarps, bool kWindowed, i
 __global__ void __launch_bounds__(64 + 32 * kEpiWarps, 1)
 tc_gemm_kernel(const __grid_constant__ CUtensorMap mapA_hi, const __grid_constant__ CUtensorMap mapA_lo,
                const __grid_constant__ CUtensorMap mapB_hi, const __grid_constant__ CUtensorMap mapB_lo,
-               const __grid_constant__ CUtensorMap mapC, const TcParams p) {
+               const __grid_constant__ OutMaps mapC, const TcParams p) {
   constexpr bool kTf32 = (kElemBytes == 4);
   constexpr bool kOutHalf = (kElemBytes == 2);
   constexpr int BK = 128 / kElemBytes;       // elements in one 128-byte slab row
@@ -606,7 +613,10 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap mapA_hi, const __grid_constan
 #pragma unroll
               for (int b2 = 0; b2 < 2; b2++) {
                 const int64_t col = n0 + c + b2 * COLS_PER_BUF;
-                if (col < p.N) tma_store_3d(&mapC, stg_base + (uint32_t)b2 * 4096u, (int)col, m_warp, (int)t.mat);
+                if (col < p.N) {
+                  for (int d = 0; d < p.n_out; d++)
+                    tma_store_3d(&mapC.m[d], stg_base + (uint32_t)b2 * 4096u, (int)col, m_warp, (int)t.mat);
+                }
               }
               bulk_commit();
             }
@@ -656,7 +666,39 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap mapA_hi, const __grid_constan
           mbar_arrive_cluster(tempty_leader + 8 * slot);
           win++;
         }
-        if (ok && gm < p.M) {
+        if (ok && p.tma_store) {
+          // Same staging as above, fed from the register accumulators: 2 x 32 columns per pass.
+          const int m_warp = t.tm * (BM * kCta) + (int)rank * BM + quarter * 32;
+          const uint32_t row_addr = stg_base + (uint32_t)lane * 128u;
+          const uint32_t sw = (uint32_t)(lane & 7);
+#pragma unroll
+          for (int c = 0; c < COLS_PER_THREAD; c += 64) {
+            if (store_leader) bulk_wait_read<0>();
+            __syncwarp();
+#pragma unroll
+            for (int l = 0; l < 2; l++) {
+              const uint32_t buf = row_addr + (uint32_t)l * 4096u;
+#pragma unroll
+              for (int q = 0; q < 8; q++)
+                st_shared_v4(buf + (((uint32_t)q ^ sw) << 4), __float_as_uint(acc[c + 32 * l + q * 4]),
+                             __float_as_uint(acc[c + 32 * l + q * 4 + 1]), __float_as_uint(acc[c + 32 * l + q * 4 + 2]),
+                             __float_as_uint(acc[c + 32 * l + q * 4 + 3]));
+            }
+            fence_proxy_async_smem();
+            __syncwarp();
+            if (store_leader && m_warp < p.M) {
+#pragma unroll
+              for (int b2 = 0; b2 < 2; b2++) {
+                const int64_t col = n0 + c + b2 * 32;
+                if (col < p.N) {
+                  for (int d = 0; d < p.n_out; d++)
+                    tma_store_3d(&mapC.m[d], stg_base + (uint32_t)b2 * 4096u, (int)col, m_warp, (int)t.mat);
+                }
+              }
+              bulk_commit();
+            }
+          }
+        } else if (ok && gm < p.M) {
 #pragma unroll
           for (int c = 0; c < COLS_PER_THREAD; c += 32) {
             float v[32];
@@ -669,8 +711,9 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap mapA_hi, const __grid_constan
     }
   }
 
-  if (warp >= 2 && !kWindowed) {
-    // Shared memory must outlive the TMA stores that read it.
+  if (warp >= 2) {
+    // Shared memory must outlive the TMA stores that read it, and stores into other devices'
+    // memory must be complete when the kernel ends.
     __syncwarp();
     if (elect_one()) bulk_wait_all();
   }
@@ -815,9 +858,9 @@ int window_slabs() {
 
 template <int kElemBytes, int kBN, int kStages, int kEpiWarps, bool kWindowed, int kCta>
 struct TcConfig {
-  // operand ring + (non-windowed kernels) two 4 KB store-staging buffers per epilogue warp + alignment slack
-  static constexpr size_t smem =
-      (size_t)kStages * (BM * 128 + (kBN / kCta) * 128) + (kWindowed ? 0 : (size_t)kEpiWarps * 8192) + 1024;
+  // operand ring + two 4 KB store-staging buffers per epilogue warp + alignment slack
+  static constexpr size_t smem = (size_t)kStages * (BM * 128 + (kBN / kCta) * 128) + (size_t)kEpiWarps * 8192 + 1024;
+  static_assert(smem <= 232448, "more shared memory than one CTA can have on sm_100");
   static constexpr int block = 64 + 32 * kEpiWarps;
   static auto kernel() { return tc_gemm_kernel<kElemBytes, kBN, kStages, kEpiWarps, kWindowed, kCta>; }
 
@@ -862,8 +905,8 @@ struct TcConfig {
     return n;
   }
 
-  static cudaError_t launch(const CUtensorMap maps[5], const TcParams& p, int sm_count, cudaStream_t stream,
-                            LaunchRecord* rec) {
+  static cudaError_t launch(const CUtensorMap maps[4], const OutMaps& outs, const TcParams& p, int sm_count,
+                            cudaStream_t stream, LaunchRecord* rec) {
     cudaError_t e = configure();
     if (e != cudaSuccess) return e;
     int64_t groups = (kCta == 2) ? max_pairs(sm_count) : sm_count;
@@ -879,7 +922,7 @@ struct TcConfig {
     attr.val.clusterDim.x = kCta; attr.val.clusterDim.y = 1; attr.val.clusterDim.z = 1;
     cfg.attrs = &attr;
     cfg.numAttrs = 1;
-    e = cudaLaunchKernelEx(&cfg, kernel(), maps[0], maps[1], maps[2], maps[3], maps[4], p);
+    e = cudaLaunchKernelEx(&cfg, kernel(), maps[0], maps[1], maps[2], maps[3], outs, p);
     if (rec) {
       rec->tile_m = BM * kCta; rec->tile_n = kBN; rec->tile_k = 128 / kElemBytes; rec->stages = kStages;
       rec->grid = grid; rec->block = block; rec->launches++;
@@ -925,8 +968,9 @@ size_t tc_scratch_bytes(const GemmProblem& p) {
 }
 
 cudaError_t launch_tc(const GemmProblem& p, cudaStream_t stream, unsigned int* status_word, void* scratch,
-                      size_t scratch_bytes, int sm_count, LaunchRecord* rec) {
+                      size_t scratch_bytes, int sm_count, LaunchRecord* rec, void* const* extra_out, int n_extra) {
   if (!tc_supported(p)) return cudaErrorNotSupported;
+  if (n_extra < 0 || n_extra > kMaxOut - 1 || (n_extra > 0 && !extra_out)) return cudaErrorInvalidValue;
   const bool f32 = p.dtype == HC_F32;
   const int eb = f32 ? 4 : 2;
   const int BK = 128 / eb;
@@ -959,8 +1003,10 @@ cudaError_t launch_tc(const GemmProblem& p, cudaStream_t stream, unsigned int* s
   const int bn = (p.N > 128) ? 256 : 128;
   const int cta = (p.M > BM && bn == 256 && !(dbg & 4)) ? 2 : 1;
   const int b_box = bn / cta;
-  CUtensorMap maps[5];
+  CUtensorMap maps[4];
+  OutMaps outs;
   memset(maps, 0, sizeof maps);
+  memset(&outs, 0, sizeof outs);
   if (!make_operand_map(&maps[0], a_hi, eb, p.a_mn_major, p.M, p.K, lda, sa, p.batch, BM) ||
       !make_operand_map(&maps[1], a_lo, eb, p.a_mn_major, p.M, p.K, lda, sa, p.batch, BM) ||
       !make_operand_map(&maps[2], b_hi, eb, p.b_mn_major, p.N, p.K, ldb, sb, p.batch, b_box) ||
@@ -990,28 +1036,39 @@ cudaError_t launch_tc(const GemmProblem& p, cudaStream_t stream, unsigned int* s
   // Results leave through TMA stores when the result can be described to TMA (16-byte aligned
   // base and pitches); the windowed float32 epilogue stores from registers.
   tp.tma_store = 0;
-  if (!windowed && tp.vec_ok && !(dbg & 128) && p.M < (1ll << 31) && p.N < (1ll << 31) &&
-      p.ldc * eb < (1ll << 40) && make_output_map(&maps[4], p.C, eb, p.N, p.M, p.ldc, p.strideC, p.batch))
+  tp.n_out = 1;
+  if (tp.vec_ok && !(dbg & 128) && p.M < (1ll << 31) && p.N < (1ll << 31) && p.ldc * eb < (1ll << 40) &&
+      make_output_map(&outs.m[0], p.C, eb, p.N, p.M, p.ldc, p.strideC, p.batch))
     tp.tma_store = 1;
+  if (n_extra > 0) {
+    // Extra destinations only exist on the TMA-store path.
+    if (!tp.tma_store) return cudaErrorNotSupported;
+    for (int i = 0; i < n_extra; i++) {
+      if (((uintptr_t)extra_out[i] & 15) != 0 ||
+          !make_output_map(&outs.m[1 + i], extra_out[i], eb, p.N, p.M, p.ldc, p.strideC, p.batch))
+        return cudaErrorNotSupported;
+    }
+    tp.n_out = 1 + n_extra;
+  }
   if (rec) rec->tiles = tp.total_tiles;
 
   if (!f32) {
     // Short contractions are bound by draining results, not by the MMA: more epilogue warps,
     // fewer operand stages.
     const bool short_k = tp.num_k_blocks <= env_int("HC_TC_SHORT_K", 8);
-    if (cta == 2 && short_k) return TcConfig<2, 256, 4, 8, false, 2>::launch(maps, tp, sm_count, stream, rec);
-    if (cta == 2) return TcConfig<2, 256, 6, 4, false, 2>::launch(maps, tp, sm_count, stream, rec);
-    if (bn == 256) return TcConfig<2, 256, 4, 4, false, 1>::launch(maps, tp, sm_count, stream, rec);
-    return TcConfig<2, 128, 6, 4, false, 1>::launch(maps, tp, sm_count, stream, rec);
+    if (cta == 2 && short_k) return TcConfig<2, 256, 4, 8, false, 2>::launch(maps, outs, tp, sm_count, stream, rec);
+    if (cta == 2) return TcConfig<2, 256, 6, 4, false, 2>::launch(maps, outs, tp, sm_count, stream, rec);
+    if (bn == 256) return TcConfig<2, 256, 4, 4, false, 1>::launch(maps, outs, tp, sm_count, stream, rec);
+    return TcConfig<2, 128, 6, 4, false, 1>::launch(maps, outs, tp, sm_count, stream, rec);
   }
   if (windowed) {
-    if (cta == 2) return TcConfig<4, 256, 6, 8, true, 2>::launch(maps, tp, sm_count, stream, rec);
-    if (bn == 256) return TcConfig<4, 256, 4, 8, true, 1>::launch(maps, tp, sm_count, stream, rec);
-    return TcConfig<4, 128, 6, 4, true, 1>::launch(maps, tp, sm_count, stream, rec);
+    if (cta == 2) return TcConfig<4, 256, 5, 8, true, 2>::launch(maps, outs, tp, sm_count, stream, rec);
+    if (bn == 256) return TcConfig<4, 256, 3, 8, true, 1>::launch(maps, outs, tp, sm_count, stream, rec);
+    return TcConfig<4, 128, 6, 4, true, 1>::launch(maps, outs, tp, sm_count, stream, rec);
   }
-  if (cta == 2) return TcConfig<4, 256, 6, 4, false, 2>::launch(maps, tp, sm_count, stream, rec);
-  if (bn == 256) return TcConfig<4, 256, 4, 4, false, 1>::launch(maps, tp, sm_count, stream, rec);
-  return TcConfig<4, 128, 6, 4, false, 1>::launch(maps, tp, sm_count, stream, rec);
+  if (cta == 2) return TcConfig<4, 256, 6, 4, false, 2>::launch(maps, outs, tp, sm_count, stream, rec);
+  if (bn == 256) return TcConfig<4, 256, 4, 4, false, 1>::launch(maps, outs, tp, sm_count, stream, rec);
+  return TcConfig<4, 128, 6, 4, false, 1>::launch(maps, outs, tp, sm_count, stream, rec);
 }
 
 }  // namespace hc

@@ -415,6 +415,103 @@ hc_status hc_matmul_colblock(hc_ctx* ctx, hc_kernel kernel, hc_dtype dtype, cons
   return run_problem(ctx, kernel, p, flop_count(1, rows, inner, col_count));
 }
 
+hc_status hc_matmul_colblock_push(hc_ctx* ctx, hc_dtype dtype, const void* a, int trans_a, const void* b, int trans_b,
+                                  int trans_out, int64_t rows, int64_t inner, int64_t cols, int64_t col_begin,
+                                  int64_t col_count, void* out, void* const* peer_outs, int n_peers) {
+  if (!ctx) return HC_ERR_INVALID_ARGUMENT;
+  std::lock_guard<std::mutex> lock(ctx->mu);
+  DeviceGuard g(ctx->device);
+  if (n_peers < 0 || n_peers > 7 || (n_peers > 0 && !peer_outs))
+    return fail(ctx, HC_ERR_INVALID_ARGUMENT, "between 0 and 7 peer results");
+  hc::GemmProblem p;
+  hc_status s = build_problem(ctx, dtype, 1, a, trans_a, b, trans_b, trans_out, rows, inner, cols, col_begin,
+                              col_count, out, &p);
+  if (s != HC_OK) return s;
+  ctx->last_flops = flop_count(1, rows, inner, col_count);
+  if (p.M == 0 || p.N == 0) return HC_OK;
+  if (p.K == 0) return fail(ctx, HC_ERR_INVALID_ARGUMENT, "pushed column blocks need a non-empty contraction");
+  if (!hc::tc_supported(p))
+    return fail(ctx, HC_ERR_NOT_IMPLEMENTED, "tensor-core kernel needs 16-byte aligned operands and leading dimensions");
+  const size_t need = hc::tc_scratch_bytes(p);
+  if (need) {
+    s = ensure_buffer(ctx, &ctx->scratch, &ctx->scratch_bytes, need);
+    if (s != HC_OK) return s;
+  }
+  // The block sits at the same offset in every device's copy of the result.
+  const ptrdiff_t offset = (const char*)p.C - (const char*)out;
+  void* extra[7];
+  for (int i = 0; i < n_peers; i++) {
+    if (!peer_outs[i]) return fail(ctx, HC_ERR_INVALID_ARGUMENT, "null peer result");
+    extra[i] = (char*)peer_outs[i] + offset;
+  }
+  cudaError_t e = hc::launch_tc(p, ctx->stream, ctx->status_word, ctx->scratch, ctx->scratch_bytes, ctx->sm_count,
+                                &ctx->last, extra, n_peers);
+  ctx->launch_count += ctx->last.launches;
+  if (e == cudaErrorNotSupported)
+    return fail(ctx, HC_ERR_NOT_IMPLEMENTED, "result buffers must be 16-byte aligned with 16-byte row pitch");
+  if (e != cudaSuccess) {
+    cudaGetLastError();
+    return fail(ctx, HC_ERR_KERNEL_FAILED, std::string("kernel launch failed: ") + cudaGetErrorString(e));
+  }
+  return HC_OK;
+}
+
+hc_status hc_shared_alloc(hc_ctx* ctx, size_t bytes, void** dptr) {
+  if (!ctx || !dptr) return HC_ERR_INVALID_ARGUMENT;
+  std::lock_guard<std::mutex> lock(ctx->mu);
+  DeviceGuard g(ctx->device);
+  *dptr = nullptr;
+  cudaError_t e = cudaMalloc(dptr, bytes ? bytes : 1);
+  if (e != cudaSuccess) {
+    *dptr = nullptr;
+    cudaGetLastError();
+    return fail(ctx, HC_ERR_ALLOCATION_FAILED, "shared allocation failed");
+  }
+  return HC_OK;
+}
+
+hc_status hc_shared_free(hc_ctx* ctx, void* dptr) {
+  if (!ctx) return HC_ERR_INVALID_ARGUMENT;
+  if (!dptr) return HC_OK;
+  std::lock_guard<std::mutex> lock(ctx->mu);
+  DeviceGuard g(ctx->device);
+  HC_CUDA_TRY(ctx, cudaStreamSynchronize(ctx->stream));
+  HC_CUDA_TRY(ctx, cudaFree(dptr));
+  return HC_OK;
+}
+
+hc_status hc_ipc_export(hc_ctx* ctx, void* dptr, void* handle_out) {
+  if (!ctx || !dptr || !handle_out) return HC_ERR_INVALID_ARGUMENT;
+  static_assert(sizeof(cudaIpcMemHandle_t) == HC_IPC_HANDLE_BYTES, "handle size");
+  std::lock_guard<std::mutex> lock(ctx->mu);
+  DeviceGuard g(ctx->device);
+  cudaIpcMemHandle_t h;
+  HC_CUDA_TRY(ctx, cudaIpcGetMemHandle(&h, dptr));
+  memcpy(handle_out, &h, sizeof h);
+  return HC_OK;
+}
+
+hc_status hc_ipc_open(hc_ctx* ctx, const void* handle, void** dptr) {
+  if (!ctx || !handle || !dptr) return HC_ERR_INVALID_ARGUMENT;
+  std::lock_guard<std::mutex> lock(ctx->mu);
+  DeviceGuard g(ctx->device);
+  cudaIpcMemHandle_t h;
+  memcpy(&h, handle, sizeof h);
+  *dptr = nullptr;
+  HC_CUDA_TRY(ctx, cudaIpcOpenMemHandle(dptr, h, cudaIpcMemLazyEnablePeerAccess));
+  return HC_OK;
+}
+
+hc_status hc_ipc_close(hc_ctx* ctx, void* dptr) {
+  if (!ctx) return HC_ERR_INVALID_ARGUMENT;
+  if (!dptr) return HC_OK;
+  std::lock_guard<std::mutex> lock(ctx->mu);
+  DeviceGuard g(ctx->device);
+  HC_CUDA_TRY(ctx, cudaStreamSynchronize(ctx->stream));
+  HC_CUDA_TRY(ctx, cudaIpcCloseMemHandle(dptr));
+  return HC_OK;
+}
+
 hc_status hc_batched_matmul_host(hc_ctx* ctx, hc_dtype dtype, int64_t matrix_count, const void* a_host, int trans_a,
                                  const void* b_host, int trans_b, int trans_out, int64_t rows, int64_t inner,
                                  int64_t cols, void* out_host) {

@@ -112,3 +112,52 @@ def matmulColumnSplit(backend: Optional[CUDABackend], rank: int, world: int, a: 
         rb = columnBlock(cols, r, world)[0]
         out[:, rb:rb + widths[r]] = recv[r, :, :widths[r]]
     return out
+
+
+class FusedColumnSplit:
+    """A product split over columns whose exchange is fused into the kernel's epilogue.
+
+    Every rank owns a full-size result buffer that the other ranks map (CUDA IPC).  Each rank
+    computes its column block and its epilogue stores every finished tile into all `world`
+    buffers (peer stores over NVLink), so after the ranks have synchronised and passed a
+    barrier each of them holds the complete product - there is no all-gather, no packing, and
+    the transfer overlaps the remaining tiles' arithmetic.  Set up once per shape, reuse per call.
+    """
+
+    def __init__(self, backend: CUDABackend, rank: int, world: int, rows: int, cols: int, dtype, group=None):
+        self.backend, self.rank, self.world, self.group = backend, rank, world, group
+        self.rows, self.cols, self.dtype = rows, cols, _as_dtype(dtype)
+        nbytes = rows * cols * self.dtype.byteSize
+        self.out = backend.sharedAllocate(nbytes)
+        handle = backend.ipcExport(self.out)
+        handles = [None] * world
+        if world > 1:
+            dist.all_gather_object(handles, handle, group=group)
+        self.peers = [backend.ipcOpen(h, nbytes) for r, h in enumerate(handles) if r != rank and h is not None]
+
+    def matmul(self, a, transA: bool, b, transB: bool, inner: int, wait: bool = True):
+        """Enqueue this rank's block (and its pushes).  With `wait`, also synchronise and pass
+        the group barrier, after which `self.out` holds the complete product on every rank."""
+        begin, count = columnBlock(self.cols, self.rank, self.world)
+        if count:
+            self.backend.matmulColumnBlockPush(a, transA, b, transB, False, self.rows, inner, self.cols, begin,
+                                               count, self.dtype, self.out, self.peers)
+        if wait:
+            self.finish()
+        return self.out
+
+    def finish(self):
+        self.backend.sync()
+        if self.world > 1:
+            dist.barrier(group=self.group)
+
+    def close(self):
+        self.backend.sync()
+        if self.world > 1:
+            dist.barrier(group=self.group)   # nobody unmaps while a peer may still be storing
+        for p in self.peers:
+            p.free()
+        self.peers = []
+        if self.world > 1:
+            dist.barrier(group=self.group)   # nobody frees while a peer still has it mapped
+        self.out.free()

@@ -158,6 +158,29 @@ hc_status hc_matmul_colblock(hc_ctx* ctx, hc_kernel kernel, hc_dtype dtype, cons
                              int64_t rows, int64_t inner, int64_t cols, int64_t col_begin,
                              int64_t col_count, void* out);
 
+/* hc_matmul_colblock fused with the exchange: every finished tile of the block is stored into
+ * `out` AND into the same place of up to 7 other devices' full-size results (`peer_outs`,
+ * pointers obtained with hc_ipc_open), from the kernel's epilogue, over NVLink peer stores.
+ * When every device of a group has run its call and synchronised, and the group has passed a
+ * host-side barrier, every device holds the complete product - no separate all-gather.
+ * Tensor-core kernel only; results must be 16-byte aligned with 16-byte row pitch.
+ * No counterpart in the reference (single-device). */
+hc_status hc_matmul_colblock_push(hc_ctx* ctx, hc_dtype dtype, const void* a, int trans_a,
+                                  const void* b, int trans_b, int trans_out, int64_t rows,
+                                  int64_t inner, int64_t cols, int64_t col_begin,
+                                  int64_t col_count, void* out, void* const* peer_outs,
+                                  int n_peers);
+
+/* Device memory that other processes on the box can map (one process per GPU), and the
+ * handle exchange for it (CUDA IPC; 64-byte opaque handles travel over any host channel).
+ * No counterpart in the reference. */
+#define HC_IPC_HANDLE_BYTES 64
+hc_status hc_shared_alloc(hc_ctx* ctx, size_t bytes, void** dptr);
+hc_status hc_shared_free(hc_ctx* ctx, void* dptr);
+hc_status hc_ipc_export(hc_ctx* ctx, void* dptr, void* handle_out);
+hc_status hc_ipc_open(hc_ctx* ctx, const void* handle, void** dptr);
+hc_status hc_ipc_close(hc_ctx* ctx, void* dptr);
+
 /* float32 `transOut(op(a) * op(b))` on the tensor cores WITHOUT allocating: no counterpart in
  * the reference.  It exists for hosts that must not allocate device memory from inside a
  * library call - a framework whose caching allocator already owns the device, or a loop that

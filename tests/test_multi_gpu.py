@@ -54,8 +54,25 @@ def _worker(rank, world, port, ret):
         be.sync()
         torch.cuda.synchronize()
         ok2 = bool(torch.equal(c, one))
+        # the same split with the exchange fused into the epilogue (peer stores, no collective)
+        from honeycrisp_b200.sharding import FusedColumnSplit
+        fused = FusedColumnSplit(be, rank, world, 512, 1024, np.float32)
+        fused.matmul(a, False, b, False, 256)
+        ok3 = bool(torch.equal(fused.out.asTorch((512, 1024), torch.float32), one))
+        fused.close()
+        ah = torch.randn((768, 320), generator=g, device="cuda").half()
+        bh = torch.randn((1536, 320), generator=g, device="cuda").half()     # stored [cols, inner]
+        torch.cuda.synchronize()
+        oneh = torch.empty((768, 1536), device="cuda", dtype=torch.float16)
+        be.matmul(ah, False, bh, True, False, 768, 320, 1536, np.float16,
+                  out=be.wrap(oneh.data_ptr(), oneh.numel() * 2, oneh), kernel=_lib.HC_KERNEL_TENSOR)
+        be.sync()
+        fusedh = FusedColumnSplit(be, rank, world, 768, 1536, np.float16)
+        fusedh.matmul(ah, False, bh, True, 320)
+        ok4 = bool(torch.equal(fusedh.out.asTorch((768, 1536), torch.float16), oneh))
+        fusedh.close()
         be.checkDeviceStatus()
-        ret[rank] = (ok1, ok2)
+        ret[rank] = (ok1, ok2, ok3, ok4)
         be.close()
     finally:
         dist.destroy_process_group()
@@ -70,4 +87,4 @@ def test_two_ranks_equal_one_device():
     mgr = mp.Manager()
     ret = mgr.dict()
     mp.spawn(_worker, args=(world, _free_port(), ret), nprocs=world, join=True)
-    assert dict(ret) == {0: (True, True), 1: (True, True)}
+    assert dict(ret) == {0: (True, True, True, True), 1: (True, True, True, True)}
