@@ -176,7 +176,7 @@ def run_reference(args):
         "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
-    print(json.dumps(line), flush=True)
+    emit(line)
 
 
 # ------------------------------------------------------------------------------------------------
@@ -342,7 +342,7 @@ def run_ours(args):
     }
     if args.all_configs:
         line["extra"] = other_configs(be, stream, rank, world) if world == 1 else multi_extra
-    print(json.dumps(line), flush=True)
+    emit(line)
     if use_dist:
         dist.destroy_process_group()
 
@@ -430,8 +430,8 @@ def run_probe(args):
     torch.cuda.synchronize()
     be.checkDeviceStatus()
     ms = e0.elapsed_time(e1) / args.steps
-    print(json.dumps({"probe": [M, K, N, cnt], "dtype": args.dtype, "flags": [ta, tb], "ms": ms,
-                      "tflops": 2.0 * cnt * M * N * K / ms / 1e9, "kernel": be.lastLaunchInfo()}), flush=True)
+    emit({"probe": [M, K, N, cnt], "dtype": args.dtype, "flags": [ta, tb], "ms": ms,
+          "tflops": 2.0 * cnt * M * N * K / ms / 1e9, "kernel": be.lastLaunchInfo()})
 
 
 def sharded_configs(be, stream, rank, world):
@@ -493,7 +493,28 @@ def sharded_configs(be, stream, rank, world):
     return res
 
 
+_REAL_STDOUT = None
+
+
+def quiet_stdout():
+    """Libraries (NCCL's version banner, for one) write to file descriptor 1.  The contract is
+    one JSON line on stdout, so everything else is sent to stderr and the line is written to
+    the saved descriptor."""
+    global _REAL_STDOUT
+    if _REAL_STDOUT is None:
+        sys.stdout.flush()
+        _REAL_STDOUT = os.fdopen(os.dup(1), "w")
+        os.dup2(2, 1)
+
+
+def emit(line: dict):
+    out = _REAL_STDOUT or sys.stdout
+    out.write(json.dumps(line) + "\n")
+    out.flush()
+
+
 def main():
+    quiet_stdout()
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=100)
