@@ -291,15 +291,18 @@ class CUDABackend:
     # -- the hot path --------------------------------------------------------------------
 
     def matmul(self, a, transA: bool, b, transB: bool, transOut: bool, rows: int, inner: int, cols: int,
-               dtype, kernel: int = L.HC_KERNEL_AUTO, out: Optional[CUDAData] = None) -> CUDAData:
+               dtype, kernel: int = L.HC_KERNEL_AUTO, out: Optional[CUDAData] = None, mark: bool = True) -> CUDAData:
         """`transOut(op(a) * op(b))`; rows x cols is the shape of op(a)*op(b) (Backend.swift:650-658)."""
         return self.batchedMatmul(1, a, transA, b, transB, transOut, rows, inner, cols, dtype, kernel=kernel,
-                                  out=out)
+                                  out=out, mark=mark)
 
     def batchedMatmul(self, matrixCount: int, a, transA: bool, b, transB: bool, transOut: bool, rows: int,
                       inner: int, cols: int, dtype, kernel: int = L.HC_KERNEL_AUTO,
-                      out: Optional[CUDAData] = None) -> CUDAData:
-        """matrixCount independent products, operands packed back to back (Backend.swift:661-669)."""
+                      out: Optional[CUDAData] = None, mark: bool = True) -> CUDAData:
+        """matrixCount independent products, operands packed back to back (Backend.swift:661-669).
+
+        `mark=False` skips the per-result completion marker (wait() then synchronises the whole
+        stream instead); launch-bound loops and CUDA-graph capture use it."""
         dt = _as_dtype(dtype)
         if dt not in _HC_DTYPE:
             raise NotImplementedByBackend(f"matmul for dtype {dt.value}")
@@ -320,7 +323,8 @@ class CUDABackend:
                                            int(bool(transA)), b_d.ptr, int(bool(transB)), int(bool(transOut)),
                                            int(rows), int(inner), int(cols), out.ptr)
         self._check(st)
-        out._mark()
+        if mark:
+            out._mark()
         out._inputs = (a_d, b_d)  # keep operands alive until the result is collected
         return out
 

@@ -70,7 +70,8 @@ def batchedMatmulSharded(backend: Optional[CUDABackend], rank: int, world: int, 
             compute(count, a_sh, transA, b_sh, transB, transOut, rows, inner, cols, dt, out)
         else:
             od = backend.wrap(out.data_ptr(), out.numel() * out.element_size(), out)
-            backend.batchedMatmul(count, a_sh, transA, b_sh, transB, transOut, rows, inner, cols, dt, out=od)
+            backend.batchedMatmul(count, a_sh, transA, b_sh, transB, transOut, rows, inner, cols, dt, out=od,
+                                  mark=False)
     return out, (begin, count)
 
 

@@ -162,3 +162,107 @@ def test_config2_shape_properties(be, flags):
     ref_cols = (A.double() @ Bm[:, cols].double()).cpu().numpy()
     got_cols = out[:, cols].float().cpu().numpy()
     assert ref.rel_frobenius(got_cols, ref_cols) < TOL_F16
+
+
+# ---- the configured workloads at full size, through properties that need no CPU product ----
+
+def _rel(x, r):
+    return float((x.double() - r.double()).norm() / r.double().norm())
+
+
+def test_config1_float32_1024_against_host_sgemm(be):
+    """float32 1024^3, U[0,1), no flags: the one case the reference sends to its library GEMM;
+    checked against the host sgemm stand-in within 1e-5 relative Frobenius error."""
+    A, B = random_operands(0, 1, 1024, 1024, 1024, np.float32, dist="uniform01")
+    host = ref.matmul(A, False, B, False, False, 1024, 1024, 1024, library_fast_path=True)
+    res, _, _ = run(be, 1, A, B, False, False, False, np.float32, 0)
+    from honeycrisp_b200 import _lib
+    assert be.lastLaunchInfo()["kernel"] == _lib.HC_KERNEL_TENSOR
+    assert ref.rel_frobenius(res, host) < TOL_F32
+
+
+def test_config3_batched_scores_full_size(be):
+    """float16 batched Q.K^T, 64 x [2048,128].[2048,128]^T: every matrix against a float64 product
+    (on the device), and bitwise equality of a batch shard computed on its own."""
+    import torch
+    g = torch.Generator(device="cuda").manual_seed(2)
+    q = torch.randn((64, 2048, 128), generator=g, device="cuda").half()
+    k = torch.randn((64, 2048, 128), generator=g, device="cuda").half()
+    out = torch.empty((64, 2048, 2048), device="cuda", dtype=torch.float16)
+    torch.cuda.synchronize()
+    be.batchedMatmul(64, q, False, k, True, False, 2048, 128, 2048, np.float16,
+                     out=be.wrap(out.data_ptr(), out.numel() * 2, out))
+    be.sync()
+    be.checkDeviceStatus()
+    for i in range(0, 64, 8):
+        want = q[i:i + 8].double() @ k[i:i + 8].double().transpose(1, 2)
+        assert _rel(out[i:i + 8], want) < TOL_F16
+    shard = torch.empty((8, 2048, 2048), device="cuda", dtype=torch.float16)
+    be.batchedMatmul(8, q[16:24], False, k[16:24], True, False, 2048, 128, 2048, np.float16,
+                     out=be.wrap(shard.data_ptr(), shard.numel() * 2, shard))
+    be.sync()
+    assert torch.equal(shard, out[16:24])
+
+
+def test_config4_linear_triple_full_size(be):
+    """Forward and both backward products of a Linear layer as autodiff issues them
+    (Linalg.swift:73-80): Y = X.W^T, dX = dY.W, dW = (X^T.dY)^T, sampled rows against float64."""
+    import torch
+    g = torch.Generator(device="cuda").manual_seed(3)
+    x = torch.randn((16384, 4096), generator=g, device="cuda").half()
+    w = ((torch.rand((16384, 4096), generator=g, device="cuda") - 0.5) / 32).half()
+    dy = torch.randn((16384, 16384), generator=g, device="cuda").half()
+    y = torch.empty((16384, 16384), device="cuda", dtype=torch.float16)
+    dx = torch.empty((16384, 4096), device="cuda", dtype=torch.float16)
+    dw = torch.empty((16384, 4096), device="cuda", dtype=torch.float16)
+    torch.cuda.synchronize()
+    wrap = lambda t: be.wrap(t.data_ptr(), t.numel() * 2, t)
+    be.matmul(x, False, w, True, False, 16384, 4096, 16384, np.float16, out=wrap(y))
+    # the backward flag triples of a (transA=F, transB=T, transOut=F) product
+    (fa, fb) = ref.matmul_grad_calls(False, True, False)
+    assert fa == (False, False, False) and fb == (True, False, True)
+    be.matmul(dy, fa[0], w, fa[1], fa[2], 16384, 16384, 4096, np.float16, out=wrap(dx))
+    be.matmul(x, fb[0], dy, fb[1], fb[2], 4096, 16384, 16384, np.float16, out=wrap(dw))
+    be.sync()
+    be.checkDeviceStatus()
+    rows = torch.randint(0, 16384, (48,), generator=torch.Generator().manual_seed(5)).cuda()
+    assert _rel(y[rows], x[rows].double() @ w.double().t()) < TOL_F16
+    assert _rel(dx[rows], dy[rows].double() @ w.double()) < TOL_F16
+    assert _rel(dw[rows], dy[:, rows].double().t() @ x.double()) < TOL_F16
+
+
+def test_config5_float32_16384_against_cuda_core_kernel(be):
+    """float32 16384^3, U[-1,1): the 3xTF32 result against the CUDA-core kernel over the whole
+    matrix (1e-5 relative Frobenius), sampled rows of both against float64, and a column block
+    computed separately equal to the same columns bit for bit."""
+    import torch
+    from honeycrisp_b200 import _lib
+    n = 16384
+    g = torch.Generator(device="cuda").manual_seed(4)
+    a = torch.rand((n, n), generator=g, device="cuda") * 2 - 1
+    b = torch.rand((n, n), generator=g, device="cuda") * 2 - 1
+    c_tc = torch.empty((n, n), device="cuda")
+    c_cc = torch.empty((n, n), device="cuda")
+    torch.cuda.synchronize()
+    wrap = lambda t: be.wrap(t.data_ptr(), t.numel() * 4, t)
+    be.matmul(a, False, b, False, False, n, n, n, np.float32, out=wrap(c_tc), kernel=_lib.HC_KERNEL_TENSOR)
+    be.matmul(a, False, b, False, False, n, n, n, np.float32, out=wrap(c_cc), kernel=_lib.HC_KERNEL_SIMT)
+    be.sync()
+    be.checkDeviceStatus()
+    num = torch.zeros((), device="cuda", dtype=torch.float64)
+    den = torch.zeros((), device="cuda", dtype=torch.float64)
+    for r0 in range(0, n, 2048):      # norms in slabs: a float64 copy of the whole matrix is 2 GiB
+        d = c_tc[r0:r0 + 2048].double() - c_cc[r0:r0 + 2048].double()
+        num += (d * d).sum()
+        den += (c_cc[r0:r0 + 2048].double() ** 2).sum()
+    assert float((num / den).sqrt()) < TOL_F32
+    rows = torch.randint(0, n, (32,), generator=torch.Generator().manual_seed(6)).cuda()
+    want = a[rows].double() @ b.double()
+    assert _rel(c_tc[rows], want) < TOL_F32
+    assert _rel(c_cc[rows], want) < TOL_F32
+    blk = torch.zeros((n, n), device="cuda")
+    be.matmulColumnBlock(a, False, b, False, False, n, n, n, 4096, 2048, np.float32, out=wrap(blk),
+                         kernel=_lib.HC_KERNEL_TENSOR)
+    be.sync()
+    assert torch.equal(blk[:, 4096:6144], c_tc[:, 4096:6144])
+    assert float(blk[:, :4096].abs().max()) == 0.0 and float(blk[:, 6144:].abs().max()) == 0.0
