@@ -74,6 +74,7 @@ SIGNATURES = {
     "hc_last_launch_info": (_int, [_vp, ctypes.POINTER(LaunchInfo)]),
     "hc_launch_count": (_i64, [_vp]),
     "hc_check_device_status": (_int, [_vp]),
+    "hc_selftest_bounded_wait": (_int, [_vp, _int]),
     "hc_version": (ctypes.c_char_p, []),
 }
 

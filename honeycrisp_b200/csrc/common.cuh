@@ -34,6 +34,7 @@ enum DeviceStatusBits : unsigned int {
   kDevTimeoutProducer = 1u,
   kDevTimeoutMma = 2u,
   kDevTimeoutEpilogue = 4u,
+  kDevTimeoutSelfTest = 8u,
 };
 
 struct LaunchRecord {
@@ -57,6 +58,8 @@ cudaError_t launch_tc(const GemmProblem& p, cudaStream_t stream, unsigned int* s
                       void* scratch, size_t scratch_bytes, int sm_count, LaunchRecord* rec,
                       void* const* extra_out = nullptr, int n_extra = 0);
 bool tc_supported(const GemmProblem& p);
+// One-thread kernel whose bounded wait is made to expire after `limit_ns` (self-test).
+cudaError_t launch_wait_probe(cudaStream_t stream, unsigned int* status_word, unsigned long long limit_ns);
 size_t tc_scratch_bytes(const GemmProblem& p);
 
 }  // namespace hc

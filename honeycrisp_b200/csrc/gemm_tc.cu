@@ -126,7 +126,8 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
   return ok != 0;
 }
 // Bounded wait.  False means: gave up (time limit, or another role of this CTA already did).
-__device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+__device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity, volatile int* abort_flag,
+                                            unsigned long long limit_ns = kWaitLimitNs) {
   const unsigned long long t0 = globaltimer_ns();
 #pragma unroll 1
   for (;;) {
@@ -134,7 +135,7 @@ __device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity, volat
     for (int i = 0; i < 64; i++)
       if (mbar_try_wait(bar, parity)) return true;
     if (*abort_flag) return false;
-    if (globaltimer_ns() - t0 > kWaitLimitNs) return false;
+    if (globaltimer_ns() - t0 > limit_ns) return false;
   }
 }
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
@@ -142,6 +143,39 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
   for (int i = 0; i < 16; i++)
     if (mbar_try_wait(bar, parity)) return true;
   return mbar_wait_slow(bar, parity, abort_flag);
+}
+
+// Long waits of a whole warp (the epilogue waits a full main loop for its accumulator): one
+// lane polls, sleeping between polls so the spinning does not compete with the issuing warps
+// for issue slots and power; when it has seen the phase complete, every lane observes the
+// barrier once itself (that returns at once and gives each lane its own acquire).
+__device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity, volatile int* abort_flag, int lane) {
+  bool ok = true;
+  if (lane == 0) {
+    ok = false;
+#pragma unroll 1
+    for (int i = 0; i < 32 && !ok; i++) ok = mbar_try_wait(bar, parity);
+    if (!ok) {
+      const unsigned long long t0 = globaltimer_ns();
+#pragma unroll 1
+      for (;;) {
+#pragma unroll 1
+        for (int i = 0; i < 32 && !ok; i++) {
+          __nanosleep(100);
+          ok = mbar_try_wait(bar, parity);
+        }
+        if (ok || *abort_flag || globaltimer_ns() - t0 > kWaitLimitNs) break;
+      }
+    }
+  }
+  ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+  if (ok) {
+    bool mine = false;
+#pragma unroll 1
+    for (int i = 0; i < 4096 && !mine; i++) mine = mbar_try_wait(bar, parity);
+    ok = __all_sync(0xffffffffu, mine);
+  }
+  return ok;
 }
 
 // Tiled TMA load of one box into this CTA's shared memory.  With kCta == 2 the completion
@@ -555,8 +589,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap mapA_hi, const __grid_constan
       const int nwin = (nkb + chunk_kb - 1) / chunk_kb;
       if (!kWindowed) {
         const uint32_t slot = win & 1;
-        bool got = mbar_wait(bar_tfull + 8 * slot, (win >> 1) & 1, abortp);
-        got = __all_sync(0xffffffffu, got);
+        const bool got = mbar_wait_warp(bar_tfull + 8 * slot, (win >> 1) & 1, abortp, lane);
         if (!got) {
           if (lane == 0) { atomicOr(p.status, kDevTimeoutEpilogue); abort_flag = 1; }
           ok = false;
@@ -640,8 +673,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap mapA_hi, const __grid_constan
         float acc[COLS_PER_THREAD];
         for (int w = 0; w < nwin && ok; w++) {
           const uint32_t slot = win & 1;
-          bool got = mbar_wait(bar_tfull + 8 * slot, (win >> 1) & 1, abortp);
-          got = __all_sync(0xffffffffu, got);
+          const bool got = mbar_wait_warp(bar_tfull + 8 * slot, (win >> 1) & 1, abortp, lane);
           if (!got) {
             if (lane == 0) { atomicOr(p.status, kDevTimeoutEpilogue); abort_flag = 1; }
             ok = false;
@@ -738,6 +770,23 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap mapA_hi, const __grid_constan
       asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)TMEM_COLS)
                    : "memory");
     }
+  }
+}
+
+// Self-test of the bounded wait: one thread waits on a barrier that nothing will ever arrive
+// on, with a short limit, through the same wait routine the GEMM kernel uses.  The wait gives
+// up, the status word gets its bit, and the kernel returns normally.
+__global__ void wait_probe_kernel(unsigned int* status, unsigned long long limit_ns) {
+  __shared__ __align__(8) uint64_t bar;
+  __shared__ int abort_flag;
+  if (threadIdx.x == 0) {
+    abort_flag = 0;
+    mbar_init(smem_u32(&bar), 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    if (!mbar_wait_slow(smem_u32(&bar), 0, &abort_flag, limit_ns)) atomicOr(status, kDevTimeoutSelfTest);
   }
 }
 
@@ -934,6 +983,11 @@ struct TcConfig {
 
 }  // namespace
 
+cudaError_t launch_wait_probe(cudaStream_t stream, unsigned int* status_word, unsigned long long limit_ns) {
+  wait_probe_kernel<<<1, 32, 0, stream>>>(status_word, limit_ns);
+  return cudaGetLastError();
+}
+
 bool tc_supported(const GemmProblem& p) {
   if (p.M <= 0 || p.N <= 0 || p.K <= 0 || p.batch <= 0) return false;
   const int eb = p.dtype == HC_F16 ? 2 : 4;
@@ -1027,7 +1081,7 @@ cudaError_t launch_tc(const GemmProblem& p, cudaStream_t stream, unsigned int* s
   tp.tiles_m = (int)((p.M + tp.tile_rows - 1) / tp.tile_rows);
   tp.tiles_n = (int)((p.N + bn - 1) / bn);
   tp.total_tiles = (int64_t)tp.tiles_m * tp.tiles_n * p.batch;
-  tp.group_m = 16 / cta;
+  tp.group_m = env_int("HC_TC_GROUP_M", 16 / cta);
   tp.a_mn_major = p.a_mn_major; tp.b_mn_major = p.b_mn_major;
   tp.C = p.C; tp.ldc = p.ldc; tp.strideC = p.strideC;
   tp.status = status_word;

@@ -591,6 +591,16 @@ hc_status hc_check_device_status(hc_ctx* ctx) {
   return HC_OK;
 }
 
+hc_status hc_selftest_bounded_wait(hc_ctx* ctx, int limit_ms) {
+  if (!ctx || limit_ms < 1 || limit_ms > 1000) return HC_ERR_INVALID_ARGUMENT;
+  std::lock_guard<std::mutex> lock(ctx->mu);
+  DeviceGuard g(ctx->device);
+  cudaError_t e = hc::launch_wait_probe(ctx->stream, ctx->status_word, (unsigned long long)limit_ms * 1000000ull);
+  ctx->launch_count += 1;
+  if (e != cudaSuccess) return cuda_fail(ctx, e, "wait probe launch");
+  return HC_OK;
+}
+
 const char* hc_version(void) { return "0.1"; }
 
 }  // extern "C"

@@ -210,6 +210,11 @@ int64_t hc_launch_count(hc_ctx* ctx);
 /* Reads and clears the device-side status word; HC_ERR_TIMEOUT if a bounded wait expired in
  * a kernel that has completed.  Synchronises the stream. */
 hc_status hc_check_device_status(hc_ctx* ctx);
+/* Failure-path self-test that harms nothing: enqueues a one-thread kernel that waits, through
+ * the same bounded-wait routine as the GEMM kernels, on a barrier nobody signals.  After
+ * `limit_ms` (1..1000) the wait gives up, sets the status word and the kernel returns; the next
+ * hc_check_device_status / hc_event_wait reports HC_ERR_TIMEOUT and the context stays usable. */
+hc_status hc_selftest_bounded_wait(hc_ctx* ctx, int limit_ms);
 /* Library version, "major.minor". */
 const char* hc_version(void);
 

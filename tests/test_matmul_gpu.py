@@ -233,3 +233,22 @@ def test_run_to_run_determinism(be):
     for _ in range(3):
         again, _, _ = run(be, 2, A, B, False, True, False, np.float16)
         assert np.array_equal(first.view(np.uint16), again.view(np.uint16))
+
+
+def test_bounded_wait_expires_and_context_stays_usable(be):
+    """Failure detection without a fault: a wait that nothing satisfies gives up after its
+    limit, the host sees HC_ERR_TIMEOUT once, and the same context keeps working."""
+    import time
+    from honeycrisp_b200 import DeviceTimeout, _lib
+    lib = _lib.load()
+    be.checkDeviceStatus()                                   # clean before
+    t0 = time.perf_counter()
+    assert lib.hc_selftest_bounded_wait(be._ctx, 20) == _lib.HC_OK
+    with pytest.raises(DeviceTimeout):
+        be.checkDeviceStatus()
+    assert 0.015 < time.perf_counter() - t0 < 2.0
+    be.checkDeviceStatus()                                   # the status word was cleared
+    A, B = random_operands(1, 1, 256, 128, 256, np.float16)
+    res, a_st, b_st = run(be, 1, A, B, False, True, False, np.float16, kernel=K().HC_KERNEL_TENSOR)
+    f64 = ref.batched_matmul_f64(1, a_st, False, b_st, True, False, 256, 128, 256)
+    assert ref.rel_frobenius(res, f64) < 2e-3
