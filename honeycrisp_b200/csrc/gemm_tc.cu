@@ -371,10 +371,13 @@ __device__ __forceinline__ TileCoord decode_tile(int64_t tile, const TcParams& p
 }
 
 // kElemBytes: 2 (float16 operands) or 4 (float32 operands consumed as TF32).
-// kBN       : tile width in output columns.
+// kBN       : columns of one tcgen05.mma (and of one accumulator buffer).
+// kNSplit   : 1, or 2 for tiles two MMAs wide (512 columns) whose halves take the two accumulator
+//             buffers: less operand traffic per flop, but the epilogue no longer overlaps the
+//             next tile (used for long contractions only).
 // kWindowed : epilogue sums accumulation windows in registers (float32 output only).
 // kCta      : 1, or 2 for CTA pairs (cluster of two, 256-row tiles, one MMA over both SMs).
-template <int kElemBytes, int kBN, int kStages, int kEpiWarps, bool kWindowed, int kCta>
+template <int kElemBytes, int kBN, int kStages, int kEpiWarps, bool kWindowed, int kCta, int kNSplit>
 __global__ void __launch_bounds__(64 + 32 * kEpiWarps, 1)
 tc_gemm_kernel(const __grid_constant__ CUtensorMap mapA_hi, const __grid_constant__ CUtensorMap mapA_lo,
                const __grid_constant__ CUtensorMap mapB_hi, const __grid_constant__ CUtensorMap mapB_lo,
@@ -384,15 +387,19 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap mapA_hi, const __grid_constan
   constexpr int BK = 128 / kElemBytes;       // elements in one 128-byte slab row
   constexpr int UMMA_K = 32 / kElemBytes;    // k per tcgen05.mma
   constexpr int CH = 128 / kElemBytes;       // M/N indices in one 128-byte row of an MN-major box
-  constexpr int BN_LOCAL = kBN / kCta;       // B columns this CTA loads
+  constexpr int BN_LOCAL = kBN / kCta;       // B columns this CTA loads per MMA-wide part of the tile
+  constexpr int TILE_N = kBN * kNSplit;
+  constexpr int ACC_SLOTS = 2 / kNSplit;     // accumulator buffers that alternate between windows
   // MN-major geometry: 16-bit data uses the 16-byte-unit swizzle with 8-row k groups, 32-bit
   // data the 32-byte-unit swizzle with 4-row k groups.  One MMA consumes UMMA_K 128-byte k-rows.
   constexpr uint32_t MN_SBO = kTf32 ? 512u : 1024u;
   constexpr uint32_t MN_MODE = kTf32 ? 1u : 2u;
-  constexpr uint32_t A_BYTES = BM * 128, B_BYTES = BN_LOCAL * 128, STAGE_BYTES = A_BYTES + B_BYTES;
+  constexpr uint32_t A_BYTES = BM * 128, B_PART_BYTES = BN_LOCAL * 128, B_BYTES = kNSplit * B_PART_BYTES,
+                     STAGE_BYTES = A_BYTES + B_BYTES;
   constexpr int TMEM_COLS = (2 * kBN <= 32) ? 32 : 2 * kBN;
   constexpr int COL_SPLIT = kEpiWarps / 4;   // epilogue warps sharing one lane quarter
-  constexpr int COLS_PER_THREAD = kBN / COL_SPLIT;
+  constexpr int COLS_PER_THREAD = TILE_N / COL_SPLIT;
+  static_assert(kNSplit == 1 || (kNSplit == 2 && !kWindowed && kBN == 256), "wide tiles: plain epilogue only");
   static_assert(kEpiWarps == 4 || kEpiWarps == 8, "epilogue warps come in groups of four");
   static_assert(TMEM_COLS == 64 || TMEM_COLS == 128 || TMEM_COLS == 256 || TMEM_COLS == 512, "power of two");
   static_assert(kCta == 1 || kCta == 2, "one CTA or a pair");
@@ -459,7 +466,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap mapA_hi, const __grid_constan
       for (int64_t tile = tile_first; ok && tile < p.total_tiles; tile += tile_step) {
         const TileCoord t = decode_tile(tile, p);
         const int m0 = t.tm * (BM * kCta) + (int)rank * BM;
-        const int n0 = t.tn * kBN + (int)rank * BN_LOCAL;
+        const int n0 = t.tn * TILE_N + (int)rank * BN_LOCAL;
         const int mat = (int)t.mat;
         for (int kb = 0; kb < nkb; kb++) {
           if (!mbar_wait(bar_empty + 8 * s, ph ^ 1, abortp)) {
@@ -487,12 +494,17 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap mapA_hi, const __grid_constan
 #pragma unroll
             for (int c = 0; c < BM / CH; c++) tma_load_3d<kCta>(sa + c * (BK * 128), ma, full, m0 + c * CH, kc, mat);
           }
-          if (!p.b_mn_major) {
-            tma_load_3d<kCta>(sb, mb, full, kc, n0, mat);
-          } else {
 #pragma unroll
-            for (int c = 0; c < BN_LOCAL / CH; c++)
-              tma_load_3d<kCta>(sb + c * (BK * 128), mb, full, n0 + c * CH, kc, mat);
+          for (int h = 0; h < kNSplit; h++) {
+            const uint32_t sbh = sb + h * B_PART_BYTES;
+            const int n0h = n0 + h * kBN;
+            if (!p.b_mn_major) {
+              tma_load_3d<kCta>(sbh, mb, full, kc, n0h, mat);
+            } else {
+#pragma unroll
+              for (int c = 0; c < BN_LOCAL / CH; c++)
+                tma_load_3d<kCta>(sbh + c * (BK * 128), mb, full, n0h + c * CH, kc, mat);
+            }
           }
           if (++s == kStages) { s = 0; ph ^= 1; }
         }
@@ -529,8 +541,8 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap mapA_hi, const __grid_constan
         for (int kb = 0; kb < nkb; kb++) {
           const int in_win = kb % chunk_kb;
           if (in_win == 0) {
-            slot = win & 1;
-            if (!mbar_wait(bar_tempty + 8 * slot, ((win >> 1) & 1) ^ 1, abortp)) {
+            slot = win % ACC_SLOTS;
+            if (!mbar_wait(bar_tempty + 8 * slot, ((win / ACC_SLOTS) & 1) ^ 1, abortp)) {
               atomicOr(p.status, kDevTimeoutMma);
               abort_flag = 1;
               ok = false;
@@ -547,13 +559,16 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap mapA_hi, const __grid_constan
           tc_fence_after();
           const uint32_t sa = smem_base + s * STAGE_BYTES, sb = sa + A_BYTES;
           const uint64_t adesc = make_smem_desc(sa, a_lbo, a_sbo, a_mode);
-          const uint64_t bdesc = make_smem_desc(sb, b_lbo, b_sbo, b_mode);
-          const uint32_t d = tmem_base + slot * kBN;
 #pragma unroll
-          for (int k = 0; k < BK / UMMA_K; k++) {
-            if (p.debug & 16) break;  // timing experiment: no MMAs
-            tc_mma<kTf32, kCta>(d, adesc + (uint64_t)((k * a_kstep) >> 4), bdesc + (uint64_t)((k * b_kstep) >> 4),
-                                idesc, (in_win | k) ? 1u : 0u);
+          for (int h = 0; h < kNSplit; h++) {
+            const uint64_t bdesc = make_smem_desc(sb + h * B_PART_BYTES, b_lbo, b_sbo, b_mode);
+            const uint32_t d = tmem_base + (kNSplit == 2 ? h : slot) * kBN;
+#pragma unroll
+            for (int k = 0; k < BK / UMMA_K; k++) {
+              if (p.debug & 16) break;  // timing experiment: no MMAs
+              tc_mma<kTf32, kCta>(d, adesc + (uint64_t)((k * a_kstep) >> 4), bdesc + (uint64_t)((k * b_kstep) >> 4),
+                                  idesc, (in_win | k) ? 1u : 0u);
+            }
           }
           tc_commit<kCta>(bar_empty + 8 * s);
           if (kCta == 2) tc_commit<kCta>(empty_peer + 8 * s);
@@ -583,20 +598,20 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap mapA_hi, const __grid_constan
     for (int64_t tile = tile_first; ok && tile < p.total_tiles; tile += tile_step) {
       const TileCoord t = decode_tile(tile, p);
       const int64_t gm = (int64_t)t.tm * (BM * kCta) + rank * BM + quarter * 32 + lane;
-      const int64_t n0 = (int64_t)t.tn * kBN + col0;
+      const int64_t n0 = (int64_t)t.tn * TILE_N + col0;
       void* cmat = kOutHalf ? (void*)((__half*)p.C + t.mat * p.strideC) : (void*)((float*)p.C + t.mat * p.strideC);
       const int64_t row_off = gm * p.ldc;
       const int nwin = (nkb + chunk_kb - 1) / chunk_kb;
       if (!kWindowed) {
-        const uint32_t slot = win & 1;
-        const bool got = mbar_wait_warp(bar_tfull + 8 * slot, (win >> 1) & 1, abortp, lane);
+        const uint32_t slot = win % ACC_SLOTS;
+        const bool got = mbar_wait_warp(bar_tfull + 8 * slot, (win / ACC_SLOTS) & 1, abortp, lane);
         if (!got) {
           if (lane == 0) { atomicOr(p.status, kDevTimeoutEpilogue); abort_flag = 1; }
           ok = false;
           break;
         }
         tc_fence_after();
-        const uint32_t tbase = tmem_base + lane_base + slot * kBN + col0;
+        const uint32_t tbase = tmem_base + lane_base + (kNSplit == 2 ? 0 : slot * kBN) + col0;
         if (p.tma_store) {
           // Each warp rounds its 32 rows x 128 bytes into a swizzled staging buffer and one lane
           // sends it with a TMA store (full 128-byte lines); two buffers per warp alternate.
@@ -905,13 +920,14 @@ int window_slabs() {
   return v < 1 ? 1 : v;
 }
 
-template <int kElemBytes, int kBN, int kStages, int kEpiWarps, bool kWindowed, int kCta>
+template <int kElemBytes, int kBN, int kStages, int kEpiWarps, bool kWindowed, int kCta, int kNSplit = 1>
 struct TcConfig {
   // operand ring + two 4 KB store-staging buffers per epilogue warp + alignment slack
-  static constexpr size_t smem = (size_t)kStages * (BM * 128 + (kBN / kCta) * 128) + (size_t)kEpiWarps * 8192 + 1024;
+  static constexpr size_t smem =
+      (size_t)kStages * (BM * 128 + kNSplit * (kBN / kCta) * 128) + (size_t)kEpiWarps * 8192 + 1024;
   static_assert(smem <= 232448, "more shared memory than one CTA can have on sm_100");
   static constexpr int block = 64 + 32 * kEpiWarps;
-  static auto kernel() { return tc_gemm_kernel<kElemBytes, kBN, kStages, kEpiWarps, kWindowed, kCta>; }
+  static auto kernel() { return tc_gemm_kernel<kElemBytes, kBN, kStages, kEpiWarps, kWindowed, kCta, kNSplit>; }
 
   static cudaError_t configure() {
     static bool configured[64] = {};
@@ -973,7 +989,7 @@ struct TcConfig {
     cfg.numAttrs = 1;
     e = cudaLaunchKernelEx(&cfg, kernel(), maps[0], maps[1], maps[2], maps[3], outs, p);
     if (rec) {
-      rec->tile_m = BM * kCta; rec->tile_n = kBN; rec->tile_k = 128 / kElemBytes; rec->stages = kStages;
+      rec->tile_m = BM * kCta; rec->tile_n = kBN * kNSplit; rec->tile_k = 128 / kElemBytes; rec->stages = kStages;
       rec->grid = grid; rec->block = block; rec->launches++;
     }
     if (e != cudaSuccess) return e;
@@ -1077,9 +1093,13 @@ cudaError_t launch_tc(const GemmProblem& p, cudaStream_t stream, unsigned int* s
   const bool windowed = f32 && !(dbg & 2);
   tp.chunk_kb = windowed ? 3 * window_slabs() : tp.num_k_blocks;
   if (tp.chunk_kb > tp.num_k_blocks) tp.chunk_kb = tp.num_k_blocks;
+  // Wide tiles (256 x 512 per CTA pair) for long float16 contractions over wide products.
+  const int wide_min_kb = env_int("HC_TC_WIDE_MIN_KB", 48);
+  const bool wide = !f32 && cta == 2 && tp.num_k_blocks >= wide_min_kb && p.N >= 1024;
+  const int tile_n = wide ? 2 * bn : bn;
   tp.tile_rows = BM * cta;
   tp.tiles_m = (int)((p.M + tp.tile_rows - 1) / tp.tile_rows);
-  tp.tiles_n = (int)((p.N + bn - 1) / bn);
+  tp.tiles_n = (int)((p.N + tile_n - 1) / tile_n);
   tp.total_tiles = (int64_t)tp.tiles_m * tp.tiles_n * p.batch;
   tp.group_m = env_int("HC_TC_GROUP_M", 16 / cta);
   tp.a_mn_major = p.a_mn_major; tp.b_mn_major = p.b_mn_major;
@@ -1110,6 +1130,7 @@ cudaError_t launch_tc(const GemmProblem& p, cudaStream_t stream, unsigned int* s
     // Short contractions are bound by draining results, not by the MMA: more epilogue warps,
     // fewer operand stages.
     const bool short_k = tp.num_k_blocks <= env_int("HC_TC_SHORT_K", 8);
+    if (wide) return TcConfig<2, 256, 4, 4, false, 2, 2>::launch(maps, outs, tp, sm_count, stream, rec);
     if (cta == 2 && short_k) return TcConfig<2, 256, 4, 8, false, 2>::launch(maps, outs, tp, sm_count, stream, rec);
     if (cta == 2) return TcConfig<2, 256, 6, 4, false, 2>::launch(maps, outs, tp, sm_count, stream, rec);
     if (bn == 256) return TcConfig<2, 256, 4, 4, false, 1>::launch(maps, outs, tp, sm_count, stream, rec);
