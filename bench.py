@@ -38,7 +38,7 @@ FLOPS_PER_GEMM = 2.0 * N_DIM ** 3
 # DRAM bytes (dram__bytes_read.sum + dram__bytes_write.sum) of one 8192^3 launch of the tensor-core
 # kernel, from the ncu capture summarised under profiles/ (mean of the two layouts
 # captured).  The algorithmic minimum is 3 * 8192^2 * 2 = 403 MB.
-NCU_DRAM_BYTES_PER_LAUNCH = 1.227e9
+NCU_DRAM_BYTES_PER_LAUNCH = 1.032e9
 
 
 def load_peaks():
