@@ -22,9 +22,9 @@
 // bit of the instruction descriptor.
 //
 // float32 runs as 3xTF32: x = hi + lo with hi, lo representable in TF32, and
-// A*B ~= A_lo*B_hi + A_hi*B_lo + A_hi*B_hi.  The split operands live in a scratch area; the
-// producer alternates between the hi and lo tensor maps so the three products of each k-slab
-// land in the same accumulator.  Tensor-core accumulation does not round to nearest, so a long
+// A*B ~= A_lo*B_hi + A_hi*B_lo + A_hi*B_hi.  The split operands live in a scratch area; every
+// pipeline slot holds the hi and lo slabs of both operands, loaded once, and the issuer runs
+// the three products of the slab from them into the same accumulator.  Tensor-core accumulation does not round to nearest, so a long
 // contraction is cut into windows: every window accumulates in tensor memory, and the
 // epilogue warps add the windows together in registers with ordinary float32 adds.
 //
@@ -46,8 +46,7 @@ constexpr unsigned long long kWaitLimitNs = 4000000000ull;  // 4 s
 
 struct TcParams {
   int64_t M, N;
-  int num_k_blocks;   // slabs per tile, counting the three passes of a split product
-  int k_phases;       // 1, or 3 for split float32 operands
+  int num_k_blocks;   // k-slabs per tile
   int chunk_kb;       // slabs per accumulation window (== num_k_blocks when not windowed)
   int tiles_m, tiles_n;
   int64_t total_tiles;
@@ -394,8 +393,11 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap mapA_hi, const __grid_constan
   // data the 32-byte-unit swizzle with 4-row k groups.  One MMA consumes UMMA_K 128-byte k-rows.
   constexpr uint32_t MN_SBO = kTf32 ? 512u : 1024u;
   constexpr uint32_t MN_MODE = kTf32 ? 1u : 2u;
+  // A pipeline slot: [A (hi) | A lo] [B (hi) | B lo]; the lo slabs exist for float32 only.
+  constexpr int PARTS = kTf32 ? 2 : 1;
   constexpr uint32_t A_BYTES = BM * 128, B_PART_BYTES = BN_LOCAL * 128, B_BYTES = kNSplit * B_PART_BYTES,
-                     STAGE_BYTES = A_BYTES + B_BYTES;
+                     STAGE_BYTES = PARTS * (A_BYTES + B_BYTES);
+  constexpr uint32_t STG_BYTES_PER_WARP = kWindowed ? 4096u : 8192u;   // store staging: one or two buffers
   constexpr int TMEM_COLS = (2 * kBN <= 32) ? 32 : 2 * kBN;
   constexpr int COL_SPLIT = kEpiWarps / 4;   // epilogue warps sharing one lane quarter
   constexpr int COLS_PER_THREAD = TILE_N / COL_SPLIT;
@@ -475,35 +477,37 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap mapA_hi, const __grid_constan
             ok = false;
             break;
           }
-          const int phase = (p.k_phases == 3) ? kb % 3 : 2;
-          const int kc = ((p.k_phases == 3) ? kb / 3 : kb) * BK;
-          // pass 0: A_lo*B_hi, pass 1: A_hi*B_lo, pass 2: A_hi*B_hi
-          const CUtensorMap* ma = (phase == 0) ? &mapA_lo : &mapA_hi;
-          const CUtensorMap* mb = (phase == 1) ? &mapB_lo : &mapB_hi;
+          const int kc = kb * BK;
           const uint32_t full = full_leader + 8 * s;
-          const uint32_t sa = smem_base + s * STAGE_BYTES, sb = sa + A_BYTES;
+          const uint32_t stage = smem_base + s * STAGE_BYTES;
           if (p.debug & 8) {  // timing experiment: no copies
             if (rank == 0) mbar_expect_tx(bar_full + 8 * s, 0);
             if (++s == kStages) { s = 0; ph ^= 1; }
             continue;
           }
           if (rank == 0) mbar_expect_tx(bar_full + 8 * s, STAGE_BYTES * kCta);
-          if (!p.a_mn_major) {
-            tma_load_3d<kCta>(sa, ma, full, kc, m0, mat);
-          } else {
 #pragma unroll
-            for (int c = 0; c < BM / CH; c++) tma_load_3d<kCta>(sa + c * (BK * 128), ma, full, m0 + c * CH, kc, mat);
-          }
-#pragma unroll
-          for (int h = 0; h < kNSplit; h++) {
-            const uint32_t sbh = sb + h * B_PART_BYTES;
-            const int n0h = n0 + h * kBN;
-            if (!p.b_mn_major) {
-              tma_load_3d<kCta>(sbh, mb, full, kc, n0h, mat);
+          for (int part = 0; part < PARTS; part++) {   // 0: the operand itself (hi), 1: its lo half
+            const CUtensorMap* ma = part ? &mapA_lo : &mapA_hi;
+            const CUtensorMap* mb = part ? &mapB_lo : &mapB_hi;
+            const uint32_t sa = stage + part * A_BYTES, sb = stage + PARTS * A_BYTES + part * B_BYTES;
+            if (!p.a_mn_major) {
+              tma_load_3d<kCta>(sa, ma, full, kc, m0, mat);
             } else {
 #pragma unroll
-              for (int c = 0; c < BN_LOCAL / CH; c++)
-                tma_load_3d<kCta>(sbh + c * (BK * 128), mb, full, n0h + c * CH, kc, mat);
+              for (int c = 0; c < BM / CH; c++) tma_load_3d<kCta>(sa + c * (BK * 128), ma, full, m0 + c * CH, kc, mat);
+            }
+#pragma unroll
+            for (int h = 0; h < kNSplit; h++) {
+              const uint32_t sbh = sb + h * B_PART_BYTES;
+              const int n0h = n0 + h * kBN;
+              if (!p.b_mn_major) {
+                tma_load_3d<kCta>(sbh, mb, full, kc, n0h, mat);
+              } else {
+#pragma unroll
+                for (int c = 0; c < BN_LOCAL / CH; c++)
+                  tma_load_3d<kCta>(sbh + c * (BK * 128), mb, full, n0h + c * CH, kc, mat);
+              }
             }
           }
           if (++s == kStages) { s = 0; ph ^= 1; }
@@ -557,17 +561,25 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap mapA_hi, const __grid_constan
             break;
           }
           tc_fence_after();
-          const uint32_t sa = smem_base + s * STAGE_BYTES, sb = sa + A_BYTES;
-          const uint64_t adesc = make_smem_desc(sa, a_lbo, a_sbo, a_mode);
+          const uint32_t stage = smem_base + s * STAGE_BYTES;
+          // float16: one product per slab.  float32: A_lo*B_hi, A_hi*B_lo, A_hi*B_hi - the two
+          // small products first, all into the same accumulator.
+          constexpr int PRODUCTS = kTf32 ? 3 : 1;
 #pragma unroll
-          for (int h = 0; h < kNSplit; h++) {
-            const uint64_t bdesc = make_smem_desc(sb + h * B_PART_BYTES, b_lbo, b_sbo, b_mode);
-            const uint32_t d = tmem_base + (kNSplit == 2 ? h : slot) * kBN;
+          for (int pr = 0; pr < PRODUCTS; pr++) {
+            const int a_part = (kTf32 && pr == 0) ? 1 : 0, b_part = (kTf32 && pr == 1) ? 1 : 0;
+            const uint32_t sa = stage + a_part * A_BYTES, sb = stage + PARTS * A_BYTES + b_part * B_BYTES;
+            const uint64_t adesc = make_smem_desc(sa, a_lbo, a_sbo, a_mode);
 #pragma unroll
-            for (int k = 0; k < BK / UMMA_K; k++) {
-              if (p.debug & 16) break;  // timing experiment: no MMAs
-              tc_mma<kTf32, kCta>(d, adesc + (uint64_t)((k * a_kstep) >> 4), bdesc + (uint64_t)((k * b_kstep) >> 4),
-                                  idesc, (in_win | k) ? 1u : 0u);
+            for (int h = 0; h < kNSplit; h++) {
+              const uint64_t bdesc = make_smem_desc(sb + h * B_PART_BYTES, b_lbo, b_sbo, b_mode);
+              const uint32_t d = tmem_base + (kNSplit == 2 ? h : slot) * kBN;
+#pragma unroll
+              for (int k = 0; k < BK / UMMA_K; k++) {
+                if (p.debug & 16) break;  // timing experiment: no MMAs
+                tc_mma<kTf32, kCta>(d, adesc + (uint64_t)((k * a_kstep) >> 4), bdesc + (uint64_t)((k * b_kstep) >> 4),
+                                    idesc, (in_win | pr | k) ? 1u : 0u);
+              }
             }
           }
           tc_commit<kCta>(bar_empty + 8 * s);
@@ -590,8 +602,9 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap mapA_hi, const __grid_constan
     const uint32_t lane_base = (uint32_t)(quarter * 32) << 16;
     // Buffers are handed back to the leader's MMA issuer.
     const uint32_t tempty_leader = (kCta == 2) ? map_to_cta(bar_tempty, 0) : bar_tempty;
-    // Staging for TMA stores: two 4 KB buffers per epilogue warp behind the operand ring.
-    const uint32_t stg_base = smem_base + kStages * STAGE_BYTES + (uint32_t)ew * 8192u;
+    // Staging for TMA stores behind the operand ring: per epilogue warp two 4 KB buffers, or one
+    // for the windowed epilogue (which stores once per tile).
+    const uint32_t stg_base = smem_base + kStages * STAGE_BYTES + (uint32_t)ew * STG_BYTES_PER_WARP;
     const bool store_leader = elect_one();
     uint32_t win = 0;
     bool ok = true;
@@ -714,34 +727,23 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap mapA_hi, const __grid_constan
           win++;
         }
         if (ok && p.tma_store) {
-          // Same staging as above, fed from the register accumulators: 2 x 32 columns per pass.
+          // Same staging as above, fed from the register accumulators: one buffer, 32 columns per pass.
           const int m_warp = t.tm * (BM * kCta) + (int)rank * BM + quarter * 32;
           const uint32_t row_addr = stg_base + (uint32_t)lane * 128u;
           const uint32_t sw = (uint32_t)(lane & 7);
 #pragma unroll
-          for (int c = 0; c < COLS_PER_THREAD; c += 64) {
+          for (int c = 0; c < COLS_PER_THREAD; c += 32) {
             if (store_leader) bulk_wait_read<0>();
             __syncwarp();
 #pragma unroll
-            for (int l = 0; l < 2; l++) {
-              const uint32_t buf = row_addr + (uint32_t)l * 4096u;
-#pragma unroll
-              for (int q = 0; q < 8; q++)
-                st_shared_v4(buf + (((uint32_t)q ^ sw) << 4), __float_as_uint(acc[c + 32 * l + q * 4]),
-                             __float_as_uint(acc[c + 32 * l + q * 4 + 1]), __float_as_uint(acc[c + 32 * l + q * 4 + 2]),
-                             __float_as_uint(acc[c + 32 * l + q * 4 + 3]));
-            }
+            for (int q = 0; q < 8; q++)
+              st_shared_v4(row_addr + (((uint32_t)q ^ sw) << 4), __float_as_uint(acc[c + q * 4]),
+                           __float_as_uint(acc[c + q * 4 + 1]), __float_as_uint(acc[c + q * 4 + 2]),
+                           __float_as_uint(acc[c + q * 4 + 3]));
             fence_proxy_async_smem();
             __syncwarp();
-            if (store_leader && m_warp < p.M) {
-#pragma unroll
-              for (int b2 = 0; b2 < 2; b2++) {
-                const int64_t col = n0 + c + b2 * 32;
-                if (col < p.N) {
-                  for (int d = 0; d < p.n_out; d++)
-                    tma_store_3d(&mapC.m[d], stg_base + (uint32_t)b2 * 4096u, (int)col, m_warp, (int)t.mat);
-                }
-              }
+            if (store_leader && m_warp < p.M && n0 + c < p.N) {
+              for (int d = 0; d < p.n_out; d++) tma_store_3d(&mapC.m[d], stg_base, (int)(n0 + c), m_warp, (int)t.mat);
               bulk_commit();
             }
           }
@@ -922,9 +924,9 @@ int window_slabs() {
 
 template <int kElemBytes, int kBN, int kStages, int kEpiWarps, bool kWindowed, int kCta, int kNSplit = 1>
 struct TcConfig {
-  // operand ring + two 4 KB store-staging buffers per epilogue warp + alignment slack
-  static constexpr size_t smem =
-      (size_t)kStages * (BM * 128 + kNSplit * (kBN / kCta) * 128) + (size_t)kEpiWarps * 8192 + 1024;
+  // operand ring (float32 slots also hold the lo slabs) + store staging + alignment slack
+  static constexpr size_t smem = (size_t)kStages * (kElemBytes == 4 ? 2 : 1) * (BM * 128 + kNSplit * (kBN / kCta) * 128) +
+                                 (size_t)kEpiWarps * (kWindowed ? 4096 : 8192) + 1024;
   static_assert(smem <= 232448, "more shared memory than one CTA can have on sm_100");
   static constexpr int block = 64 + 32 * kEpiWarps;
   static auto kernel() { return tc_gemm_kernel<kElemBytes, kBN, kStages, kEpiWarps, kWindowed, kCta, kNSplit>; }
@@ -1086,12 +1088,11 @@ cudaError_t launch_tc(const GemmProblem& p, cudaStream_t stream, unsigned int* s
   TcParams tp;
   tp.M = p.M; tp.N = p.N;
   const int kslabs = (int)((p.K + BK - 1) / BK);
-  tp.k_phases = f32 ? 3 : 1;
-  tp.num_k_blocks = kslabs * tp.k_phases;
+  tp.num_k_blocks = kslabs;
   // float32: a window bounds the number of truncating tensor-core accumulations that feed one
   // correctly rounded float32 add in the epilogue.
   const bool windowed = f32 && !(dbg & 2);
-  tp.chunk_kb = windowed ? 3 * window_slabs() : tp.num_k_blocks;
+  tp.chunk_kb = windowed ? window_slabs() : tp.num_k_blocks;
   if (tp.chunk_kb > tp.num_k_blocks) tp.chunk_kb = tp.num_k_blocks;
   // Wide tiles (256 x 512 per CTA pair) for long float16 contractions over wide products.
   const int wide_min_kb = env_int("HC_TC_WIDE_MIN_KB", 48);
@@ -1137,13 +1138,13 @@ cudaError_t launch_tc(const GemmProblem& p, cudaStream_t stream, unsigned int* s
     return TcConfig<2, 128, 6, 4, false, 1>::launch(maps, outs, tp, sm_count, stream, rec);
   }
   if (windowed) {
-    if (cta == 2) return TcConfig<4, 256, 5, 8, true, 2>::launch(maps, outs, tp, sm_count, stream, rec);
-    if (bn == 256) return TcConfig<4, 256, 3, 8, true, 1>::launch(maps, outs, tp, sm_count, stream, rec);
-    return TcConfig<4, 128, 6, 4, true, 1>::launch(maps, outs, tp, sm_count, stream, rec);
+    if (cta == 2) return TcConfig<4, 256, 3, 8, true, 2>::launch(maps, outs, tp, sm_count, stream, rec);
+    if (bn == 256) return TcConfig<4, 256, 2, 8, true, 1>::launch(maps, outs, tp, sm_count, stream, rec);
+    return TcConfig<4, 128, 3, 4, true, 1>::launch(maps, outs, tp, sm_count, stream, rec);
   }
-  if (cta == 2) return TcConfig<4, 256, 6, 4, false, 2>::launch(maps, outs, tp, sm_count, stream, rec);
-  if (bn == 256) return TcConfig<4, 256, 4, 4, false, 1>::launch(maps, outs, tp, sm_count, stream, rec);
-  return TcConfig<4, 128, 6, 4, false, 1>::launch(maps, outs, tp, sm_count, stream, rec);
+  if (cta == 2) return TcConfig<4, 256, 3, 4, false, 2>::launch(maps, outs, tp, sm_count, stream, rec);
+  if (bn == 256) return TcConfig<4, 256, 2, 4, false, 1>::launch(maps, outs, tp, sm_count, stream, rec);
+  return TcConfig<4, 128, 3, 4, false, 1>::launch(maps, outs, tp, sm_count, stream, rec);
 }
 
 }  // namespace hc
