@@ -810,28 +810,54 @@ __global__ void wait_probe_kernel(unsigned int* status, unsigned long long limit
 // Splits float32 into two TF32-representable parts: hi = nearest TF32 of x, lo = nearest TF32
 // of (x - hi).  x - hi is exact in float32.  Non-finite x: hi = x, lo = 0, so infinities and
 // NaNs propagate through the hi*hi product only.
-__global__ void split_tf32_kernel(const float* __restrict__ src, float* __restrict__ hi, float* __restrict__ lo,
-                                  int64_t rows, int64_t width, int64_t ld_src, int64_t ld_dst, int64_t stride_src,
-                                  int64_t stride_dst, int64_t batch) {
-  const int64_t total = batch * rows * width;
-  for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
-    const int64_t c = i % width, r = (i / width) % rows, b = i / (width * rows);
-    const float x = src[b * stride_src + r * ld_src + c];
-    uint32_t hbits;
-    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(hbits) : "f"(x));
-    float h = __uint_as_float(hbits & 0xFFFFE000u);
-    float l = 0.0f;
-    if (isfinite(x)) {
-      if (!isfinite(h)) h = __uint_as_float(__float_as_uint(x) & 0xFFFFE000u);
-      const float d = x - h;
-      uint32_t lbits;
-      asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(lbits) : "f"(d));
-      l = __uint_as_float(lbits & 0xFFFFE000u);
-    } else {
-      h = x;
+struct SplitJob {
+  const float* src;
+  float *hi, *lo;
+  int64_t rows, width, ld_src, ld_dst, stride_src, stride_dst, batch;
+  int vec4;   // rows, pitches and bases allow 16-byte accesses
+};
+
+__device__ __forceinline__ void split_one(float x, float& h, float& l) {
+  uint32_t hbits;
+  asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(hbits) : "f"(x));
+  h = __uint_as_float(hbits & 0xFFFFE000u);
+  l = 0.0f;
+  if (isfinite(x)) {
+    if (!isfinite(h)) h = __uint_as_float(__float_as_uint(x) & 0xFFFFE000u);
+    const float d = x - h;
+    uint32_t lbits;
+    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(lbits) : "f"(d));
+    l = __uint_as_float(lbits & 0xFFFFE000u);
+  } else {
+    h = x;
+  }
+}
+
+// One launch splits both operands: the first `blocks_a` blocks work on A, the rest on B.
+__global__ void __launch_bounds__(256) split_tf32_kernel(const SplitJob ja, const SplitJob jb, int blocks_a) {
+  const bool is_a = (int)blockIdx.x < blocks_a;
+  const SplitJob& j = is_a ? ja : jb;
+  const int64_t bid = is_a ? blockIdx.x : blockIdx.x - blocks_a;
+  const int64_t nblk = is_a ? blocks_a : (int64_t)gridDim.x - blocks_a;
+  if (j.vec4) {
+    const int64_t w4 = j.width / 4, total = j.batch * j.rows * w4;
+    for (int64_t i = bid * blockDim.x + threadIdx.x; i < total; i += nblk * blockDim.x) {
+      const int64_t c = (i % w4) * 4, r = (i / w4) % j.rows, b = i / (w4 * j.rows);
+      const float4 x = *(const float4*)(j.src + b * j.stride_src + r * j.ld_src + c);
+      float4 h, l;
+      split_one(x.x, h.x, l.x); split_one(x.y, h.y, l.y); split_one(x.z, h.z, l.z); split_one(x.w, h.w, l.w);
+      *(float4*)(j.hi + b * j.stride_dst + r * j.ld_dst + c) = h;
+      *(float4*)(j.lo + b * j.stride_dst + r * j.ld_dst + c) = l;
     }
-    hi[b * stride_dst + r * ld_dst + c] = h;
-    lo[b * stride_dst + r * ld_dst + c] = l;
+  } else {
+    const int64_t total = j.batch * j.rows * j.width;
+    for (int64_t i = bid * blockDim.x + threadIdx.x; i < total; i += nblk * blockDim.x) {
+      const int64_t c = i % j.width, r = (i / j.width) % j.rows, b = i / (j.width * j.rows);
+      float h, l;
+      split_one(j.src[b * j.stride_src + r * j.ld_src + c], h, l);
+      j.hi[b * j.stride_dst + r * j.ld_dst + c] = h;
+      j.lo[b * j.stride_dst + r * j.ld_dst + c] = l;
+    }
   }
 }
 
@@ -1057,14 +1083,23 @@ cudaError_t launch_tc(const GemmProblem& p, cudaStream_t stream, unsigned int* s
     float* ah = base; float* al = (float*)((char*)ah + s.a_bytes);
     float* bh = (float*)((char*)al + s.a_bytes); float* bl = (float*)((char*)bh + s.b_bytes);
     const int threads = 256;
-    auto blocks = [&](int64_t n) { int64_t b = (n + threads - 1) / threads; return (int)(b > 148 * 16 ? 148 * 16 : (b < 1 ? 1 : b)); };
-    split_tf32_kernel<<<blocks(p.batch * s.a_rows * s.a_width), threads, 0, stream>>>(
-        (const float*)p.A, ah, al, s.a_rows, s.a_width, p.lda, s.a_ld, p.strideA, s.a_mat, p.batch);
-    split_tf32_kernel<<<blocks(p.batch * s.b_rows * s.b_width), threads, 0, stream>>>(
-        (const float*)p.B, bh, bl, s.b_rows, s.b_width, p.ldb, s.b_ld, p.strideB, s.b_mat, p.batch);
+    auto vec_ok4 = [](const void* src, int64_t width, int64_t ld, int64_t stride, int64_t batch) {
+      return (int)(width % 4 == 0 && ld % 4 == 0 && ((uintptr_t)src & 15) == 0 && (batch == 1 || stride % 4 == 0));
+    };
+    SplitJob ja{(const float*)p.A, ah, al, s.a_rows, s.a_width, p.lda, s.a_ld, p.strideA, s.a_mat, p.batch,
+                vec_ok4(p.A, s.a_width, p.lda, p.strideA, p.batch)};
+    SplitJob jb{(const float*)p.B, bh, bl, s.b_rows, s.b_width, p.ldb, s.b_ld, p.strideB, s.b_mat, p.batch,
+                vec_ok4(p.B, s.b_width, p.ldb, p.strideB, p.batch)};
+    auto blocks = [&](const SplitJob& j) {
+      const int64_t work = j.batch * j.rows * (j.vec4 ? j.width / 4 : j.width);
+      int64_t b = (work + threads - 1) / threads;
+      return (int)(b > 148 * 8 ? 148 * 8 : (b < 1 ? 1 : b));
+    };
+    const int blocks_a = blocks(ja), blocks_b = blocks(jb);
+    split_tf32_kernel<<<blocks_a + blocks_b, threads, 0, stream>>>(ja, jb, blocks_a);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return e;
-    if (rec) { rec->launches += 2; rec->scratch_bytes = 2 * s.a_bytes + 2 * s.b_bytes; }
+    if (rec) { rec->launches += 1; rec->scratch_bytes = 2 * s.a_bytes + 2 * s.b_bytes; }
     a_hi = ah; a_lo = al; b_hi = bh; b_lo = bl;
     lda = s.a_ld; ldb = s.b_ld; sa = s.a_mat; sb = s.b_mat;
   }
@@ -1072,7 +1107,11 @@ cudaError_t launch_tc(const GemmProblem& p, cudaStream_t stream, unsigned int* s
   // Tile shape: 256 columns unless the product is narrow; CTA pairs (256 rows) when there is
   // more than one 128-row block of output.
   const int dbg = debug_flags();
-  const int bn = (p.N > 128) ? 256 : 128;
+  // ... and 128 x 128 single-CTA tiles when 256 x 256 pairs would leave more than half of the
+  // SMs without a tile.
+  const int64_t pair_tiles = ((p.M + 255) / 256) * ((p.N + 255) / 256) * p.batch;
+  const bool few_tiles = pair_tiles * 4 <= sm_count;
+  const int bn = (p.N > 128 && !few_tiles) ? 256 : 128;
   const int cta = (p.M > BM && bn == 256 && !(dbg & 4)) ? 2 : 1;
   const int b_box = bn / cta;
   CUtensorMap maps[4];
