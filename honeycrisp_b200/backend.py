@@ -350,8 +350,11 @@ class CUDABackend:
 
     def batchedMatmulHost(self, matrixCount: int, a: np.ndarray, transA: bool, b: np.ndarray, transB: bool,
                           transOut: bool, rows: int, inner: int, cols: int, dtype,
-                          out: Optional[np.ndarray] = None) -> np.ndarray:
-        """Host arrays in, host array out: stage, multiply, read back, in one library call."""
+                          out: Optional[np.ndarray] = None, asynchronous: bool = False) -> np.ndarray:
+        """Host arrays in, host array out: stage, multiply, read back, in one library call.
+
+        With `asynchronous`, the call only enqueues (copy-in, product and copy-out overlap with
+        the neighbouring calls' stages); `out` is valid after hostSync()."""
         dt = _as_dtype(dtype)
         if dt not in _HC_DTYPE:
             raise NotImplementedByBackend(f"matmul for dtype {dt.value}")
@@ -363,8 +366,12 @@ class CUDABackend:
             out = np.empty(matrixCount * rows * cols, dtype=dt.numpy)
         elif out.dtype != dt.numpy or out.size < matrixCount * rows * cols or not out.flags.c_contiguous:
             raise ValueError("bad host output array")
-        st = L.load().hc_batched_matmul_host(self._ctx, _HC_DTYPE[dt], int(matrixCount), a.ctypes.data,
-                                             int(bool(transA)), b.ctypes.data, int(bool(transB)),
-                                             int(bool(transOut)), int(rows), int(inner), int(cols), out.ctypes.data)
+        fn = L.load().hc_batched_matmul_host_async if asynchronous else L.load().hc_batched_matmul_host
+        st = fn(self._ctx, _HC_DTYPE[dt], int(matrixCount), a.ctypes.data, int(bool(transA)), b.ctypes.data,
+                int(bool(transB)), int(bool(transOut)), int(rows), int(inner), int(cols), out.ctypes.data)
         self._check(st)
         return out
+
+    def hostSync(self):
+        """Wait for every asynchronous host-buffer product enqueued so far."""
+        self._check(L.load().hc_host_sync(self._ctx))

@@ -25,6 +25,16 @@ struct hc_ctx {
   // Device staging buffers of the host-buffer entry point.
   void* stage[3] = {nullptr, nullptr, nullptr};
   size_t stage_bytes[3] = {0, 0, 0};
+  // Pipelined host-buffer products: two slots of staging buffers, copy streams in both
+  // directions, and the events that chain copy-in -> product -> copy-out.
+  struct HostSlot {
+    void* buf[3] = {nullptr, nullptr, nullptr};
+    size_t bytes[3] = {0, 0, 0};
+    cudaEvent_t in_done = nullptr, product_done = nullptr, out_done = nullptr;
+    bool busy = false;
+  } slot[2];
+  cudaStream_t in_stream = nullptr, out_stream = nullptr;
+  int next_slot = 0;
 };
 
 struct hc_event {
@@ -255,6 +265,16 @@ void hc_destroy(hc_ctx* ctx) {
   if (ctx->scratch) cudaFree(ctx->scratch);
   for (int i = 0; i < 3; i++)
     if (ctx->stage[i]) cudaFree(ctx->stage[i]);
+  for (auto& sl : ctx->slot) {
+    if (sl.out_done) cudaEventSynchronize(sl.out_done);
+    for (int i = 0; i < 3; i++)
+      if (sl.buf[i]) cudaFree(sl.buf[i]);
+    if (sl.in_done) cudaEventDestroy(sl.in_done);
+    if (sl.product_done) cudaEventDestroy(sl.product_done);
+    if (sl.out_done) cudaEventDestroy(sl.out_done);
+  }
+  if (ctx->in_stream) cudaStreamDestroy(ctx->in_stream);
+  if (ctx->out_stream) cudaStreamDestroy(ctx->out_stream);
   cudaFree(ctx->status_word);
   cudaStreamDestroy(ctx->own_stream);
   cudaGetLastError();
@@ -541,6 +561,79 @@ hc_status hc_batched_matmul_host(hc_ctx* ctx, hc_dtype dtype, int64_t matrix_cou
   if (s != HC_OK) return s;
   if (bytes[2]) HC_CUDA_TRY(ctx, cudaMemcpyAsync(out_host, ctx->stage[2], bytes[2], cudaMemcpyDeviceToHost, ctx->stream));
   HC_CUDA_TRY(ctx, cudaStreamSynchronize(ctx->stream));
+  return HC_OK;
+}
+
+hc_status hc_batched_matmul_host_async(hc_ctx* ctx, hc_dtype dtype, int64_t matrix_count, const void* a_host,
+                                       int trans_a, const void* b_host, int trans_b, int trans_out, int64_t rows,
+                                       int64_t inner, int64_t cols, void* out_host) {
+  if (!ctx) return HC_ERR_INVALID_ARGUMENT;
+  std::lock_guard<std::mutex> lock(ctx->mu);
+  DeviceGuard g(ctx->device);
+  if (dtype != HC_F16 && dtype != HC_F32)
+    return fail(ctx, HC_ERR_NOT_IMPLEMENTED, "matmul: only float16 and float32 are implemented");
+  if (matrix_count < 0 || rows < 0 || inner < 0 || cols < 0)
+    return fail(ctx, HC_ERR_INVALID_ARGUMENT, "negative dimension");
+  const size_t eb = dtype == HC_F16 ? 2 : 4;
+  const size_t bytes[3] = {(size_t)(matrix_count * rows * inner) * eb, (size_t)(matrix_count * inner * cols) * eb,
+                           (size_t)(matrix_count * rows * cols) * eb};
+  if ((bytes[0] && !a_host) || (bytes[1] && !b_host) || (bytes[2] && !out_host))
+    return fail(ctx, HC_ERR_INVALID_ARGUMENT, "null operand");
+  if (!ctx->in_stream) {
+    HC_CUDA_TRY(ctx, cudaStreamCreateWithFlags(&ctx->in_stream, cudaStreamNonBlocking));
+    HC_CUDA_TRY(ctx, cudaStreamCreateWithFlags(&ctx->out_stream, cudaStreamNonBlocking));
+  }
+  hc_ctx::HostSlot& sl = ctx->slot[ctx->next_slot];
+  ctx->next_slot ^= 1;
+  if (!sl.in_done) {
+    HC_CUDA_TRY(ctx, cudaEventCreateWithFlags(&sl.in_done, cudaEventDisableTiming));
+    HC_CUDA_TRY(ctx, cudaEventCreateWithFlags(&sl.product_done, cudaEventDisableTiming));
+    HC_CUDA_TRY(ctx, cudaEventCreateWithFlags(&sl.out_done, cudaEventDisableTiming));
+  }
+  // The slot's previous product (two calls ago) must have left its buffers.
+  if (sl.busy) HC_CUDA_TRY(ctx, cudaEventSynchronize(sl.out_done));
+  sl.busy = false;
+  for (int i = 0; i < 3; i++) {
+    if (bytes[i] > sl.bytes[i] || !sl.buf[i]) {
+      if (sl.buf[i]) HC_CUDA_TRY(ctx, cudaFree(sl.buf[i]));
+      sl.buf[i] = nullptr;
+      sl.bytes[i] = 0;
+      cudaError_t e = cudaMalloc(&sl.buf[i], bytes[i] ? bytes[i] : 1);
+      if (e != cudaSuccess) {
+        sl.buf[i] = nullptr;
+        cudaGetLastError();
+        return fail(ctx, HC_ERR_ALLOCATION_FAILED, "staging allocation failed");
+      }
+      sl.bytes[i] = bytes[i] ? bytes[i] : 1;
+    }
+  }
+  if (bytes[0]) HC_CUDA_TRY(ctx, cudaMemcpyAsync(sl.buf[0], a_host, bytes[0], cudaMemcpyHostToDevice, ctx->in_stream));
+  if (bytes[1]) HC_CUDA_TRY(ctx, cudaMemcpyAsync(sl.buf[1], b_host, bytes[1], cudaMemcpyHostToDevice, ctx->in_stream));
+  HC_CUDA_TRY(ctx, cudaEventRecord(sl.in_done, ctx->in_stream));
+  HC_CUDA_TRY(ctx, cudaStreamWaitEvent(ctx->stream, sl.in_done, 0));
+  hc::GemmProblem p;
+  hc_status s = build_problem(ctx, dtype, matrix_count, sl.buf[0], trans_a, sl.buf[1], trans_b, trans_out, rows, inner,
+                              cols, 0, cols, sl.buf[2], &p);
+  if (s != HC_OK) return s;
+  s = run_problem(ctx, HC_KERNEL_AUTO, p, flop_count(matrix_count, rows, inner, cols));
+  if (s != HC_OK) return s;
+  HC_CUDA_TRY(ctx, cudaEventRecord(sl.product_done, ctx->stream));
+  HC_CUDA_TRY(ctx, cudaStreamWaitEvent(ctx->out_stream, sl.product_done, 0));
+  if (bytes[2])
+    HC_CUDA_TRY(ctx, cudaMemcpyAsync(out_host, sl.buf[2], bytes[2], cudaMemcpyDeviceToHost, ctx->out_stream));
+  HC_CUDA_TRY(ctx, cudaEventRecord(sl.out_done, ctx->out_stream));
+  sl.busy = true;
+  return HC_OK;
+}
+
+hc_status hc_host_sync(hc_ctx* ctx) {
+  if (!ctx) return HC_ERR_INVALID_ARGUMENT;
+  std::lock_guard<std::mutex> lock(ctx->mu);
+  DeviceGuard g(ctx->device);
+  for (auto& sl : ctx->slot) {
+    if (sl.busy) HC_CUDA_TRY(ctx, cudaEventSynchronize(sl.out_done));
+    sl.busy = false;
+  }
   return HC_OK;
 }
 

@@ -147,6 +147,18 @@ hc_status hc_batched_matmul_host(hc_ctx* ctx, hc_dtype dtype, int64_t matrix_cou
                                  int trans_b, int trans_out, int64_t rows, int64_t inner,
                                  int64_t cols, void* out_host);
 
+/* The same, pipelined: the call enqueues copy-in, product and copy-out on three streams and
+ * returns; up to two products are in flight, so the copy-in of one overlaps the product and the
+ * copy-out of the one before (host links are full duplex).  `out_host` is valid after hc_host_sync
+ * (or after two further _async calls).  Use pinned host memory; pageable memory serialises the
+ * copies.  This is the asynchronous form the reference's backends have by construction: a
+ * product returns a Tensor whose data is awaited later (Sources/Honeycrisp/Tensor.swift:618-621). */
+hc_status hc_batched_matmul_host_async(hc_ctx* ctx, hc_dtype dtype, int64_t matrix_count,
+                                       const void* a_host, int trans_a, const void* b_host,
+                                       int trans_b, int trans_out, int64_t rows, int64_t inner,
+                                       int64_t cols, void* out_host);
+hc_status hc_host_sync(hc_ctx* ctx);
+
 /* One column block of a product, for splitting a large GEMM over devices: computes columns
  * [col_begin, col_begin+col_count) of op(a)*op(b) (of its transpose's rows when trans_out) and
  * writes them in place into the FULL-size `out`.  `b` is the full operand; only the block's

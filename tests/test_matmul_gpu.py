@@ -252,3 +252,23 @@ def test_bounded_wait_expires_and_context_stays_usable(be):
     res, a_st, b_st = run(be, 1, A, B, False, True, False, np.float16, kernel=K().HC_KERNEL_TENSOR)
     f64 = ref.batched_matmul_f64(1, a_st, False, b_st, True, False, 256, 128, 256)
     assert ref.rel_frobenius(res, f64) < 2e-3
+
+
+def test_pipelined_host_products_equal_the_blocking_form(be):
+    """Five products in flight through the two-slot pipeline, different shapes and dtypes; each
+    result equals the blocking host call bit for bit."""
+    cases = [(np.float16, 2, 96, 160, 72, False, True), (np.float32, 1, 256, 128, 384, False, False),
+             (np.float16, 1, 384, 256, 512, True, False), (np.float16, 3, 64, 64, 64, True, True),
+             (np.float32, 1, 130, 67, 129, False, False)]
+    want, outs, keep = [], [], []
+    for i, (dt, cnt, M, Kd, N, ta, tb) in enumerate(cases):
+        A, B = random_operands(20 + i, cnt, M, Kd, N, dt)
+        a_st, b_st = stored(A, ta), stored(B, tb)
+        keep.append((a_st, b_st))
+        want.append(be.batchedMatmulHost(cnt, a_st, ta, b_st, tb, False, M, Kd, N, dt).copy())
+    for (dt, cnt, M, Kd, N, ta, tb), (a_st, b_st) in zip(cases, keep):
+        outs.append(be.batchedMatmulHost(cnt, a_st, ta, b_st, tb, False, M, Kd, N, dt, asynchronous=True))
+    be.hostSync()
+    be.checkDeviceStatus()
+    for w, o in zip(want, outs):
+        assert np.array_equal(w.view(np.uint8), o.view(np.uint8))
