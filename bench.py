@@ -406,7 +406,22 @@ def other_configs(be, stream, rank, world):
 
     ms = timed(triple, 5)
     res["c4_f16_linear_triple"] = {"ms": ms, "tflops": 3 * 2 * 16384 * 16384 * 4096 / ms / 1e9}
-    del x, w, dy, y, dx, dw
+    del w, y, dx, dw
+    # The same work as Honeycrisp's Linear issues it (weight [in,out]; forward with the bias add
+    # fused into the epilogue; backward dX = dY.W^T, dW = X^T.dY, db = column sum of dY).
+    from honeycrisp_b200 import Linear
+    layer = Linear(be, 4096, 16384, dtype=np.float16, seed=3)
+
+    def layer_step():
+        layer.weightGrad = None
+        layer.biasGrad = None
+        layer(x, (16384, 4096))
+        layer.backward(x, (16384, 4096), dy)
+
+    ms = timed(layer_step, 5)
+    res["linear_layer_fwd_bwd_f16"] = {"ms": ms, "tflops": 3 * 2 * 16384 * 16384 * 4096 / ms / 1e9,
+                                       "includes": "fused bias add, bias-gradient column sum"}
+    del x, dy, layer
     a = torch.rand((16384, 16384), generator=g, device="cuda") * 2 - 1
     b = torch.rand((16384, 16384), generator=g, device="cuda") * 2 - 1
     o = torch.empty((16384, 16384), device="cuda"); od = be.wrap(o.data_ptr(), o.numel() * 4, o)

@@ -62,6 +62,10 @@ SIGNATURES = {
     "hc_batched_matmul_host_async": (_int, [_vp, _int, _i64, _vp, _int, _vp, _int, _int, _i64, _i64, _i64, _vp]),
     "hc_host_sync": (_int, [_vp]),
     "hc_matmul_colblock": (_int, [_vp, _int, _int, _vp, _int, _vp, _int, _int, _i64, _i64, _i64, _i64, _i64, _vp]),
+    "hc_linear_forward": (_int, [_vp, _int, _vp, _vp, _vp, _i64, _i64, _i64, _vp]),
+    "hc_column_sum": (_int, [_vp, _int, _vp, _i64, _i64, _vp]),
+    "hc_cast": (_int, [_vp, _int, _int, _vp, _i64, _vp]),
+    "hc_add": (_int, [_vp, _int, _vp, _vp, _i64, _vp]),
     "hc_matmul_colblock_push": (_int, [_vp, _int, _vp, _int, _vp, _int, _int, _i64, _i64, _i64, _i64, _i64, _vp,
                                       ctypes.POINTER(_vp), _int]),
     "hc_shared_alloc": (_int, [_vp, _sz, ctypes.POINTER(_vp)]),

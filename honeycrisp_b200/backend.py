@@ -372,6 +372,57 @@ class CUDABackend:
         self._check(st)
         return out
 
+    # -- around a Linear layer ---------------------------------------------------------------
+
+    def linearForward(self, x, weight, bias, rows: int, inCount: int, outCount: int, dtype,
+                      out: Optional[CUDAData] = None) -> CUDAData:
+        """x[rows,in] * weight[in,out] + bias[out] with the add fused into the product's epilogue
+        (Linear.callAsFunction, Trainable.swift:530-546).  `bias` may be None."""
+        dt = _as_dtype(dtype)
+        if dt not in _HC_DTYPE:
+            raise NotImplementedByBackend(f"linear for dtype {dt.value}")
+        x_d, w_d = self._device_operand(x, dt), self._device_operand(weight, dt)
+        b_d = self._device_operand(bias, dt) if bias is not None else None
+        if out is None:
+            out = self.allocate(rows * outCount * dt.byteSize)
+        self._check(L.load().hc_linear_forward(self._ctx, _HC_DTYPE[dt], x_d.ptr, w_d.ptr, b_d.ptr if b_d else None,
+                                               int(rows), int(inCount), int(outCount), out.ptr))
+        out._mark()
+        out._inputs = (x_d, w_d, b_d)
+        return out
+
+    def columnSum(self, x, rows: int, cols: int, dtype) -> CUDAData:
+        """Sum over the rows of x[rows,cols] (reduce(.sum) over the leading axis, Backend.swift:524-531)."""
+        dt = _as_dtype(dtype)
+        x_d = self._device_operand(x, dt)
+        out = self.allocate(cols * dt.byteSize)
+        self._check(L.load().hc_column_sum(self._ctx, _HC_DTYPE[dt], x_d.ptr, int(rows), int(cols), out.ptr))
+        out._mark()
+        out._inputs = (x_d,)
+        return out
+
+    def cast(self, x, count: int, inType, outType) -> CUDAData:
+        """Backend.cast (Backend.swift:489-494) between float16 and float32."""
+        di, do = _as_dtype(inType), _as_dtype(outType)
+        if di not in _HC_DTYPE or do not in _HC_DTYPE:
+            raise NotImplementedByBackend(f"cast {di.value} -> {do.value}")
+        x_d = self._device_operand(x, di)
+        out = self.allocate(count * do.byteSize)
+        self._check(L.load().hc_cast(self._ctx, _HC_DTYPE[di], _HC_DTYPE[do], x_d.ptr, int(count), out.ptr))
+        out._mark()
+        out._inputs = (x_d,)
+        return out
+
+    def add(self, a, b, count: int, dtype) -> CUDAData:
+        """binaryOp(.add) on equal shapes (gradient accumulation, Tensor.swift:370-372)."""
+        dt = _as_dtype(dtype)
+        a_d, b_d = self._device_operand(a, dt), self._device_operand(b, dt)
+        out = self.allocate(count * dt.byteSize)
+        self._check(L.load().hc_add(self._ctx, _HC_DTYPE[dt], a_d.ptr, b_d.ptr, int(count), out.ptr))
+        out._mark()
+        out._inputs = (a_d, b_d)
+        return out
+
     def hostSync(self):
         """Wait for every asynchronous host-buffer product enqueued so far."""
         self._check(L.load().hc_host_sync(self._ctx))

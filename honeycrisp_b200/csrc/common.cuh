@@ -27,6 +27,9 @@ struct GemmProblem {
   int a_mn_major, b_mn_major;
   int64_t lda, ldb, ldc;              // leading dimensions, elements
   int64_t strideA, strideB, strideC;  // distance between consecutive matrices, elements
+  // Optional row vector of N elements (same dtype) added to every row of the product after it has
+  // been rounded to the output dtype: the `h + bias` of Linear (Trainable.swift:539-544).
+  const void* bias = nullptr;
 };
 
 // Word in device memory that kernels set when a bounded wait gives up.
@@ -62,6 +65,13 @@ bool tc_supported(const GemmProblem& p);
 cudaError_t launch_wait_probe(cudaStream_t stream, unsigned int* status_word, unsigned long long limit_ns);
 size_t tc_scratch_bytes(const GemmProblem& p);
 
+}  // namespace hc
+
+// Elementwise and reduction helpers around a Linear product (csrc/linear_ops.cu).
+namespace hc {
+cudaError_t launch_column_sum(hc_dtype dtype, const void* x, void* out, int64_t rows, int64_t cols, cudaStream_t stream);
+cudaError_t launch_cast(hc_dtype from, hc_dtype to, const void* x, void* out, int64_t count, cudaStream_t stream);
+cudaError_t launch_add(hc_dtype dtype, const void* a, const void* b, void* out, int64_t count, cudaStream_t stream);
 }  // namespace hc
 
 // Context internals shared between translation units (defined in hc_api.cu).

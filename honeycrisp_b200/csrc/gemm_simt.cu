@@ -30,7 +30,7 @@ template <> __device__ __forceinline__ __half from_float<__half>(float v) { retu
 
 template <typename T, bool EXACT>
 __global__ void __launch_bounds__(THREADS)
-simt_gemm_kernel(const T* __restrict__ A, const T* __restrict__ B, T* __restrict__ C,
+simt_gemm_kernel(const T* __restrict__ A, const T* __restrict__ B, T* __restrict__ C, const T* __restrict__ bias,
                  int64_t M, int64_t N, int64_t K,
                  int64_t a_rs, int64_t a_cs,   // A(m,k) = A[m*a_rs + k*a_cs]
                  int64_t b_rs, int64_t b_cs,   // B(k,n) = B[k*b_rs + n*b_cs]
@@ -113,7 +113,12 @@ simt_gemm_kernel(const T* __restrict__ A, const T* __restrict__ B, T* __restrict
 #pragma unroll
     for (int j = 0; j < TN; j++) {
       int64_t gn = n0 + tx * TN + j;
-      if (gn < N) C[gm * ldc + gn] = from_float<T>(acc[i][j]);
+      if (gn < N) {
+        T r = from_float<T>(acc[i][j]);
+        // Linear's bias: a second operation on the rounded product (widen, add, narrow).
+        if (bias) r = from_float<T>(__fadd_rn(to_float<T>(r), to_float<T>(bias[gn])));
+        C[gm * ldc + gn] = r;
+      }
     }
   }
 }
@@ -138,11 +143,11 @@ cudaError_t launch_typed(const GemmProblem& p, bool exact, cudaStream_t stream, 
     T* C = (T*)p.C + b0 * p.strideC;
     if (exact) {
       simt_gemm_kernel<T, true><<<grid, THREADS, 0, stream>>>(
-          A, B, C, p.M, p.N, p.K, a_rs, a_cs, b_rs, b_cs, p.ldc, p.strideA, p.strideB, p.strideC,
+          A, B, C, (const T*)p.bias, p.M, p.N, p.K, a_rs, a_cs, b_rs, b_cs, p.ldc, p.strideA, p.strideB, p.strideC,
           (int)tiles_n);
     } else {
       simt_gemm_kernel<T, false><<<grid, THREADS, 0, stream>>>(
-          A, B, C, p.M, p.N, p.K, a_rs, a_cs, b_rs, b_cs, p.ldc, p.strideA, p.strideB, p.strideC,
+          A, B, C, (const T*)p.bias, p.M, p.N, p.K, a_rs, a_cs, b_rs, b_cs, p.ldc, p.strideA, p.strideB, p.strideC,
           (int)tiles_n);
     }
     if (rec) { rec->launches++; rec->grid = (int)(tiles_m * tiles_n); }

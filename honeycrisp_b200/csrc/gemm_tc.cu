@@ -58,6 +58,7 @@ struct TcParams {
   int vec_ok;         // C base and ldc allow 16-byte stores
   int tile_rows;      // 128 per CTA of the group
   int tma_store;      // results leave through shared memory and TMA stores (else direct stores)
+  const void* bias;   // optional row vector added to the rounded product (Linear), or null
   int n_out;          // destinations of every result tile: this device's result, then peers' copies
   int debug;
 };
@@ -310,6 +311,40 @@ __device__ __forceinline__ uint64_t make_smem_desc(uint32_t addr, uint32_t lbo_b
 __host__ __device__ constexpr uint32_t make_idesc(bool tf32, int a_mn, int b_mn, int m, int n) {
   return (1u << 4) | ((tf32 ? 2u : 0u) << 7) | ((tf32 ? 2u : 0u) << 10) | ((uint32_t)(a_mn & 1) << 15) |
          ((uint32_t)(b_mn & 1) << 16) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
+}
+
+// Linear's `h + bias` on W consecutive columns starting at `col`, as the reference computes it:
+// the product is first rounded to the output dtype, then widened, added, and narrowed again by
+// the caller (BackendCPU.swift:295-303 after the matmul's own writeBuffer).
+template <bool kHalf, int W>
+__device__ __forceinline__ void add_bias(const void* bias, int64_t col, int64_t N, float (&x)[W]) {
+  if (kHalf) {
+    const __half* b = (const __half*)bias + col;
+    if (W == 8 && col + 8 <= N && (((uintptr_t)b) & 15) == 0) {
+      const uint4 u = __ldg((const uint4*)b);
+      const __half2* h2 = (const __half2*)&u;
+#pragma unroll
+      for (int i = 0; i < 4; i++) {
+        const float2 f = __half22float2(h2[i]);
+        x[2 * i] = __fadd_rn(__half2float(__float2half_rn(x[2 * i])), f.x);
+        x[2 * i + 1] = __fadd_rn(__half2float(__float2half_rn(x[2 * i + 1])), f.y);
+      }
+    } else {
+#pragma unroll
+      for (int i = 0; i < W; i++)
+        if (col + i < N) x[i] = __fadd_rn(__half2float(__float2half_rn(x[i])), __half2float(__ldg(b + i)));
+    }
+  } else {
+    const float* b = (const float*)bias + col;
+    if (W == 4 && col + 4 <= N && (((uintptr_t)b) & 15) == 0) {
+      const float4 f = __ldg((const float4*)b);
+      x[0] = __fadd_rn(x[0], f.x); x[1] = __fadd_rn(x[1], f.y); x[2] = __fadd_rn(x[2], f.z); x[3] = __fadd_rn(x[3], f.w);
+    } else {
+#pragma unroll
+      for (int i = 0; i < W; i++)
+        if (col + i < N) x[i] = __fadd_rn(x[i], __ldg(b + i));
+    }
+  }
 }
 
 template <bool kHalf>
@@ -651,11 +686,14 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap mapA_hi, const __grid_constan
                 const uint32_t buf = row_addr + (uint32_t)(l >> 1) * 4096u;
 #pragma unroll
                 for (int q = 0; q < 4; q++) {
+                  float x[8];
+#pragma unroll
+                  for (int e = 0; e < 8; e++) x[e] = __uint_as_float(r[l][q * 8 + e]);
+                  if (p.bias) add_bias<true, 8>(p.bias, n0 + c + 32 * l + q * 8, p.N, x);
                   uint32_t h[4];
 #pragma unroll
                   for (int e = 0; e < 4; e++) {
-                    __half2 v2 = __floats2half2_rn(__uint_as_float(r[l][q * 8 + 2 * e]),
-                                                   __uint_as_float(r[l][q * 8 + 2 * e + 1]));
+                    __half2 v2 = __floats2half2_rn(x[2 * e], x[2 * e + 1]);
                     h[e] = *(uint32_t*)&v2;
                   }
                   st_shared_v4(buf + (((uint32_t)(q + 4 * (l & 1)) ^ sw) << 4), h[0], h[1], h[2], h[3]);
@@ -663,9 +701,14 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap mapA_hi, const __grid_constan
               } else {
                 const uint32_t buf = row_addr + (uint32_t)l * 4096u;
 #pragma unroll
-                for (int q = 0; q < 8; q++)
-                  st_shared_v4(buf + (((uint32_t)q ^ sw) << 4), r[l][q * 4], r[l][q * 4 + 1], r[l][q * 4 + 2],
-                               r[l][q * 4 + 3]);
+                for (int q = 0; q < 8; q++) {
+                  float x[4];
+#pragma unroll
+                  for (int e = 0; e < 4; e++) x[e] = __uint_as_float(r[l][q * 4 + e]);
+                  if (p.bias) add_bias<false, 4>(p.bias, n0 + c + 32 * l + q * 4, p.N, x);
+                  st_shared_v4(buf + (((uint32_t)q ^ sw) << 4), __float_as_uint(x[0]), __float_as_uint(x[1]),
+                               __float_as_uint(x[2]), __float_as_uint(x[3]));
+                }
               }
             }
             fence_proxy_async_smem();
@@ -691,6 +734,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap mapA_hi, const __grid_constan
             float v[32];
 #pragma unroll
             for (int j = 0; j < 32; j++) v[j] = __uint_as_float(r[j]);
+            if (p.bias) add_bias<kOutHalf, 32>(p.bias, n0 + c, p.N, v);
             if (gm < p.M && n0 + c < p.N) store_row32<kOutHalf>(cmat, row_off, n0 + c, p.N, v, p.vec_ok != 0);
           }
         }
@@ -736,10 +780,14 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap mapA_hi, const __grid_constan
             if (store_leader) bulk_wait_read<0>();
             __syncwarp();
 #pragma unroll
-            for (int q = 0; q < 8; q++)
-              st_shared_v4(row_addr + (((uint32_t)q ^ sw) << 4), __float_as_uint(acc[c + q * 4]),
-                           __float_as_uint(acc[c + q * 4 + 1]), __float_as_uint(acc[c + q * 4 + 2]),
-                           __float_as_uint(acc[c + q * 4 + 3]));
+            for (int q = 0; q < 8; q++) {
+              float x[4];
+#pragma unroll
+              for (int e = 0; e < 4; e++) x[e] = acc[c + q * 4 + e];
+              if (p.bias) add_bias<false, 4>(p.bias, n0 + c + q * 4, p.N, x);
+              st_shared_v4(row_addr + (((uint32_t)q ^ sw) << 4), __float_as_uint(x[0]), __float_as_uint(x[1]),
+                           __float_as_uint(x[2]), __float_as_uint(x[3]));
+            }
             fence_proxy_async_smem();
             __syncwarp();
             if (store_leader && m_warp < p.M && n0 + c < p.N) {
@@ -753,6 +801,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap mapA_hi, const __grid_constan
             float v[32];
 #pragma unroll
             for (int j = 0; j < 32; j++) v[j] = acc[c + j];
+            if (p.bias) add_bias<kOutHalf, 32>(p.bias, n0 + c, p.N, v);
             if (n0 + c < p.N) store_row32<kOutHalf>(cmat, row_off, n0 + c, p.N, v, p.vec_ok != 0);
           }
         }
@@ -1145,6 +1194,7 @@ cudaError_t launch_tc(const GemmProblem& p, cudaStream_t stream, unsigned int* s
   tp.a_mn_major = p.a_mn_major; tp.b_mn_major = p.b_mn_major;
   tp.C = p.C; tp.ldc = p.ldc; tp.strideC = p.strideC;
   tp.status = status_word;
+  tp.bias = p.bias;
   tp.vec_ok = (((uintptr_t)p.C & 15) == 0 && (p.ldc * eb) % 16 == 0 && (p.strideC * eb) % 16 == 0) ? 1 : 0;
   tp.debug = dbg;
   // Results leave through TMA stores when the result can be described to TMA (16-byte aligned

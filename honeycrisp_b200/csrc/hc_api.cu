@@ -684,6 +684,53 @@ hc_status hc_check_device_status(hc_ctx* ctx) {
   return HC_OK;
 }
 
+hc_status hc_linear_forward(hc_ctx* ctx, hc_dtype dtype, const void* x, const void* weight, const void* bias,
+                            int64_t rows, int64_t in_count, int64_t out_count, void* out) {
+  if (!ctx) return HC_ERR_INVALID_ARGUMENT;
+  std::lock_guard<std::mutex> lock(ctx->mu);
+  DeviceGuard g(ctx->device);
+  hc::GemmProblem p;
+  hc_status s = build_problem(ctx, dtype, 1, x, 0, weight, 0, 0, rows, in_count, out_count, 0, out_count, out, &p);
+  if (s != HC_OK) return s;
+  if (in_count == 0 && bias && rows > 0 && out_count > 0)
+    return fail(ctx, HC_ERR_INVALID_ARGUMENT, "linear forward needs a non-empty input dimension");
+  p.bias = bias;
+  return run_problem(ctx, HC_KERNEL_AUTO, p, flop_count(1, rows, in_count, out_count));
+}
+
+hc_status hc_column_sum(hc_ctx* ctx, hc_dtype dtype, const void* x, int64_t rows, int64_t cols, void* out) {
+  if (!ctx || rows < 0 || cols < 0 || (cols > 0 && !out) || (rows * cols > 0 && !x)) return HC_ERR_INVALID_ARGUMENT;
+  if (dtype != HC_F16 && dtype != HC_F32) return HC_ERR_NOT_IMPLEMENTED;
+  std::lock_guard<std::mutex> lock(ctx->mu);
+  DeviceGuard g(ctx->device);
+  cudaError_t e = hc::launch_column_sum(dtype, x, out, rows, cols, ctx->stream);
+  ctx->launch_count += 1;
+  if (e != cudaSuccess) return cuda_fail(ctx, e, "column sum");
+  return HC_OK;
+}
+
+hc_status hc_cast(hc_ctx* ctx, hc_dtype from, hc_dtype to, const void* x, int64_t count, void* out) {
+  if (!ctx || count < 0 || (count > 0 && (!x || !out))) return HC_ERR_INVALID_ARGUMENT;
+  if ((from != HC_F16 && from != HC_F32) || (to != HC_F16 && to != HC_F32)) return HC_ERR_NOT_IMPLEMENTED;
+  std::lock_guard<std::mutex> lock(ctx->mu);
+  DeviceGuard g(ctx->device);
+  cudaError_t e = hc::launch_cast(from, to, x, out, count, ctx->stream);
+  ctx->launch_count += 1;
+  if (e != cudaSuccess) return cuda_fail(ctx, e, "cast");
+  return HC_OK;
+}
+
+hc_status hc_add(hc_ctx* ctx, hc_dtype dtype, const void* a, const void* b, int64_t count, void* out) {
+  if (!ctx || count < 0 || (count > 0 && (!a || !b || !out))) return HC_ERR_INVALID_ARGUMENT;
+  if (dtype != HC_F16 && dtype != HC_F32) return HC_ERR_NOT_IMPLEMENTED;
+  std::lock_guard<std::mutex> lock(ctx->mu);
+  DeviceGuard g(ctx->device);
+  cudaError_t e = hc::launch_add(dtype, a, b, out, count, ctx->stream);
+  ctx->launch_count += 1;
+  if (e != cudaSuccess) return cuda_fail(ctx, e, "add");
+  return HC_OK;
+}
+
 hc_status hc_selftest_bounded_wait(hc_ctx* ctx, int limit_ms) {
   if (!ctx || limit_ms < 1 || limit_ms > 1000) return HC_ERR_INVALID_ARGUMENT;
   std::lock_guard<std::mutex> lock(ctx->mu);

@@ -1,0 +1,97 @@
+// The small operations either side of a Linear layer's products, so that its forward and
+// backward pass stay on the device: the bias gradient (a column sum), dtype casts, and the
+// elementwise add of gradient accumulation.  All three are bound by HBM bandwidth.
+//
+// They restate the reference CPU backend exactly:
+//   reduce(.sum) over the leading axis: one float accumulator per column, rows in ascending
+//     order, narrowed once (Sources/Honeycrisp/BackendCPU.swift:808-827);
+//   cast: widen/narrow through Float (BackendCPU.swift:2018-2058);
+//   binaryOp(.add) on equal shapes: widen, add, narrow (BackendCPU.swift:295-303).
+#include "common.cuh"
+
+namespace hc {
+namespace {
+
+template <typename T> __device__ __forceinline__ float widen(T v);
+template <> __device__ __forceinline__ float widen<float>(float v) { return v; }
+template <> __device__ __forceinline__ float widen<__half>(__half v) { return __half2float(v); }
+template <typename T> __device__ __forceinline__ T narrow(float v);
+template <> __device__ __forceinline__ float narrow<float>(float v) { return v; }
+template <> __device__ __forceinline__ __half narrow<__half>(float v) { return __float2half_rn(v); }
+
+// One thread per column walks the rows in order (the reference's summation order), eight
+// loads in flight; consecutive threads read consecutive columns, so every row is read coalesced.
+template <typename T>
+__global__ void __launch_bounds__(128) column_sum_kernel(const T* __restrict__ x, T* __restrict__ out, int64_t rows,
+                                                         int64_t cols) {
+  const int64_t c = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
+  if (c >= cols) return;
+  float sum = 0.0f;
+  int64_t r = 0;
+  for (; r + 8 <= rows; r += 8) {
+    float v[8];
+#pragma unroll
+    for (int i = 0; i < 8; i++) v[i] = widen<T>(x[(r + i) * cols + c]);
+#pragma unroll
+    for (int i = 0; i < 8; i++) sum = __fadd_rn(sum, v[i]);
+  }
+  for (; r < rows; r++) sum = __fadd_rn(sum, widen<T>(x[r * cols + c]));
+  out[c] = narrow<T>(sum);
+}
+
+template <typename TI, typename TO>
+__global__ void cast_kernel(const TI* __restrict__ x, TO* __restrict__ out, int64_t n) {
+  for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x)
+    out[i] = narrow<TO>(widen<TI>(x[i]));
+}
+
+template <typename T>
+__global__ void add_kernel(const T* __restrict__ a, const T* __restrict__ b, T* __restrict__ out, int64_t n) {
+  for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x)
+    out[i] = narrow<T>(__fadd_rn(widen<T>(a[i]), widen<T>(b[i])));
+}
+
+int grid_for(int64_t n, int threads) {
+  int64_t b = (n + threads - 1) / threads;
+  return (int)(b > 148 * 16 ? 148 * 16 : (b < 1 ? 1 : b));
+}
+
+}  // namespace
+
+cudaError_t launch_column_sum(hc_dtype dtype, const void* x, void* out, int64_t rows, int64_t cols, cudaStream_t stream) {
+  if (cols <= 0) return cudaSuccess;
+  const int threads = 128;
+  const int64_t blocks = (cols + threads - 1) / threads;
+  if (blocks > 2147483647LL) return cudaErrorInvalidValue;
+  if (dtype == HC_F16)
+    column_sum_kernel<__half><<<(unsigned)blocks, threads, 0, stream>>>((const __half*)x, (__half*)out, rows, cols);
+  else
+    column_sum_kernel<float><<<(unsigned)blocks, threads, 0, stream>>>((const float*)x, (float*)out, rows, cols);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_cast(hc_dtype from, hc_dtype to, const void* x, void* out, int64_t count, cudaStream_t stream) {
+  if (count <= 0) return cudaSuccess;
+  const int threads = 256, grid = grid_for(count, threads);
+  if (from == HC_F16 && to == HC_F32)
+    cast_kernel<__half, float><<<grid, threads, 0, stream>>>((const __half*)x, (float*)out, count);
+  else if (from == HC_F32 && to == HC_F16)
+    cast_kernel<float, __half><<<grid, threads, 0, stream>>>((const float*)x, (__half*)out, count);
+  else if (from == HC_F16)
+    cast_kernel<__half, __half><<<grid, threads, 0, stream>>>((const __half*)x, (__half*)out, count);
+  else
+    cast_kernel<float, float><<<grid, threads, 0, stream>>>((const float*)x, (float*)out, count);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_add(hc_dtype dtype, const void* a, const void* b, void* out, int64_t count, cudaStream_t stream) {
+  if (count <= 0) return cudaSuccess;
+  const int threads = 256, grid = grid_for(count, threads);
+  if (dtype == HC_F16)
+    add_kernel<__half><<<grid, threads, 0, stream>>>((const __half*)a, (const __half*)b, (__half*)out, count);
+  else
+    add_kernel<float><<<grid, threads, 0, stream>>>((const float*)a, (const float*)b, (float*)out, count);
+  return cudaGetLastError();
+}
+
+}  // namespace hc

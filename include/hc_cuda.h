@@ -170,6 +170,30 @@ hc_status hc_matmul_colblock(hc_ctx* ctx, hc_kernel kernel, hc_dtype dtype, cons
                              int64_t rows, int64_t inner, int64_t cols, int64_t col_begin,
                              int64_t col_count, void* out);
 
+/* ---- around a Linear layer (next to the hot path) ------------------------------------------ */
+
+/* out[rows,out_count] = x[rows,in_count] * weight[in_count,out_count] + bias[out_count], the
+ * bias added in the product's epilogue.  `bias` may be NULL.  Numerically this is the
+ * reference's two operations: the product rounded to `dtype`, then a broadcast add in `dtype`.
+ * Replaces: Linear.callAsFunction (Sources/Honeycrisp/Trainable.swift:530-546) =
+ * Tensor.matmul + Backend.binaryOp(.add) (Backend.swift:178-185, CPU body BackendCPU.swift:267-306). */
+hc_status hc_linear_forward(hc_ctx* ctx, hc_dtype dtype, const void* x, const void* weight,
+                            const void* bias, int64_t rows, int64_t in_count, int64_t out_count,
+                            void* out);
+/* out[cols] = sum over rows of x[rows,cols]: the bias gradient of a Linear layer.  One float
+ * accumulator per column, rows in ascending order, narrowed once.
+ * Replaces: Backend.reduce(.sum) over the leading axis as issued by reduceBroadcast
+ * (Backend.swift:524-531; CPU body BackendCPU.swift:808-827; use at Tensor.swift:865-868). */
+hc_status hc_column_sum(hc_ctx* ctx, hc_dtype dtype, const void* x, int64_t rows, int64_t cols,
+                        void* out);
+/* Elementwise dtype conversion (Linear's castParams).
+ * Replaces: Backend.cast (Backend.swift:489-494). */
+hc_status hc_cast(hc_ctx* ctx, hc_dtype from, hc_dtype to, const void* x, int64_t count, void* out);
+/* out = a + b on equal shapes: gradient accumulation of a parameter used more than once.
+ * Replaces: Backend.binaryOp(.add) without broadcasting (use at Tensor.swift:370-372,
+ * Trainable.swift:258-266). */
+hc_status hc_add(hc_ctx* ctx, hc_dtype dtype, const void* a, const void* b, int64_t count, void* out);
+
 /* hc_matmul_colblock fused with the exchange: every finished tile of the block is stored into
  * `out` AND into the same place of up to 7 other devices' full-size results (`peer_outs`,
  * pointers obtained with hc_ipc_open), from the kernel's epilogue, over NVLink peer stores.

@@ -193,3 +193,49 @@ def matmul_grad_calls(trans_a, trans_b, trans_out):
     dA = matmul(a: grad, transA: transOut, b: B, transB: !transB, transOut: transA)
     dB = matmul(a: A, transA: !transA, b: grad, transB: transOut, transOut: transB)."""
     return ((bool(trans_out), not trans_b, bool(trans_a)), (not trans_a, bool(trans_out), bool(trans_b)))
+
+
+# ---- around a Linear layer -----------------------------------------------------------------
+
+def broadcast_add_rows(h, bias, rows, cols):
+    """binaryOp(.add) of h[rows,cols] and bias[cols] broadcast over rows, both of one dtype: widen
+    to Float, add, narrow (Sources/Honeycrisp/BackendCPU.swift:295-303; float32 goes through
+    vDSP_vadd only when neither side is broadcast, :276)."""
+    h = np.asarray(h).reshape(rows, cols)
+    bias = np.asarray(bias).reshape(cols)
+    assert h.dtype == bias.dtype
+    out = h.astype(np.float32) + bias.astype(np.float32)[None, :]
+    return (out.astype(h.dtype) if h.dtype == np.float32 else float_to_half(out)).reshape(-1)
+
+
+def linear_forward(x, weight, bias, rows, in_count, out_count):
+    """Linear.callAsFunction (Sources/Honeycrisp/Trainable.swift:530-546): matmul with no flags,
+    then the broadcast add of the bias when there is one."""
+    h = matmul(x, False, weight, False, False, rows, in_count, out_count)
+    return h if bias is None else broadcast_add_rows(h, bias, rows, out_count)
+
+
+def column_sum(x, rows, cols):
+    """reduce(.sum) over the leading axis: one Float accumulator per column, rows ascending,
+    narrowed once (BackendCPU.swift:808-827).  For float32 the reference calls vDSP_sve
+    (:792-806), whose order is unknown; this is the literal loop for both dtypes."""
+    x = np.asarray(x).reshape(rows, cols)
+    acc = np.zeros(cols, dtype=np.float32)
+    for r in range(rows):
+        acc = acc + x[r].astype(np.float32)
+    return acc if x.dtype == np.float32 else float_to_half(acc)
+
+
+def cast(x, out_dtype):
+    """Backend.cast through Float (BackendCPU.swift:2018-2058)."""
+    x = np.asarray(x)
+    if out_dtype == np.float16:
+        return float_to_half(x.astype(np.float32))
+    return x.astype(np.float32)
+
+
+def add(a, b):
+    """binaryOp(.add) on equal shapes: widen, add, narrow."""
+    a, b = np.asarray(a), np.asarray(b)
+    out = a.astype(np.float32) + b.astype(np.float32)
+    return out if a.dtype == np.float32 else float_to_half(out).reshape(a.shape)

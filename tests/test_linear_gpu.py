@@ -1,0 +1,111 @@
+"""A Linear layer's forward and backward pass on the device, against the CPU oracle."""
+import numpy as np
+import pytest
+
+from oracle import reference_cpu as ref
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def be():
+    from honeycrisp_b200 import CUDABackend
+    b = CUDABackend(0)
+    yield b
+    b.checkDeviceStatus()
+    b.close()
+
+
+@pytest.mark.parametrize("dtype", [np.float32, np.float16])
+@pytest.mark.parametrize("rows,n_in,n_out", [(4, 5, 3), (2, 3, 4), (130, 67, 129), (64, 128, 32)])
+def test_fused_bias_is_bit_identical_to_matmul_then_add_small(be, rows, n_in, n_out, dtype):
+    """Shapes TMA cannot describe (and the reference's own Linear(4 -> 5) test size) run on the
+    CUDA-core kernel, whose product is bit-identical to the CPU loop for float16; the fused bias
+    add must then match the reference's separate add bit for bit."""
+    rng = np.random.default_rng(rows + n_in)
+    x = rng.standard_normal((rows, n_in)).astype(dtype)
+    w = rng.standard_normal((n_in, n_out)).astype(dtype)
+    b = rng.standard_normal(n_out).astype(dtype)
+    got = be.linearForward(x, w, b, rows, n_in, n_out, dtype).onCPU(dtype)[: rows * n_out]
+    h = be.matmul(x, False, w, False, False, rows, n_in, n_out, dtype).onCPU(dtype)[: rows * n_out]
+    assert np.array_equal(got.view(np.uint8), ref.broadcast_add_rows(h, b, rows, n_out).view(np.uint8))
+    want = ref.linear_forward(x, w, b, rows, n_in, n_out)
+    if dtype == np.float16:
+        assert np.array_equal(got.view(np.uint16), want.view(np.uint16))
+    else:
+        assert ref.rel_frobenius(got, want) < 1e-5
+    none = be.linearForward(x, w, None, rows, n_in, n_out, dtype).onCPU(dtype)[: rows * n_out]
+    assert np.array_equal(none.view(np.uint8), h.view(np.uint8))
+
+
+@pytest.mark.parametrize("dtype,tol", [(np.float32, 1e-5), (np.float16, 2e-3)])
+@pytest.mark.parametrize("rows,n_in,n_out", [(256, 128, 256), (1000, 520, 776), (384, 64, 96), (2048, 4096, 1024)])
+def test_fused_bias_on_the_tensor_core_path(be, rows, n_in, n_out, dtype, tol):
+    """The tensor-core epilogue adds the bias to the rounded product: identical, bit for bit, to
+    this library's own product followed by the oracle's add; and within tolerance of float64."""
+    from honeycrisp_b200 import _lib
+    rng = np.random.default_rng(n_out)
+    x = rng.standard_normal((rows, n_in)).astype(dtype)
+    w = (rng.standard_normal((n_in, n_out)) / np.sqrt(n_in)).astype(dtype)
+    b = rng.standard_normal(n_out).astype(dtype)
+    got = be.linearForward(x, w, b, rows, n_in, n_out, dtype).onCPU(dtype)[: rows * n_out]
+    assert be.lastLaunchInfo()["kernel"] == _lib.HC_KERNEL_TENSOR
+    h = be.matmul(x, False, w, False, False, rows, n_in, n_out, dtype).onCPU(dtype)[: rows * n_out]
+    assert np.array_equal(got.view(np.uint8), ref.broadcast_add_rows(h, b, rows, n_out).view(np.uint8))
+    f64 = (x.astype(np.float64) @ w.astype(np.float64) + b.astype(np.float64)).reshape(-1)
+    assert ref.rel_frobenius(got, f64) < tol
+
+
+@pytest.mark.parametrize("dtype", [np.float32, np.float16])
+@pytest.mark.parametrize("rows,cols", [(1, 7), (9, 1), (33, 130), (4096, 520), (257, 4099)])
+def test_column_sum_is_bit_identical_to_the_cpu_loop(be, rows, cols, dtype):
+    x = np.random.default_rng(rows * cols).standard_normal((rows, cols)).astype(dtype)
+    got = be.columnSum(x, rows, cols, dtype).onCPU(dtype)[:cols]
+    want = ref.column_sum(x, rows, cols)
+    assert np.array_equal(got.view(np.uint8), want.view(np.uint8))
+
+
+def test_cast_and_add_are_bit_identical(be):
+    rng = np.random.default_rng(9)
+    x32 = (rng.standard_normal(100003) * 1e3).astype(np.float32)
+    x32[:4] = [np.inf, -np.inf, 65520.0, 1e-8]
+    h = be.cast(x32, x32.size, np.float32, np.float16).onCPU(np.float16)[: x32.size]
+    assert np.array_equal(h.view(np.uint16), ref.cast(x32, np.float16).view(np.uint16))
+    back = be.cast(h, h.size, np.float16, np.float32).onCPU(np.float32)[: h.size]
+    assert np.array_equal(back.view(np.uint32), ref.cast(h, np.float32).view(np.uint32))
+    for dt in (np.float32, np.float16):
+        a = rng.standard_normal(50001).astype(dt)
+        b = rng.standard_normal(50001).astype(dt)
+        got = be.add(a, b, a.size, dt).onCPU(dt)[: a.size]
+        assert np.array_equal(got.view(np.uint8), ref.add(a, b).reshape(-1).view(np.uint8))
+
+
+@pytest.mark.parametrize("dtype,tol", [(np.float32, 1e-5), (np.float16, 2e-3)])
+def test_linear_layer_forward_and_backward(be, dtype, tol):
+    """Linear(inCount -> outCount) on a [batch, seq, in] input: output, input gradient, weight
+    gradient and bias gradient against the oracle's products and sums."""
+    from honeycrisp_b200 import Linear
+    layer = Linear(be, 256, 384, dtype=dtype, seed=3)
+    w = layer.weight.onCPU(dtype)[: 256 * 384].reshape(256, 384)
+    assert np.abs(w.astype(np.float32)).max() <= np.sqrt(3.0) / np.sqrt(256) + 1e-3
+    rng = np.random.default_rng(1)
+    b = rng.standard_normal(384).astype(dtype)
+    layer.bias = be.collection(b, dtype)
+    x = rng.standard_normal((4, 96, 256)).astype(dtype)
+    y, yshape = layer(x, x.shape)
+    assert yshape == [4, 96, 384]
+    rows = 4 * 96
+    want_y = ref.linear_forward(x.reshape(rows, 256), w, b, rows, 256, 384)
+    assert ref.rel_frobenius(y.onCPU(dtype)[: rows * 384], want_y) < tol
+    g = rng.standard_normal((4, 96, 384)).astype(dtype)
+    dx = layer.backward(x, x.shape, g)
+    (fa, fb) = ref.matmul_grad_calls(False, False, False)
+    want_dx = ref.matmul(g.reshape(rows, 384), fa[0], w, fa[1], fa[2], rows, 384, 256)
+    want_dw = ref.matmul(x.reshape(rows, 256), fb[0], g.reshape(rows, 384), fb[1], fb[2], 256, rows, 384)
+    assert ref.rel_frobenius(dx.onCPU(dtype)[: rows * 256], want_dx) < tol
+    assert ref.rel_frobenius(layer.weightGrad.onCPU(dtype)[: 256 * 384], want_dw) < tol
+    want_db = ref.column_sum(g.reshape(rows, 384), rows, 384)
+    assert np.array_equal(layer.biasGrad.onCPU(dtype)[:384].view(np.uint8), want_db.view(np.uint8))
+    # a second backward accumulates (Param.addGrad)
+    layer.backward(x, x.shape, g)
+    assert np.array_equal(layer.biasGrad.onCPU(dtype)[:384].view(np.uint8), ref.add(want_db, want_db).reshape(-1).view(np.uint8))

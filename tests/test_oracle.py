@@ -129,3 +129,44 @@ def test_empty_dimensions():
     assert z.shape == (12,) and np.all(z == 0)
     z = ref.matmul(np.zeros((0, 5), np.float16), False, np.zeros((5, 4), np.float16), False, False, 0, 5, 4)
     assert z.size == 0
+
+
+# ---- the operations around a Linear layer -----------------------------------------------------
+
+@pytest.mark.parametrize("dtype", [np.float32, np.float16])
+def test_linear_forward_is_matmul_then_broadcast_add(dtype):
+    rng = np.random.default_rng(2)
+    x = rng.standard_normal((6, 4)).astype(dtype)
+    w = rng.standard_normal((4, 5)).astype(dtype)      # Linear(4 -> 5), the size HoneycrispTests.swift:700-727 uses
+    b = rng.standard_normal(5).astype(dtype)
+    y = ref.linear_forward(x, w, b, 6, 4, 5)
+    h = ref.matmul(x, False, w, False, False, 6, 4, 5)
+    manual = (h.reshape(6, 5).astype(np.float32) + b.astype(np.float32)).astype(dtype).reshape(-1)
+    assert np.array_equal(y.view(np.uint8), manual.view(np.uint8))
+    assert np.array_equal(ref.linear_forward(x, w, None, 6, 4, 5).view(np.uint8), h.view(np.uint8))
+    f64 = (x.astype(np.float64) @ w.astype(np.float64) + b.astype(np.float64)).reshape(-1)
+    assert ref.rel_frobenius(y, f64) < (1e-6 if dtype == np.float32 else 2e-3)
+
+
+def test_column_sum_order_and_rounding():
+    # 2048 + 1 + 1 in float16: summed in float32 and narrowed once gives 2050; narrowing after
+    # every add would stay at 2048.
+    x = np.array([[2048.0], [1.0], [1.0]], dtype=np.float16)
+    assert float(ref.column_sum(x, 3, 1)[0]) == 2050.0
+    rng = np.random.default_rng(3)
+    x = rng.standard_normal((500, 37)).astype(np.float32)
+    s = ref.column_sum(x, 500, 37)
+    assert ref.rel_frobenius(s, x.astype(np.float64).sum(axis=0)) < 1e-6
+    seq = np.zeros(37, dtype=np.float32)
+    for r in range(500):
+        seq += x[r]
+    assert np.array_equal(s.view(np.uint32), seq.view(np.uint32))
+
+
+def test_cast_and_add_helpers():
+    x = np.array([1.0, 65519.0, 65520.0, -1e-8, np.inf], dtype=np.float32)
+    with np.errstate(over="ignore"):
+        assert np.array_equal(ref.cast(x, np.float16).view(np.uint16), x.astype(np.float16).view(np.uint16))
+    a = np.array([1000.0, 0.5], dtype=np.float16)
+    b = np.array([0.25, 0.5], dtype=np.float16)
+    assert ref.add(a, b).tolist() == [1000.0, 1.0]
