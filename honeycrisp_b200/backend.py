@@ -423,6 +423,26 @@ class CUDABackend:
         out._inputs = (a_d, b_d)
         return out
 
+    def seed(self, x: int):
+        """RandomGenerator.seed (Sources/Honeycrisp/Random.swift:57-64): state = [seed, 0]."""
+        self._rng_state = [int(x) & 0xFFFFFFFFFFFFFFFF, 0]
+
+    def sample(self, count: int, dist: str, dtype) -> CUDAData:
+        """RandomGenerator.sample(count:dist:dtype:): `dist` is "uniform" or "normal"; advances
+        the generator state exactly as the reference's CPU generator does."""
+        dt = _as_dtype(dtype)
+        if dt not in _HC_DTYPE:
+            raise NotImplementedByBackend(f"random for dtype {dt.value}")
+        if not hasattr(self, "_rng_state"):
+            self.seed(0)
+        out = self.allocate(count * dt.byteSize)
+        nxt = ctypes.c_uint64()
+        self._check(L.load().hc_random(self._ctx, 1 if dist == "normal" else 0, _HC_DTYPE[dt], self._rng_state[0],
+                                       self._rng_state[1], int(count), out.ptr, ctypes.byref(nxt)))
+        self._rng_state[1] = nxt.value
+        out._mark()
+        return out
+
     def hostSync(self):
         """Wait for every asynchronous host-buffer product enqueued so far."""
         self._check(L.load().hc_host_sync(self._ctx))

@@ -731,6 +731,20 @@ hc_status hc_add(hc_ctx* ctx, hc_dtype dtype, const void* a, const void* b, int6
   return HC_OK;
 }
 
+hc_status hc_random(hc_ctx* ctx, int normal, hc_dtype dtype, uint64_t seed, uint64_t offset, int64_t count, void* out,
+                    uint64_t* next_offset) {
+  if (!ctx || count < 0 || (count > 0 && !out)) return HC_ERR_INVALID_ARGUMENT;
+  if (dtype != HC_F16 && dtype != HC_F32) return HC_ERR_NOT_IMPLEMENTED;
+  std::lock_guard<std::mutex> lock(ctx->mu);
+  DeviceGuard g(ctx->device);
+  cudaError_t e = hc::launch_random(normal ? 1 : 0, dtype, seed, offset, count, out, ctx->stream);
+  ctx->launch_count += count > 0 ? 1 : 0;
+  if (e != cudaSuccess) return cuda_fail(ctx, e, "random");
+  // The reference's loops run `through: count`: one counter value more than the outputs need.
+  if (next_offset) *next_offset = offset + (uint64_t)(normal ? count / 2 + 1 : count / 4 + 1);
+  return HC_OK;
+}
+
 hc_status hc_selftest_bounded_wait(hc_ctx* ctx, int limit_ms) {
   if (!ctx || limit_ms < 1 || limit_ms > 1000) return HC_ERR_INVALID_ARGUMENT;
   std::lock_guard<std::mutex> lock(ctx->mu);

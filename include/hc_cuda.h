@@ -194,6 +194,15 @@ hc_status hc_cast(hc_ctx* ctx, hc_dtype from, hc_dtype to, const void* x, int64_
  * Trainable.swift:258-266). */
 hc_status hc_add(hc_ctx* ctx, hc_dtype dtype, const void* a, const void* b, int64_t count, void* out);
 
+/* `count` samples of Honeycrisp's generator, bit-compatible with its CPU backend for the uniform
+ * distribution (normal samples go through logf/cosf/sinf and agree to a few ulps): Philox-4x32-10
+ * keyed by `seed`, counter starting at `offset`.  `*next_offset` receives the generator's offset
+ * after the call (the state is the pair [seed, offset]).  normal == 0: U[0,1]; else N(0,1).
+ * Replaces: RandomGenerator._sample (Sources/Honeycrisp/BackendCPU.swift:78-123,177-221), which
+ * backs Tensor(rand:) / Tensor(randn:). */
+hc_status hc_random(hc_ctx* ctx, int normal, hc_dtype dtype, uint64_t seed, uint64_t offset,
+                    int64_t count, void* out, uint64_t* next_offset);
+
 /* hc_matmul_colblock fused with the exchange: every finished tile of the block is stored into
  * `out` AND into the same place of up to 7 other devices' full-size results (`peer_outs`,
  * pointers obtained with hc_ipc_open), from the kernel's epilogue, over NVLink peer stores.

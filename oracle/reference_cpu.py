@@ -239,3 +239,52 @@ def add(a, b):
     a, b = np.asarray(a), np.asarray(b)
     out = a.astype(np.float32) + b.astype(np.float32)
     return out if a.dtype == np.float32 else float_to_half(out).reshape(a.shape)
+
+
+# ---- the generator behind Tensor(rand:) / Tensor(randn:) ------------------------------------
+
+def philox4x32_10(seed, offsets):
+    """Philox-4x32-10 as Sources/Honeycrisp/BackendCPU.swift:177-199 writes it: counter
+    (offset_lo, offset_hi, 0, 0), key (seed_lo, seed_hi).  `offsets`: uint64 array; returns
+    uint32 [len, 4]."""
+    offsets = np.asarray(offsets, dtype=np.uint64)
+    c0 = (offsets & np.uint64(0xFFFFFFFF)).astype(np.uint64)
+    c1 = (offsets >> np.uint64(32)).astype(np.uint64)
+    c2 = np.zeros_like(c0)
+    c3 = np.zeros_like(c0)
+    k0 = np.uint64(int(seed) & 0xFFFFFFFF)
+    k1 = np.uint64((int(seed) >> 32) & 0xFFFFFFFF)
+    A, B, M = np.uint64(0xD2511F53), np.uint64(0xCD9E8D57), np.uint64(0xFFFFFFFF)
+    for _ in range(10):
+        p0, p2 = c0, c2
+        pb, pa = B * p2, A * p0
+        c0 = (pb >> np.uint64(32)) ^ c1 ^ k0
+        c2 = (pa >> np.uint64(32)) ^ c3 ^ k1
+        c1 = pb & M
+        c3 = pa & M
+        k0 = (k0 + np.uint64(0x9E3779B9)) & M
+        k1 = (k1 + np.uint64(0xBB67AE85)) & M
+    return np.stack([c0, c1, c2, c3], axis=1).astype(np.uint32)
+
+
+def random_sample(seed, offset, count, dist, dtype):
+    """CPURandomGenerator._sample (BackendCPU.swift:78-123).  Returns (values, next_offset)."""
+    if dist == "uniform":
+        n = count // 4 + 1                       # stride(from: 0, through: count, by: 4)
+        words = philox4x32_10(seed, np.arange(n, dtype=np.uint64) + np.uint64(offset)).reshape(-1)[:count]
+        vals = (words.astype(np.float64) / np.float64(0xFFFFFFFF)).astype(np.float32)
+    else:
+        n = count // 2 + 1                       # stride(from: 0, through: count, by: 2)
+        w = philox4x32_10(seed, np.arange(n, dtype=np.uint64) + np.uint64(offset))
+        # Loop index i (one counter value) writes positions i..i+3 from its word pairs (c0,c1) and
+        # (c2,c3); index i+2 then overwrites i+2 and i+3.  So every position below `count` ends up
+        # holding the (c0,c1) pair of the counter value number floor(position / 2).
+        denom = np.float32(0xFFFFFFFF)           # Float(0xffff_ffff) == 2^32
+        u1 = np.maximum(np.float32(1e-5), w[:, 0].astype(np.float32) / denom)
+        u2 = w[:, 1].astype(np.float32) / denom
+        r = np.sqrt(np.float32(-2.0) * np.log(u1))
+        phi = np.float32(2.0) * np.float32(np.pi) * u2
+        pairs = np.stack([(r * np.cos(phi)).astype(np.float32), (r * np.sin(phi)).astype(np.float32)], axis=1)
+        vals = pairs.reshape(-1)[:count]
+    vals = vals if dtype == np.float32 else float_to_half(vals)
+    return vals, int(offset) + n

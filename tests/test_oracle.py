@@ -170,3 +170,33 @@ def test_cast_and_add_helpers():
     a = np.array([1000.0, 0.5], dtype=np.float16)
     b = np.array([0.25, 0.5], dtype=np.float16)
     assert ref.add(a, b).tolist() == [1000.0, 1.0]
+
+
+# ---- the generator behind Tensor(rand:) / Tensor(randn:) ---------------------------------------
+
+def test_philox_known_answer_and_counter_layout():
+    """Philox-4x32-10 with zero key and counter gives the published known-answer words; the
+    reference puts the 64-bit offset in counter words 0 and 1 and the seed in the key
+    (BackendCPU.swift:177-199)."""
+    w = ref.philox4x32_10(0, [0])[0]
+    assert [int(x) for x in w] == [0x6627E8D5, 0xE169C58D, 0xBC57AC4C, 0x9B00DBD8]
+    a = ref.philox4x32_10(5, [7, 8, (1 << 32) + 7])
+    assert len({tuple(r) for r in a.tolist()}) == 3            # offsets beyond 32 bits matter
+    assert not np.array_equal(ref.philox4x32_10(6, [7])[0], a[0])
+
+
+def test_generator_statistics_and_state_as_the_reference_tests_them():
+    """BackendTests.swift:1800-1824: moments of 100 000 samples, and restoring the state
+    reproduces the same tensors."""
+    x, off = ref.random_sample(0, 0, 100000, "normal", np.float32)
+    assert abs(float(x.mean())) < 0.03 and abs(float(x.std()) - 1) < 0.03
+    z, off2 = ref.random_sample(0, off, 100000, "uniform", np.float32)
+    assert abs(float(z.mean()) - 0.5) < 0.03 and abs(float(z.std()) - 0.288675135) < 0.03
+    assert off == 50001 and off2 == 50001 + 25001             # loops run `through: count`
+    a, o1 = ref.random_sample(3, 10, 1234, "normal", np.float32)
+    b, o2 = ref.random_sample(3, o1, 1234, "normal", np.float32)
+    assert not np.array_equal(a, b)
+    c, _ = ref.random_sample(3, 10, 1234, "normal", np.float32)
+    d, _ = ref.random_sample(3, o1, 1234, "normal", np.float32)
+    assert np.array_equal(a, c) and np.array_equal(b, d)
+    assert float(z.max()) <= 1.0 and float(z.min()) >= 0.0
