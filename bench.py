@@ -422,6 +422,33 @@ def other_configs(be, stream, rank, world):
     res["linear_layer_fwd_bwd_f16"] = {"ms": ms, "tflops": 3 * 2 * 16384 * 16384 * 4096 / ms / 1e9,
                                        "includes": "fused bias add, bias-gradient column sum"}
     del x, dy, layer
+    # The reference's own benchmark protocol (Sources/HCMatrixBench/Entrypoint.swift:12-27): fp16
+    # `m1.t() &* m2`, one warm-up and one timed run including the wait, wall clock, 2*inner^2*outer
+    # flop; only the square cases pass the reference's shape assert.  "folded" passes the transpose
+    # as a flag instead of materialising it.
+    proto = {}
+    for inner in (512, 1024, 2048):
+        be.seed(0)
+        m1 = be.sample(inner * inner, "uniform", np.float16)
+        m2 = be.sample(inner * inner, "uniform", np.float16)
+        be.sync()
+
+        def run_mat():
+            t = be.transpose(m1, 1, inner, inner, np.float16)
+            be.matmul(t, False, m2, False, False, inner, inner, inner, np.float16).wait()
+
+        def run_fold():
+            be.matmul(m1, True, m2, False, False, inner, inner, inner, np.float16).wait()
+
+        out = {}
+        for name, fn in (("materialised", run_mat), ("folded", run_fold)):
+            fn()
+            t0 = time.perf_counter()
+            fn()
+            dt = time.perf_counter() - t0
+            out[name + "_gflops"] = 2.0 * inner ** 3 / dt / 1e9
+        proto[str(inner)] = out
+    res["hcmatrixbench_protocol_f16"] = proto
     a = torch.rand((16384, 16384), generator=g, device="cuda") * 2 - 1
     b = torch.rand((16384, 16384), generator=g, device="cuda") * 2 - 1
     o = torch.empty((16384, 16384), device="cuda"); od = be.wrap(o.data_ptr(), o.numel() * 4, o)

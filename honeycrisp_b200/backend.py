@@ -423,6 +423,17 @@ class CUDABackend:
         out._inputs = (a_d, b_d)
         return out
 
+    def transpose(self, x, matrixCount: int, rows: int, cols: int, dtype) -> CUDAData:
+        """The materialised `t()` of the last two axes (Index.swift:359-362)."""
+        dt = _as_dtype(dtype)
+        x_d = self._device_operand(x, dt)
+        out = self.allocate(matrixCount * rows * cols * dt.byteSize)
+        self._check(L.load().hc_transpose(self._ctx, _HC_DTYPE[dt], int(matrixCount), x_d.ptr, int(rows), int(cols),
+                                          out.ptr))
+        out._mark()
+        out._inputs = (x_d,)
+        return out
+
     def seed(self, x: int):
         """RandomGenerator.seed (Sources/Honeycrisp/Random.swift:57-64): state = [seed, 0]."""
         self._rng_state = [int(x) & 0xFFFFFFFFFFFFFFFF, 0]

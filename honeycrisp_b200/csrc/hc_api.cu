@@ -731,6 +731,19 @@ hc_status hc_add(hc_ctx* ctx, hc_dtype dtype, const void* a, const void* b, int6
   return HC_OK;
 }
 
+hc_status hc_transpose(hc_ctx* ctx, hc_dtype dtype, int64_t matrix_count, const void* in, int64_t rows, int64_t cols,
+                       void* out) {
+  if (!ctx || matrix_count < 0 || rows < 0 || cols < 0) return HC_ERR_INVALID_ARGUMENT;
+  if (matrix_count * rows * cols > 0 && (!in || !out)) return HC_ERR_INVALID_ARGUMENT;
+  if (dtype != HC_F16 && dtype != HC_F32) return HC_ERR_NOT_IMPLEMENTED;
+  std::lock_guard<std::mutex> lock(ctx->mu);
+  DeviceGuard g(ctx->device);
+  cudaError_t e = hc::launch_transpose(dtype, matrix_count, in, out, rows, cols, ctx->stream);
+  ctx->launch_count += 1;
+  if (e != cudaSuccess) return cuda_fail(ctx, e, "transpose");
+  return HC_OK;
+}
+
 hc_status hc_random(hc_ctx* ctx, int normal, hc_dtype dtype, uint64_t seed, uint64_t offset, int64_t count, void* out,
                     uint64_t* next_offset) {
   if (!ctx || count < 0 || (count > 0 && !out)) return HC_ERR_INVALID_ARGUMENT;

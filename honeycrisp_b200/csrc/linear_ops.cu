@@ -19,8 +19,9 @@ template <typename T> __device__ __forceinline__ T narrow(float v);
 template <> __device__ __forceinline__ float narrow<float>(float v) { return v; }
 template <> __device__ __forceinline__ __half narrow<__half>(float v) { return __float2half_rn(v); }
 
-// One thread per column walks the rows in order (the reference's summation order), eight
-// loads in flight; consecutive threads read consecutive columns, so every row is read coalesced.
+// One thread per column (or per pair of float16 columns) walks the rows in order - the
+// reference's summation order - with 32 loads in flight; consecutive threads read consecutive
+// columns, so every row is read coalesced.
 template <typename T>
 __global__ void __launch_bounds__(128) column_sum_kernel(const T* __restrict__ x, T* __restrict__ out, int64_t rows,
                                                          int64_t cols) {
@@ -28,15 +29,41 @@ __global__ void __launch_bounds__(128) column_sum_kernel(const T* __restrict__ x
   if (c >= cols) return;
   float sum = 0.0f;
   int64_t r = 0;
-  for (; r + 8 <= rows; r += 8) {
-    float v[8];
+  for (; r + 32 <= rows; r += 32) {
+    float v[32];
 #pragma unroll
-    for (int i = 0; i < 8; i++) v[i] = widen<T>(x[(r + i) * cols + c]);
+    for (int i = 0; i < 32; i++) v[i] = widen<T>(x[(r + i) * cols + c]);
 #pragma unroll
-    for (int i = 0; i < 8; i++) sum = __fadd_rn(sum, v[i]);
+    for (int i = 0; i < 32; i++) sum = __fadd_rn(sum, v[i]);
   }
   for (; r < rows; r++) sum = __fadd_rn(sum, widen<T>(x[r * cols + c]));
   out[c] = narrow<T>(sum);
+}
+
+// float16 with an even number of columns: two columns per thread through 4-byte loads.
+__global__ void __launch_bounds__(128) column_sum_half2_kernel(const __half2* __restrict__ x, __half2* __restrict__ out,
+                                                               int64_t rows, int64_t col_pairs) {
+  const int64_t c = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
+  if (c >= col_pairs) return;
+  float s0 = 0.0f, s1 = 0.0f;
+  int64_t r = 0;
+  for (; r + 32 <= rows; r += 32) {
+    __half2 v[32];
+#pragma unroll
+    for (int i = 0; i < 32; i++) v[i] = x[(r + i) * col_pairs + c];
+#pragma unroll
+    for (int i = 0; i < 32; i++) {
+      const float2 f = __half22float2(v[i]);
+      s0 = __fadd_rn(s0, f.x);
+      s1 = __fadd_rn(s1, f.y);
+    }
+  }
+  for (; r < rows; r++) {
+    const float2 f = __half22float2(x[r * col_pairs + c]);
+    s0 = __fadd_rn(s0, f.x);
+    s1 = __fadd_rn(s1, f.y);
+  }
+  out[c] = __floats2half2_rn(s0, s1);
 }
 
 template <typename TI, typename TO>
@@ -51,6 +78,25 @@ __global__ void add_kernel(const T* __restrict__ a, const T* __restrict__ b, T* 
     out[i] = narrow<T>(__fadd_rn(widen<T>(a[i]), widen<T>(b[i])));
 }
 
+// Materialised transpose of `batch` dense [rows, cols] matrices through 32 x 33 shared tiles.
+template <typename T>
+__global__ void transpose_kernel(const T* __restrict__ in, T* __restrict__ out, int64_t rows, int64_t cols) {
+  __shared__ T tile[32][33];
+  const int64_t mat = blockIdx.z;
+  in += mat * rows * cols;
+  out += mat * rows * cols;
+  const int64_t c0 = (int64_t)blockIdx.x * 32, r0 = (int64_t)blockIdx.y * 32;
+  for (int j = threadIdx.y; j < 32; j += blockDim.y) {
+    const int64_t r = r0 + j, c = c0 + threadIdx.x;
+    if (r < rows && c < cols) tile[j][threadIdx.x] = in[r * cols + c];
+  }
+  __syncthreads();
+  for (int j = threadIdx.y; j < 32; j += blockDim.y) {
+    const int64_t c = c0 + j, r = r0 + threadIdx.x;   // out is [cols, rows]
+    if (r < rows && c < cols) out[c * rows + r] = tile[threadIdx.x][j];
+  }
+}
+
 int grid_for(int64_t n, int threads) {
   int64_t b = (n + threads - 1) / threads;
   return (int)(b > 148 * 16 ? 148 * 16 : (b < 1 ? 1 : b));
@@ -63,10 +109,26 @@ cudaError_t launch_column_sum(hc_dtype dtype, const void* x, void* out, int64_t 
   const int threads = 128;
   const int64_t blocks = (cols + threads - 1) / threads;
   if (blocks > 2147483647LL) return cudaErrorInvalidValue;
-  if (dtype == HC_F16)
+  if (dtype == HC_F16 && cols % 2 == 0 && (((uintptr_t)x | (uintptr_t)out) & 3) == 0) {
+    const int64_t pairs = cols / 2, pb = (pairs + threads - 1) / threads;
+    column_sum_half2_kernel<<<(unsigned)pb, threads, 0, stream>>>((const __half2*)x, (__half2*)out, rows, pairs);
+  } else if (dtype == HC_F16)
     column_sum_kernel<__half><<<(unsigned)blocks, threads, 0, stream>>>((const __half*)x, (__half*)out, rows, cols);
   else
     column_sum_kernel<float><<<(unsigned)blocks, threads, 0, stream>>>((const float*)x, (float*)out, rows, cols);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_transpose(hc_dtype dtype, int64_t batch, const void* in, void* out, int64_t rows, int64_t cols,
+                             cudaStream_t stream) {
+  if (batch <= 0 || rows <= 0 || cols <= 0) return cudaSuccess;
+  const int64_t gx = (cols + 31) / 32, gy = (rows + 31) / 32;
+  if (gy > 65535 || batch > 65535 || gx > 2147483647LL) return cudaErrorInvalidValue;
+  dim3 grid((unsigned)gx, (unsigned)gy, (unsigned)batch), block(32, 8);
+  if (dtype == HC_F16)
+    transpose_kernel<__half><<<grid, block, 0, stream>>>((const __half*)in, (__half*)out, rows, cols);
+  else
+    transpose_kernel<float><<<grid, block, 0, stream>>>((const float*)in, (float*)out, rows, cols);
   return cudaGetLastError();
 }
 

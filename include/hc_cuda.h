@@ -194,6 +194,14 @@ hc_status hc_cast(hc_ctx* ctx, hc_dtype from, hc_dtype to, const void* x, int64_
  * Trainable.swift:258-266). */
 hc_status hc_add(hc_ctx* ctx, hc_dtype dtype, const void* a, const void* b, int64_t count, void* out);
 
+/* out[cols,rows] = in[rows,cols]^T for `matrix_count` matrices: the materialising `t()` of the
+ * reference (a gather through axisPermutation, Sources/Honeycrisp/Index.swift:238-266,359-362;
+ * Backend.swift:609-616,803-805).  A backend that keeps its tensors' layouts would instead pass
+ * the transpose as a flag of the product; this exists because the reference's benchmark times the
+ * two together (Sources/HCMatrixBench/Entrypoint.swift:17). */
+hc_status hc_transpose(hc_ctx* ctx, hc_dtype dtype, int64_t matrix_count, const void* in,
+                       int64_t rows, int64_t cols, void* out);
+
 /* `count` samples of Honeycrisp's generator, bit-compatible with its CPU backend for the uniform
  * distribution (normal samples go through logf/cosf/sinf and agree to a few ulps): Philox-4x32-10
  * keyed by `seed`, counter starting at `offset`.  `*next_offset` receives the generator's offset

@@ -109,3 +109,24 @@ def test_linear_layer_forward_and_backward(be, dtype, tol):
     # a second backward accumulates (Param.addGrad)
     layer.backward(x, x.shape, g)
     assert np.array_equal(layer.biasGrad.onCPU(dtype)[:384].view(np.uint8), ref.add(want_db, want_db).reshape(-1).view(np.uint8))
+
+
+@pytest.mark.parametrize("dtype", [np.float32, np.float16])
+@pytest.mark.parametrize("cnt,rows,cols", [(1, 1, 1), (1, 2, 3), (3, 33, 65), (2, 1000, 31), (1, 2048, 512)])
+def test_materialised_transpose(be, cnt, rows, cols, dtype):
+    x = np.random.default_rng(cols).standard_normal((cnt, rows, cols)).astype(dtype)
+    got = be.transpose(x, cnt, rows, cols, dtype).onCPU(dtype)[: x.size].reshape(cnt, cols, rows)
+    assert np.array_equal(got, np.swapaxes(x, 1, 2))
+
+
+def test_transposed_operand_equals_the_transpose_flag(be):
+    """`m1.t() &* m2` as the reference's benchmark issues it (a materialised transpose, then a
+    plain product) equals the product with transA set, bit for bit."""
+    rng = np.random.default_rng(4)
+    m1 = rng.random((1024, 1024), dtype=np.float32).astype(np.float16)
+    m2 = rng.random((1024, 1024), dtype=np.float32).astype(np.float16)
+    m1_d, m2_d = be.collection(m1, np.float16), be.collection(m2, np.float16)
+    t = be.transpose(m1_d, 1, 1024, 1024, np.float16)
+    a = be.matmul(t, False, m2_d, False, False, 1024, 1024, 1024, np.float16).onCPU(np.float16)
+    b = be.matmul(m1_d, True, m2_d, False, False, 1024, 1024, 1024, np.float16).onCPU(np.float16)
+    assert np.array_equal(a.view(np.uint16), b.view(np.uint16))
