@@ -284,7 +284,14 @@ void hc_destroy(hc_ctx* ctx) {
 hc_status hc_set_stream(hc_ctx* ctx, void* cuda_stream) {
   if (!ctx) return HC_ERR_INVALID_ARGUMENT;
   std::lock_guard<std::mutex> lock(ctx->mu);
-  ctx->stream = cuda_stream ? (cudaStream_t)cuda_stream : ctx->own_stream;
+  cudaStream_t next = cuda_stream ? (cudaStream_t)cuda_stream : ctx->own_stream;
+  if (next != ctx->stream) {
+    // Work already enqueued may still use the context's work areas (split operands, staging);
+    // nothing on the new stream is ordered after it, so let it finish first.
+    DeviceGuard g(ctx->device);
+    HC_CUDA_TRY(ctx, cudaStreamSynchronize(ctx->stream));
+    ctx->stream = next;
+  }
   return HC_OK;
 }
 

@@ -1,0 +1,171 @@
+// hc_cuda.hpp - C++ mirror of the part of Honeycrisp's `Backend` interface that libhccuda
+// serves, header-only over the C ABI in hc_cuda.h.
+//
+// The reference's host language is Swift; where no Swift toolchain exists this is the compiled
+// host side.  Names and argument meaning follow the reference:
+//   Backend::matmul / batchedMatmul          Sources/Honeycrisp/Backend.swift:650-669
+//   TensorData (byteCount, wait, onCPU)      Sources/Honeycrisp/Tensor.swift:69-85
+//   BackendError (allocationFailed, kernelFailed, notImplemented)   Backend.swift:6-16
+// A primitive a backend does not override throws BackendError::notImplemented, the reference's
+// convention for partial backends.
+#ifndef HC_CUDA_HPP_
+#define HC_CUDA_HPP_
+
+#include <cstdint>
+#include <cstring>
+#include <memory>
+#include <stdexcept>
+#include <string>
+#include <vector>
+
+#include "hc_cuda.h"
+
+namespace honeycrisp {
+
+enum class DType { float16, float32, int64 };
+
+inline size_t byteSize(DType t) { return t == DType::float16 ? 2 : t == DType::float32 ? 4 : 8; }
+
+struct BackendError : std::runtime_error {
+  enum class Kind { allocationFailed, kernelFailed, notImplemented } kind;
+  BackendError(Kind k, const std::string& what) : std::runtime_error(what), kind(k) {}
+  static BackendError notImplemented(const std::string& op) { return {Kind::notImplemented, "not implemented: " + op}; }
+};
+
+class Backend;
+
+/// A buffer of tensor data owned by a backend (Tensor.Data).
+class TensorData {
+ public:
+  virtual ~TensorData() = default;
+  virtual size_t byteCount() const = 0;
+  virtual void wait() = 0;
+  /// The bytes on the host.
+  virtual std::vector<unsigned char> onCPU() = 0;
+};
+
+/// The operator table.  Every primitive defaults to notImplemented (Backend.swift:28-892).
+class Backend {
+ public:
+  virtual ~Backend() = default;
+  virtual std::shared_ptr<TensorData> collection(const void* host, size_t count, DType) {
+    (void)host; (void)count;
+    throw BackendError::notImplemented("collection");
+  }
+  virtual std::shared_ptr<TensorData> matmul(const std::shared_ptr<TensorData>& a, bool transA,
+                                             const std::shared_ptr<TensorData>& b, bool transB, bool transOut,
+                                             int64_t rows, int64_t inner, int64_t cols, DType dtype) {
+    (void)a; (void)transA; (void)b; (void)transB; (void)transOut; (void)rows; (void)inner; (void)cols; (void)dtype;
+    throw BackendError::notImplemented("matmul");
+  }
+  virtual std::shared_ptr<TensorData> batchedMatmul(int64_t matrixCount, const std::shared_ptr<TensorData>& a,
+                                                    bool transA, const std::shared_ptr<TensorData>& b, bool transB,
+                                                    bool transOut, int64_t rows, int64_t inner, int64_t cols,
+                                                    DType dtype) {
+    (void)matrixCount; (void)a; (void)transA; (void)b; (void)transB; (void)transOut; (void)rows; (void)inner;
+    (void)cols; (void)dtype;
+    throw BackendError::notImplemented("batchedMatmul");
+  }
+};
+
+class CUDABackend;
+
+class CUDAData : public TensorData {
+ public:
+  CUDAData(hc_ctx* ctx, size_t bytes) : ctx_(ctx), bytes_(bytes) {
+    if (hc_alloc(ctx_, bytes_, &ptr_) != HC_OK) throw BackendError(BackendError::Kind::allocationFailed, "allocation failed");
+  }
+  ~CUDAData() override {
+    if (event_) hc_event_destroy(event_);
+    hc_free(ctx_, ptr_);
+  }
+  size_t byteCount() const override { return bytes_; }
+  void* pointer() const { return ptr_; }
+  void mark() {
+    if (event_) hc_event_destroy(event_);
+    event_ = nullptr;
+    if (hc_event_record(ctx_, &event_) != HC_OK) throw BackendError(BackendError::Kind::kernelFailed, hc_last_error(ctx_));
+  }
+  void wait() override {
+    const hc_status st = event_ ? hc_event_wait(event_) : hc_sync(ctx_);
+    if (st != HC_OK) throw BackendError(BackendError::Kind::kernelFailed, hc_last_error(ctx_));
+    inputs_.clear();
+  }
+  std::vector<unsigned char> onCPU() override {
+    std::vector<unsigned char> host(bytes_ ? bytes_ : 1);
+    if (bytes_ && (hc_d2h(ctx_, host.data(), ptr_, bytes_) != HC_OK || hc_sync(ctx_) != HC_OK))
+      throw BackendError(BackendError::Kind::kernelFailed, hc_last_error(ctx_));
+    wait();
+    host.resize(bytes_);
+    return host;
+  }
+  void keep(std::shared_ptr<TensorData> a, std::shared_ptr<TensorData> b) { inputs_ = {std::move(a), std::move(b)}; }
+
+ private:
+  hc_ctx* ctx_;
+  size_t bytes_;
+  void* ptr_ = nullptr;
+  hc_event* event_ = nullptr;
+  std::vector<std::shared_ptr<TensorData>> inputs_;   // operands stay alive until the product has run
+};
+
+/// `Backend.defaultBackend = try CUDABackend()` in the reference's terms.
+class CUDABackend : public Backend {
+ public:
+  explicit CUDABackend(int device = 0) {
+    const hc_status st = hc_init(device, &ctx_);
+    if (st != HC_OK) throw BackendError(BackendError::Kind::kernelFailed, std::string("hc_init: ") + hc_status_string(st));
+  }
+  ~CUDABackend() override { hc_destroy(ctx_); }
+  CUDABackend(const CUDABackend&) = delete;
+  CUDABackend& operator=(const CUDABackend&) = delete;
+
+  std::shared_ptr<TensorData> collection(const void* host, size_t count, DType dtype) override {
+    auto d = std::make_shared<CUDAData>(ctx_, count * byteSize(dtype));
+    check(hc_h2d(ctx_, d->pointer(), host, count * byteSize(dtype)));
+    check(hc_sync(ctx_));
+    return d;
+  }
+
+  std::shared_ptr<TensorData> matmul(const std::shared_ptr<TensorData>& a, bool transA,
+                                     const std::shared_ptr<TensorData>& b, bool transB, bool transOut, int64_t rows,
+                                     int64_t inner, int64_t cols, DType dtype) override {
+    return batchedMatmul(1, a, transA, b, transB, transOut, rows, inner, cols, dtype);
+  }
+
+  std::shared_ptr<TensorData> batchedMatmul(int64_t matrixCount, const std::shared_ptr<TensorData>& a, bool transA,
+                                            const std::shared_ptr<TensorData>& b, bool transB, bool transOut,
+                                            int64_t rows, int64_t inner, int64_t cols, DType dtype) override {
+    if (dtype != DType::float16 && dtype != DType::float32) throw BackendError::notImplemented("matmul for int64");
+    auto da = std::dynamic_pointer_cast<CUDAData>(a), db = std::dynamic_pointer_cast<CUDAData>(b);
+    // Operands of another backend's data type are staged through onCPU, as the reference's GPU
+    // backend does (Sources/Honeycrisp/BackendMPS.swift:585-620).
+    if (!da) { auto h = a->onCPU(); da = std::static_pointer_cast<CUDAData>(collection(h.data(), h.size() / byteSize(dtype), dtype)); }
+    if (!db) { auto h = b->onCPU(); db = std::static_pointer_cast<CUDAData>(collection(h.data(), h.size() / byteSize(dtype), dtype)); }
+    const size_t eb = byteSize(dtype);
+    if (da->byteCount() < (size_t)(matrixCount * rows * inner) * eb || db->byteCount() < (size_t)(matrixCount * inner * cols) * eb)
+      throw std::invalid_argument("matmul: operand smaller than its stated shape");
+    auto out = std::make_shared<CUDAData>(ctx_, (size_t)(matrixCount * rows * cols) * eb);
+    check(hc_batched_matmul(ctx_, dtype == DType::float16 ? HC_F16 : HC_F32, matrixCount, da->pointer(), transA,
+                            db->pointer(), transB, transOut, rows, inner, cols, out->pointer()));
+    out->mark();
+    out->keep(da, db);
+    return out;
+  }
+
+  hc_ctx* context() const { return ctx_; }
+
+ private:
+  void check(hc_status st) {
+    if (st == HC_OK) return;
+    const std::string msg = hc_last_error(ctx_);
+    if (st == HC_ERR_ALLOCATION_FAILED) throw BackendError(BackendError::Kind::allocationFailed, msg);
+    if (st == HC_ERR_NOT_IMPLEMENTED) throw BackendError(BackendError::Kind::notImplemented, msg);
+    if (st == HC_ERR_INVALID_ARGUMENT) throw std::invalid_argument(msg);
+    throw BackendError(BackendError::Kind::kernelFailed, msg.empty() ? hc_status_string(st) : msg);
+  }
+  hc_ctx* ctx_ = nullptr;
+};
+
+}  // namespace honeycrisp
+#endif  // HC_CUDA_HPP_

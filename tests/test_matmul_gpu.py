@@ -272,3 +272,48 @@ def test_pipelined_host_products_equal_the_blocking_form(be):
     be.checkDeviceStatus()
     for w, o in zip(want, outs):
         assert np.array_equal(w.view(np.uint8), o.view(np.uint8))
+
+
+def test_argument_errors_come_back_as_status_codes(be):
+    """Misuse never aborts: the reference traps these with #alwaysAssert before the backend; the
+    library reports them."""
+    import ctypes
+    from honeycrisp_b200 import _lib
+    lib = _lib.load()
+    buf = be.allocate(64)
+    c = be._ctx
+    assert lib.hc_matmul(c, _lib.HC_F32, buf.ptr, 0, buf.ptr, 0, 0, -1, 2, 2, buf.ptr) == _lib.HC_ERR_INVALID_ARGUMENT
+    assert lib.hc_matmul(c, _lib.HC_F32, None, 0, buf.ptr, 0, 0, 2, 2, 2, buf.ptr) == _lib.HC_ERR_INVALID_ARGUMENT
+    assert lib.hc_matmul(c, 7, buf.ptr, 0, buf.ptr, 0, 0, 2, 2, 2, buf.ptr) == _lib.HC_ERR_NOT_IMPLEMENTED
+    big = 1 << 40
+    assert lib.hc_matmul(c, _lib.HC_F32, buf.ptr, 0, buf.ptr, 0, 0, big, big, big, buf.ptr) == _lib.HC_ERR_INVALID_ARGUMENT
+    assert lib.hc_batched_matmul_ex(c, 9, _lib.HC_F32, 1, buf.ptr, 0, buf.ptr, 0, 0, 2, 2, 2, buf.ptr) == _lib.HC_ERR_INVALID_ARGUMENT
+    assert lib.hc_matmul_colblock(c, 0, _lib.HC_F32, buf.ptr, 0, buf.ptr, 0, 0, 2, 2, 2, 1, 2, buf.ptr) == _lib.HC_ERR_INVALID_ARGUMENT
+    assert b"column block" in lib.hc_last_error(c)
+    p = ctypes.c_void_p()
+    assert lib.hc_alloc(c, 1 << 60, ctypes.byref(p)) == _lib.HC_ERR_ALLOCATION_FAILED and not p.value
+    be.checkDeviceStatus()
+    # and the context still works
+    z = be.matmul(np.ones((2, 2), np.float32), False, np.ones((2, 2), np.float32), False, False, 2, 2, 2, np.float32)
+    assert z.onCPU(np.float32)[:4].tolist() == [2, 2, 2, 2]
+
+
+def test_two_contexts_and_stream_switching(be):
+    """A second context on the same device, and a context moved between streams, give the same
+    bits as the module's context."""
+    import torch
+    from honeycrisp_b200 import CUDABackend
+    A, B = random_operands(31, 1, 512, 256, 768, np.float32)
+    want, _, _ = run(be, 1, A, B, False, False, False, np.float32, kernel=K().HC_KERNEL_TENSOR)
+    other = CUDABackend(0)
+    try:
+        for _ in range(2):
+            s = torch.cuda.Stream()
+            other.useStream(s.cuda_stream)
+            got, _, _ = run(other, 1, A, B, False, False, False, np.float32, kernel=K().HC_KERNEL_TENSOR)
+            assert np.array_equal(got.view(np.uint32), want.view(np.uint32))
+            other.useStream(None)
+            got, _, _ = run(other, 1, A, B, False, False, False, np.float32, kernel=K().HC_KERNEL_TENSOR)
+            assert np.array_equal(got.view(np.uint32), want.view(np.uint32))
+    finally:
+        other.close()
