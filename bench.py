@@ -489,7 +489,21 @@ def run_probe(args):
     torch.cuda.synchronize()
     be.checkDeviceStatus()
     ms = e0.elapsed_time(e1) / args.steps
-    emit({"probe": [M, K, N, cnt], "dtype": args.dtype, "flags": [ta, tb], "ms": ms,
+    if args.graph:
+        # the same launches replayed from a CUDA graph: device time without the host's launch rate
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=stream):
+            for _ in range(args.steps):
+                be.batchedMatmul(cnt, a, ta, b, tb, False, M, K, N, npdt, out=od, mark=False)
+        graph.replay()
+        e0.record(stream)
+        for _ in range(5):
+            graph.replay()
+        e1.record(stream)
+        torch.cuda.synchronize()
+        be.checkDeviceStatus()
+        ms = e0.elapsed_time(e1) / (5 * args.steps)
+    emit({"probe": [M, K, N, cnt], "dtype": args.dtype, "flags": [ta, tb], "ms": ms, "graph": bool(args.graph),
           "tflops": 2.0 * cnt * M * N * K / ms / 1e9, "kernel": be.lastLaunchInfo()})
 
 
@@ -597,6 +611,7 @@ def main():
     ap.add_argument("--probe", default=None, help="M,K,N[,count]: run one product a few times (profiler target)")
     ap.add_argument("--dtype", choices=["f16", "f32"], default="f16")
     ap.add_argument("--flags", default="0,1", help="transA,transB for --probe")
+    ap.add_argument("--graph", action="store_true", help="--probe: time CUDA-graph replays of the launches")
     args = ap.parse_args()
     if args.probe:
         run_probe(args)

@@ -1,21 +1,30 @@
 // Tensor-core matrix product for sm_100a: tcgen05.mma with the accumulator in tensor memory,
-// operands brought into shared memory by TMA through an mbarrier ring.
+// operands brought into shared memory by TMA through an mbarrier ring, results leaving through
+// shared memory and TMA stores.
 //
-// One persistent CTA per SM walks a list of 128 x BN output tiles.  Inside a CTA:
+// One persistent CTA per SM walks a list of output tiles.  Inside a CTA:
 //   warp 0, one lane : TMA producer.  Fills a ring of kStages shared-memory slots with one
 //                      128-byte-wide k-slab of A and of B per slot (128B-swizzled).
 //   warp 1, one lane : MMA issuer.  For every filled slot issues the tcgen05.mma instructions
-//                      of that slab into one of two accumulator buffers in tensor memory, then
-//                      commits the slot back to the producer.
-//   warps 2..        : epilogue.  Drain a finished accumulator buffer (tcgen05.ld), round and
-//                      store it, and hand the buffer back, while the issuer already works on
-//                      the other buffer.
+//                      of that slab into an accumulator buffer in tensor memory, then commits
+//                      the slot back to the producer.
+//   warps 2..        : epilogue.  Drain a finished accumulator (tcgen05.ld), round, stage the
+//                      rows in swizzled shared memory and send them with TMA stores, then hand
+//                      the accumulator back, while the issuer already works on the other one.
+// The issuing lanes are chosen with elect.sync, never by comparing the lane index: only then
+// does the compiler keep descriptors in uniform registers, and a tcgen05.mma issues in a few
+// cycles instead of ~220.
 //
-// Large products run the same roles on CTA pairs (cta_group::2): the two CTAs of a cluster own
-// the upper and lower 128 rows of a 256-row tile, each loads its own rows of A and its own half
-// of the B columns, and the leader CTA issues one MMA that spans both SMs.  That halves the
-// shared-memory traffic per flop, which is what bounds the single-CTA form.  Every copy is an
-// ordinary per-CTA TMA load into the CTA's own shared memory.
+// Tile shapes:
+//   128 x 128 / 128 x 256 on one CTA     narrow or small products;
+//   256 x 256 on a CTA pair              cta_group::2: the two CTAs of a cluster own the upper and
+//                                        lower 128 rows, each loads its own rows of A and its own
+//                                        half of the B columns, the leader issues one MMA that
+//                                        spans both SMs; two accumulator buffers alternate;
+//   256 x 512 on a CTA pair              long float16 contractions: two MMAs per k-step share the
+//                                        A slab and fill both accumulator buffers - least operand
+//                                        traffic per flop, no epilogue overlap.
+// Every copy is an ordinary per-CTA TMA load into the CTA's own shared memory.
 //
 // Transposed operands are never moved: a "K-major" operand (contracted index contiguous) and
 // an "MN-major" one (row/column index contiguous) differ only in the TMA box shape and in one
@@ -24,9 +33,14 @@
 // float32 runs as 3xTF32: x = hi + lo with hi, lo representable in TF32, and
 // A*B ~= A_lo*B_hi + A_hi*B_lo + A_hi*B_hi.  The split operands live in a scratch area; every
 // pipeline slot holds the hi and lo slabs of both operands, loaded once, and the issuer runs
-// the three products of the slab from them into the same accumulator.  Tensor-core accumulation does not round to nearest, so a long
-// contraction is cut into windows: every window accumulates in tensor memory, and the
-// epilogue warps add the windows together in registers with ordinary float32 adds.
+// the three products of the slab from them into the same accumulator.  Tensor-core accumulation
+// truncates instead of rounding, so a long contraction is cut into windows: every window
+// accumulates in tensor memory, and the epilogue warps add the windows together in registers
+// with ordinary float32 adds.
+//
+// Optional extras of the epilogue: a bias row added to the rounded product (Linear), and up
+// to seven more destinations for every result block (other devices' copies of the result,
+// written with peer TMA stores).
 //
 // Every wait in this file is bounded: after a time limit the waiting thread records a bit in
 // the context's status word, raises a CTA-wide abort flag and the CTA leaves through the
@@ -98,6 +112,13 @@ __device__ __forceinline__ uint32_t map_to_cta(uint32_t addr, uint32_t rank) {
   asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(rank));
   return r;
 }
+// Programmatic dependent launch: a kernel launched with the stream-serialization attribute may
+// start while its predecessor in the stream is still draining.  `pdl_release` lets the successor
+// be scheduled as soon as every CTA of this grid has issued it (or exited); `pdl_wait` blocks
+// until the predecessor has completed and its memory is visible.  Both are no-ops for an
+// ordinary launch.  Everything before pdl_wait must touch no global memory.
+__device__ __forceinline__ void pdl_release() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void cluster_sync_all() {
   asm volatile("barrier.cluster.arrive.release.aligned;\nbarrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
@@ -446,6 +467,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap mapA_hi, const __grid_constan
   __shared__ uint32_t tmem_base_slot;
   __shared__ int abort_flag;
 
+  pdl_release();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t rank = (kCta == 2) ? cluster_ctarank() : 0u;
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -486,6 +508,9 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap mapA_hi, const __grid_constan
   tc_fence_after();
   const uint32_t tmem_base = tmem_base_slot;
   volatile int* abortp = &abort_flag;
+  // Barriers and tensor memory are set up; from here on the kernel reads operands that an
+  // earlier kernel in the stream may have produced and overwrites results it may have read.
+  pdl_wait();
 
   const int nkb = p.num_k_blocks;
   const int chunk_kb = p.chunk_kb;
@@ -884,6 +909,8 @@ __device__ __forceinline__ void split_one(float x, float& h, float& l) {
 
 // One launch splits both operands: the first `blocks_a` blocks work on A, the rest on B.
 __global__ void __launch_bounds__(256) split_tf32_kernel(const SplitJob ja, const SplitJob jb, int blocks_a) {
+  pdl_release();
+  pdl_wait();
   const bool is_a = (int)blockIdx.x < blocks_a;
   const SplitJob& j = is_a ? ja : jb;
   const int64_t bid = is_a ? blockIdx.x : blockIdx.x - blocks_a;
@@ -997,6 +1024,13 @@ int window_slabs() {
   return v < 1 ? 1 : v;
 }
 
+// Successive kernels of this library in one stream may overlap their prologue with the
+// predecessor's tail (programmatic dependent launch); HC_TC_PDL=0 turns that off.
+bool overlap_launches() {
+  static int v = env_int("HC_TC_PDL", 1);
+  return v != 0;
+}
+
 template <int kElemBytes, int kBN, int kStages, int kEpiWarps, bool kWindowed, int kCta, int kNSplit = 1>
 struct TcConfig {
   // operand ring (float32 slots also hold the lo slabs) + store staging + alignment slack
@@ -1059,11 +1093,13 @@ struct TcConfig {
     cfg.blockDim = dim3(block);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = stream;
-    cudaLaunchAttribute attr;
-    attr.id = cudaLaunchAttributeClusterDimension;
-    attr.val.clusterDim.x = kCta; attr.val.clusterDim.y = 1; attr.val.clusterDim.z = 1;
-    cfg.attrs = &attr;
-    cfg.numAttrs = 1;
+    cudaLaunchAttribute attr[2];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = kCta; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = overlap_launches() ? 2 : 1;
     e = cudaLaunchKernelEx(&cfg, kernel(), maps[0], maps[1], maps[2], maps[3], outs, p);
     if (rec) {
       rec->tile_m = BM * kCta; rec->tile_n = kBN * kNSplit; rec->tile_k = 128 / kElemBytes; rec->stages = kStages;
@@ -1145,7 +1181,19 @@ cudaError_t launch_tc(const GemmProblem& p, cudaStream_t stream, unsigned int* s
       return (int)(b > 148 * 8 ? 148 * 8 : (b < 1 ? 1 : b));
     };
     const int blocks_a = blocks(ja), blocks_b = blocks(jb);
-    split_tf32_kernel<<<blocks_a + blocks_b, threads, 0, stream>>>(ja, jb, blocks_a);
+    {
+      cudaLaunchConfig_t scfg = {};
+      scfg.gridDim = dim3((unsigned)(blocks_a + blocks_b));
+      scfg.blockDim = dim3(threads);
+      scfg.stream = stream;
+      cudaLaunchAttribute sattr;
+      sattr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+      sattr.val.programmaticStreamSerializationAllowed = 1;
+      scfg.attrs = &sattr;
+      scfg.numAttrs = overlap_launches() ? 1 : 0;
+      cudaError_t se = cudaLaunchKernelEx(&scfg, split_tf32_kernel, ja, jb, blocks_a);
+      if (se != cudaSuccess) return se;
+    }
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return e;
     if (rec) { rec->launches += 1; rec->scratch_bytes = 2 * s.a_bytes + 2 * s.b_bytes; }
