@@ -40,7 +40,9 @@ def run(be, count, A, B, ta, tb, to, dtype, kernel):
 # narrow (128-column tile), batched, more tiles than SMs.
 SHAPES = [(128, 64, 256, 1), (256, 64, 256, 1), (128, 64, 128, 1), (256, 256, 512, 1), (200, 136, 328, 2),
           (1000, 520, 776, 3), (136, 72, 264, 3), (1024, 1024, 1024, 1), (384, 8, 96, 2), (2048, 128, 2048, 4),
-          (5000, 64, 1032, 1)]
+          (5000, 64, 1032, 1),
+          # long contractions over wide products take the 256 x 512 tiles: ragged in every dimension, batched
+          (304, 3080, 1096, 2), (1024, 4096, 1024, 1)]
 
 
 @pytest.mark.parametrize("shape", SHAPES)
@@ -51,7 +53,7 @@ def test_half_all_flag_combinations(be, shape):
         res, a_st, b_st = run(be, cnt, A, B, ta, tb, to, np.float16, TENSOR())
         f64 = ref.batched_matmul_f64(cnt, a_st, ta, b_st, tb, to, M, Kd, N)
         assert ref.rel_frobenius(res, f64) < TOL_F16, (shape, ta, tb, to)
-        if M * N * Kd * cnt <= 64 * 1024 * 1024:
+        if M * N * Kd * cnt <= 64 * 1024 * 1024 or (ta, tb, to) == (False, True, False):
             # against the reference CPU loop itself: same float32 accumulation, different order
             orc = ref.batched_matmul(cnt, a_st, ta, b_st, tb, to, M, Kd, N)
             assert ref.rel_frobenius(res, orc) < 1e-3, (shape, ta, tb, to)
