@@ -143,10 +143,19 @@ def cpu_operands():
 
 
 def calibrate_rows(threads, a32, b32, out32, target_s):
+    """Rows per product (a multiple of the thread count) so that one sample takes about target_s."""
     dt, _ = cpu_sample(threads, threads, a32, b32, out32)   # one row per thread
     per_row = dt / threads
     rows = int(max(threads, min(N_DIM, target_s / max(per_row, 1e-9))))
-    return (rows // threads) * threads or threads
+    rows = (rows // threads) * threads or threads
+    if rows > threads:
+        # Second point: throughput per row is not constant (caches, memory bandwidth shared by the
+        # threads), so correct the estimate with a sample of the chosen size.
+        dt, _ = cpu_sample(rows, threads, a32, b32, out32)
+        if dt > 1.3 * target_s or dt < 0.6 * target_s:
+            rows = int(max(threads, min(N_DIM, rows * target_s / dt)))
+            rows = (rows // threads) * threads or threads
+    return rows
 
 
 def run_reference(args):

@@ -100,7 +100,15 @@ def load() -> ctypes.CDLL:
         return _lib
     path = _build.LIB_PATH
     if not os.path.exists(path) or os.environ.get("HC_CUDA_REBUILD") == "1":
-        path = _build.build()
+        path = _build.build(force=True)
+    elif _build._stale():
+        # Sources are newer than the library: rebuild if a compiler is at hand, otherwise say so
+        # and use what is there (a copied tree can carry arbitrary file times).
+        try:
+            path = _build.build()
+        except Exception as e:  # noqa: BLE001
+            import warnings
+            warnings.warn(f"libhccuda.so is older than its sources and could not be rebuilt: {e}")
     L = ctypes.CDLL(path)
     for name, (res, args) in SIGNATURES.items():
         fn = getattr(L, name)  # AttributeError if the library lacks a declared symbol

@@ -377,8 +377,10 @@ hc_status hc_event_wait(hc_event* ev) {
   if (e != cudaSuccess) return cuda_fail(ctx, e, "event wait");
   unsigned int word = 0;
   // The status word is only written by kernels; reading it after the event is race-free for
-  // everything enqueued before the event.
-  e = cudaMemcpy(&word, ctx->status_word, sizeof word, cudaMemcpyDeviceToHost);
+  // everything enqueued before the event.  The copy runs on the context's own (non-blocking)
+  // stream so that it does not synchronise with unrelated streams of the process.
+  e = cudaMemcpyAsync(&word, ctx->status_word, sizeof word, cudaMemcpyDeviceToHost, ctx->own_stream);
+  if (e == cudaSuccess) e = cudaStreamSynchronize(ctx->own_stream);
   if (e != cudaSuccess) return cuda_fail(ctx, e, "status read");
   if (word) {
     char msg[96];
@@ -681,9 +683,11 @@ hc_status hc_check_device_status(hc_ctx* ctx) {
   DeviceGuard g(ctx->device);
   HC_CUDA_TRY(ctx, cudaStreamSynchronize(ctx->stream));
   unsigned int word = 0;
-  HC_CUDA_TRY(ctx, cudaMemcpy(&word, ctx->status_word, sizeof word, cudaMemcpyDeviceToHost));
+  HC_CUDA_TRY(ctx, cudaMemcpyAsync(&word, ctx->status_word, sizeof word, cudaMemcpyDeviceToHost, ctx->own_stream));
+  HC_CUDA_TRY(ctx, cudaStreamSynchronize(ctx->own_stream));
   if (word) {
-    HC_CUDA_TRY(ctx, cudaMemset(ctx->status_word, 0, sizeof word));
+    HC_CUDA_TRY(ctx, cudaMemsetAsync(ctx->status_word, 0, sizeof word, ctx->own_stream));
+    HC_CUDA_TRY(ctx, cudaStreamSynchronize(ctx->own_stream));
     char msg[96];
     snprintf(msg, sizeof msg, "a bounded device-side wait expired (status bits 0x%x)", word);
     return fail(ctx, HC_ERR_TIMEOUT, msg);
