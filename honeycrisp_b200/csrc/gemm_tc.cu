@@ -453,7 +453,10 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap mapA_hi, const __grid_constan
   constexpr int PARTS = kTf32 ? 2 : 1;
   constexpr uint32_t A_BYTES = BM * 128, B_PART_BYTES = BN_LOCAL * 128, B_BYTES = kNSplit * B_PART_BYTES,
                      STAGE_BYTES = PARTS * (A_BYTES + B_BYTES);
-  constexpr uint32_t STG_BYTES_PER_WARP = kWindowed ? 4096u : 8192u;   // store staging: one or two buffers
+  // Store staging per epilogue warp: two 4 KB buffers, or one where shared memory is short (the
+  // windowed epilogue, and eight epilogue warps next to the 48 KB slots of the 512-wide tiles).
+  constexpr int STG_BUFS = (kWindowed || (kEpiWarps == 8 && kNSplit == 2)) ? 1 : 2;
+  constexpr uint32_t STG_BYTES_PER_WARP = STG_BUFS * 4096u;
   constexpr int TMEM_COLS = (2 * kBN <= 32) ? 32 : 2 * kBN;
   constexpr int COL_SPLIT = kEpiWarps / 4;   // epilogue warps sharing one lane quarter
   constexpr int COLS_PER_THREAD = TILE_N / COL_SPLIT;
@@ -689,13 +692,13 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap mapA_hi, const __grid_constan
           // Each warp rounds its 32 rows x 128 bytes into a swizzled staging buffer and one lane
           // sends it with a TMA store (full 128-byte lines); two buffers per warp alternate.
           constexpr int COLS_PER_BUF = kOutHalf ? 64 : 32;   // columns in one 128-byte staging row
-          constexpr int LOADS = kOutHalf ? 4 : 2;            // tcgen05.ld.x32 per pass (two buffers)
-          static_assert(COLS_PER_THREAD % (2 * COLS_PER_BUF) == 0, "a pass fills both staging buffers");
+          constexpr int LOADS = STG_BUFS * (kOutHalf ? 2 : 1);   // tcgen05.ld.x32 per pass (all staging buffers)
+          static_assert(COLS_PER_THREAD % (STG_BUFS * COLS_PER_BUF) == 0, "a pass fills every staging buffer");
           const int m_warp = t.tm * (BM * kCta) + (int)rank * BM + quarter * 32;
           const uint32_t row_addr = stg_base + (uint32_t)lane * 128u;
           const uint32_t sw = (uint32_t)(lane & 7);
 #pragma unroll 1
-          for (int c = 0; c < COLS_PER_THREAD; c += 2 * COLS_PER_BUF) {
+          for (int c = 0; c < COLS_PER_THREAD; c += STG_BUFS * COLS_PER_BUF) {
             uint32_t r[LOADS][32];
 #pragma unroll
             for (int l = 0; l < LOADS; l++) tmem_ld_x32(tbase + c + 32 * l, r[l]);
@@ -740,7 +743,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap mapA_hi, const __grid_constan
             __syncwarp();
             if (store_leader && m_warp < p.M) {
 #pragma unroll
-              for (int b2 = 0; b2 < 2; b2++) {
+              for (int b2 = 0; b2 < STG_BUFS; b2++) {
                 const int64_t col = n0 + c + b2 * COLS_PER_BUF;
                 if (col < p.N) {
                   for (int d = 0; d < p.n_out; d++)
@@ -1035,7 +1038,7 @@ template <int kElemBytes, int kBN, int kStages, int kEpiWarps, bool kWindowed, i
 struct TcConfig {
   // operand ring (float32 slots also hold the lo slabs) + store staging + alignment slack
   static constexpr size_t smem = (size_t)kStages * (kElemBytes == 4 ? 2 : 1) * (BM * 128 + kNSplit * (kBN / kCta) * 128) +
-                                 (size_t)kEpiWarps * (kWindowed ? 4096 : 8192) + 1024;
+                                 (size_t)kEpiWarps * ((kWindowed || (kEpiWarps == 8 && kNSplit == 2)) ? 4096 : 8192) + 1024;
   static_assert(smem <= 232448, "more shared memory than one CTA can have on sm_100");
   static constexpr int block = 64 + 32 * kEpiWarps;
   static auto kernel() { return tc_gemm_kernel<kElemBytes, kBN, kStages, kEpiWarps, kWindowed, kCta, kNSplit>; }
@@ -1268,6 +1271,8 @@ cudaError_t launch_tc(const GemmProblem& p, cudaStream_t stream, unsigned int* s
     // Short contractions are bound by draining results, not by the MMA: more epilogue warps,
     // fewer operand stages.
     const bool short_k = tp.num_k_blocks <= env_int("HC_TC_SHORT_K", 8);
+    if (wide && env_int("HC_TC_WIDE_EPI8", 1))
+      return TcConfig<2, 256, 4, 8, false, 2, 2>::launch(maps, outs, tp, sm_count, stream, rec);
     if (wide) return TcConfig<2, 256, 4, 4, false, 2, 2>::launch(maps, outs, tp, sm_count, stream, rec);
     if (cta == 2 && short_k) return TcConfig<2, 256, 4, 8, false, 2>::launch(maps, outs, tp, sm_count, stream, rec);
     if (cta == 2) return TcConfig<2, 256, 6, 4, false, 2>::launch(maps, outs, tp, sm_count, stream, rec);
