@@ -99,7 +99,10 @@ def load() -> ctypes.CDLL:
     if _lib is not None:
         return _lib
     path = _build.LIB_PATH
-    if not os.path.exists(path) or os.environ.get("HC_CUDA_REBUILD") == "1":
+    override = os.environ.get("HC_CUDA_LIB")     # a differently built libhccuda.so, for A/B runs
+    if override:
+        path = override
+    elif not os.path.exists(path) or os.environ.get("HC_CUDA_REBUILD") == "1":
         path = _build.build(force=True)
     elif _build._stale():
         # Sources are newer than the library: rebuild if a compiler is at hand, otherwise say so
