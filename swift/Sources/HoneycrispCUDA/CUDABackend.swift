@@ -105,8 +105,19 @@ open class CUDABackend: Backend, @unchecked Sendable {
 
   deinit { hc_destroy(ctx) }
 
-  func offload<T>(_ fn: @escaping () throws -> T) async throws -> T {
-    try await worker.schedule(fn)
+  /// Run a blocking piece of work (a sync, a copy) on the backend's worker thread and resume
+  /// the caller with its result - the same hand-off CPUBackend.serialize makes
+  /// (BackendCPU.swift:235-248) over Backend.WorkerThread.schedule (Backend.swift:160-162).
+  func offload<T>(_ fn: @escaping @Sendable () throws -> T) async throws -> T {
+    try await withCheckedThrowingContinuation { continuation in
+      worker.schedule {
+        do {
+          continuation.resume(returning: try fn())
+        } catch {
+          continuation.resume(throwing: error)
+        }
+      }
+    }
   }
 
   func check(_ st: hc_status) throws {
