@@ -1234,7 +1234,7 @@ cudaError_t launch_tc(const GemmProblem& p, cudaStream_t stream, unsigned int* s
   tp.chunk_kb = windowed ? window_slabs() : tp.num_k_blocks;
   if (tp.chunk_kb > tp.num_k_blocks) tp.chunk_kb = tp.num_k_blocks;
   // Wide tiles (256 x 512 per CTA pair) for long float16 contractions over wide products.
-  const int wide_min_kb = env_int("HC_TC_WIDE_MIN_KB", 48);
+  const int wide_min_kb = env_int("HC_TC_WIDE_MIN_KB", 32);
   const bool wide = !f32 && cta == 2 && tp.num_k_blocks >= wide_min_kb && p.N >= 1024;
   const int tile_n = wide ? 2 * bn : bn;
   tp.tile_rows = BM * cta;
