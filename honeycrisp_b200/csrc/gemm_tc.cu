@@ -940,6 +940,27 @@ __global__ void __launch_bounds__(256) split_tf32_kernel(const SplitJob ja, cons
   }
 }
 
+// float16 operands whose base or pitches TMA cannot address are copied once into a packed,
+// 16-byte aligned area (same values, leading dimension rounded up to eight elements).
+struct RepackJob {
+  const __half* src;
+  __half* dst;
+  int64_t rows, width, ld_src, ld_dst, stride_src, stride_dst, batch;
+};
+__global__ void __launch_bounds__(256) repack_f16_kernel(const RepackJob ja, const RepackJob jb, int blocks_a) {
+  pdl_release();
+  pdl_wait();
+  const bool is_a = (int)blockIdx.x < blocks_a;
+  const RepackJob& j = is_a ? ja : jb;
+  const int64_t bid = is_a ? blockIdx.x : blockIdx.x - blocks_a;
+  const int64_t nblk = is_a ? blocks_a : (int64_t)gridDim.x - blocks_a;
+  const int64_t total = j.batch * j.rows * j.width;
+  for (int64_t i = bid * blockDim.x + threadIdx.x; i < total; i += nblk * blockDim.x) {
+    const int64_t c = i % j.width, r = (i / j.width) % j.rows, b = i / (j.width * j.rows);
+    j.dst[b * j.stride_dst + r * j.ld_dst + c] = j.src[b * j.stride_src + r * j.ld_src + c];
+  }
+}
+
 // ---- host side ------------------------------------------------------------------------------
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
@@ -1120,12 +1141,13 @@ cudaError_t launch_wait_probe(cudaStream_t stream, unsigned int* status_word, un
   return cudaGetLastError();
 }
 
+// Any product of sane size runs on the tensor cores: operands TMA cannot address directly
+// (unaligned base, pitches that are not 16-byte multiples) are repacked into the work area first
+// - the float32 split does that anyway - and a result TMA cannot address is stored from registers.
 bool tc_supported(const GemmProblem& p) {
   if (p.M <= 0 || p.N <= 0 || p.K <= 0 || p.batch <= 0) return false;
-  const int eb = p.dtype == HC_F16 ? 2 : 4;
-  if (!operand_ok(p.A, eb, p.lda, p.strideA, p.batch, p.M, p.K)) return false;
-  if (!operand_ok(p.B, eb, p.ldb, p.strideB, p.batch, p.N, p.K)) return false;
-  if (p.M >= (1ll << 31) - 256 || p.N >= (1ll << 31) - 256 || p.K >= (1ll << 31) - 256) return false;
+  if (p.M >= (1ll << 31) - 256 || p.N >= (1ll << 31) - 256 || p.K >= (1ll << 31) - 256 || p.batch >= (1ll << 31))
+    return false;
   return encode_fn() != nullptr;
 }
 
@@ -1147,8 +1169,30 @@ static SplitLayout split_layout(const GemmProblem& p) {
   return s;
 }
 
+// float16 operands that need repacking: packed copy with the leading dimension rounded to 8.
+struct RepackLayout {
+  bool a, b;
+  int64_t a_rows, a_width, a_ld, a_mat, b_rows, b_width, b_ld, b_mat;
+  size_t a_bytes, b_bytes;
+};
+static RepackLayout repack_layout(const GemmProblem& p) {
+  RepackLayout r;
+  r.a = !operand_ok(p.A, 2, p.lda, p.strideA, p.batch, p.M, p.K);
+  r.b = !operand_ok(p.B, 2, p.ldb, p.strideB, p.batch, p.N, p.K);
+  r.a_rows = p.a_mn_major ? p.K : p.M; r.a_width = p.a_mn_major ? p.M : p.K;
+  r.b_rows = p.b_mn_major ? p.K : p.N; r.b_width = p.b_mn_major ? p.N : p.K;
+  r.a_ld = (r.a_width + 7) & ~7ll; r.b_ld = (r.b_width + 7) & ~7ll;
+  r.a_mat = r.a_rows * r.a_ld; r.b_mat = r.b_rows * r.b_ld;
+  r.a_bytes = r.a ? (((size_t)(r.a_mat * p.batch) * 2 + 255) & ~(size_t)255) : 0;
+  r.b_bytes = r.b ? (((size_t)(r.b_mat * p.batch) * 2 + 255) & ~(size_t)255) : 0;
+  return r;
+}
+
 size_t tc_scratch_bytes(const GemmProblem& p) {
-  if (p.dtype != HC_F32) return 0;
+  if (p.dtype != HC_F32) {
+    const RepackLayout r = repack_layout(p);
+    return r.a_bytes + r.b_bytes;
+  }
   const SplitLayout s = split_layout(p);
   return 2 * s.a_bytes + 2 * s.b_bytes;
 }
@@ -1164,6 +1208,36 @@ cudaError_t launch_tc(const GemmProblem& p, cudaStream_t stream, unsigned int* s
 
   const void *a_hi = p.A, *a_lo = p.A, *b_hi = p.B, *b_lo = p.B;
   int64_t lda = p.lda, ldb = p.ldb, sa = p.strideA, sb = p.strideB;
+  if (!f32) {
+    const RepackLayout r = repack_layout(p);
+    if (r.a || r.b) {
+      if (!scratch || scratch_bytes < r.a_bytes + r.b_bytes) return cudaErrorInvalidValue;
+      __half* ra = (__half*)scratch;
+      __half* rb = (__half*)((char*)scratch + r.a_bytes);
+      RepackJob ja{(const __half*)p.A, ra, r.a_rows, r.a_width, p.lda, r.a_ld, p.strideA, r.a_mat, r.a ? p.batch : 0};
+      RepackJob jb{(const __half*)p.B, rb, r.b_rows, r.b_width, p.ldb, r.b_ld, p.strideB, r.b_mat, r.b ? p.batch : 0};
+      auto blocks = [&](const RepackJob& j) {
+        const int64_t work = j.batch * j.rows * j.width;
+        int64_t b = (work + 255) / 256;
+        return (int)(b > 148 * 8 ? 148 * 8 : b);   // zero blocks for an operand that stays in place
+      };
+      const int blocks_a = blocks(ja), blocks_b = blocks(jb);
+      cudaLaunchConfig_t rcfg = {};
+      rcfg.gridDim = dim3((unsigned)(blocks_a + blocks_b));
+      rcfg.blockDim = dim3(256);
+      rcfg.stream = stream;
+      cudaLaunchAttribute rattr;
+      rattr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+      rattr.val.programmaticStreamSerializationAllowed = 1;
+      rcfg.attrs = &rattr;
+      rcfg.numAttrs = overlap_launches() ? 1 : 0;
+      cudaError_t re = cudaLaunchKernelEx(&rcfg, repack_f16_kernel, ja, jb, blocks_a);
+      if (re != cudaSuccess) return re;
+      if (rec) { rec->launches += 1; rec->scratch_bytes = r.a_bytes + r.b_bytes; }
+      if (r.a) { a_hi = a_lo = ra; lda = r.a_ld; sa = r.a_mat; }
+      if (r.b) { b_hi = b_lo = rb; ldb = r.b_ld; sb = r.b_mat; }
+    }
+  }
   if (f32) {
     const SplitLayout s = split_layout(p);
     if (!scratch || scratch_bytes < 2 * s.a_bytes + 2 * s.b_bytes) return cudaErrorInvalidValue;

@@ -171,8 +171,7 @@ hc_status run_problem(hc_ctx* ctx, hc_kernel kernel, const hc::GemmProblem& p, i
   cudaError_t e;
   if (chosen == HC_KERNEL_TENSOR) {
     if (!hc::tc_supported(p))
-      return fail(ctx, HC_ERR_NOT_IMPLEMENTED,
-                  "tensor-core kernel needs 16-byte aligned operands and leading dimensions");
+      return fail(ctx, HC_ERR_NOT_IMPLEMENTED, "product too large for the tensor-core kernel's 32-bit tile coordinates");
     const size_t need = hc::tc_scratch_bytes(p);
     if (need) {
       hc_status s = ensure_buffer(ctx, &ctx->scratch, &ctx->scratch_bytes, need);

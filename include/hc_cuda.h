@@ -60,8 +60,9 @@ typedef enum hc_kernel {
   HC_KERNEL_SIMT = 1,       /* CUDA-core kernel, fused multiply-add, any shape/alignment */
   HC_KERNEL_SIMT_EXACT = 2, /* same, separate multiply and add in k order: bit-identical to
                                the reference CPU loop (BackendCPU.swift:1290-1300) */
-  HC_KERNEL_TENSOR = 3      /* tcgen05 path: fp16 direct; fp32 as 3xTF32 split operands.
-                               HC_ERR_NOT_IMPLEMENTED if the shape cannot be described to TMA */
+  HC_KERNEL_TENSOR = 3      /* tcgen05 path: fp16 direct; fp32 as 3xTF32 split operands.  Operands
+                               whose base or row pitch is not 16-byte aligned are repacked into
+                               the context's work area first. */
 } hc_kernel;
 
 typedef struct hc_launch_info {

@@ -207,15 +207,32 @@ def test_undersized_operand_is_rejected(be):
         be.matmul(np.zeros(5, np.float32), False, np.zeros(6, np.float32), False, False, 2, 3, 2, np.float32)
 
 
-def test_tensor_kernel_refuses_misaligned_shapes_and_auto_falls_back(be):
-    from honeycrisp_b200 import NotImplementedByBackend
-    A, B = random_operands(2, 1, 130, 67, 129, np.float16)   # leading dimensions not 16-byte multiples
-    with pytest.raises(NotImplementedByBackend):
-        run(be, 1, A, B, False, False, False, np.float16, kernel=K().HC_KERNEL_TENSOR)
+def test_misaligned_operands_are_repacked_for_the_tensor_cores(be):
+    """Leading dimensions that are not 16-byte multiples (and an operand at an odd address) cannot
+    be described to TMA; the operands are copied once into the aligned work area and the product
+    still runs on the tensor cores, in every flag combination and both dtypes."""
+    for dtype, tol in ((np.float16, 2e-3), (np.float32, 1e-5)):
+        for (ta, tb, to) in FLAG_COMBOS:
+            A, B = random_operands(2, 2, 130, 67, 129, dtype)
+            res, a_st, b_st = run(be, 2, A, B, ta, tb, to, dtype, kernel=K().HC_KERNEL_TENSOR)
+            info = be.lastLaunchInfo()
+            assert info["kernel"] == K().HC_KERNEL_TENSOR and info["scratch_bytes"] > 0
+            orc = ref.batched_matmul(2, a_st, ta, b_st, tb, to, 130, 67, 129, library_fast_path=False)
+            assert ref.rel_frobenius(res, orc) < tol, (dtype, ta, tb, to)
+    # an operand that starts two bytes into an allocation
+    A, B = random_operands(3, 1, 256, 128, 264, np.float16)
+    raw = be.collection(np.concatenate([np.zeros(1, np.float16), A.reshape(-1)]), np.float16)
+    shifted = be.wrap(raw.ptr + 2, A.size * 2, owner=raw)
+    got = be.matmul(shifted, False, B.reshape(-1), False, False, 256, 128, 264, np.float16,
+                    kernel=K().HC_KERNEL_TENSOR).onCPU(np.float16)[: 256 * 264]
+    want = be.matmul(A.reshape(-1), False, B.reshape(-1), False, False, 256, 128, 264, np.float16,
+                     kernel=K().HC_KERNEL_TENSOR).onCPU(np.float16)[: 256 * 264]
+    assert np.array_equal(got.view(np.uint16), want.view(np.uint16))
+    # the default dispatch sends tiny products to the CUDA-core kernel, bit-identical to the CPU loop
+    A, B = random_operands(4, 1, 30, 17, 29, np.float16)
     res, a_st, b_st = run(be, 1, A, B, False, False, False, np.float16, kernel=0)
     assert be.lastLaunchInfo()["kernel"] == K().HC_KERNEL_SIMT
-    orc = ref.matmul(a_st, False, b_st, False, False, 130, 67, 129)
-    assert np.array_equal(res.view(np.uint16), orc.view(np.uint16))
+    assert np.array_equal(res.view(np.uint16), ref.matmul(a_st, False, b_st, False, False, 30, 17, 29).view(np.uint16))
 
 
 def test_host_buffer_entry_point(be):
