@@ -512,7 +512,38 @@ def run_probe(args):
         torch.cuda.synchronize()
         be.checkDeviceStatus()
         ms = e0.elapsed_time(e1) / (5 * args.steps)
+    lib_ms = None
+    if args.compare_library:
+        # the vendor library (cuBLAS through torch.matmul) on the same operands, timed the same way
+        if args.dtype == "f32":
+            torch.backends.cuda.matmul.allow_tf32 = False
+        A = a.transpose(-1, -2) if ta else a
+        B = b.transpose(-1, -2) if tb else b
+        ref_out = torch.empty_like(out)
+        run_lib = lambda: torch.matmul(A, B, out=ref_out)
+        for _ in range(3):
+            run_lib()
+        if args.graph:
+            g2 = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g2, stream=stream):
+                for _ in range(args.steps):
+                    run_lib()
+            g2.replay()
+            e0.record(stream)
+            for _ in range(5):
+                g2.replay()
+            e1.record(stream)
+            torch.cuda.synchronize()
+            lib_ms = e0.elapsed_time(e1) / (5 * args.steps)
+        else:
+            e0.record(stream)
+            for _ in range(args.steps):
+                run_lib()
+            e1.record(stream)
+            torch.cuda.synchronize()
+            lib_ms = e0.elapsed_time(e1) / args.steps
     emit({"probe": [M, K, N, cnt], "dtype": args.dtype, "flags": [ta, tb], "ms": ms, "graph": bool(args.graph),
+          "library_ms": lib_ms, "library_tflops": (2.0 * cnt * M * N * K / lib_ms / 1e9) if lib_ms else None,
           "tflops": 2.0 * cnt * M * N * K / ms / 1e9, "kernel": be.lastLaunchInfo()})
 
 
@@ -621,6 +652,7 @@ def main():
     ap.add_argument("--dtype", choices=["f16", "f32"], default="f16")
     ap.add_argument("--flags", default="0,1", help="transA,transB for --probe")
     ap.add_argument("--graph", action="store_true", help="--probe: time CUDA-graph replays of the launches")
+    ap.add_argument("--compare-library", action="store_true", help="--probe: also time torch.matmul (cuBLAS)")
     args = ap.parse_args()
     if args.probe:
         run_probe(args)
