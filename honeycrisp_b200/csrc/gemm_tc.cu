@@ -159,7 +159,23 @@ __device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity, volat
     if (globaltimer_ns() - t0 > limit_ns) return false;
   }
 }
+// The non-blocking probe: it answers in about half the time of try_wait (which may suspend
+// the thread), so every wait starts with it - in a full pipeline the phase is usually complete.
+__device__ __forceinline__ bool mbar_test_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+      "selp.u32 %0, 1, 0, p;\n"
+      "}\n"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+  if (mbar_test_wait(bar, parity)) return true;
 #pragma unroll 1
   for (int i = 0; i < 16; i++)
     if (mbar_try_wait(bar, parity)) return true;
@@ -425,6 +441,13 @@ __device__ __forceinline__ TileCoord decode_tile(int64_t tile, const TcParams& p
   return t;
 }
 
+// Store staging buffers (4 KB each) per epilogue warp: two that alternate, or one where shared
+// memory is short (the windowed epilogue, and eight epilogue warps next to the 48 KB slots of the
+// 512-wide tiles) or where a warp's share of the tile is a single buffer wide.
+__host__ __device__ constexpr int staging_bufs(int elem_bytes, int bn, int epi_warps, bool windowed, int nsplit) {
+  return (windowed || (epi_warps == 8 && nsplit == 2) || (bn * nsplit / (epi_warps / 4)) < 2 * (128 / elem_bytes)) ? 1 : 2;
+}
+
 // kElemBytes: 2 (float16 operands) or 4 (float32 operands consumed as TF32).
 // kBN       : columns of one tcgen05.mma (and of one accumulator buffer).
 // kNSplit   : 1, or 2 for tiles two MMAs wide (512 columns) whose halves take the two accumulator
@@ -432,7 +455,9 @@ __device__ __forceinline__ TileCoord decode_tile(int64_t tile, const TcParams& p
 //             next tile (used for long contractions only).
 // kWindowed : epilogue sums accumulation windows in registers (float32 output only).
 // kCta      : 1, or 2 for CTA pairs (cluster of two, 256-row tiles, one MMA over both SMs).
-template <int kElemBytes, int kBN, int kStages, int kEpiWarps, bool kWindowed, int kCta, int kNSplit>
+// kSlabs    : 128-byte k slabs per pipeline slot.  Two halve the barrier round trips per k, which
+//             is what bounds the small tile shapes (their MMAs are shorter than the issue loop).
+template <int kElemBytes, int kBN, int kStages, int kEpiWarps, bool kWindowed, int kCta, int kNSplit, int kSlabs>
 __global__ void __launch_bounds__(64 + 32 * kEpiWarps, 1)
 tc_gemm_kernel(const __grid_constant__ CUtensorMap mapA_hi, const __grid_constant__ CUtensorMap mapA_lo,
                const __grid_constant__ CUtensorMap mapB_hi, const __grid_constant__ CUtensorMap mapB_lo,
@@ -452,10 +477,9 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap mapA_hi, const __grid_constan
   // A pipeline slot: [A (hi) | A lo] [B (hi) | B lo]; the lo slabs exist for float32 only.
   constexpr int PARTS = kTf32 ? 2 : 1;
   constexpr uint32_t A_BYTES = BM * 128, B_PART_BYTES = BN_LOCAL * 128, B_BYTES = kNSplit * B_PART_BYTES,
-                     STAGE_BYTES = PARTS * (A_BYTES + B_BYTES);
-  // Store staging per epilogue warp: two 4 KB buffers, or one where shared memory is short (the
-  // windowed epilogue, and eight epilogue warps next to the 48 KB slots of the 512-wide tiles).
-  constexpr int STG_BUFS = (kWindowed || (kEpiWarps == 8 && kNSplit == 2)) ? 1 : 2;
+                     SLAB_BYTES = PARTS * (A_BYTES + B_BYTES), STAGE_BYTES = kSlabs * SLAB_BYTES;
+  static_assert(kSlabs == 1 || !kWindowed, "accumulation windows count single slabs");
+  constexpr int STG_BUFS = staging_bufs(kElemBytes, kBN, kEpiWarps, kWindowed, kNSplit);
   constexpr uint32_t STG_BYTES_PER_WARP = STG_BUFS * 4096u;
   constexpr int TMEM_COLS = (2 * kBN <= 32) ? 32 : 2 * kBN;
   constexpr int COL_SPLIT = kEpiWarps / 4;   // epilogue warps sharing one lane quarter
@@ -511,9 +535,10 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap mapA_hi, const __grid_constan
   tc_fence_after();
   const uint32_t tmem_base = tmem_base_slot;
   volatile int* abortp = &abort_flag;
-  // Barriers and tensor memory are set up; from here on the kernel reads operands that an
-  // earlier kernel in the stream may have produced and overwrites results it may have read.
-  pdl_wait();
+  // Barriers and tensor memory are set up.  Each role that touches global memory (the producer
+  // reads operands an earlier kernel in the stream may have produced, the epilogue overwrites
+  // results it may have read) waits for that kernel below, after the part of its own setup that
+  // only needs the launch parameters: tensor-map prefetch and the first tile's coordinates.
 
   const int nkb = p.num_k_blocks;
   const int chunk_kb = p.chunk_kb;
@@ -525,11 +550,17 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap mapA_hi, const __grid_constan
       asm volatile("prefetch.tensormap [%0];" ::"l"((unsigned long long)&mapA_hi) : "memory");
       asm volatile("prefetch.tensormap [%0];" ::"l"((unsigned long long)&mapB_hi) : "memory");
       // Completion bytes of both CTAs of a pair are counted on the leader's barrier.
+      if (kTf32) {
+        asm volatile("prefetch.tensormap [%0];" ::"l"((unsigned long long)&mapA_lo) : "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"((unsigned long long)&mapB_lo) : "memory");
+      }
       const uint32_t full_leader = (kCta == 2) ? map_to_cta(bar_full, 0) : bar_full;
       uint32_t s = 0, ph = 0;
       bool ok = true;
+      TileCoord t = decode_tile(tile_first < p.total_tiles ? tile_first : 0, p);
+      pdl_wait();
       for (int64_t tile = tile_first; ok && tile < p.total_tiles; tile += tile_step) {
-        const TileCoord t = decode_tile(tile, p);
+        if (tile != tile_first) t = decode_tile(tile, p);
         const int m0 = t.tm * (BM * kCta) + (int)rank * BM;
         const int n0 = t.tn * TILE_N + (int)rank * BN_LOCAL;
         const int mat = (int)t.mat;
@@ -540,15 +571,18 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap mapA_hi, const __grid_constan
             ok = false;
             break;
           }
-          const int kc = kb * BK;
           const uint32_t full = full_leader + 8 * s;
-          const uint32_t stage = smem_base + s * STAGE_BYTES;
           if (p.debug & 8) {  // timing experiment: no copies
             if (rank == 0) mbar_expect_tx(bar_full + 8 * s, 0);
             if (++s == kStages) { s = 0; ph ^= 1; }
             continue;
           }
           if (rank == 0) mbar_expect_tx(bar_full + 8 * s, STAGE_BYTES * kCta);
+          // A slab past the end of K lies outside the tensor and arrives as zeros.
+#pragma unroll
+          for (int j = 0; j < kSlabs; j++) {
+          const int kc = (kb * kSlabs + j) * BK;
+          const uint32_t stage = smem_base + s * STAGE_BYTES + j * SLAB_BYTES;
 #pragma unroll
           for (int part = 0; part < PARTS; part++) {   // 0: the operand itself (hi), 1: its lo half
             const CUtensorMap* ma = part ? &mapA_lo : &mapA_hi;
@@ -572,6 +606,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap mapA_hi, const __grid_constan
                   tma_load_3d<kCta>(sbh + c * (BK * 128), mb, full, n0h + c * CH, kc, mat);
               }
             }
+          }
           }
           if (++s == kStages) { s = 0; ph ^= 1; }
         }
@@ -605,8 +640,12 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap mapA_hi, const __grid_constan
       uint32_t s = 0, ph = 0, win = 0, slot = 0;
       bool ok = true;
       for (int64_t tile = tile_first; ok && tile < p.total_tiles; tile += tile_step) {
+        // This loop is one thread's serial instruction stream and has to stay shorter than the
+        // MMAs of one k block take to execute (512 clocks for a 256x256 pair tile), or the tensor
+        // pipe waits for the issuer: no division, no blocking probe on the usual path.
+        int in_win = -1;   // position of this k block in its accumulation window
         for (int kb = 0; kb < nkb; kb++) {
-          const int in_win = kb % chunk_kb;
+          if (++in_win == chunk_kb) in_win = 0;
           if (in_win == 0) {
             slot = win % ACC_SLOTS;
             if (!mbar_wait(bar_tempty + 8 * slot, ((win / ACC_SLOTS) & 1) ^ 1, abortp)) {
@@ -624,10 +663,12 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap mapA_hi, const __grid_constan
             break;
           }
           tc_fence_after();
-          const uint32_t stage = smem_base + s * STAGE_BYTES;
           // float16: one product per slab.  float32: A_lo*B_hi, A_hi*B_lo, A_hi*B_hi - the two
           // small products first, all into the same accumulator.
           constexpr int PRODUCTS = kTf32 ? 3 : 1;
+#pragma unroll
+          for (int j = 0; j < kSlabs; j++) {
+          const uint32_t stage = smem_base + s * STAGE_BYTES + j * SLAB_BYTES;
 #pragma unroll
           for (int pr = 0; pr < PRODUCTS; pr++) {
             const int a_part = (kTf32 && pr == 0) ? 1 : 0, b_part = (kTf32 && pr == 1) ? 1 : 0;
@@ -641,9 +682,10 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap mapA_hi, const __grid_constan
               for (int k = 0; k < BK / UMMA_K; k++) {
                 if (p.debug & 16) break;  // timing experiment: no MMAs
                 tc_mma<kTf32, kCta>(d, adesc + (uint64_t)((k * a_kstep) >> 4), bdesc + (uint64_t)((k * b_kstep) >> 4),
-                                    idesc, (in_win | pr | k) ? 1u : 0u);
+                                    idesc, (in_win | j | pr | k) ? 1u : 0u);
               }
             }
+          }
           }
           tc_commit<kCta>(bar_empty + 8 * s);
           if (kCta == 2) tc_commit<kCta>(empty_peer + 8 * s);
@@ -671,8 +713,11 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap mapA_hi, const __grid_constan
     const bool store_leader = elect_one();
     uint32_t win = 0;
     bool ok = true;
+    if (store_leader && p.tma_store) asm volatile("prefetch.tensormap [%0];" ::"l"((unsigned long long)&mapC.m[0]) : "memory");
+    TileCoord t = decode_tile(tile_first < p.total_tiles ? tile_first : 0, p);
+    pdl_wait();
     for (int64_t tile = tile_first; ok && tile < p.total_tiles; tile += tile_step) {
-      const TileCoord t = decode_tile(tile, p);
+      if (tile != tile_first) t = decode_tile(tile, p);
       const int64_t gm = (int64_t)t.tm * (BM * kCta) + rank * BM + quarter * 32 + lane;
       const int64_t n0 = (int64_t)t.tn * TILE_N + col0;
       void* cmat = kOutHalf ? (void*)((__half*)p.C + t.mat * p.strideC) : (void*)((float*)p.C + t.mat * p.strideC);
@@ -1055,14 +1100,14 @@ bool overlap_launches() {
   return v != 0;
 }
 
-template <int kElemBytes, int kBN, int kStages, int kEpiWarps, bool kWindowed, int kCta, int kNSplit = 1>
+template <int kElemBytes, int kBN, int kStages, int kEpiWarps, bool kWindowed, int kCta, int kNSplit = 1, int kSlabs = 1>
 struct TcConfig {
   // operand ring (float32 slots also hold the lo slabs) + store staging + alignment slack
-  static constexpr size_t smem = (size_t)kStages * (kElemBytes == 4 ? 2 : 1) * (BM * 128 + kNSplit * (kBN / kCta) * 128) +
-                                 (size_t)kEpiWarps * ((kWindowed || (kEpiWarps == 8 && kNSplit == 2)) ? 4096 : 8192) + 1024;
+  static constexpr size_t smem = (size_t)kStages * kSlabs * (kElemBytes == 4 ? 2 : 1) * (BM * 128 + kNSplit * (kBN / kCta) * 128) +
+                                 (size_t)kEpiWarps * staging_bufs(kElemBytes, kBN, kEpiWarps, kWindowed, kNSplit) * 4096 + 1024;
   static_assert(smem <= 232448, "more shared memory than one CTA can have on sm_100");
   static constexpr int block = 64 + 32 * kEpiWarps;
-  static auto kernel() { return tc_gemm_kernel<kElemBytes, kBN, kStages, kEpiWarps, kWindowed, kCta, kNSplit>; }
+  static auto kernel() { return tc_gemm_kernel<kElemBytes, kBN, kStages, kEpiWarps, kWindowed, kCta, kNSplit, kSlabs>; }
 
   static cudaError_t configure() {
     static bool configured[64] = {};
@@ -1126,7 +1171,7 @@ struct TcConfig {
     cfg.numAttrs = overlap_launches() ? 2 : 1;
     e = cudaLaunchKernelEx(&cfg, kernel(), maps[0], maps[1], maps[2], maps[3], outs, p);
     if (rec) {
-      rec->tile_m = BM * kCta; rec->tile_n = kBN * kNSplit; rec->tile_k = 128 / kElemBytes; rec->stages = kStages;
+      rec->tile_m = BM * kCta; rec->tile_n = kBN * kNSplit; rec->tile_k = kSlabs * 128 / kElemBytes; rec->stages = kStages;
       rec->grid = grid; rec->block = block; rec->launches++;
     }
     if (e != cudaSuccess) return e;
@@ -1278,15 +1323,53 @@ cudaError_t launch_tc(const GemmProblem& p, cudaStream_t stream, unsigned int* s
     lda = s.a_ld; ldb = s.b_ld; sa = s.a_mat; sb = s.b_mat;
   }
 
-  // Tile shape: 256 columns unless the product is narrow; CTA pairs (256 rows) when there is
-  // more than one 128-row block of output.
+  // Tile shape.  float16 picks the cheapest of six shapes by a wave model: the cost of a shape is
+  // (waves of tiles over the SMs) x (clocks per tile), with the clocks per 64-wide k block of each
+  // shape measured on large products (relative to 600 for the 256x256 pair) and a fixed cost per
+  // tile for refilling the pipeline.  Large tiles move the fewest operand bytes per flop and win
+  // whenever there are enough tiles to fill the SMs; for small products the small pair shapes
+  // spread the work over more SMs, which shortens the one wave there is.  Only the 256x512
+  // shape cannot hide the result drain behind the next tile.
+  // float32 keeps two rules: 256 columns unless the product is narrow, and 128x128 tiles when
+  // 256x256 pairs would idle more than half the SMs.
   const int dbg = debug_flags();
-  // ... and 128 x 128 single-CTA tiles when 256 x 256 pairs would leave more than half of the
-  // SMs without a tile.
-  const int64_t pair_tiles = ((p.M + 255) / 256) * ((p.N + 255) / 256) * p.batch;
-  const bool few_tiles = pair_tiles * 4 <= sm_count;
-  const int bn = (p.N > 128 && !few_tiles) ? 256 : 128;
-  const int cta = (p.M > BM && bn == 256 && !(dbg & 4)) ? 2 : 1;
+  const int kslabs = (int)((p.K + BK - 1) / BK);
+  enum Shape { SHAPE_AUTO = 0, SHAPE_WIDE, SHAPE_PAIR, SHAPE_C1_256, SHAPE_C1_128, SHAPE_PAIR_128, SHAPE_PAIR_64,
+               SHAPE_COUNT };
+  int shape = SHAPE_AUTO;
+  if (!f32) {
+    const bool pairs_ok = p.M > BM && !(dbg & 4);
+    const bool wide_ok = pairs_ok && p.N >= 1024 && kslabs >= env_int("HC_TC_WIDE_MIN_KB", 32);
+    struct Cand { int shape; bool ok; int rows, cols, slots; double clk_per_kb, drain_per_tile; };
+    const double drain = 2400.0, refill = 300.0;
+    const Cand cands[SHAPE_COUNT - 1] = {
+        {SHAPE_WIDE, wide_ok, 256, 512, sm_count / 2, 1140.0, drain},
+        {SHAPE_PAIR, pairs_ok && p.N > 128, 256, 256, sm_count / 2, 600.0, 0.0},
+        {SHAPE_C1_256, p.N > 128, 128, 256, sm_count, 680.0, 0.0},
+        {SHAPE_C1_128, true, 128, 128, sm_count, 410.0, 0.0},
+        {SHAPE_PAIR_128, pairs_ok && p.N > 64, 256, 128, sm_count / 2, 340.0, 0.0},
+        // 32 columns of B per CTA: half a 128-byte row of an MN-major box, which the copy cannot split
+        {SHAPE_PAIR_64, pairs_ok && !p.b_mn_major, 256, 64, sm_count / 2, 265.0, 0.0},
+    };
+    double best = 0.0;
+    for (const Cand& c : cands) {
+      if (!c.ok || c.slots < 1) continue;
+      const int64_t tiles = ((p.M + c.rows - 1) / c.rows) * ((p.N + c.cols - 1) / c.cols) * p.batch;
+      const int64_t waves = (tiles + c.slots - 1) / c.slots;
+      const double cost =
+          (double)waves * (kslabs * c.clk_per_kb + c.drain_per_tile + refill) + (c.drain_per_tile > 0 ? 0.0 : drain);
+      if (shape == SHAPE_AUTO || cost < best) { shape = c.shape; best = cost; }
+    }
+    const int forced = env_int("HC_TC_SHAPE", 0);
+    if (forced >= 1 && forced < SHAPE_COUNT && cands[forced - 1].ok) shape = forced;
+  } else {
+    const int64_t pair_tiles = ((p.M + 255) / 256) * ((p.N + 255) / 256) * p.batch;
+    const bool few_tiles = pair_tiles * 4 <= sm_count;
+    const bool wide_cols = p.N > 128 && !few_tiles;
+    shape = !wide_cols ? SHAPE_C1_128 : (p.M > BM && !(dbg & 4)) ? SHAPE_PAIR : SHAPE_C1_256;
+  }
+  const int bn = (shape == SHAPE_C1_128 || shape == SHAPE_PAIR_128) ? 128 : shape == SHAPE_PAIR_64 ? 64 : 256;
+  const int cta = (shape == SHAPE_C1_256 || shape == SHAPE_C1_128) ? 1 : 2;
   const int b_box = bn / cta;
   CUtensorMap maps[4];
   OutMaps outs;
@@ -1300,16 +1383,18 @@ cudaError_t launch_tc(const GemmProblem& p, cudaStream_t stream, unsigned int* s
 
   TcParams tp;
   tp.M = p.M; tp.N = p.N;
-  const int kslabs = (int)((p.K + BK - 1) / BK);
-  tp.num_k_blocks = kslabs;
+  // Pipeline slots of the small float16 shapes hold two k slabs.
+  // Short contractions are bound by draining results, not by the MMA: they get more epilogue
+  // warps and fewer operand stages.
+  const bool short_k = kslabs <= env_int("HC_TC_SHORT_K", 8);
+  const int slabs = (!f32 && (shape == SHAPE_PAIR_64 || shape == SHAPE_PAIR_128 || shape == SHAPE_C1_128)) ? 2 : 1;
+  tp.num_k_blocks = (kslabs + slabs - 1) / slabs;
   // float32: a window bounds the number of truncating tensor-core accumulations that feed one
   // correctly rounded float32 add in the epilogue.
   const bool windowed = f32 && !(dbg & 2);
   tp.chunk_kb = windowed ? window_slabs() : tp.num_k_blocks;
   if (tp.chunk_kb > tp.num_k_blocks) tp.chunk_kb = tp.num_k_blocks;
-  // Wide tiles (256 x 512 per CTA pair) for long float16 contractions over wide products.
-  const int wide_min_kb = env_int("HC_TC_WIDE_MIN_KB", 32);
-  const bool wide = !f32 && cta == 2 && tp.num_k_blocks >= wide_min_kb && p.N >= 1024;
+  const bool wide = shape == SHAPE_WIDE;
   const int tile_n = wide ? 2 * bn : bn;
   tp.tile_rows = BM * cta;
   tp.tiles_m = (int)((p.M + tp.tile_rows - 1) / tp.tile_rows);
@@ -1342,16 +1427,15 @@ cudaError_t launch_tc(const GemmProblem& p, cudaStream_t stream, unsigned int* s
   if (rec) rec->tiles = tp.total_tiles;
 
   if (!f32) {
-    // Short contractions are bound by draining results, not by the MMA: more epilogue warps,
-    // fewer operand stages.
-    const bool short_k = tp.num_k_blocks <= env_int("HC_TC_SHORT_K", 8);
     if (wide && env_int("HC_TC_WIDE_EPI8", 1))
       return TcConfig<2, 256, 4, 8, false, 2, 2>::launch(maps, outs, tp, sm_count, stream, rec);
     if (wide) return TcConfig<2, 256, 4, 4, false, 2, 2>::launch(maps, outs, tp, sm_count, stream, rec);
+    if (shape == SHAPE_PAIR_128) return TcConfig<2, 128, 4, 4, false, 2, 1, 2>::launch(maps, outs, tp, sm_count, stream, rec);
+    if (shape == SHAPE_PAIR_64) return TcConfig<2, 64, 4, 4, false, 2, 1, 2>::launch(maps, outs, tp, sm_count, stream, rec);
     if (cta == 2 && short_k) return TcConfig<2, 256, 4, 8, false, 2>::launch(maps, outs, tp, sm_count, stream, rec);
     if (cta == 2) return TcConfig<2, 256, 6, 4, false, 2>::launch(maps, outs, tp, sm_count, stream, rec);
     if (bn == 256) return TcConfig<2, 256, 4, 4, false, 1>::launch(maps, outs, tp, sm_count, stream, rec);
-    return TcConfig<2, 128, 6, 4, false, 1>::launch(maps, outs, tp, sm_count, stream, rec);
+    return TcConfig<2, 128, 3, 4, false, 1, 1, 2>::launch(maps, outs, tp, sm_count, stream, rec);
   }
   if (windowed) {
     if (cta == 2) return TcConfig<4, 256, 3, 8, true, 2>::launch(maps, outs, tp, sm_count, stream, rec);

@@ -59,6 +59,37 @@ def test_half_all_flag_combinations(be, shape):
             assert ref.rel_frobenius(res, orc) < 1e-3, (shape, ta, tb, to)
 
 
+# HC_TC_SHAPE forces one of the six float16 tile shapes (read at every launch) where the product
+# admits it; AUTO picks among them by cost, so each needs its own parity run.
+TILE_SHAPES = {1: (256, 512), 2: (256, 256), 3: (128, 256), 4: (128, 128), 5: (256, 128), 6: (256, 64)}
+
+
+@pytest.mark.parametrize("forced", sorted(TILE_SHAPES))
+def test_half_every_tile_shape(be, forced, monkeypatch):
+    monkeypatch.setenv("HC_TC_SHAPE", str(forced))
+    M, Kd, N, cnt = 520, 2056, 1096, 2   # ragged in every dimension, long enough for the 512-wide tiles
+    used = set()
+    for (ta, tb, to) in FLAG_COMBOS:
+        A, B = random_operands(forced, cnt, M, Kd, N, np.float16)
+        res, a_st, b_st = run(be, cnt, A, B, ta, tb, to, np.float16, TENSOR())
+        info = be.lastLaunchInfo()
+        used.add((info["tile_m"], info["tile_n"]))
+        f64 = ref.batched_matmul_f64(cnt, a_st, ta, b_st, tb, to, M, Kd, N)
+        assert ref.rel_frobenius(res, f64) < TOL_F16, (forced, ta, tb, to, info)
+    assert TILE_SHAPES[forced] in used, (forced, used)
+
+
+def test_half_small_products_take_small_pair_tiles(be):
+    # one wave either way: the smaller shape spreads it over more SMs
+    for (n, tile) in [(512, (256, 64)), (1536, (256, 128)), (2048, (256, 256))]:
+        A, B = random_operands(n, 1, n, n, n, np.float16)
+        res, a_st, b_st = run(be, 1, A, B, False, True, False, np.float16, TENSOR())
+        info = be.lastLaunchInfo()
+        assert (info["tile_m"], info["tile_n"]) == tile, (n, info)
+        f64 = ref.batched_matmul_f64(1, a_st, False, b_st, True, False, n, n, n)
+        assert ref.rel_frobenius(res, f64) < TOL_F16
+
+
 @pytest.mark.parametrize("shape", [(128, 32, 256, 1), (256, 32, 256, 1), (256, 256, 512, 1), (200, 132, 328, 2),
                                    (1000, 516, 776, 2), (1024, 1024, 1024, 1), (384, 4, 96, 2)])
 @pytest.mark.parametrize("dist", ["uniform01", "uniform11"])
