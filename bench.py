@@ -469,13 +469,22 @@ def other_configs(be, stream, rank, world):
 
 def run_probe(args):
     """A few launches of ONE product, for profiler captures:
-    `--probe M,K,N[,count] --dtype f16|f32 --flags tA,tB --steps K`."""
+    `--probe M,K,N[,count] --dtype f16|f32 --flags tA,tB --steps K`.  Several products separated
+    by `:` run one after the other in one process (a size sweep) and print one JSON list."""
+    specs = args.probe.split(":")
+    if len(specs) == 1:
+        emit(probe_one(args, specs[0]))
+    else:
+        emit({"probes": [probe_one(args, spec) for spec in specs]})
+
+
+def probe_one(args, spec):
     import numpy as np
     import torch
 
     from honeycrisp_b200 import CUDABackend
 
-    dims = [int(x) for x in args.probe.split(",")]
+    dims = [int(x) for x in spec.split(",")]
     M, K, N = dims[:3]
     cnt = dims[3] if len(dims) > 3 else 1
     ta, tb = (bool(int(x)) for x in args.flags.split(","))
@@ -542,9 +551,11 @@ def run_probe(args):
             e1.record(stream)
             torch.cuda.synchronize()
             lib_ms = e0.elapsed_time(e1) / args.steps
-    emit({"probe": [M, K, N, cnt], "dtype": args.dtype, "flags": [ta, tb], "ms": ms, "graph": bool(args.graph),
-          "library_ms": lib_ms, "library_tflops": (2.0 * cnt * M * N * K / lib_ms / 1e9) if lib_ms else None,
-          "tflops": 2.0 * cnt * M * N * K / ms / 1e9, "kernel": be.lastLaunchInfo()})
+    info = be.lastLaunchInfo()
+    be.close()
+    return {"probe": [M, K, N, cnt], "dtype": args.dtype, "flags": [ta, tb], "ms": ms, "graph": bool(args.graph),
+            "library_ms": lib_ms, "library_tflops": (2.0 * cnt * M * N * K / lib_ms / 1e9) if lib_ms else None,
+            "tflops": 2.0 * cnt * M * N * K / ms / 1e9, "kernel": info}
 
 
 def sharded_configs(be, stream, rank, world):

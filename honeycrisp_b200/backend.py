@@ -94,6 +94,8 @@ class CUDAData:
 
     def wait(self) -> None:
         """Tensor.Data.wait(): block until the buffer's producer has run; rethrow its failure."""
+        if not self.backend._ctx:
+            raise KernelFailed("wait() on a buffer whose backend has been closed")
         if self._event:
             self.backend._check(L.load().hc_event_wait(self._event))
         else:

@@ -38,7 +38,8 @@ struct hc_ctx {
 };
 
 struct hc_event {
-  hc_ctx* ctx;
+  hc_ctx* ctx;     // for waiting (status word); not touched by hc_event_destroy
+  int device;      // a marker may be destroyed after its context
   cudaEvent_t ev;
 };
 
@@ -357,6 +358,7 @@ hc_status hc_event_record(hc_ctx* ctx, hc_event** out) {
   hc_event* ev = new (std::nothrow) hc_event();
   if (!ev) return HC_ERR_ALLOCATION_FAILED;
   ev->ctx = ctx;
+  ev->device = ctx->device;
   cudaError_t e = cudaEventCreate(&ev->ev);
   if (e == cudaSuccess) e = cudaEventRecord(ev->ev, ctx->stream);
   if (e != cudaSuccess) {
@@ -399,7 +401,7 @@ hc_status hc_event_elapsed_ms(hc_event* start, hc_event* stop, float* ms) {
 
 void hc_event_destroy(hc_event* ev) {
   if (!ev) return;
-  DeviceGuard g(ev->ctx->device);
+  DeviceGuard g(ev->device);
   cudaEventDestroy(ev->ev);
   delete ev;
 }

@@ -113,6 +113,8 @@ hc_status hc_event_record(hc_ctx* ctx, hc_event** out);
 hc_status hc_event_wait(hc_event* ev);
 /* Milliseconds between two completed events of the same context. */
 hc_status hc_event_elapsed_ms(hc_event* start, hc_event* stop, float* ms);
+/* A marker may be destroyed after its context (garbage-collected hosts release buffers late);
+ * waiting on it or timing with it after hc_destroy is an error of the caller. */
 void hc_event_destroy(hc_event* ev);
 
 /* ---- the hot path ------------------------------------------------------------------------ */

@@ -334,3 +334,21 @@ def test_two_contexts_and_stream_switching(be):
             assert np.array_equal(got.view(np.uint32), want.view(np.uint32))
     finally:
         other.close()
+
+
+def test_results_may_outlive_their_backend():
+    """A host with garbage collection releases result buffers late: after the backend that made
+    them is closed.  That must neither crash nor leave an error behind for the next context."""
+    from honeycrisp_b200 import CUDABackend
+    A, B = random_operands(5, 1, 256, 256, 256, np.float16)
+    results = []
+    for _ in range(2):
+        be = CUDABackend(0)
+        out = be.matmul(stored(A, False), False, stored(B, False), False, False, 256, 256, 256, np.float16)
+        results.append(out.onCPU(np.float16).copy())
+        be.checkDeviceStatus()
+        be.close()
+        with pytest.raises(Exception):
+            out.wait()
+        del out   # its completion marker is destroyed after the context
+    assert np.array_equal(results[0], results[1])
