@@ -30,6 +30,13 @@ struct GemmProblem {
   // Optional row vector of N elements (same dtype) added to every row of the product after it has
   // been rounded to the output dtype: the `h + bias` of Linear (Trainable.swift:539-544).
   const void* bias = nullptr;
+  // The contraction may not be cut into parts (which needs a float32 work area of
+  // parts x batch x M x N): set by callers whose work area has a fixed size.
+  bool no_split = false;
+  // Rows and columns of the whole product when this problem is a block of it (0: not a block).
+  // Tile shape and the cut of the contraction are chosen for the whole product, so that a block
+  // computed on its own is bitwise the block of the whole.
+  int64_t plan_M = 0, plan_N = 0;
 };
 
 // Word in device memory that kernels set when a bounded wait gives up.
@@ -54,7 +61,8 @@ cudaError_t launch_simt(const GemmProblem& p, bool exact, cudaStream_t stream, L
 // tcgen05 kernel.  Returns cudaErrorNotSupported when TMA cannot describe the operands
 // (misaligned base or leading dimension); the caller then uses the CUDA-core kernel.
 // `status_word` is the device status word of the context; `scratch`/`scratch_bytes` is a
-// caller-provided work area for the float32 split operands (see tc_scratch_bytes).
+// caller-provided work area of at least tc_scratch_bytes(p, sm_count) bytes (float32 split
+// operands, repacked float16 operands, partial matrices of a cut contraction).
 // `extra_out`: up to 7 more result buffers of the same shape and pitch as p.C (other devices'
 // copies, mapped into this process); every result tile is stored to each of them as well.
 cudaError_t launch_tc(const GemmProblem& p, cudaStream_t stream, unsigned int* status_word,
@@ -63,7 +71,7 @@ cudaError_t launch_tc(const GemmProblem& p, cudaStream_t stream, unsigned int* s
 bool tc_supported(const GemmProblem& p);
 // One-thread kernel whose bounded wait is made to expire after `limit_ns` (self-test).
 cudaError_t launch_wait_probe(cudaStream_t stream, unsigned int* status_word, unsigned long long limit_ns);
-size_t tc_scratch_bytes(const GemmProblem& p);
+size_t tc_scratch_bytes(const GemmProblem& p, int sm_count);
 
 }  // namespace hc
 

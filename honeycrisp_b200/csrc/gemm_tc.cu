@@ -60,7 +60,9 @@ constexpr unsigned long long kWaitLimitNs = 4000000000ull;  // 4 s
 
 struct TcParams {
   int64_t M, N;
-  int num_k_blocks;   // k-slabs per tile
+  int num_k_blocks;   // pipeline slots (of one or two k slabs) along the whole contraction
+  int splits;         // parts the contraction is cut into (1: none); part z of matrix m is "matrix" m*splits+z
+  int kb_per_split;   // slots per part (the last part may be shorter)
   int chunk_kb;       // slabs per accumulation window (== num_k_blocks when not windowed)
   int tiles_m, tiles_n;
   int64_t total_tiles;
@@ -444,8 +446,23 @@ __device__ __forceinline__ TileCoord decode_tile(int64_t tile, const TcParams& p
 // Store staging buffers (4 KB each) per epilogue warp: two that alternate, or one where shared
 // memory is short (the windowed epilogue, and eight epilogue warps next to the 48 KB slots of the
 // 512-wide tiles) or where a warp's share of the tile is a single buffer wide.
-__host__ __device__ constexpr int staging_bufs(int elem_bytes, int bn, int epi_warps, bool windowed, int nsplit) {
-  return (windowed || (epi_warps == 8 && nsplit == 2) || (bn * nsplit / (epi_warps / 4)) < 2 * (128 / elem_bytes)) ? 1 : 2;
+__host__ __device__ constexpr int staging_bufs(int out_bytes, int bn, int epi_warps, bool windowed, int nsplit) {
+  return (windowed || (epi_warps == 8 && nsplit == 2) || (bn * nsplit / (epi_warps / 4)) < 2 * (128 / out_bytes)) ? 1 : 2;
+}
+
+// With the contraction cut into parts, tiles are numbered over batch x parts "matrices": the
+// operands of matrix v / parts, k slots [kb0, kb0 + count), the result into partial matrix v.
+struct KRange { int mat, kb0, count; };
+__device__ __forceinline__ KRange k_range(int64_t vmat, const TcParams& p) {
+  KRange r;
+  if (p.splits <= 1) {
+    r.mat = (int)vmat; r.kb0 = 0; r.count = p.num_k_blocks;
+  } else {
+    r.mat = (int)(vmat / p.splits);
+    r.kb0 = (int)(vmat - (int64_t)r.mat * p.splits) * p.kb_per_split;
+    r.count = min(p.kb_per_split, p.num_k_blocks - r.kb0);
+  }
+  return r;
 }
 
 // kElemBytes: 2 (float16 operands) or 4 (float32 operands consumed as TF32).
@@ -457,13 +474,15 @@ __host__ __device__ constexpr int staging_bufs(int elem_bytes, int bn, int epi_w
 // kCta      : 1, or 2 for CTA pairs (cluster of two, 256-row tiles, one MMA over both SMs).
 // kSlabs    : 128-byte k slabs per pipeline slot.  Two halve the barrier round trips per k, which
 //             is what bounds the small tile shapes (their MMAs are shorter than the issue loop).
-template <int kElemBytes, int kBN, int kStages, int kEpiWarps, bool kWindowed, int kCta, int kNSplit, int kSlabs>
+// kPartial  : float16 operands, float32 results: the partial sums of a contraction cut into parts.
+template <int kElemBytes, int kBN, int kStages, int kEpiWarps, bool kWindowed, int kCta, int kNSplit, int kSlabs,
+          bool kPartial>
 __global__ void __launch_bounds__(64 + 32 * kEpiWarps, 1)
 tc_gemm_kernel(const __grid_constant__ CUtensorMap mapA_hi, const __grid_constant__ CUtensorMap mapA_lo,
                const __grid_constant__ CUtensorMap mapB_hi, const __grid_constant__ CUtensorMap mapB_lo,
                const __grid_constant__ OutMaps mapC, const TcParams p) {
   constexpr bool kTf32 = (kElemBytes == 4);
-  constexpr bool kOutHalf = (kElemBytes == 2);
+  constexpr bool kOutHalf = (kElemBytes == 2) && !kPartial;
   constexpr int BK = 128 / kElemBytes;       // elements in one 128-byte slab row
   constexpr int UMMA_K = 32 / kElemBytes;    // k per tcgen05.mma
   constexpr int CH = 128 / kElemBytes;       // M/N indices in one 128-byte row of an MN-major box
@@ -479,7 +498,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap mapA_hi, const __grid_constan
   constexpr uint32_t A_BYTES = BM * 128, B_PART_BYTES = BN_LOCAL * 128, B_BYTES = kNSplit * B_PART_BYTES,
                      SLAB_BYTES = PARTS * (A_BYTES + B_BYTES), STAGE_BYTES = kSlabs * SLAB_BYTES;
   static_assert(kSlabs == 1 || !kWindowed, "accumulation windows count single slabs");
-  constexpr int STG_BUFS = staging_bufs(kElemBytes, kBN, kEpiWarps, kWindowed, kNSplit);
+  constexpr int STG_BUFS = staging_bufs(kOutHalf ? 2 : 4, kBN, kEpiWarps, kWindowed, kNSplit);
   constexpr uint32_t STG_BYTES_PER_WARP = STG_BUFS * 4096u;
   constexpr int TMEM_COLS = (2 * kBN <= 32) ? 32 : 2 * kBN;
   constexpr int COL_SPLIT = kEpiWarps / 4;   // epilogue warps sharing one lane quarter
@@ -563,8 +582,9 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap mapA_hi, const __grid_constan
         if (tile != tile_first) t = decode_tile(tile, p);
         const int m0 = t.tm * (BM * kCta) + (int)rank * BM;
         const int n0 = t.tn * TILE_N + (int)rank * BN_LOCAL;
-        const int mat = (int)t.mat;
-        for (int kb = 0; kb < nkb; kb++) {
+        const KRange kr = k_range(t.mat, p);
+        const int mat = kr.mat;
+        for (int kb = 0; kb < kr.count; kb++) {
           if (!mbar_wait(bar_empty + 8 * s, ph ^ 1, abortp)) {
             atomicOr(p.status, kDevTimeoutProducer);
             abort_flag = 1;
@@ -581,7 +601,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap mapA_hi, const __grid_constan
           // A slab past the end of K lies outside the tensor and arrives as zeros.
 #pragma unroll
           for (int j = 0; j < kSlabs; j++) {
-          const int kc = (kb * kSlabs + j) * BK;
+          const int kc = ((kr.kb0 + kb) * kSlabs + j) * BK;
           const uint32_t stage = smem_base + s * STAGE_BYTES + j * SLAB_BYTES;
 #pragma unroll
           for (int part = 0; part < PARTS; part++) {   // 0: the operand itself (hi), 1: its lo half
@@ -644,7 +664,8 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap mapA_hi, const __grid_constan
         // MMAs of one k block take to execute (512 clocks for a 256x256 pair tile), or the tensor
         // pipe waits for the issuer: no division, no blocking probe on the usual path.
         int in_win = -1;   // position of this k block in its accumulation window
-        for (int kb = 0; kb < nkb; kb++) {
+        const int nkb_t = (p.splits > 1) ? k_range(decode_tile(tile, p).mat, p).count : nkb;
+        for (int kb = 0; kb < nkb_t; kb++) {
           if (++in_win == chunk_kb) in_win = 0;
           if (in_win == 0) {
             slot = win % ACC_SLOTS;
@@ -689,7 +710,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap mapA_hi, const __grid_constan
           }
           tc_commit<kCta>(bar_empty + 8 * s);
           if (kCta == 2) tc_commit<kCta>(empty_peer + 8 * s);
-          if (in_win == chunk_kb - 1 || kb == nkb - 1) {
+          if (in_win == chunk_kb - 1 || kb == nkb_t - 1) {
             tc_commit<kCta>(bar_tfull + 8 * slot);
             if (kCta == 2) tc_commit<kCta>(tfull_peer + 8 * slot);
             win++;
@@ -722,7 +743,8 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap mapA_hi, const __grid_constan
       const int64_t n0 = (int64_t)t.tn * TILE_N + col0;
       void* cmat = kOutHalf ? (void*)((__half*)p.C + t.mat * p.strideC) : (void*)((float*)p.C + t.mat * p.strideC);
       const int64_t row_off = gm * p.ldc;
-      const int nwin = (nkb + chunk_kb - 1) / chunk_kb;
+      const int nkb_t = (p.splits > 1) ? k_range(t.mat, p).count : nkb;
+      const int nwin = (nkb_t + chunk_kb - 1) / chunk_kb;
       if (!kWindowed) {
         const uint32_t slot = win % ACC_SLOTS;
         const bool got = mbar_wait_warp(bar_tfull + 8 * slot, (win / ACC_SLOTS) & 1, abortp, lane);
@@ -929,6 +951,66 @@ __global__ void wait_probe_kernel(unsigned int* status, unsigned long long limit
   }
 }
 
+// Second half of a cut contraction: result = round(sum over parts, ascending, of the float32
+// partial matrices) (+ bias, as a second rounded operation for float16, exactly like the
+// epilogue of the uncut kernel).  Four columns per thread; the partial matrices have a row pitch
+// that is a multiple of four floats, so every load is one aligned float4.
+struct ReduceJob {
+  const float* ws;
+  void* C;
+  const void* bias;
+  int64_t M, N, ws_ld, batch, ldc, strideC;
+  int parts, vec_ok;
+};
+
+template <bool kHalf>
+__global__ void __launch_bounds__(256) splitk_reduce_kernel(const ReduceJob j) {
+  pdl_release();
+  pdl_wait();
+  const int64_t groups = j.ws_ld / 4;
+  const int64_t total = j.batch * j.M * groups;
+  const int64_t part_stride = j.M * j.ws_ld;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t g = i % groups, row = (i / groups) % j.M, mat = i / (groups * j.M);
+    const int64_t n = g * 4;
+    const float* src = j.ws + (mat * j.parts) * part_stride + row * j.ws_ld + n;
+    float4 acc = __ldg((const float4*)src);
+    for (int z = 1; z < j.parts; z++) {
+      const float4 v = __ldg((const float4*)(src + z * part_stride));
+      acc.x = __fadd_rn(acc.x, v.x); acc.y = __fadd_rn(acc.y, v.y);
+      acc.z = __fadd_rn(acc.z, v.z); acc.w = __fadd_rn(acc.w, v.w);
+    }
+    float x[4] = {acc.x, acc.y, acc.z, acc.w};
+    const int valid = (int)min((int64_t)4, j.N - n);
+    if (kHalf) {
+      __half h[4];
+#pragma unroll
+      for (int e = 0; e < 4; e++) {
+        h[e] = __float2half_rn(x[e]);
+        if (j.bias && e < valid)
+          h[e] = __float2half_rn(__fadd_rn(__half2float(h[e]), __half2float(__ldg((const __half*)j.bias + n + e))));
+      }
+      __half* dst = (__half*)j.C + mat * j.strideC + row * j.ldc + n;
+      if (valid == 4 && j.vec_ok) {
+        *(uint2*)dst = *(const uint2*)h;
+      } else {
+        for (int e = 0; e < valid; e++) dst[e] = h[e];
+      }
+    } else {
+      if (j.bias)
+#pragma unroll
+        for (int e = 0; e < 4; e++)
+          if (e < valid) x[e] = __fadd_rn(x[e], __ldg((const float*)j.bias + n + e));
+      float* dst = (float*)j.C + mat * j.strideC + row * j.ldc + n;
+      if (valid == 4 && j.vec_ok) {
+        *(float4*)dst = make_float4(x[0], x[1], x[2], x[3]);
+      } else {
+        for (int e = 0; e < valid; e++) dst[e] = x[e];
+      }
+    }
+  }
+}
+
 // Splits float32 into two TF32-representable parts: hi = nearest TF32 of x, lo = nearest TF32
 // of (x - hi).  x - hi is exact in float32.  Non-finite x: hi = x, lo = 0, so infinities and
 // NaNs propagate through the hi*hi product only.
@@ -1100,14 +1182,15 @@ bool overlap_launches() {
   return v != 0;
 }
 
-template <int kElemBytes, int kBN, int kStages, int kEpiWarps, bool kWindowed, int kCta, int kNSplit = 1, int kSlabs = 1>
+template <int kElemBytes, int kBN, int kStages, int kEpiWarps, bool kWindowed, int kCta, int kNSplit = 1, int kSlabs = 1,
+          bool kPartial = false>
 struct TcConfig {
   // operand ring (float32 slots also hold the lo slabs) + store staging + alignment slack
   static constexpr size_t smem = (size_t)kStages * kSlabs * (kElemBytes == 4 ? 2 : 1) * (BM * 128 + kNSplit * (kBN / kCta) * 128) +
-                                 (size_t)kEpiWarps * staging_bufs(kElemBytes, kBN, kEpiWarps, kWindowed, kNSplit) * 4096 + 1024;
+                                 (size_t)kEpiWarps * staging_bufs((kElemBytes == 2 && !kPartial) ? 2 : 4, kBN, kEpiWarps, kWindowed, kNSplit) * 4096 + 1024;
   static_assert(smem <= 232448, "more shared memory than one CTA can have on sm_100");
   static constexpr int block = 64 + 32 * kEpiWarps;
-  static auto kernel() { return tc_gemm_kernel<kElemBytes, kBN, kStages, kEpiWarps, kWindowed, kCta, kNSplit, kSlabs>; }
+  static auto kernel() { return tc_gemm_kernel<kElemBytes, kBN, kStages, kEpiWarps, kWindowed, kCta, kNSplit, kSlabs, kPartial>; }
 
   static cudaError_t configure() {
     static bool configured[64] = {};
@@ -1233,13 +1316,122 @@ static RepackLayout repack_layout(const GemmProblem& p) {
   return r;
 }
 
-size_t tc_scratch_bytes(const GemmProblem& p) {
+// ---- choice of tile shape and of a cut of the contraction ------------------------------------
+enum Shape { SHAPE_AUTO = 0, SHAPE_WIDE, SHAPE_PAIR, SHAPE_C1_256, SHAPE_C1_128, SHAPE_PAIR_128, SHAPE_PAIR_64,
+             SHAPE_COUNT };
+
+struct TcPlan {
+  int shape = SHAPE_PAIR;
+  int slabs = 1;            // k slabs per pipeline slot
+  int splits = 1;           // parts of the contraction (1: none)
+  int kb_per_split = 0;     // slots per part
+  int64_t ws_ld = 0;        // row pitch (floats) of one partial matrix
+  size_t ws_bytes = 0;      // float32 partial sums: splits x batch x M x ws_ld
+};
+
+constexpr size_t kMaxSplitWorkspace = 256ull << 20;
+
+// The cost model.  A shape costs (waves of tiles over the SMs) x (clocks per tile); the clocks
+// per 64-wide k block of each float16 shape are measured on large products (relative to 600 for
+// the 256x256 pair), plus a fixed cost per tile for refilling the pipeline.  Large tiles move the
+// fewest operand bytes per flop and win whenever there are enough tiles to fill the SMs; for small
+// products the small pair shapes spread the work over more SMs, which shortens the one wave there
+// is.  Only the 256x512 shape cannot hide the result drain behind the next tile.
+// When even the smallest shape leaves most SMs idle and the contraction is long (the weight
+// gradient of a small Linear layer: few outputs, many tokens), the contraction is cut into up to
+// 16 parts that run as separate tiles into float32 partial matrices, summed in ascending part
+// order by a second kernel (splitk_reduce_kernel): deterministic, and float16 still rounds once.
+// float32 keeps two shape rules: 256 columns unless the product is narrow, and 128x128 tiles
+// when 256x256 pairs would idle more than half the SMs.
+TcPlan plan_tc(const GemmProblem& p, int sm_count, bool may_split) {
+  const bool f32 = p.dtype == HC_F32;
+  const int BK = f32 ? 32 : 64;
+  const int dbg = debug_flags();
+  const int kslabs = (int)((p.K + BK - 1) / BK);
+  // A block of a larger product is planned as the whole product.
+  const int64_t M = p.plan_M > 0 ? p.plan_M : p.M, N = p.plan_N > 0 ? p.plan_N : p.N;
+  const bool pairs_ok = M > BM && !(dbg & 4);
+  struct Cand { int shape; bool ok; int rows, cols, slots, slabs; double clk_per_slab, drain_per_tile; bool splittable; };
+  const double drain = 2400.0, refill = 300.0;
+  const int pair_slots = sm_count / 2;
+  Cand cands[SHAPE_COUNT - 1];
+  int n_cands = 0;
+  if (!f32) {
+    const bool wide_ok = pairs_ok && N >= 1024 && kslabs >= env_int("HC_TC_WIDE_MIN_KB", 32);
+    cands[n_cands++] = {SHAPE_WIDE, wide_ok, 256, 512, pair_slots, 1, 1140.0, drain, false};
+    cands[n_cands++] = {SHAPE_PAIR, pairs_ok && N > 128, 256, 256, pair_slots, 1, 600.0, 0.0, true};
+    cands[n_cands++] = {SHAPE_C1_256, N > 128, 128, 256, sm_count, 1, 680.0, 0.0, false};
+    cands[n_cands++] = {SHAPE_C1_128, true, 128, 128, sm_count, 2, 410.0, 0.0, true};
+    cands[n_cands++] = {SHAPE_PAIR_128, pairs_ok && N > 64, 256, 128, pair_slots, 2, 340.0, 0.0, true};
+    // 32 columns of B per CTA: half a 128-byte row of an MN-major box, which the copy cannot split
+    cands[n_cands++] = {SHAPE_PAIR_64, pairs_ok && !p.b_mn_major, 256, 64, pair_slots, 2, 265.0, 0.0, true};
+  } else {
+    const int64_t pair_tiles = ((M + 255) / 256) * ((N + 255) / 256) * p.batch;
+    const bool few_tiles = pair_tiles * 4 <= sm_count;
+    const bool wide_cols = N > 128 && !few_tiles;
+    const int shape = !wide_cols ? SHAPE_C1_128 : pairs_ok ? SHAPE_PAIR : SHAPE_C1_256;
+    // one 32-wide slab of the three products: 12 MMAs
+    if (shape == SHAPE_PAIR) cands[n_cands++] = {SHAPE_PAIR, true, 256, 256, pair_slots, 1, 1620.0, 0.0, true};
+    else if (shape == SHAPE_C1_256) cands[n_cands++] = {SHAPE_C1_256, true, 128, 256, sm_count, 1, 1800.0, 0.0, true};
+    else cands[n_cands++] = {SHAPE_C1_128, true, 128, 128, sm_count, 1, 960.0, 0.0, true};
+  }
+  const int forced = f32 ? 0 : env_int("HC_TC_SHAPE", 0);
+  const int forced_splits = env_int("HC_TC_SPLITS", 0);   // 1: never cut; n > 1: cut into n where possible
+  int choices[8] = {1, 2, 3, 4, 6, 8, 12, 16};
+  int n_choices = 8;
+  if (forced_splits > 1) { choices[0] = forced_splits > 64 ? 64 : forced_splits; n_choices = 1; }
+  TcPlan best;
+  double best_cost = -1.0;
+  for (int ci = 0; ci < n_cands; ci++) {
+    const Cand& c = cands[ci];
+    if (!c.ok || c.slots < 1) continue;
+    if (forced >= 1 && forced < SHAPE_COUNT && cands[forced - 1].ok && c.shape != forced) continue;
+    const int64_t tiles = ((M + c.rows - 1) / c.rows) * ((N + c.cols - 1) / c.cols) * p.batch;
+    const int kslots = (kslabs + c.slabs - 1) / c.slabs;
+    const int64_t ws_ld = (p.N + 3) & ~3ll;   // of this block
+    const bool can_split = may_split && c.splittable && !p.no_split && forced_splits != 1;
+    for (int i = 0; i < n_choices; i++) {
+      int want = can_split ? choices[i] : 1;
+      if (want > kslots) want = kslots;
+      if (want < 1) want = 1;
+      int per = (kslots + want - 1) / want;
+      if (want > 1 && forced_splits <= 1 && per * c.slabs < 8) break;   // at least 8 slabs per part
+      if (want > 1 && forced_splits <= 1 && tiles >= c.slots) break;    // a full wave needs no cut
+      const int parts = (kslots + per - 1) / per;
+      const size_t ws = parts > 1 ? (size_t)parts * p.batch * p.M * ws_ld * 4 : 0;
+      // the limit applies to the whole product, so that a block of it is cut like the whole
+      if (parts > 1 && (size_t)parts * p.batch * M * ((N + 3) & ~3ll) * 4 > kMaxSplitWorkspace) break;
+      const int64_t units = tiles * parts;
+      const int64_t waves = (units + c.slots - 1) / c.slots;
+      double cost = (double)waves * ((double)per * c.slabs * c.clk_per_slab + c.drain_per_tile + refill) +
+                    (c.drain_per_tile > 0 ? 0.0 : drain);
+      if (parts > 1) cost += 2500.0 + (double)ws / 3000.0;   // the second launch and its traffic
+      if (best_cost < 0 || cost < best_cost) {
+        best_cost = cost;
+        best.shape = c.shape; best.slabs = c.slabs; best.splits = parts; best.kb_per_split = per;
+        best.ws_ld = ws_ld; best.ws_bytes = ws;
+      }
+      if (!can_split) break;
+    }
+  }
+  return best;
+}
+
+static size_t operand_scratch_bytes(const GemmProblem& p) {
   if (p.dtype != HC_F32) {
     const RepackLayout r = repack_layout(p);
     return r.a_bytes + r.b_bytes;
   }
   const SplitLayout s = split_layout(p);
   return 2 * s.a_bytes + 2 * s.b_bytes;
+}
+
+// Work area of one product: re-laid operands (float32 hi/lo parts, repacked float16), then,
+// 256-byte aligned, the partial matrices of a cut contraction.
+size_t tc_scratch_bytes(const GemmProblem& p, int sm_count) {
+  const size_t ops = operand_scratch_bytes(p);
+  const TcPlan plan = plan_tc(p, sm_count, true);
+  return plan.ws_bytes ? ((ops + 255) & ~(size_t)255) + plan.ws_bytes : ops;
 }
 
 cudaError_t launch_tc(const GemmProblem& p, cudaStream_t stream, unsigned int* status_word, void* scratch,
@@ -1323,51 +1515,10 @@ cudaError_t launch_tc(const GemmProblem& p, cudaStream_t stream, unsigned int* s
     lda = s.a_ld; ldb = s.b_ld; sa = s.a_mat; sb = s.b_mat;
   }
 
-  // Tile shape.  float16 picks the cheapest of six shapes by a wave model: the cost of a shape is
-  // (waves of tiles over the SMs) x (clocks per tile), with the clocks per 64-wide k block of each
-  // shape measured on large products (relative to 600 for the 256x256 pair) and a fixed cost per
-  // tile for refilling the pipeline.  Large tiles move the fewest operand bytes per flop and win
-  // whenever there are enough tiles to fill the SMs; for small products the small pair shapes
-  // spread the work over more SMs, which shortens the one wave there is.  Only the 256x512
-  // shape cannot hide the result drain behind the next tile.
-  // float32 keeps two rules: 256 columns unless the product is narrow, and 128x128 tiles when
-  // 256x256 pairs would idle more than half the SMs.
   const int dbg = debug_flags();
   const int kslabs = (int)((p.K + BK - 1) / BK);
-  enum Shape { SHAPE_AUTO = 0, SHAPE_WIDE, SHAPE_PAIR, SHAPE_C1_256, SHAPE_C1_128, SHAPE_PAIR_128, SHAPE_PAIR_64,
-               SHAPE_COUNT };
-  int shape = SHAPE_AUTO;
-  if (!f32) {
-    const bool pairs_ok = p.M > BM && !(dbg & 4);
-    const bool wide_ok = pairs_ok && p.N >= 1024 && kslabs >= env_int("HC_TC_WIDE_MIN_KB", 32);
-    struct Cand { int shape; bool ok; int rows, cols, slots; double clk_per_kb, drain_per_tile; };
-    const double drain = 2400.0, refill = 300.0;
-    const Cand cands[SHAPE_COUNT - 1] = {
-        {SHAPE_WIDE, wide_ok, 256, 512, sm_count / 2, 1140.0, drain},
-        {SHAPE_PAIR, pairs_ok && p.N > 128, 256, 256, sm_count / 2, 600.0, 0.0},
-        {SHAPE_C1_256, p.N > 128, 128, 256, sm_count, 680.0, 0.0},
-        {SHAPE_C1_128, true, 128, 128, sm_count, 410.0, 0.0},
-        {SHAPE_PAIR_128, pairs_ok && p.N > 64, 256, 128, sm_count / 2, 340.0, 0.0},
-        // 32 columns of B per CTA: half a 128-byte row of an MN-major box, which the copy cannot split
-        {SHAPE_PAIR_64, pairs_ok && !p.b_mn_major, 256, 64, sm_count / 2, 265.0, 0.0},
-    };
-    double best = 0.0;
-    for (const Cand& c : cands) {
-      if (!c.ok || c.slots < 1) continue;
-      const int64_t tiles = ((p.M + c.rows - 1) / c.rows) * ((p.N + c.cols - 1) / c.cols) * p.batch;
-      const int64_t waves = (tiles + c.slots - 1) / c.slots;
-      const double cost =
-          (double)waves * (kslabs * c.clk_per_kb + c.drain_per_tile + refill) + (c.drain_per_tile > 0 ? 0.0 : drain);
-      if (shape == SHAPE_AUTO || cost < best) { shape = c.shape; best = cost; }
-    }
-    const int forced = env_int("HC_TC_SHAPE", 0);
-    if (forced >= 1 && forced < SHAPE_COUNT && cands[forced - 1].ok) shape = forced;
-  } else {
-    const int64_t pair_tiles = ((p.M + 255) / 256) * ((p.N + 255) / 256) * p.batch;
-    const bool few_tiles = pair_tiles * 4 <= sm_count;
-    const bool wide_cols = p.N > 128 && !few_tiles;
-    shape = !wide_cols ? SHAPE_C1_128 : (p.M > BM && !(dbg & 4)) ? SHAPE_PAIR : SHAPE_C1_256;
-  }
+  const TcPlan plan = plan_tc(p, sm_count, n_extra == 0);
+  const int shape = plan.shape;
   const int bn = (shape == SHAPE_C1_128 || shape == SHAPE_PAIR_128) ? 128 : shape == SHAPE_PAIR_64 ? 64 : 256;
   const int cta = (shape == SHAPE_C1_256 || shape == SHAPE_C1_128) ? 1 : 2;
   const int b_box = bn / cta;
@@ -1383,12 +1534,14 @@ cudaError_t launch_tc(const GemmProblem& p, cudaStream_t stream, unsigned int* s
 
   TcParams tp;
   tp.M = p.M; tp.N = p.N;
-  // Pipeline slots of the small float16 shapes hold two k slabs.
   // Short contractions are bound by draining results, not by the MMA: they get more epilogue
   // warps and fewer operand stages.
   const bool short_k = kslabs <= env_int("HC_TC_SHORT_K", 8);
-  const int slabs = (!f32 && (shape == SHAPE_PAIR_64 || shape == SHAPE_PAIR_128 || shape == SHAPE_C1_128)) ? 2 : 1;
+  const int slabs = plan.slabs;   // pipeline slots of the small float16 shapes hold two k slabs
   tp.num_k_blocks = (kslabs + slabs - 1) / slabs;
+  const bool cut = plan.splits > 1;
+  tp.splits = plan.splits;
+  tp.kb_per_split = cut ? plan.kb_per_split : tp.num_k_blocks;
   // float32: a window bounds the number of truncating tensor-core accumulations that feed one
   // correctly rounded float32 add in the epilogue.
   const bool windowed = f32 && !(dbg & 2);
@@ -1399,24 +1552,38 @@ cudaError_t launch_tc(const GemmProblem& p, cudaStream_t stream, unsigned int* s
   tp.tile_rows = BM * cta;
   tp.tiles_m = (int)((p.M + tp.tile_rows - 1) / tp.tile_rows);
   tp.tiles_n = (int)((p.N + tile_n - 1) / tile_n);
-  tp.total_tiles = (int64_t)tp.tiles_m * tp.tiles_n * p.batch;
+  tp.total_tiles = (int64_t)tp.tiles_m * tp.tiles_n * p.batch * plan.splits;
   tp.group_m = env_int("HC_TC_GROUP_M", 16 / cta);
   tp.a_mn_major = p.a_mn_major; tp.b_mn_major = p.b_mn_major;
-  tp.C = p.C; tp.ldc = p.ldc; tp.strideC = p.strideC;
   tp.status = status_word;
-  tp.bias = p.bias;
-  tp.vec_ok = (((uintptr_t)p.C & 15) == 0 && (p.ldc * eb) % 16 == 0 && (p.strideC * eb) % 16 == 0) ? 1 : 0;
   tp.debug = dbg;
+  // Where the tiles go: the result itself, or - for a cut contraction - float32 partial matrices
+  // in the work area (part z of matrix m at index m * parts + z), which a second kernel sums.
+  void* out_base = p.C;
+  int out_bytes = eb;
+  int64_t out_ld = p.ldc, out_stride = p.strideC, out_mats = p.batch;
+  tp.bias = p.bias;
+  if (cut) {
+    const size_t off = (operand_scratch_bytes(p) + 255) & ~(size_t)255;
+    if (!scratch || scratch_bytes < off + plan.ws_bytes) return cudaErrorInvalidValue;
+    out_base = (char*)scratch + off;
+    out_bytes = 4;
+    out_ld = plan.ws_ld; out_stride = p.M * plan.ws_ld; out_mats = p.batch * plan.splits;
+    tp.bias = nullptr;
+    if (rec) rec->scratch_bytes = off + plan.ws_bytes;
+  }
+  tp.C = out_base; tp.ldc = out_ld; tp.strideC = out_stride;
+  tp.vec_ok = (((uintptr_t)out_base & 15) == 0 && (out_ld * out_bytes) % 16 == 0 && (out_stride * out_bytes) % 16 == 0) ? 1 : 0;
   // Results leave through TMA stores when the result can be described to TMA (16-byte aligned
-  // base and pitches); the windowed float32 epilogue stores from registers.
+  // base and pitches); otherwise from registers.
   tp.tma_store = 0;
   tp.n_out = 1;
-  if (tp.vec_ok && !(dbg & 128) && p.M < (1ll << 31) && p.N < (1ll << 31) && p.ldc * eb < (1ll << 40) &&
-      make_output_map(&outs.m[0], p.C, eb, p.N, p.M, p.ldc, p.strideC, p.batch))
+  if (tp.vec_ok && !(dbg & 128) && p.M < (1ll << 31) && p.N < (1ll << 31) && out_ld * out_bytes < (1ll << 40) &&
+      make_output_map(&outs.m[0], out_base, out_bytes, p.N, p.M, out_ld, out_stride, out_mats))
     tp.tma_store = 1;
   if (n_extra > 0) {
     // Extra destinations only exist on the TMA-store path.
-    if (!tp.tma_store) return cudaErrorNotSupported;
+    if (!tp.tma_store || cut) return cudaErrorNotSupported;
     for (int i = 0; i < n_extra; i++) {
       if (((uintptr_t)extra_out[i] & 15) != 0 ||
           !make_output_map(&outs.m[1 + i], extra_out[i], eb, p.N, p.M, p.ldc, p.strideC, p.batch))
@@ -1426,25 +1593,57 @@ cudaError_t launch_tc(const GemmProblem& p, cudaStream_t stream, unsigned int* s
   }
   if (rec) rec->tiles = tp.total_tiles;
 
-  if (!f32) {
-    if (wide && env_int("HC_TC_WIDE_EPI8", 1))
-      return TcConfig<2, 256, 4, 8, false, 2, 2>::launch(maps, outs, tp, sm_count, stream, rec);
-    if (wide) return TcConfig<2, 256, 4, 4, false, 2, 2>::launch(maps, outs, tp, sm_count, stream, rec);
-    if (shape == SHAPE_PAIR_128) return TcConfig<2, 128, 4, 4, false, 2, 1, 2>::launch(maps, outs, tp, sm_count, stream, rec);
-    if (shape == SHAPE_PAIR_64) return TcConfig<2, 64, 4, 4, false, 2, 1, 2>::launch(maps, outs, tp, sm_count, stream, rec);
-    if (cta == 2 && short_k) return TcConfig<2, 256, 4, 8, false, 2>::launch(maps, outs, tp, sm_count, stream, rec);
-    if (cta == 2) return TcConfig<2, 256, 6, 4, false, 2>::launch(maps, outs, tp, sm_count, stream, rec);
-    if (bn == 256) return TcConfig<2, 256, 4, 4, false, 1>::launch(maps, outs, tp, sm_count, stream, rec);
-    return TcConfig<2, 128, 3, 4, false, 1, 1, 2>::launch(maps, outs, tp, sm_count, stream, rec);
+  cudaError_t ge;
+  if (!f32 && cut) {
+    if (shape == SHAPE_PAIR_128) ge = TcConfig<2, 128, 4, 4, false, 2, 1, 2, true>::launch(maps, outs, tp, sm_count, stream, rec);
+    else if (shape == SHAPE_PAIR_64) ge = TcConfig<2, 64, 4, 4, false, 2, 1, 2, true>::launch(maps, outs, tp, sm_count, stream, rec);
+    else if (shape == SHAPE_PAIR) ge = TcConfig<2, 256, 6, 4, false, 2, 1, 1, true>::launch(maps, outs, tp, sm_count, stream, rec);
+    else if (shape == SHAPE_C1_128) ge = TcConfig<2, 128, 3, 4, false, 1, 1, 2, true>::launch(maps, outs, tp, sm_count, stream, rec);
+    else return cudaErrorInvalidValue;
+  } else if (!f32) {
+    if (wide && env_int("HC_TC_WIDE_EPI8", 1)) ge = TcConfig<2, 256, 4, 8, false, 2, 2>::launch(maps, outs, tp, sm_count, stream, rec);
+    else if (wide) ge = TcConfig<2, 256, 4, 4, false, 2, 2>::launch(maps, outs, tp, sm_count, stream, rec);
+    else if (shape == SHAPE_PAIR_128) ge = TcConfig<2, 128, 4, 4, false, 2, 1, 2>::launch(maps, outs, tp, sm_count, stream, rec);
+    else if (shape == SHAPE_PAIR_64) ge = TcConfig<2, 64, 4, 4, false, 2, 1, 2>::launch(maps, outs, tp, sm_count, stream, rec);
+    else if (cta == 2 && short_k) ge = TcConfig<2, 256, 4, 8, false, 2>::launch(maps, outs, tp, sm_count, stream, rec);
+    else if (cta == 2) ge = TcConfig<2, 256, 6, 4, false, 2>::launch(maps, outs, tp, sm_count, stream, rec);
+    else if (bn == 256) ge = TcConfig<2, 256, 4, 4, false, 1>::launch(maps, outs, tp, sm_count, stream, rec);
+    else ge = TcConfig<2, 128, 3, 4, false, 1, 1, 2>::launch(maps, outs, tp, sm_count, stream, rec);
+  } else if (windowed) {
+    if (cta == 2) ge = TcConfig<4, 256, 3, 8, true, 2>::launch(maps, outs, tp, sm_count, stream, rec);
+    else if (bn == 256) ge = TcConfig<4, 256, 2, 8, true, 1>::launch(maps, outs, tp, sm_count, stream, rec);
+    else ge = TcConfig<4, 128, 3, 4, true, 1>::launch(maps, outs, tp, sm_count, stream, rec);
+  } else {
+    if (cta == 2) ge = TcConfig<4, 256, 3, 4, false, 2>::launch(maps, outs, tp, sm_count, stream, rec);
+    else if (bn == 256) ge = TcConfig<4, 256, 2, 4, false, 1>::launch(maps, outs, tp, sm_count, stream, rec);
+    else ge = TcConfig<4, 128, 3, 4, false, 1>::launch(maps, outs, tp, sm_count, stream, rec);
   }
-  if (windowed) {
-    if (cta == 2) return TcConfig<4, 256, 3, 8, true, 2>::launch(maps, outs, tp, sm_count, stream, rec);
-    if (bn == 256) return TcConfig<4, 256, 2, 8, true, 1>::launch(maps, outs, tp, sm_count, stream, rec);
-    return TcConfig<4, 128, 3, 4, true, 1>::launch(maps, outs, tp, sm_count, stream, rec);
-  }
-  if (cta == 2) return TcConfig<4, 256, 3, 4, false, 2>::launch(maps, outs, tp, sm_count, stream, rec);
-  if (bn == 256) return TcConfig<4, 256, 2, 4, false, 1>::launch(maps, outs, tp, sm_count, stream, rec);
-  return TcConfig<4, 128, 3, 4, false, 1>::launch(maps, outs, tp, sm_count, stream, rec);
+  if (ge != cudaSuccess || !cut) return ge;
+
+  // Sum the parts in ascending order, add the bias, round once, store the result.
+  ReduceJob job;
+  job.ws = (const float*)out_base; job.C = p.C; job.bias = p.bias;
+  job.M = p.M; job.N = p.N; job.ws_ld = plan.ws_ld; job.batch = p.batch; job.parts = plan.splits;
+  job.ldc = p.ldc; job.strideC = p.strideC;
+  const int out_align = f32 ? 15 : 7;   // four results per thread: 16 bytes of float32, 8 of float16
+  job.vec_ok = (((uintptr_t)p.C & out_align) == 0 && p.ldc % 4 == 0 && p.strideC % 4 == 0) ? 1 : 0;
+  const int64_t work = p.batch * p.M * (plan.ws_ld / 4);
+  int64_t blocks = (work + 255) / 256;
+  if (blocks > 148 * 8) blocks = 148 * 8;
+  cudaLaunchConfig_t rcfg = {};
+  rcfg.gridDim = dim3((unsigned)blocks);
+  rcfg.blockDim = dim3(256);
+  rcfg.stream = stream;
+  cudaLaunchAttribute rattr;
+  rattr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  rattr.val.programmaticStreamSerializationAllowed = 1;
+  rcfg.attrs = &rattr;
+  rcfg.numAttrs = overlap_launches() ? 1 : 0;
+  cudaError_t re = f32 ? cudaLaunchKernelEx(&rcfg, splitk_reduce_kernel<false>, job)
+                       : cudaLaunchKernelEx(&rcfg, splitk_reduce_kernel<true>, job);
+  if (re != cudaSuccess) return re;
+  if (rec) rec->launches += 1;
+  return cudaGetLastError();
 }
 
 }  // namespace hc

@@ -134,6 +134,7 @@ hc_status build_problem(hc_ctx* ctx, hc_dtype dtype, int64_t count, const void* 
     p->b_mn_major = trans_b ? 0 : 1; p->ldb = trans_b ? inner : cols; p->strideB = inner * cols;
     p->B = bp + (trans_b ? col_begin * inner : col_begin) * eb;
     p->C = cp + col_begin * eb; p->ldc = cols;
+    p->plan_M = rows; p->plan_N = cols;
   } else {
     // out[cols, rows] = op(b)^T * op(a)^T; block = rows of out.
     p->M = col_count; p->N = rows;
@@ -141,6 +142,7 @@ hc_status build_problem(hc_ctx* ctx, hc_dtype dtype, int64_t count, const void* 
     p->A = bp + (trans_b ? col_begin * inner : col_begin) * eb;
     p->B = ap; p->b_mn_major = trans_a ? 1 : 0; p->ldb = trans_a ? rows : inner; p->strideB = rows * inner;
     p->C = cp + col_begin * rows * eb; p->ldc = rows;
+    p->plan_M = cols; p->plan_N = rows;
   }
   return HC_OK;
 }
@@ -173,7 +175,7 @@ hc_status run_problem(hc_ctx* ctx, hc_kernel kernel, const hc::GemmProblem& p, i
   if (chosen == HC_KERNEL_TENSOR) {
     if (!hc::tc_supported(p))
       return fail(ctx, HC_ERR_NOT_IMPLEMENTED, "product too large for the tensor-core kernel's 32-bit tile coordinates");
-    const size_t need = hc::tc_scratch_bytes(p);
+    const size_t need = hc::tc_scratch_bytes(p, ctx->sm_count);
     if (need) {
       hc_status s = ensure_buffer(ctx, &ctx->scratch, &ctx->scratch_bytes, need);
       if (s != HC_OK) return s;
@@ -462,7 +464,7 @@ hc_status hc_matmul_colblock_push(hc_ctx* ctx, hc_dtype dtype, const void* a, in
   if (p.K == 0) return fail(ctx, HC_ERR_INVALID_ARGUMENT, "pushed column blocks need a non-empty contraction");
   if (!hc::tc_supported(p))
     return fail(ctx, HC_ERR_NOT_IMPLEMENTED, "tensor-core kernel needs 16-byte aligned operands and leading dimensions");
-  const size_t need = hc::tc_scratch_bytes(p);
+  const size_t need = hc::tc_scratch_bytes(p, ctx->sm_count);
   if (need) {
     s = ensure_buffer(ctx, &ctx->scratch, &ctx->scratch_bytes, need);
     if (s != HC_OK) return s;

@@ -83,7 +83,8 @@ hc_status hc_matmul_f32_static_scratch(hc_ctx* ctx, const void* a, int trans_a, 
   if (!hc::tc_supported(p))
     return hc::ctx_fail(ctx, HC_ERR_NOT_IMPLEMENTED,
                         "tensor-core kernel needs 16-byte aligned operands and leading dimensions");
-  const size_t need = hc::tc_scratch_bytes(p);
+  p.no_split = true;   // the work area is fixed: operands only, no partial matrices
+  const size_t need = hc::tc_scratch_bytes(p, hc::ctx_sm_count(ctx));
   if (need > (size_t)HC_STATIC_SCRATCH_BYTES) {
     char msg[160];
     snprintf(msg, sizeof msg,

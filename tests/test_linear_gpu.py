@@ -40,7 +40,10 @@ def test_fused_bias_is_bit_identical_to_matmul_then_add_small(be, rows, n_in, n_
 
 
 @pytest.mark.parametrize("dtype,tol", [(np.float32, 1e-5), (np.float16, 2e-3)])
-@pytest.mark.parametrize("rows,n_in,n_out", [(256, 128, 256), (1000, 520, 776), (384, 64, 96), (2048, 4096, 1024)])
+@pytest.mark.parametrize("rows,n_in,n_out", [(256, 128, 256), (1000, 520, 776), (384, 64, 96), (2048, 4096, 1024),
+                                             # long contractions over few outputs: cut into parts, bias added by the
+                                             # kernel that sums them (aligned, and a result pitch no vector store fits)
+                                             (256, 4096, 256), (264, 4104, 198)])
 def test_fused_bias_on_the_tensor_core_path(be, rows, n_in, n_out, dtype, tol):
     """The tensor-core epilogue adds the bias to the rounded product: identical, bit for bit, to
     this library's own product followed by the oracle's add; and within tolerance of float64."""

@@ -90,6 +90,70 @@ def test_half_small_products_take_small_pair_tiles(be):
         assert ref.rel_frobenius(res, f64) < TOL_F16
 
 
+# Few outputs and a long contraction (the weight gradient of a small Linear layer): the
+# contraction is cut into parts that run as separate tiles into float32 partial matrices, summed
+# in ascending order by a second kernel.
+CUT_SHAPES = [(512, 4096, 512, 1), (264, 8200, 328, 3), (128, 4096, 256, 1), (1024, 16384, 1024, 1),
+              (520, 4104, 72, 2)]
+
+
+@pytest.mark.parametrize("shape", CUT_SHAPES)
+def test_half_cut_contraction(be, shape):
+    M, Kd, N, cnt = shape
+    for (ta, tb, to) in FLAG_COMBOS:
+        A, B = random_operands(M + N, cnt, M, Kd, N, np.float16, scale=0.25)
+        res, a_st, b_st = run(be, cnt, A, B, ta, tb, to, np.float16, TENSOR())
+        info = be.lastLaunchInfo()
+        rows_t, cols_t = (N, M) if to else (M, N)
+        whole_tiles = -(-rows_t // info["tile_m"]) * -(-cols_t // info["tile_n"]) * cnt
+        assert info["tiles"] >= 2 * whole_tiles, (shape, ta, tb, to, info)   # it was cut
+        f64 = ref.batched_matmul_f64(cnt, a_st, ta, b_st, tb, to, M, Kd, N)
+        assert ref.rel_frobenius(res, f64) < TOL_F16, (shape, ta, tb, to, info)
+
+
+@pytest.mark.parametrize("parts", [1, 2, 5, 16, 64])
+def test_half_forced_cuts_agree(be, parts, monkeypatch):
+    """HC_TC_SPLITS forces the number of parts (1: never cut).  Every cut gives the float64
+    product within the float16 tolerance, and a result that float16 represents exactly
+    (small integers) is identical whatever the cut."""
+    monkeypatch.setenv("HC_TC_SPLITS", str(parts))
+    M, Kd, N = 264, 2120, 200
+    A, B = random_operands(3, 1, M, Kd, N, np.float16, scale=0.25)
+    res, a_st, b_st = run(be, 1, A, B, False, False, False, np.float16, TENSOR())
+    f64 = ref.batched_matmul_f64(1, a_st, False, b_st, False, False, M, Kd, N)
+    assert ref.rel_frobenius(res, f64) < TOL_F16, parts
+    Ai, Bi = random_operands(4, 1, M, Kd, N, np.float16, dist="smallint")
+    resi, ai, bi = run(be, 1, Ai, Bi, False, True, False, np.float16, TENSOR())
+    exact = ref.batched_matmul_f64(1, ai, False, bi, True, False, M, Kd, N)
+    assert np.array_equal(resi, exact.reshape(-1).astype(np.float16)), parts
+
+
+@pytest.mark.parametrize("shape", [(512, 4096, 512, 1), (200, 2056, 136, 2), (128, 8192, 128, 1)])
+def test_float_cut_contraction(be, shape):
+    M, Kd, N, cnt = shape
+    for (ta, tb, to) in FLAG_COMBOS:
+        A, B = random_operands(M + N + 1, cnt, M, Kd, N, np.float32, dist="uniform11")
+        res, a_st, b_st = run(be, cnt, A, B, ta, tb, to, np.float32, TENSOR())
+        info = be.lastLaunchInfo()
+        f64 = ref.batched_matmul_f64(cnt, a_st, ta, b_st, tb, to, M, Kd, N)
+        assert ref.rel_frobenius(res, f64) < TOL_F32, (shape, ta, tb, to, info)
+
+
+def test_column_block_of_cut_product_equals_whole(be):
+    """A block planned as the whole product is cut the same way: bitwise the whole's columns."""
+    from honeycrisp_b200 import _lib
+    M, Kd, N = 384, 4096, 512
+    for dtype in (np.float16, np.float32):
+        A, B = random_operands(12, 1, M, Kd, N, dtype, scale=0.25)
+        full, a_st, b_st = run(be, 1, A, B, False, True, False, dtype, TENSOR())
+        out = be.allocate(M * N * np.dtype(dtype).itemsize)
+        for (b0, cnt) in ((0, 128), (128, 256), (384, 128)):
+            be.matmulColumnBlock(a_st, False, b_st, True, False, M, Kd, N, b0, cnt, dtype, out=out,
+                                 kernel=_lib.HC_KERNEL_TENSOR)
+        got = out.onCPU(dtype)[: M * N]
+        assert np.array_equal(got.view(np.uint8), full.view(np.uint8)), dtype
+
+
 @pytest.mark.parametrize("shape", [(128, 32, 256, 1), (256, 32, 256, 1), (256, 256, 512, 1), (200, 132, 328, 2),
                                    (1000, 516, 776, 2), (1024, 1024, 1024, 1), (384, 4, 96, 2)])
 @pytest.mark.parametrize("dist", ["uniform01", "uniform11"])
