@@ -124,6 +124,12 @@ __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;"
 __device__ __forceinline__ void cluster_sync_all() {
   asm volatile("barrier.cluster.arrive.release.aligned;\nbarrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
+// Rendezvous without memory ordering: for the teardown, where the CTAs of a pair only have to
+// know that the other has stopped signalling (a releasing arrive first waits for the thread's
+// outstanding writes to be visible cluster-wide, about 0.5 us at the end of every launch).
+__device__ __forceinline__ void cluster_rendezvous() {
+  asm volatile("barrier.cluster.arrive.relaxed.aligned;\nbarrier.cluster.wait.aligned;" ::: "memory");
+}
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
   asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
 }
@@ -134,6 +140,12 @@ __device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
 // Arrive on a barrier given by its cluster-wide address (this CTA's or the partner's).
 __device__ __forceinline__ void mbar_arrive_cluster(uint32_t bar) {
   asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+// The same without memory ordering.  Handing an accumulator buffer back to the MMA issuer orders
+// tensor-memory accesses only, which tcgen05.fence does on both sides of the barrier; a releasing
+// arrive here waited about 1400 clocks for the epilogue's own stores on every tile.
+__device__ __forceinline__ void mbar_arrive_cluster_relaxed(uint32_t bar) {
+  asm volatile("mbarrier.arrive.relaxed.cluster.shared::cluster.b64 _, [%0];" ::"r"(bar) : "memory");
 }
 __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
   uint32_t ok;
@@ -577,12 +589,12 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap mapA_hi, const __grid_constan
       uint32_t s = 0, ph = 0;
       bool ok = true;
       TileCoord t = decode_tile(tile_first < p.total_tiles ? tile_first : 0, p);
+      KRange kr = k_range(t.mat, p);
       pdl_wait();
       for (int64_t tile = tile_first; ok && tile < p.total_tiles; tile += tile_step) {
-        if (tile != tile_first) t = decode_tile(tile, p);
+        if (tile != tile_first) { t = decode_tile(tile, p); kr = k_range(t.mat, p); }
         const int m0 = t.tm * (BM * kCta) + (int)rank * BM;
         const int n0 = t.tn * TILE_N + (int)rank * BN_LOCAL;
-        const KRange kr = k_range(t.mat, p);
         const int mat = kr.mat;
         for (int kb = 0; kb < kr.count; kb++) {
           if (!mbar_wait(bar_empty + 8 * s, ph ^ 1, abortp)) {
@@ -834,7 +846,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap mapA_hi, const __grid_constan
           }
         }
         tc_fence_before();
-        mbar_arrive_cluster(tempty_leader + 8 * slot);
+        mbar_arrive_cluster_relaxed(tempty_leader + 8 * slot);
         win++;
       } else {
         float acc[COLS_PER_THREAD];
@@ -862,7 +874,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap mapA_hi, const __grid_constan
             }
           }
           tc_fence_before();
-          mbar_arrive_cluster(tempty_leader + 8 * slot);
+          mbar_arrive_cluster_relaxed(tempty_leader + 8 * slot);
           win++;
         }
         if (ok && p.tma_store) {
@@ -914,7 +926,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap mapA_hi, const __grid_constan
   __syncwarp();
   tc_fence_before();
   __syncthreads();
-  if (kCta == 2) cluster_sync_all();   // neither CTA leaves while the other may still signal it
+  if (kCta == 2) cluster_rendezvous();   // neither CTA leaves while the other may still signal it
   tc_fence_after();
   if (abort_flag) {
     // Give copies and MMAs that were already issued time to land before the CTA's
