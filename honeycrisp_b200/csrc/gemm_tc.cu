@@ -3,20 +3,26 @@
 // shared memory and TMA stores.
 //
 // One persistent CTA per SM walks a list of output tiles.  Inside a CTA:
-//   warp 0, one lane : TMA producer.  Fills a ring of kStages shared-memory slots with one
-//                      128-byte-wide k-slab of A and of B per slot (128B-swizzled).
+//   warp 0, one lane : TMA producer of A.  Fills a ring of kStages shared-memory slots with one
+//                      or two 128-byte-wide k-slabs of A per slot (128B-swizzled) and announces
+//                      the slot's bytes to its barrier.
+//   last warp, one lane : TMA producer of B, into the same slots.
 //   warp 1, one lane : MMA issuer.  For every filled slot issues the tcgen05.mma instructions
-//                      of that slab into an accumulator buffer in tensor memory, then commits
-//                      the slot back to the producer.
+//                      of its slabs into an accumulator buffer in tensor memory, then commits
+//                      the slot back to the producers.
 //   warps 2..        : epilogue.  Drain a finished accumulator (tcgen05.ld), round, stage the
 //                      rows in swizzled shared memory and send them with TMA stores, then hand
 //                      the accumulator back, while the issuer already works on the other one.
+// Each of these single-thread loops has to stay shorter than the MMAs of one slot execute
+// (512 clocks for a 256x256 pair tile and one slab): no division, non-blocking barrier probes
+// first, and the copies split over two threads (one tensor copy costs its thread ~115 clocks).
 // The issuing lanes are chosen with elect.sync, never by comparing the lane index: only then
 // does the compiler keep descriptors in uniform registers, and a tcgen05.mma issues in a few
 // cycles instead of ~220.
 //
 // Tile shapes:
-//   128 x 128 / 128 x 256 on one CTA     narrow or small products;
+//   128 x 128 / 128 x 256 on one CTA     products of at most 128 rows;
+//   256 x 128 / 256 x 64 on a CTA pair   products too small to fill the SMs with larger tiles;
 //   256 x 256 on a CTA pair              cta_group::2: the two CTAs of a cluster own the upper and
 //                                        lower 128 rows, each loads its own rows of A and its own
 //                                        half of the B columns, the leader issues one MMA that
@@ -489,7 +495,7 @@ __device__ __forceinline__ KRange k_range(int64_t vmat, const TcParams& p) {
 // kPartial  : float16 operands, float32 results: the partial sums of a contraction cut into parts.
 template <int kElemBytes, int kBN, int kStages, int kEpiWarps, bool kWindowed, int kCta, int kNSplit, int kSlabs,
           bool kPartial>
-__global__ void __launch_bounds__(64 + 32 * kEpiWarps, 1)
+__global__ void __launch_bounds__(96 + 32 * kEpiWarps, 1)
 tc_gemm_kernel(const __grid_constant__ CUtensorMap mapA_hi, const __grid_constant__ CUtensorMap mapA_lo,
                const __grid_constant__ CUtensorMap mapB_hi, const __grid_constant__ CUtensorMap mapB_lo,
                const __grid_constant__ OutMaps mapC, const TcParams p) {
@@ -575,16 +581,22 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap mapA_hi, const __grid_constan
   const int chunk_kb = p.chunk_kb;
   const int64_t tile_first = blockIdx.x / kCta, tile_step = gridDim.x / kCta;
 
-  if (warp == 0) {
-    // ---------------------------------------------------------------- TMA producer
+  constexpr int kWarpProducerB = 2 + kEpiWarps;
+  if (warp == 0 || warp == kWarpProducerB) {
+    // ---------------------------------------------------------------- TMA producers
+    // Issuing one tensor copy costs its thread about 115 clocks, and a slot takes two to eight of
+    // them (two slabs; two boxes per slab for an MN-major operand): one thread doing all of it
+    // is slower than the MMAs of the small tile shapes and of transposed operands.  Warp 0 copies
+    // A and announces the slot's bytes, the last warp copies B; both watch the same barriers.
+    const bool do_a = (warp == 0), do_b = !do_a;
     if (elect_one()) {
-      asm volatile("prefetch.tensormap [%0];" ::"l"((unsigned long long)&mapA_hi) : "memory");
-      asm volatile("prefetch.tensormap [%0];" ::"l"((unsigned long long)&mapB_hi) : "memory");
-      // Completion bytes of both CTAs of a pair are counted on the leader's barrier.
+      if (do_a) asm volatile("prefetch.tensormap [%0];" ::"l"((unsigned long long)&mapA_hi) : "memory");
+      if (do_b) asm volatile("prefetch.tensormap [%0];" ::"l"((unsigned long long)&mapB_hi) : "memory");
       if (kTf32) {
-        asm volatile("prefetch.tensormap [%0];" ::"l"((unsigned long long)&mapA_lo) : "memory");
-        asm volatile("prefetch.tensormap [%0];" ::"l"((unsigned long long)&mapB_lo) : "memory");
+        if (do_a) asm volatile("prefetch.tensormap [%0];" ::"l"((unsigned long long)&mapA_lo) : "memory");
+        if (do_b) asm volatile("prefetch.tensormap [%0];" ::"l"((unsigned long long)&mapB_lo) : "memory");
       }
+      // Completion bytes of both CTAs of a pair are counted on the leader's barrier.
       const uint32_t full_leader = (kCta == 2) ? map_to_cta(bar_full, 0) : bar_full;
       uint32_t s = 0, ph = 0;
       bool ok = true;
@@ -605,11 +617,13 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap mapA_hi, const __grid_constan
           }
           const uint32_t full = full_leader + 8 * s;
           if (p.debug & 8) {  // timing experiment: no copies
-            if (rank == 0) mbar_expect_tx(bar_full + 8 * s, 0);
+            if (rank == 0 && do_a) mbar_expect_tx(bar_full + 8 * s, 0);
             if (++s == kStages) { s = 0; ph ^= 1; }
             continue;
           }
-          if (rank == 0) mbar_expect_tx(bar_full + 8 * s, STAGE_BYTES * kCta);
+          // (copies of B may complete before the bytes are announced: the count goes negative
+          // for a moment, and the phase cannot complete before this arrive)
+          if (rank == 0 && do_a) mbar_expect_tx(bar_full + 8 * s, STAGE_BYTES * kCta);
           // A slab past the end of K lies outside the tensor and arrives as zeros.
 #pragma unroll
           for (int j = 0; j < kSlabs; j++) {
@@ -620,14 +634,16 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap mapA_hi, const __grid_constan
             const CUtensorMap* ma = part ? &mapA_lo : &mapA_hi;
             const CUtensorMap* mb = part ? &mapB_lo : &mapB_hi;
             const uint32_t sa = stage + part * A_BYTES, sb = stage + PARTS * A_BYTES + part * B_BYTES;
-            if (!p.a_mn_major) {
-              tma_load_3d<kCta>(sa, ma, full, kc, m0, mat);
-            } else {
+            if (do_a) {
+              if (!p.a_mn_major) {
+                tma_load_3d<kCta>(sa, ma, full, kc, m0, mat);
+              } else {
 #pragma unroll
-              for (int c = 0; c < BM / CH; c++) tma_load_3d<kCta>(sa + c * (BK * 128), ma, full, m0 + c * CH, kc, mat);
+                for (int c = 0; c < BM / CH; c++) tma_load_3d<kCta>(sa + c * (BK * 128), ma, full, m0 + c * CH, kc, mat);
+              }
             }
 #pragma unroll
-            for (int h = 0; h < kNSplit; h++) {
+            for (int h = 0; do_b && h < kNSplit; h++) {
               const uint32_t sbh = sb + h * B_PART_BYTES;
               const int n0h = n0 + h * kBN;
               if (!p.b_mn_major) {
@@ -643,7 +659,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap mapA_hi, const __grid_constan
           if (++s == kStages) { s = 0; ph ^= 1; }
         }
       }
-      if (kCta == 2 && ok) {
+      if (kCta == 2 && ok && do_a) {
         // Drain: every slot's release (an asynchronous arrive from the leader's MMA commits)
         // must have landed in this CTA's barriers before the CTA may exit.
         for (int i = 0; i < kStages; i++) {
@@ -731,7 +747,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap mapA_hi, const __grid_constan
         }
       }
     }
-  } else {
+  } else if (warp < kWarpProducerB) {
     // ---------------------------------------------------------------- epilogue
     const int ew = warp - 2;
     const int quarter = warp & 3;            // tensor-memory lanes this warp may read
@@ -916,7 +932,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap mapA_hi, const __grid_constan
     }
   }
 
-  if (warp >= 2) {
+  if (warp >= 2 && warp < kWarpProducerB) {
     // Shared memory must outlive the TMA stores that read it, and stores into other devices'
     // memory must be complete when the kernel ends.
     __syncwarp();
@@ -1201,7 +1217,7 @@ struct TcConfig {
   static constexpr size_t smem = (size_t)kStages * kSlabs * (kElemBytes == 4 ? 2 : 1) * (BM * 128 + kNSplit * (kBN / kCta) * 128) +
                                  (size_t)kEpiWarps * staging_bufs((kElemBytes == 2 && !kPartial) ? 2 : 4, kBN, kEpiWarps, kWindowed, kNSplit) * 4096 + 1024;
   static_assert(smem <= 232448, "more shared memory than one CTA can have on sm_100");
-  static constexpr int block = 64 + 32 * kEpiWarps;
+  static constexpr int block = 96 + 32 * kEpiWarps;   // producers A and B, MMA issuer, epilogue warps
   static auto kernel() { return tc_gemm_kernel<kElemBytes, kBN, kStages, kEpiWarps, kWindowed, kCta, kNSplit, kSlabs, kPartial>; }
 
   static cudaError_t configure() {
