@@ -1285,8 +1285,9 @@ struct TcConfig {
       rec->tile_m = BM * kCta; rec->tile_n = kBN * kNSplit; rec->tile_k = kSlabs * 128 / kElemBytes; rec->stages = kStages;
       rec->grid = grid; rec->block = block; rec->launches++;
     }
-    if (e != cudaSuccess) return e;
-    return cudaGetLastError();
+    // cudaLaunchKernelEx reports this launch's own failure; the thread's sticky-less "last error"
+    // may hold another library's earlier error and is not this launch's to report.
+    return e;
   }
 };
 
@@ -1369,8 +1370,7 @@ constexpr size_t kMaxSplitWorkspace = 256ull << 20;
 // gradient of a small Linear layer: few outputs, many tokens), the contraction is cut into up to
 // 16 parts that run as separate tiles into float32 partial matrices, summed in ascending part
 // order by a second kernel (splitk_reduce_kernel): deterministic, and float16 still rounds once.
-// float32 keeps two shape rules: 256 columns unless the product is narrow, and 128x128 tiles
-// when 256x256 pairs would idle more than half the SMs.
+// float32 (3xTF32, 12 MMAs per 32-wide slab) goes through the same model with its own clocks.
 TcPlan plan_tc(const GemmProblem& p, int sm_count, bool may_split) {
   const bool f32 = p.dtype == HC_F32;
   const int BK = f32 ? 32 : 64;
@@ -1394,16 +1394,17 @@ TcPlan plan_tc(const GemmProblem& p, int sm_count, bool may_split) {
     // 32 columns of B per CTA: half a 128-byte row of an MN-major box, which the copy cannot split
     cands[n_cands++] = {SHAPE_PAIR_64, pairs_ok && !p.b_mn_major, 256, 64, pair_slots, 2, 265.0, 0.0, true};
   } else {
-    const int64_t pair_tiles = ((M + 255) / 256) * ((N + 255) / 256) * p.batch;
-    const bool few_tiles = pair_tiles * 4 <= sm_count;
-    const bool wide_cols = N > 128 && !few_tiles;
-    const int shape = !wide_cols ? SHAPE_C1_128 : pairs_ok ? SHAPE_PAIR : SHAPE_C1_256;
-    // one 32-wide slab of the three products: 12 MMAs
-    if (shape == SHAPE_PAIR) cands[n_cands++] = {SHAPE_PAIR, true, 256, 256, pair_slots, 1, 1620.0, 0.0, true};
-    else if (shape == SHAPE_C1_256) cands[n_cands++] = {SHAPE_C1_256, true, 128, 256, sm_count, 1, 1800.0, 0.0, true};
-    else cands[n_cands++] = {SHAPE_C1_128, true, 128, 128, sm_count, 1, 960.0, 0.0, true};
+    // float32 (3xTF32): 12 MMAs per 32-wide slab; clocks per slab measured the same way.  The small
+    // pair shapes need the windowed epilogue (they are not built for the no-window debug mode).
+    const bool small_ok = pairs_ok && !(dbg & 2);
+    cands[n_cands++] = {SHAPE_WIDE, false, 256, 512, pair_slots, 1, 0.0, 0.0, false};
+    cands[n_cands++] = {SHAPE_PAIR, pairs_ok && N > 128, 256, 256, pair_slots, 1, 1700.0, 0.0, true};
+    cands[n_cands++] = {SHAPE_C1_256, N > 128, 128, 256, sm_count, 1, 1900.0, 0.0, true};
+    cands[n_cands++] = {SHAPE_C1_128, true, 128, 128, sm_count, 1, 1130.0, 0.0, true};
+    cands[n_cands++] = {SHAPE_PAIR_128, small_ok && N > 64, 256, 128, pair_slots, 1, 950.0, 0.0, true};
+    cands[n_cands++] = {SHAPE_PAIR_64, small_ok, 256, 64, pair_slots, 1, 615.0, 0.0, true};
   }
-  const int forced = f32 ? 0 : env_int("HC_TC_SHAPE", 0);
+  const int forced = env_int("HC_TC_SHAPE", 0);
   const int forced_splits = env_int("HC_TC_SPLITS", 0);   // 1: never cut; n > 1: cut into n where possible
   int choices[8] = {1, 2, 3, 4, 6, 8, 12, 16};
   int n_choices = 8;
@@ -1536,8 +1537,6 @@ cudaError_t launch_tc(const GemmProblem& p, cudaStream_t stream, unsigned int* s
       cudaError_t se = cudaLaunchKernelEx(&scfg, split_tf32_kernel, ja, jb, blocks_a);
       if (se != cudaSuccess) return se;
     }
-    cudaError_t e = cudaGetLastError();
-    if (e != cudaSuccess) return e;
     if (rec) { rec->launches += 1; rec->scratch_bytes = 2 * s.a_bytes + 2 * s.b_bytes; }
     a_hi = ah; a_lo = al; b_hi = bh; b_lo = bl;
     lda = s.a_ld; ldb = s.b_ld; sa = s.a_mat; sb = s.b_mat;
@@ -1638,7 +1637,9 @@ cudaError_t launch_tc(const GemmProblem& p, cudaStream_t stream, unsigned int* s
     else if (bn == 256) ge = TcConfig<2, 256, 4, 4, false, 1>::launch(maps, outs, tp, sm_count, stream, rec);
     else ge = TcConfig<2, 128, 3, 4, false, 1, 1, 2>::launch(maps, outs, tp, sm_count, stream, rec);
   } else if (windowed) {
-    if (cta == 2) ge = TcConfig<4, 256, 3, 8, true, 2>::launch(maps, outs, tp, sm_count, stream, rec);
+    if (shape == SHAPE_PAIR_128) ge = TcConfig<4, 128, 3, 4, true, 2>::launch(maps, outs, tp, sm_count, stream, rec);
+    else if (shape == SHAPE_PAIR_64) ge = TcConfig<4, 64, 4, 4, true, 2>::launch(maps, outs, tp, sm_count, stream, rec);
+    else if (cta == 2) ge = TcConfig<4, 256, 3, 8, true, 2>::launch(maps, outs, tp, sm_count, stream, rec);
     else if (bn == 256) ge = TcConfig<4, 256, 2, 8, true, 1>::launch(maps, outs, tp, sm_count, stream, rec);
     else ge = TcConfig<4, 128, 3, 4, true, 1>::launch(maps, outs, tp, sm_count, stream, rec);
   } else {
@@ -1671,7 +1672,7 @@ cudaError_t launch_tc(const GemmProblem& p, cudaStream_t stream, unsigned int* s
                        : cudaLaunchKernelEx(&rcfg, splitk_reduce_kernel<true>, job);
   if (re != cudaSuccess) return re;
   if (rec) rec->launches += 1;
-  return cudaGetLastError();
+  return cudaSuccess;
 }
 
 }  // namespace hc

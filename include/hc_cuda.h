@@ -121,7 +121,12 @@ void hc_event_destroy(hc_event* ev);
 
 /* out = trans_out(op(a) * op(b)).
  * Replaces: Backend.matmul(a:transA:b:transB:transOut:rows:inner:cols:dtype:)
- * (Sources/Honeycrisp/Backend.swift:650-658; CPU body BackendCPU.swift:1222-1232). */
+ * (Sources/Honeycrisp/Backend.swift:650-658; CPU body BackendCPU.swift:1222-1232).
+ * The products may use the context's work area, a device buffer that only grows (to the
+ * largest need seen: float32 operands split into TF32 parts, float16 operands repacked to an
+ * aligned pitch, and at most 256 MiB of float32 partial sums when a long contraction over few
+ * outputs is cut into parts); growing it is the only allocation a product makes.  Results do
+ * not depend on how the work is tiled, cut or scheduled: the same call gives the same bits. */
 hc_status hc_matmul(hc_ctx* ctx, hc_dtype dtype, const void* a, int trans_a, const void* b,
                     int trans_b, int trans_out, int64_t rows, int64_t inner, int64_t cols,
                     void* out);

@@ -79,6 +79,22 @@ def test_half_every_tile_shape(be, forced, monkeypatch):
     assert TILE_SHAPES[forced] in used, (forced, used)
 
 
+@pytest.mark.parametrize("forced", [2, 3, 4, 5, 6])
+def test_float_every_tile_shape(be, forced, monkeypatch):
+    monkeypatch.setenv("HC_TC_SHAPE", str(forced))
+    monkeypatch.setenv("HC_TC_SPLITS", "1")
+    M, Kd, N, cnt = 520, 264, 1096, 2
+    used = set()
+    for (ta, tb, to) in FLAG_COMBOS:
+        A, B = random_operands(forced, cnt, M, Kd, N, np.float32, dist="uniform11")
+        res, a_st, b_st = run(be, cnt, A, B, ta, tb, to, np.float32, TENSOR())
+        info = be.lastLaunchInfo()
+        used.add((info["tile_m"], info["tile_n"]))
+        f64 = ref.batched_matmul_f64(cnt, a_st, ta, b_st, tb, to, M, Kd, N)
+        assert ref.rel_frobenius(res, f64) < TOL_F32, (forced, ta, tb, to, info)
+    assert TILE_SHAPES[forced] in used, (forced, used)
+
+
 def test_half_small_products_take_small_pair_tiles(be):
     # one wave either way: the smaller shape spreads it over more SMs
     for (n, tile) in [(512, (256, 64)), (1536, (256, 128)), (2048, (256, 256))]:
