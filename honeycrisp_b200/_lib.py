@@ -39,6 +39,13 @@ class LaunchInfo(ctypes.Structure):
     ]
 
 
+class PlanInfo(ctypes.Structure):
+    _fields_ = [
+        ("tile_m", _int), ("tile_n", _int), ("ctas_per_tile", _int), ("slabs_per_slot", _int),
+        ("parts", _int), ("slots_per_part", _int), ("tiles", _i64), ("workspace_bytes", _sz),
+    ]
+
+
 # name -> (restype, argtypes); the complete export list of include/hc_cuda.h
 SIGNATURES = {
     "hc_init": (_int, [_int, ctypes.POINTER(_vp)]),
@@ -80,6 +87,7 @@ SIGNATURES = {
     "hc_status_string": (ctypes.c_char_p, [_int]),
     "hc_last_error": (ctypes.c_char_p, [_vp]),
     "hc_last_launch_info": (_int, [_vp, ctypes.POINTER(LaunchInfo)]),
+    "hc_plan_product": (_int, [_int, _i64, _int, _int, _int, _i64, _i64, _i64, _int, ctypes.POINTER(PlanInfo)]),
     "hc_launch_count": (_i64, [_vp]),
     "hc_check_device_status": (_int, [_vp]),
     "hc_selftest_bounded_wait": (_int, [_vp, _int]),

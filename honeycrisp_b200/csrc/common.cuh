@@ -72,6 +72,9 @@ bool tc_supported(const GemmProblem& p);
 // One-thread kernel whose bounded wait is made to expire after `limit_ns` (self-test).
 cudaError_t launch_wait_probe(cudaStream_t stream, unsigned int* status_word, unsigned long long limit_ns);
 size_t tc_scratch_bytes(const GemmProblem& p, int sm_count);
+// The tiling the tensor-core path would choose for `p` (host arithmetic only).
+struct PlanSummary { int tile_m, tile_n, ctas, slabs, parts, slots_per_part; int64_t tiles; size_t ws_bytes; };
+PlanSummary tc_describe_plan(const GemmProblem& p, int sm_count);
 
 }  // namespace hc
 

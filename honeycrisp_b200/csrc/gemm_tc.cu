@@ -58,6 +58,8 @@
 
 #include "common.cuh"
 
+extern "C" char** environ;
+
 namespace hc {
 namespace {
 
@@ -1186,6 +1188,36 @@ bool operand_ok(const void* base, int elem_bytes, int64_t ld, int64_t stride_mat
   return true;
 }
 
+// Per-launch diagnostic switches, gathered in one pass over the environment (a getenv per
+// switch costs a scan each, a few microseconds per launch in total).
+struct Tunables {
+  int wide_min_kb = 32;   // HC_TC_WIDE_MIN_KB: k blocks from which the 256x512 tile is considered
+  int shape = 0;          // HC_TC_SHAPE: force a tile shape (1..6)
+  int splits = 0;         // HC_TC_SPLITS: 1 never cut the contraction, n > 1 cut into n parts
+  int short_k = 8;        // HC_TC_SHORT_K: slabs up to which the eight-warp epilogue config is used
+  int group_m = 0;        // HC_TC_GROUP_M: tile rows sharing a sweep over the columns (0: default)
+  int wide_epi8 = 1;      // HC_TC_WIDE_EPI8: eight epilogue warps on the 256x512 tile
+};
+Tunables read_tunables() {
+  Tunables t;
+  for (char** e = environ; e && *e; e++) {
+    const char* s = *e;
+    if (s[0] != 'H' || strncmp(s, "HC_TC_", 6) != 0) continue;
+    const char* eq = strchr(s, '=');
+    if (!eq) continue;
+    const char* k = s + 6;
+    const size_t n = (size_t)(eq - k);
+    const int v = atoi(eq + 1);
+    if (n == 5 && !strncmp(k, "SHAPE", 5)) t.shape = v;
+    else if (n == 6 && !strncmp(k, "SPLITS", 6)) t.splits = v;
+    else if (n == 11 && !strncmp(k, "WIDE_MIN_KB", 11)) t.wide_min_kb = v;
+    else if (n == 7 && !strncmp(k, "SHORT_K", 7)) t.short_k = v;
+    else if (n == 7 && !strncmp(k, "GROUP_M", 7)) t.group_m = v;
+    else if (n == 9 && !strncmp(k, "WIDE_EPI8", 9)) t.wide_epi8 = v;
+  }
+  return t;
+}
+
 int env_int(const char* name, int fallback) {
   const char* e = getenv(name);
   return e ? atoi(e) : fallback;
@@ -1371,7 +1403,7 @@ constexpr size_t kMaxSplitWorkspace = 256ull << 20;
 // 16 parts that run as separate tiles into float32 partial matrices, summed in ascending part
 // order by a second kernel (splitk_reduce_kernel): deterministic, and float16 still rounds once.
 // float32 (3xTF32, 12 MMAs per 32-wide slab) goes through the same model with its own clocks.
-TcPlan plan_tc(const GemmProblem& p, int sm_count, bool may_split) {
+TcPlan plan_tc(const GemmProblem& p, int sm_count, bool may_split, const Tunables& tun) {
   const bool f32 = p.dtype == HC_F32;
   const int BK = f32 ? 32 : 64;
   const int dbg = debug_flags();
@@ -1385,7 +1417,7 @@ TcPlan plan_tc(const GemmProblem& p, int sm_count, bool may_split) {
   Cand cands[SHAPE_COUNT - 1];
   int n_cands = 0;
   if (!f32) {
-    const bool wide_ok = pairs_ok && N >= 1024 && kslabs >= env_int("HC_TC_WIDE_MIN_KB", 32);
+    const bool wide_ok = pairs_ok && N >= 1024 && kslabs >= tun.wide_min_kb;
     cands[n_cands++] = {SHAPE_WIDE, wide_ok, 256, 512, pair_slots, 1, 1140.0, drain, false};
     cands[n_cands++] = {SHAPE_PAIR, pairs_ok && N > 128, 256, 256, pair_slots, 1, 600.0, 0.0, true};
     cands[n_cands++] = {SHAPE_C1_256, N > 128, 128, 256, sm_count, 1, 680.0, 0.0, false};
@@ -1404,8 +1436,8 @@ TcPlan plan_tc(const GemmProblem& p, int sm_count, bool may_split) {
     cands[n_cands++] = {SHAPE_PAIR_128, small_ok && N > 64, 256, 128, pair_slots, 1, 950.0, 0.0, true};
     cands[n_cands++] = {SHAPE_PAIR_64, small_ok, 256, 64, pair_slots, 1, 615.0, 0.0, true};
   }
-  const int forced = env_int("HC_TC_SHAPE", 0);
-  const int forced_splits = env_int("HC_TC_SPLITS", 0);   // 1: never cut; n > 1: cut into n where possible
+  const int forced = tun.shape;
+  const int forced_splits = tun.splits;   // 1: never cut; n > 1: cut into n where possible
   int choices[8] = {1, 2, 3, 4, 6, 8, 12, 16};
   int n_choices = 8;
   if (forced_splits > 1) { choices[0] = forced_splits > 64 ? 64 : forced_splits; n_choices = 1; }
@@ -1459,8 +1491,24 @@ static size_t operand_scratch_bytes(const GemmProblem& p) {
 // 256-byte aligned, the partial matrices of a cut contraction.
 size_t tc_scratch_bytes(const GemmProblem& p, int sm_count) {
   const size_t ops = operand_scratch_bytes(p);
-  const TcPlan plan = plan_tc(p, sm_count, true);
+  const TcPlan plan = plan_tc(p, sm_count, true, read_tunables());
   return plan.ws_bytes ? ((ops + 255) & ~(size_t)255) + plan.ws_bytes : ops;
+}
+
+PlanSummary tc_describe_plan(const GemmProblem& p, int sm_count) {
+  const TcPlan plan = plan_tc(p, sm_count, true, read_tunables());
+  static const int kRows[SHAPE_COUNT] = {0, 256, 256, 128, 128, 256, 256};
+  static const int kCols[SHAPE_COUNT] = {0, 512, 256, 256, 128, 128, 64};
+  PlanSummary r;
+  r.tile_m = kRows[plan.shape]; r.tile_n = kCols[plan.shape];
+  r.ctas = r.tile_m / BM;
+  r.slabs = plan.slabs; r.parts = plan.splits;
+  const int BK = p.dtype == HC_F32 ? 32 : 64;
+  const int kslots = (int)(((p.K + BK - 1) / BK + plan.slabs - 1) / plan.slabs);
+  r.slots_per_part = plan.splits > 1 ? plan.kb_per_split : kslots;
+  r.tiles = ((p.M + r.tile_m - 1) / r.tile_m) * ((p.N + r.tile_n - 1) / r.tile_n) * p.batch * plan.splits;
+  r.ws_bytes = plan.ws_bytes;
+  return r;
 }
 
 cudaError_t launch_tc(const GemmProblem& p, cudaStream_t stream, unsigned int* status_word, void* scratch,
@@ -1544,7 +1592,8 @@ cudaError_t launch_tc(const GemmProblem& p, cudaStream_t stream, unsigned int* s
 
   const int dbg = debug_flags();
   const int kslabs = (int)((p.K + BK - 1) / BK);
-  const TcPlan plan = plan_tc(p, sm_count, n_extra == 0);
+  const Tunables tun = read_tunables();
+  const TcPlan plan = plan_tc(p, sm_count, n_extra == 0, tun);
   const int shape = plan.shape;
   const int bn = (shape == SHAPE_C1_128 || shape == SHAPE_PAIR_128) ? 128 : shape == SHAPE_PAIR_64 ? 64 : 256;
   const int cta = (shape == SHAPE_C1_256 || shape == SHAPE_C1_128) ? 1 : 2;
@@ -1554,16 +1603,22 @@ cudaError_t launch_tc(const GemmProblem& p, cudaStream_t stream, unsigned int* s
   memset(maps, 0, sizeof maps);
   memset(&outs, 0, sizeof outs);
   if (!make_operand_map(&maps[0], a_hi, eb, p.a_mn_major, p.M, p.K, lda, sa, p.batch, BM) ||
-      !make_operand_map(&maps[1], a_lo, eb, p.a_mn_major, p.M, p.K, lda, sa, p.batch, BM) ||
-      !make_operand_map(&maps[2], b_hi, eb, p.b_mn_major, p.N, p.K, ldb, sb, p.batch, b_box) ||
-      !make_operand_map(&maps[3], b_lo, eb, p.b_mn_major, p.N, p.K, ldb, sb, p.batch, b_box))
+      !make_operand_map(&maps[2], b_hi, eb, p.b_mn_major, p.N, p.K, ldb, sb, p.batch, b_box))
     return cudaErrorNotSupported;
+  if (f32) {
+    if (!make_operand_map(&maps[1], a_lo, eb, p.a_mn_major, p.M, p.K, lda, sa, p.batch, BM) ||
+        !make_operand_map(&maps[3], b_lo, eb, p.b_mn_major, p.N, p.K, ldb, sb, p.batch, b_box))
+      return cudaErrorNotSupported;
+  } else {
+    maps[1] = maps[0];   // float16 has no lo parts; the kernel never reads these two
+    maps[3] = maps[2];
+  }
 
   TcParams tp;
   tp.M = p.M; tp.N = p.N;
   // Short contractions are bound by draining results, not by the MMA: they get more epilogue
   // warps and fewer operand stages.
-  const bool short_k = kslabs <= env_int("HC_TC_SHORT_K", 8);
+  const bool short_k = kslabs <= tun.short_k;
   const int slabs = plan.slabs;   // pipeline slots of the small float16 shapes hold two k slabs
   tp.num_k_blocks = (kslabs + slabs - 1) / slabs;
   const bool cut = plan.splits > 1;
@@ -1580,7 +1635,7 @@ cudaError_t launch_tc(const GemmProblem& p, cudaStream_t stream, unsigned int* s
   tp.tiles_m = (int)((p.M + tp.tile_rows - 1) / tp.tile_rows);
   tp.tiles_n = (int)((p.N + tile_n - 1) / tile_n);
   tp.total_tiles = (int64_t)tp.tiles_m * tp.tiles_n * p.batch * plan.splits;
-  tp.group_m = env_int("HC_TC_GROUP_M", 16 / cta);
+  tp.group_m = tun.group_m > 0 ? tun.group_m : 16 / cta;
   tp.a_mn_major = p.a_mn_major; tp.b_mn_major = p.b_mn_major;
   tp.status = status_word;
   tp.debug = dbg;
@@ -1628,7 +1683,7 @@ cudaError_t launch_tc(const GemmProblem& p, cudaStream_t stream, unsigned int* s
     else if (shape == SHAPE_C1_128) ge = TcConfig<2, 128, 3, 4, false, 1, 1, 2, true>::launch(maps, outs, tp, sm_count, stream, rec);
     else return cudaErrorInvalidValue;
   } else if (!f32) {
-    if (wide && env_int("HC_TC_WIDE_EPI8", 1)) ge = TcConfig<2, 256, 4, 8, false, 2, 2>::launch(maps, outs, tp, sm_count, stream, rec);
+    if (wide && tun.wide_epi8) ge = TcConfig<2, 256, 4, 8, false, 2, 2>::launch(maps, outs, tp, sm_count, stream, rec);
     else if (wide) ge = TcConfig<2, 256, 4, 4, false, 2, 2>::launch(maps, outs, tp, sm_count, stream, rec);
     else if (shape == SHAPE_PAIR_128) ge = TcConfig<2, 128, 4, 4, false, 2, 1, 2>::launch(maps, outs, tp, sm_count, stream, rec);
     else if (shape == SHAPE_PAIR_64) ge = TcConfig<2, 64, 4, 4, false, 2, 1, 2>::launch(maps, outs, tp, sm_count, stream, rec);

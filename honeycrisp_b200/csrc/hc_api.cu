@@ -674,6 +674,31 @@ hc_status hc_last_launch_info(hc_ctx* ctx, hc_launch_info* out) {
   return HC_OK;
 }
 
+hc_status hc_plan_product(hc_dtype dtype, int64_t matrix_count, int trans_a, int trans_b, int trans_out, int64_t rows,
+                          int64_t inner, int64_t cols, int sm_count, hc_plan_info* out) {
+  if (!out || (dtype != HC_F16 && dtype != HC_F32) || matrix_count < 1 || rows < 1 || inner < 1 || cols < 1 ||
+      sm_count < 2)
+    return HC_ERR_INVALID_ARGUMENT;
+  // The same folding as build_problem: a transposed output swaps the operand roles.
+  hc::GemmProblem p;
+  p.dtype = dtype; p.batch = matrix_count; p.K = inner;
+  p.A = p.B = nullptr; p.C = nullptr;
+  if (!trans_out) {
+    p.M = rows; p.N = cols;
+    p.a_mn_major = trans_a ? 1 : 0; p.b_mn_major = trans_b ? 0 : 1;
+  } else {
+    p.M = cols; p.N = rows;
+    p.a_mn_major = trans_b ? 0 : 1; p.b_mn_major = trans_a ? 1 : 0;
+  }
+  p.lda = p.a_mn_major ? p.M : p.K; p.ldb = p.b_mn_major ? p.N : p.K; p.ldc = p.N;
+  p.strideA = p.M * p.K; p.strideB = p.N * p.K; p.strideC = p.M * p.N;
+  const hc::PlanSummary r = hc::tc_describe_plan(p, sm_count);
+  out->tile_m = r.tile_m; out->tile_n = r.tile_n; out->ctas_per_tile = r.ctas;
+  out->slabs_per_slot = r.slabs; out->parts = r.parts; out->slots_per_part = r.slots_per_part;
+  out->tiles = r.tiles; out->workspace_bytes = r.ws_bytes;
+  return HC_OK;
+}
+
 int64_t hc_launch_count(hc_ctx* ctx) {
   if (!ctx) return 0;
   std::lock_guard<std::mutex> lock(ctx->mu);

@@ -266,6 +266,23 @@ const char* hc_status_string(hc_status s);
 const char* hc_last_error(hc_ctx* ctx);
 /* Geometry of the most recent product launched on this context. */
 hc_status hc_last_launch_info(hc_ctx* ctx, hc_launch_info* out);
+/* How the tensor-core path would tile a product on a device with `sm_count` SMs: tile shape,
+ * k slabs per pipeline slot, parts the contraction is cut into and the float32 work area those
+ * parts need.  Pure host arithmetic (no device, no context): the launch code calls the same
+ * routine, so tests can check the choice without a GPU.  No counterpart in the reference, which
+ * leaves tiling to MPSGraph / vDSP. */
+typedef struct hc_plan_info {
+  int tile_m, tile_n;      /* output tile of one CTA or CTA pair */
+  int ctas_per_tile;       /* 1, or 2 for a CTA pair (cta_group::2) */
+  int slabs_per_slot;      /* 128-byte k slabs per pipeline slot */
+  int parts;               /* 1, or the number of parts of a cut contraction */
+  int slots_per_part;      /* pipeline slots each part walks */
+  int64_t tiles;           /* tiles x parts over all matrices */
+  size_t workspace_bytes;  /* float32 partial sums (0 when parts == 1) */
+} hc_plan_info;
+hc_status hc_plan_product(hc_dtype dtype, int64_t matrix_count, int trans_a, int trans_b,
+                          int trans_out, int64_t rows, int64_t inner, int64_t cols, int sm_count,
+                          hc_plan_info* out);
 /* Kernels launched on this context since creation (each matrix product may launch several). */
 int64_t hc_launch_count(hc_ctx* ctx);
 /* Reads and clears the device-side status word; HC_ERR_TIMEOUT if a bounded wait expired in
