@@ -524,7 +524,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap mapA_hi, const __grid_constan
   constexpr int COL_SPLIT = kEpiWarps / 4;   // epilogue warps sharing one lane quarter
   constexpr int COLS_PER_THREAD = TILE_N / COL_SPLIT;
   static_assert(kNSplit == 1 || (kNSplit == 2 && !kWindowed && kBN == 256), "wide tiles: plain epilogue only");
-  static_assert(kEpiWarps == 4 || kEpiWarps == 8, "epilogue warps come in groups of four");
+  static_assert(kEpiWarps == 4 || kEpiWarps == 8 || kEpiWarps == 16, "epilogue warps come in groups of four");
   static_assert(TMEM_COLS == 64 || TMEM_COLS == 128 || TMEM_COLS == 256 || TMEM_COLS == 512, "power of two");
   static_assert(kCta == 1 || kCta == 2, "one CTA or a pair");
 
@@ -1617,7 +1617,9 @@ cudaError_t launch_tc(const GemmProblem& p, cudaStream_t stream, unsigned int* s
   TcParams tp;
   tp.M = p.M; tp.N = p.N;
   // Short contractions are bound by draining results, not by the MMA: they get more epilogue
-  // warps and fewer operand stages.
+  // warps (eight up to 8 slabs, sixteen up to 2: each warp's drain is a serial chain of tensor-
+  // memory load, conversion, proxy fence and TMA store, and more chains in flight hide more of
+  // it - measured +8 % at K = 128, nothing at K = 256, -3 % at K = 512) and fewer operand stages.
   const bool short_k = kslabs <= tun.short_k;
   const int slabs = plan.slabs;   // pipeline slots of the small float16 shapes hold two k slabs
   tp.num_k_blocks = (kslabs + slabs - 1) / slabs;
@@ -1687,6 +1689,7 @@ cudaError_t launch_tc(const GemmProblem& p, cudaStream_t stream, unsigned int* s
     else if (wide) ge = TcConfig<2, 256, 4, 4, false, 2, 2>::launch(maps, outs, tp, sm_count, stream, rec);
     else if (shape == SHAPE_PAIR_128) ge = TcConfig<2, 128, 4, 4, false, 2, 1, 2>::launch(maps, outs, tp, sm_count, stream, rec);
     else if (shape == SHAPE_PAIR_64) ge = TcConfig<2, 64, 4, 4, false, 2, 1, 2>::launch(maps, outs, tp, sm_count, stream, rec);
+    else if (cta == 2 && short_k && kslabs <= 2) ge = TcConfig<2, 256, 4, 16, false, 2>::launch(maps, outs, tp, sm_count, stream, rec);
     else if (cta == 2 && short_k) ge = TcConfig<2, 256, 4, 8, false, 2>::launch(maps, outs, tp, sm_count, stream, rec);
     else if (cta == 2) ge = TcConfig<2, 256, 6, 4, false, 2>::launch(maps, outs, tp, sm_count, stream, rec);
     else if (bn == 256) ge = TcConfig<2, 256, 4, 4, false, 1>::launch(maps, outs, tp, sm_count, stream, rec);
