@@ -607,7 +607,39 @@ def sharded_configs(be, stream, rank, world):
         del graph
     except Exception as e:  # capture is an optimisation of the measurement, not of the product
         res["c3_batch_sharded_graph"] = {"error": str(e)[:200]}
-    del q, k, o
+    del o
+    # The whole batch on rank 0 alone, in the same run and measured the same way: the
+    # denominator of the strong-scaling ratio on this box.
+    if world > 1:
+        one_ms = 0.0
+        if rank == 0:
+            try:
+                o1 = torch.empty(64 * 2048 * 2048, device="cuda", dtype=torch.float16)
+                whole = lambda: batchedMatmulSharded(be, 0, 1, 64, q, False, k, True, False, 2048, 128, 2048,
+                                                     np.float16, out=o1)
+                whole()
+                graph = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(graph, stream=stream):
+                    for _ in range(20):
+                        whole()
+                graph.replay()
+                torch.cuda.synchronize()
+                e0 = torch.cuda.Event(enable_timing=True); e1 = torch.cuda.Event(enable_timing=True)
+                e0.record(stream)
+                for _ in range(5):
+                    graph.replay()
+                e1.record(stream)
+                torch.cuda.synchronize()
+                one_ms = e0.elapsed_time(e1) / 100
+                del graph, o1
+            except Exception:
+                one_ms = 0.0
+        dist.barrier()
+        one_ms = max_ms(one_ms)
+        sharded = res.get("c3_batch_sharded_graph", {}).get("ms")
+        if one_ms > 0 and sharded:
+            res["c3_one_gpu_same_run_graph"] = {"ms": one_ms, "speedup_of_sharding": one_ms / sharded}
+    del q, k
     n = 16384
     g = torch.Generator(device="cuda").manual_seed(4)
     a = torch.rand((n, n), generator=g, device="cuda") * 2 - 1
