@@ -935,10 +935,14 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap mapA_hi, const __grid_constan
   }
 
   if (warp >= 2 && warp < kWarpProducerB) {
-    // Shared memory must outlive the TMA stores that read it, and stores into other devices'
-    // memory must be complete when the kernel ends.
+    // Shared memory must outlive the TMA stores that read it.  Their writes to this device are
+    // complete when the grid is (no wait needed: about 450 clocks saved at the end of every
+    // launch); stores into other devices' memory are waited for in full.
     __syncwarp();
-    if (elect_one()) bulk_wait_all();
+    if (elect_one()) {
+      if (p.n_out > 1) bulk_wait_all();
+      else bulk_wait_read<0>();
+    }
   }
   // ---------------------------------------------------------------- teardown
   __syncwarp();
