@@ -129,12 +129,15 @@ __device__ __forceinline__ uint32_t map_to_cta(uint32_t addr, uint32_t rank) {
 // ordinary launch.  Everything before pdl_wait must touch no global memory.
 __device__ __forceinline__ void pdl_release() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
-__device__ __forceinline__ void cluster_sync_all() {
-  asm volatile("barrier.cluster.arrive.release.aligned;\nbarrier.cluster.wait.acquire.aligned;" ::: "memory");
-}
 // Rendezvous without memory ordering: for the teardown, where the CTAs of a pair only have to
 // know that the other has stopped signalling (a releasing arrive first waits for the thread's
 // outstanding writes to be visible cluster-wide, about 0.5 us at the end of every launch).
+// Setup rendezvous of a CTA pair: the thread that initialised the barriers has published them
+// with fence.mbarrier_init.release.cluster, so the arrive itself needs no release (which would
+// wait for every thread's earlier writes); the wait acquires.
+__device__ __forceinline__ void cluster_sync_after_barrier_init() {
+  asm volatile("barrier.cluster.arrive.relaxed.aligned;\nbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
 __device__ __forceinline__ void cluster_rendezvous() {
   asm volatile("barrier.cluster.arrive.relaxed.aligned;\nbarrier.cluster.wait.aligned;" ::: "memory");
 }
@@ -451,8 +454,16 @@ struct TileCoord { int64_t mat; int tm, tn; };
 __device__ __forceinline__ TileCoord decode_tile(int64_t tile, const TcParams& p) {
   const int64_t per_mat = (int64_t)p.tiles_m * p.tiles_n;
   TileCoord t;
-  t.mat = tile / per_mat;
-  const int r = (int)(tile % per_mat);
+  int r;
+  if (p.total_tiles <= 0x7fffffffll) {   // the usual case: 32-bit division, a fraction of the 64-bit one's latency
+    const uint32_t tl = (uint32_t)tile, pm = (uint32_t)per_mat;
+    const uint32_t m = tl / pm;
+    t.mat = m;
+    r = (int)(tl - m * pm);
+  } else {
+    t.mat = tile / per_mat;
+    r = (int)(tile % per_mat);
+  }
   const int per_group = p.group_m * p.tiles_n;
   const int g = r / per_group;
   const int first_m = g * p.group_m;
@@ -478,8 +489,8 @@ __device__ __forceinline__ KRange k_range(int64_t vmat, const TcParams& p) {
   if (p.splits <= 1) {
     r.mat = (int)vmat; r.kb0 = 0; r.count = p.num_k_blocks;
   } else {
-    r.mat = (int)(vmat / p.splits);
-    r.kb0 = (int)(vmat - (int64_t)r.mat * p.splits) * p.kb_per_split;
+    r.mat = (int)((uint32_t)vmat / (uint32_t)p.splits);   // batch x parts fits 32 bits (host checks)
+    r.kb0 = (int)((uint32_t)vmat - (uint32_t)r.mat * (uint32_t)p.splits) * p.kb_per_split;
     r.count = min(p.kb_per_split, p.num_k_blocks - r.kb0);
   }
   return r;
@@ -570,7 +581,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap mapA_hi, const __grid_constan
   }
   tc_fence_before();
   __syncthreads();
-  if (kCta == 2) cluster_sync_all();   // the partner's barriers are initialised before anyone signals them
+  if (kCta == 2) cluster_sync_after_barrier_init();   // the partner's barriers are initialised before anyone signals them
   tc_fence_after();
   const uint32_t tmem_base = tmem_base_slot;
   volatile int* abortp = &abort_flag;
@@ -604,14 +615,20 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap mapA_hi, const __grid_constan
       bool ok = true;
       TileCoord t = decode_tile(tile_first < p.total_tiles ? tile_first : 0, p);
       KRange kr = k_range(t.mat, p);
+      // The ring starts empty: the first kStages slots of the first tile need no wait, and their
+      // byte counts can be announced before the previous kernel is waited for.
+      const int free_slots = (tile_first < p.total_tiles && !(p.debug & 8)) ? min(kStages, kr.count) : 0;
+      if (do_a && rank == 0)
+        for (int i = 0; i < free_slots; i++) mbar_expect_tx(bar_full + 8 * i, STAGE_BYTES * kCta);
       pdl_wait();
       for (int64_t tile = tile_first; ok && tile < p.total_tiles; tile += tile_step) {
         if (tile != tile_first) { t = decode_tile(tile, p); kr = k_range(t.mat, p); }
+        const int prearmed = (tile == tile_first) ? free_slots : 0;
         const int m0 = t.tm * (BM * kCta) + (int)rank * BM;
         const int n0 = t.tn * TILE_N + (int)rank * BN_LOCAL;
         const int mat = kr.mat;
         for (int kb = 0; kb < kr.count; kb++) {
-          if (!mbar_wait(bar_empty + 8 * s, ph ^ 1, abortp)) {
+          if (kb >= prearmed && !mbar_wait(bar_empty + 8 * s, ph ^ 1, abortp)) {
             atomicOr(p.status, kDevTimeoutProducer);
             abort_flag = 1;
             ok = false;
@@ -625,7 +642,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap mapA_hi, const __grid_constan
           }
           // (copies of B may complete before the bytes are announced: the count goes negative
           // for a moment, and the phase cannot complete before this arrive)
-          if (rank == 0 && do_a) mbar_expect_tx(bar_full + 8 * s, STAGE_BYTES * kCta);
+          if (rank == 0 && do_a && kb >= prearmed) mbar_expect_tx(bar_full + 8 * s, STAGE_BYTES * kCta);
           // A slab past the end of K lies outside the tensor and arrives as zeros.
 #pragma unroll
           for (int j = 0; j < kSlabs; j++) {
@@ -1454,7 +1471,8 @@ TcPlan plan_tc(const GemmProblem& p, int sm_count, bool may_split, const Tunable
     const int64_t tiles = ((M + c.rows - 1) / c.rows) * ((N + c.cols - 1) / c.cols) * p.batch;
     const int kslots = (kslabs + c.slabs - 1) / c.slabs;
     const int64_t ws_ld = (p.N + 3) & ~3ll;   // of this block
-    const bool can_split = may_split && c.splittable && !p.no_split && forced_splits != 1;
+    // (matrix index x parts must stay a 32-bit tensor-map coordinate)
+    const bool can_split = may_split && c.splittable && !p.no_split && forced_splits != 1 && p.batch < (1ll << 24);
     for (int i = 0; i < n_choices; i++) {
       int want = can_split ? choices[i] : 1;
       if (want > kslots) want = kslots;
