@@ -31,6 +31,10 @@
 //                                        A slab and fill both accumulator buffers - least operand
 //                                        traffic per flop, no epilogue overlap.
 // Every copy is an ordinary per-CTA TMA load into the CTA's own shared memory.
+// The shape is chosen per launch by a cost model (plan_tc: waves of tiles x clocks per tile).
+// When even the smallest shape fills less than one wave and the contraction is long, the
+// contraction is cut into parts that run as separate tiles into float32 partial matrices, which
+// splitk_reduce_kernel sums in ascending order.
 //
 // Transposed operands are never moved: a "K-major" operand (contracted index contiguous) and
 // an "MN-major" one (row/column index contiguous) differ only in the TMA box shape and in one
