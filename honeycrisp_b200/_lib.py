@@ -57,6 +57,9 @@ SIGNATURES = {
     "hc_free": (_int, [_vp, _vp]),
     "hc_h2d": (_int, [_vp, _vp, _vp, _sz]),
     "hc_d2h": (_int, [_vp, _vp, _vp, _sz]),
+    "hc_d2h_async": (_int, [_vp, _vp, _vp, _sz, ctypes.POINTER(_vp)]),
+    "hc_h2d_async": (_int, [_vp, _vp, _vp, _sz, ctypes.POINTER(_vp)]),
+    "hc_enqueue_wait": (_int, [_vp, _vp]),
     "hc_sync": (_int, [_vp]),
     "hc_event_record": (_int, [_vp, ctypes.POINTER(_vp)]),
     "hc_event_wait": (_int, [_vp]),

@@ -67,6 +67,33 @@ def _as_dtype(dtype) -> DType:
 _HC_DTYPE = {DType.float16: L.HC_F16, DType.float32: L.HC_F32}
 
 
+class ReadBack:
+    """An asynchronous device-to-host copy in flight (CUDAData.readInto)."""
+
+    def __init__(self, source: "CUDAData", host_array: np.ndarray, event: int):
+        self._source, self.array, self._event = source, host_array, event   # keeps the source alive
+
+    def wait(self) -> np.ndarray:
+        if self._event:
+            lib = L.load()
+            st = lib.hc_event_wait(self._event)
+            lib.hc_event_destroy(self._event)
+            self._event = None
+            self._source.backend._check(st)
+        return self.array
+
+    def __del__(self):
+        try:
+            if self._event:
+                L.load().hc_event_destroy(self._event)
+        except Exception:
+            pass
+
+
+class Upload(ReadBack):
+    """An asynchronous host-to-device copy in flight (CUDAData.writeFrom)."""
+
+
 class CUDAData:
     """Device buffer handle: the `Tensor.Data` of this backend.
 
@@ -111,6 +138,28 @@ class CUDAData:
         if self._event:
             self.backend._check(L.load().hc_event_wait(self._event))
         return out.view(dtype)
+
+    def writeFrom(self, host_array: np.ndarray) -> "Upload":
+        """Start copying `host_array` (pinned memory for a true DMA) into this buffer on a side
+        stream, after the work enqueued so far.  Work that reads the buffer must be ordered
+        behind the copy with backend.enqueueWait(upload) - or upload.wait() on the host."""
+        if not host_array.flags["C_CONTIGUOUS"] or host_array.nbytes > self.byteCount:
+            raise ValueError("writeFrom: need a contiguous host array no larger than the buffer")
+        ev = ctypes.c_void_p()
+        self.backend._check(L.load().hc_h2d_async(self.backend._ctx, self.ptr, host_array.ctypes.data,
+                                                  host_array.nbytes, ctypes.byref(ev)))
+        return Upload(self, host_array, ev.value)
+
+    def readInto(self, host_array: np.ndarray) -> "ReadBack":
+        """Start copying this buffer into `host_array` (pinned memory for a true DMA) on a side
+        stream, ordered after the work enqueued so far; later products keep running.  The
+        returned handle's wait() blocks until the bytes have arrived."""
+        if not host_array.flags["C_CONTIGUOUS"] or host_array.nbytes > self.byteCount:
+            raise ValueError("readInto: need a contiguous host array no larger than the buffer")
+        ev = ctypes.c_void_p()
+        self.backend._check(L.load().hc_d2h_async(self.backend._ctx, host_array.ctypes.data, self.ptr,
+                                                  host_array.nbytes, ctypes.byref(ev)))
+        return ReadBack(self, host_array, ev.value)
 
     def asTorch(self, shape, torch_dtype):
         """The buffer as a torch tensor that aliases it (no copy); the tensor keeps this handle alive."""
@@ -199,6 +248,12 @@ class CUDABackend:
     def useStream(self, cuda_stream_ptr: Optional[int]):
         """Enqueue this backend's work on a stream owned by the caller (None: its own)."""
         self._check(L.load().hc_set_stream(self._ctx, cuda_stream_ptr or None))
+
+    def enqueueWait(self, transfer: "ReadBack"):
+        """Work enqueued after this call starts only when `transfer` (an Upload or ReadBack) has
+        completed; the host does not block."""
+        if transfer._event:
+            self._check(L.load().hc_enqueue_wait(self._ctx, transfer._event))
 
     def sync(self):
         self._check(L.load().hc_sync(self._ctx))

@@ -344,6 +344,71 @@ hc_status hc_d2h(hc_ctx* ctx, void* dst, const void* src, size_t bytes) {
   return HC_OK;
 }
 
+hc_status hc_d2h_async(hc_ctx* ctx, void* dst_host, const void* src_device, size_t bytes, hc_event** done) {
+  if (!ctx || !done || (bytes && (!dst_host || !src_device))) return HC_ERR_INVALID_ARGUMENT;
+  *done = nullptr;
+  std::lock_guard<std::mutex> lock(ctx->mu);
+  DeviceGuard g(ctx->device);
+  if (!ctx->in_stream) {
+    HC_CUDA_TRY(ctx, cudaStreamCreateWithFlags(&ctx->in_stream, cudaStreamNonBlocking));
+    HC_CUDA_TRY(ctx, cudaStreamCreateWithFlags(&ctx->out_stream, cudaStreamNonBlocking));
+  }
+  hc_event* ev = new (std::nothrow) hc_event();
+  if (!ev) return HC_ERR_ALLOCATION_FAILED;
+  ev->ctx = ctx;
+  ev->device = ctx->device;
+  // The marker first stands for "everything enqueued so far": the side stream waits for it, the
+  // copy follows, and the marker is then moved behind the copy.
+  cudaError_t e = cudaEventCreate(&ev->ev);
+  if (e == cudaSuccess) e = cudaEventRecord(ev->ev, ctx->stream);
+  if (e == cudaSuccess) e = cudaStreamWaitEvent(ctx->out_stream, ev->ev, 0);
+  if (e == cudaSuccess && bytes) e = cudaMemcpyAsync(dst_host, src_device, bytes, cudaMemcpyDeviceToHost, ctx->out_stream);
+  if (e == cudaSuccess) e = cudaEventRecord(ev->ev, ctx->out_stream);
+  if (e != cudaSuccess) {
+    if (ev->ev) cudaEventDestroy(ev->ev);
+    delete ev;
+    return cuda_fail(ctx, e, "asynchronous read-back");
+  }
+  *done = ev;
+  return HC_OK;
+}
+
+hc_status hc_h2d_async(hc_ctx* ctx, void* dst_device, const void* src_host, size_t bytes, hc_event** done) {
+  if (!ctx || !done || (bytes && (!dst_device || !src_host))) return HC_ERR_INVALID_ARGUMENT;
+  *done = nullptr;
+  std::lock_guard<std::mutex> lock(ctx->mu);
+  DeviceGuard g(ctx->device);
+  if (!ctx->in_stream) {
+    HC_CUDA_TRY(ctx, cudaStreamCreateWithFlags(&ctx->in_stream, cudaStreamNonBlocking));
+    HC_CUDA_TRY(ctx, cudaStreamCreateWithFlags(&ctx->out_stream, cudaStreamNonBlocking));
+  }
+  hc_event* ev = new (std::nothrow) hc_event();
+  if (!ev) return HC_ERR_ALLOCATION_FAILED;
+  ev->ctx = ctx;
+  ev->device = ctx->device;
+  // Ordered after everything enqueued so far, so that earlier readers of the destination are done.
+  cudaError_t e = cudaEventCreate(&ev->ev);
+  if (e == cudaSuccess) e = cudaEventRecord(ev->ev, ctx->stream);
+  if (e == cudaSuccess) e = cudaStreamWaitEvent(ctx->in_stream, ev->ev, 0);
+  if (e == cudaSuccess && bytes) e = cudaMemcpyAsync(dst_device, src_host, bytes, cudaMemcpyHostToDevice, ctx->in_stream);
+  if (e == cudaSuccess) e = cudaEventRecord(ev->ev, ctx->in_stream);
+  if (e != cudaSuccess) {
+    if (ev->ev) cudaEventDestroy(ev->ev);
+    delete ev;
+    return cuda_fail(ctx, e, "asynchronous upload");
+  }
+  *done = ev;
+  return HC_OK;
+}
+
+hc_status hc_enqueue_wait(hc_ctx* ctx, hc_event* ev) {
+  if (!ctx || !ev) return HC_ERR_INVALID_ARGUMENT;
+  std::lock_guard<std::mutex> lock(ctx->mu);
+  DeviceGuard g(ctx->device);
+  HC_CUDA_TRY(ctx, cudaStreamWaitEvent(ctx->stream, ev->ev, 0));
+  return HC_OK;
+}
+
 hc_status hc_sync(hc_ctx* ctx) {
   if (!ctx) return HC_ERR_INVALID_ARGUMENT;
   std::lock_guard<std::mutex> lock(ctx->mu);

@@ -103,6 +103,26 @@ hc_status hc_free(hc_ctx* ctx, void* dptr);
  * Replaces: Tensor.Data.onCPU / MPSBackend.gpuBuffer staging (BackendMPS.swift:585-620). */
 hc_status hc_h2d(hc_ctx* ctx, void* dst_device, const void* src_host, size_t bytes);
 hc_status hc_d2h(hc_ctx* ctx, void* dst_host, const void* src_device, size_t bytes);
+/* Read a device buffer back to (pinned) host memory without stalling the context's stream: the
+ * copy runs on a side stream after everything enqueued so far, later products keep running, and
+ * `*done` completes when the bytes are in `dst_host` (hc_event_wait, then hc_event_destroy).  The
+ * device buffer must stay alive and unmodified until then.  Mirrors awaiting one result's data
+ * while the backend works on the next (Sources/Honeycrisp/Tensor.swift:618-621; the reference's
+ * GPU backend completes each command buffer on its own, BackendMPS.swift:2694-2720). */
+hc_status hc_d2h_async(hc_ctx* ctx, void* dst_host, const void* src_device, size_t bytes,
+                       hc_event** done);
+/* The other direction: copy (pinned) host memory into a device buffer on a side stream, ordered
+ * after everything enqueued so far (so earlier readers of `dst_device` are done) but not ahead
+ * of anything enqueued later: work that reads `dst_device` must be told to wait with
+ * hc_enqueue_wait(ctx, *done).  This is how the operands of the next step are brought in while
+ * the results of the current one are still being read back (host links are full duplex).
+ * Mirrors Backend.collection (Sources/Honeycrisp/Backend.swift:794-800) issued ahead of use. */
+hc_status hc_h2d_async(hc_ctx* ctx, void* dst_device, const void* src_host, size_t bytes,
+                       hc_event** done);
+/* Work enqueued on the context after this call starts only when `ev` has completed; the host
+ * does not block.  (The reference expresses the same dependency by awaiting the input Tensor's
+ * Task inside the consuming operation, Sources/Honeycrisp/Tensor.swift:618-621.) */
+hc_status hc_enqueue_wait(hc_ctx* ctx, hc_event* ev);
 hc_status hc_sync(hc_ctx* ctx);
 
 /* Completion markers; they back Tensor.Data.wait() (Sources/Honeycrisp/Tensor.swift:69-85,

@@ -352,3 +352,44 @@ def test_results_may_outlive_their_backend():
             out.wait()
         del out   # its completion marker is destroyed after the context
     assert np.array_equal(results[0], results[1])
+
+
+def test_async_read_back_while_later_products_run(be):
+    """readInto copies a result on a side stream after the work enqueued so far; products issued
+    afterwards do not wait for it, and the bytes equal a blocking read."""
+    import torch
+    A, B = random_operands(21, 1, 512, 384, 640, np.float16)
+    a_st, b_st = stored(A, False), stored(B, False)
+    outs = [be.matmul(a_st, False, b_st, False, to, 512, 384, 640, np.float16) for to in (False, True)]
+    hosts = [torch.empty(512 * 640, dtype=torch.float16).pin_memory().numpy() for _ in outs]
+    reads = [o.readInto(h) for o, h in zip(outs, hosts)]
+    later = be.matmul(a_st, False, b_st, False, False, 512, 384, 640, np.float16)   # enqueued behind the reads
+    for r, o in zip(reads, outs):
+        got = r.wait()
+        assert np.array_equal(got.view(np.uint16), o.onCPU(np.float16)[: 512 * 640].view(np.uint16))
+    assert np.array_equal(later.onCPU(np.float16).view(np.uint16), outs[0].onCPU(np.float16).view(np.uint16))
+    with pytest.raises(ValueError):
+        outs[0].readInto(np.zeros(512 * 640 + 8, dtype=np.float16))
+
+
+def test_async_upload_ordered_by_a_device_side_wait(be):
+    """writeFrom copies on a side stream; enqueueWait makes the product that reads the buffer
+    wait for it on the device.  Repeated with changing contents, so a product that ran ahead of
+    its upload would be caught."""
+    import torch
+    M, Kd, N = 256, 192, 320
+    da, db = be.allocate(M * Kd * 2), be.allocate(Kd * N * 2)
+    ha = torch.empty(M * Kd, dtype=torch.float16).pin_memory().numpy()
+    hb = torch.empty(Kd * N, dtype=torch.float16).pin_memory().numpy()
+    for seed in range(4):
+        A, B = random_operands(seed, 1, M, Kd, N, np.float16)
+        ha[:] = A.reshape(-1); hb[:] = B.reshape(-1)
+        ups = [da.writeFrom(ha), db.writeFrom(hb)]
+        for u in ups:
+            be.enqueueWait(u)
+        out = be.matmul(da, False, db, False, False, M, Kd, N, np.float16)
+        res = out.onCPU(np.float16)[: M * N]
+        for u in ups:
+            u.wait()                                  # the pinned arrays are rewritten next round
+        want = ref.batched_matmul(1, stored(A, False), False, stored(B, False), False, False, M, Kd, N)
+        assert ref.rel_frobenius(res, want) < 1e-3, seed
