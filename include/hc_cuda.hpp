@@ -99,6 +99,23 @@ class CUDAData : public TensorData {
     host.resize(bytes_);
     return host;
   }
+  /// Start reading this buffer into (pinned) host memory on a side stream; later products keep
+  /// running.  Wait on the returned marker with hc_event_wait and release it with hc_event_destroy.
+  hc_event* readInto(void* host, size_t bytes) {
+    hc_event* done = nullptr;
+    if (bytes > bytes_ || hc_d2h_async(ctx_, host, ptr_, bytes, &done) != HC_OK)
+      throw BackendError(BackendError::Kind::kernelFailed, hc_last_error(ctx_));
+    return done;
+  }
+  /// Start filling this buffer from (pinned) host memory on a side stream; with `order` the work
+  /// enqueued afterwards waits for the copy on the device.
+  hc_event* writeFrom(const void* host, size_t bytes, bool order = true) {
+    hc_event* done = nullptr;
+    if (bytes > bytes_ || hc_h2d_async(ctx_, ptr_, host, bytes, &done) != HC_OK ||
+        (order && hc_enqueue_wait(ctx_, done) != HC_OK))
+      throw BackendError(BackendError::Kind::kernelFailed, hc_last_error(ctx_));
+    return done;
+  }
   void keep(std::shared_ptr<TensorData> a, std::shared_ptr<TensorData> b) { inputs_ = {std::move(a), std::move(b)}; }
 
  private:
