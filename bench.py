@@ -337,7 +337,8 @@ def run_ours(args):
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         staged_s = float(t.item())
     e2e_staged = {"value": FLOPS_PER_GEMM * 4 * e2e_steps * world / staged_s / 1e12, "unit": UNIT,
-                  "h2d_bytes_per_step": 2 * n * n * 2, "d2h_bytes_per_step": d2h, "steps": e2e_steps,
+                  "h2d_bytes_per_step": world * 2 * n * n * 2, "d2h_bytes_per_step": world * d2h, "steps": e2e_steps,
+                  "bytes_are": "whole job (all ranks), like value",
                   "what": ("A and B uploaded once per step (hc_h2d_async, the next step's while this step's results "
                            "are read back), four products on them, each result read back with hc_d2h_async while the "
                            "next product runs; a step ends when its four results are in host memory")}
@@ -405,7 +406,8 @@ def run_ours(args):
         # (hc_batched_matmul_host_async), which stages both operands again for every product.
         "e2e": e2e_staged,
         "e2e_host_buffer_call_per_product": {
-            "value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "steps": e2e_steps,
+            "value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": world * h2d, "d2h_bytes_per_step": world * d2h,
+            "steps": e2e_steps,
             "what": "hc_batched_matmul_host_async per product: A and B staged from host memory four times per step"},
         "gpu_launches": launches,
         "roofline": roofline,
