@@ -131,6 +131,41 @@ def cpu_sample(rows_per_combo: int, threads: int, a32, b32, out32):
     return dt, 4 * 2.0 * rows_per_combo * N_DIM * N_DIM
 
 
+def cpu_sgemm_baseline(threads: int, a32, b32):
+    """The reference's float32 fast path on the host: CPUBackend.matmul with no flags calls the
+    platform sgemm (vDSP_mmul, BackendCPU.swift:1245-1258); here the same call through the host
+    BLAS the oracle found.  Configuration 1 (1024^3, U[0,1), seed 0) on all cores and on one,
+    and the headline shape (8192^3, float16 values widened) on all cores."""
+    import numpy as np
+    from oracle import reference_cpu as ref
+    kind, _, where = ref.find_sgemm()
+    if kind is None:
+        return {"unavailable": where}
+    rng = np.random.default_rng(0)
+    a1 = rng.random((1024, 1024), dtype=np.float32); b1 = rng.random((1024, 1024), dtype=np.float32)
+
+    def best_of(fn, reps, warm=True):
+        if warm:
+            fn()
+        best = float("inf")
+        for _ in range(reps):
+            t0 = time.perf_counter(); fn(); best = min(best, time.perf_counter() - t0)
+        return best
+
+    out = {"library": where, "cores": threads}
+    ref.set_sgemm_threads(threads)
+    t = best_of(lambda: ref.matmul(a1, False, b1, False, False, 1024, 1024, 1024), 5)
+    out["c1_1024_all_cores"] = {"ms": t * 1e3, "tflops": 2 * 1024 ** 3 / t / 1e12}
+    ref.set_sgemm_threads(1)
+    t = best_of(lambda: ref.matmul(a1, False, b1, False, False, 1024, 1024, 1024), 2)
+    out["c1_1024_one_thread"] = {"ms": t * 1e3, "tflops": 2 * 1024 ** 3 / t / 1e12,
+                                 "note": "the reference's CPU backend runs on one worker thread"}
+    ref.set_sgemm_threads(threads)
+    t = best_of(lambda: ref.matmul(a32, False, b32, False, False, N_DIM, N_DIM, N_DIM), 1, warm=False)
+    out["headline_shape_8192_all_cores"] = {"ms": t * 1e3, "tflops": 2.0 * N_DIM ** 3 / t / 1e12}
+    return out
+
+
 def cpu_operands():
     import numpy as np
     rng = np.random.default_rng(1)
@@ -387,6 +422,7 @@ def run_ours(args):
     a32, b32, out32 = cpu_operands()
     rows = calibrate_rows(threads, a32, b32, out32, target_s=12.0)
     dt, fl = cpu_sample(rows, threads, a32, b32, out32)
+    cpu_sgemm = cpu_sgemm_baseline(threads, a32, b32)
     cpu_baseline = {
         "value": fl / dt / 1e12, "unit": UNIT, "cores": threads, "kind": "port",
         "sample": (f"{rows} of {N_DIM} output rows of each of the four products ({dt:.1f} s) through the port of "
@@ -412,6 +448,7 @@ def run_ours(args):
         "gpu_launches": launches,
         "roofline": roofline,
         "cpu_baseline": cpu_baseline,
+        "cpu_sgemm_baseline": cpu_sgemm,
     }
     if args.all_configs:
         line["extra"] = other_configs(be, stream, rank, world) if world == 1 else multi_extra
