@@ -152,11 +152,8 @@ __device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
   asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes)
                : "memory");
 }
-// Arrive on a barrier given by its cluster-wide address (this CTA's or the partner's).
-__device__ __forceinline__ void mbar_arrive_cluster(uint32_t bar) {
-  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(bar) : "memory");
-}
-// The same without memory ordering.  Handing an accumulator buffer back to the MMA issuer orders
+// Arrive, without memory ordering, on a barrier given by its cluster-wide address (this CTA's or
+// the partner's).  Handing an accumulator buffer back to the MMA issuer orders
 // tensor-memory accesses only, which tcgen05.fence does on both sides of the barrier; a releasing
 // arrive here waited about 1400 clocks for the epilogue's own stores on every tile.
 __device__ __forceinline__ void mbar_arrive_cluster_relaxed(uint32_t bar) {

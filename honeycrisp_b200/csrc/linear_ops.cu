@@ -66,6 +66,113 @@ __global__ void __launch_bounds__(128) column_sum_half2_kernel(const __half2* __
   out[c] = __floats2half2_rn(s0, s1);
 }
 
+// The same sum for tall inputs, fed through shared memory.  One thread per column keeps the
+// reference's order but leaves too few loads in flight to fill HBM (8192 threads x 32 loads for
+// 16384 float16 columns: about 1 TB/s).  Here a CTA owns a strip of kStripBytes of every row; all
+// 256 threads stream the strip through a ring of four 128-row stages with 16-byte asynchronous
+// copies, and the strip's kStripBytes / 4 summing threads walk each stage top to bottom: the same
+// additions in the same order, one accumulator per column, narrowed once.
+template <typename T, int kStripBytes>
+__global__ void __launch_bounds__(256) column_sum_staged_kernel(const T* __restrict__ x, T* __restrict__ out,
+                                                                int64_t rows, int64_t cols) {
+  constexpr int ROWS = 128, STAGES = 4, CHUNKS = kStripBytes / 16, PER_STAGE = ROWS * CHUNKS;
+  extern __shared__ __align__(16) unsigned char ring[];   // [STAGES][ROWS][kStripBytes]
+  const int tid = threadIdx.x;
+  const int64_t row_bytes = cols * (int64_t)sizeof(T);
+  const int64_t col0b = (int64_t)blockIdx.x * kStripBytes;
+  const int valid_chunks = (int)min((int64_t)CHUNKS, (row_bytes - col0b + 15) / 16);
+  const unsigned char* src = (const unsigned char*)x + col0b;
+  const int64_t blocks = (rows + ROWS - 1) / ROWS;
+
+  auto load = [&](int64_t rb) {
+    if (rb < blocks) {
+      unsigned char* dst = ring + (size_t)(rb % STAGES) * ROWS * kStripBytes;
+      for (int idx = tid; idx < PER_STAGE; idx += 256) {
+        const int r = idx / CHUNKS, ch = idx % CHUNKS;
+        const int64_t grow = rb * ROWS + r;
+        if (grow < rows && ch < valid_chunks) {
+          const unsigned int d = (unsigned int)__cvta_generic_to_shared(dst + r * kStripBytes + ch * 16);
+          asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(d), "l"(src + grow * row_bytes + ch * 16)
+                       : "memory");
+        }
+      }
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");   // one group per stage, empty past the end
+  };
+
+  for (int s = 0; s < STAGES - 1; s++) load(s);
+  float s0 = 0.0f, s1 = 0.0f;
+  const bool summing = tid < kStripBytes / 4;
+  for (int64_t rb = 0; rb < blocks; rb++) {
+    asm volatile("cp.async.wait_group %0;" ::"n"(STAGES - 2) : "memory");
+    __syncthreads();                 // stage rb has landed for every thread; stage rb - 1 is free
+    load(rb + STAGES - 1);
+    if (summing) {
+      const unsigned char* st = ring + (size_t)(rb % STAGES) * ROWS * kStripBytes + tid * 4;
+      const int n = (int)min((int64_t)ROWS, rows - rb * ROWS);
+      // The additions of one column form a dependent chain (that is the reference's order); the
+      // shared-memory reads do not, so a full stage is unrolled far enough to keep them ahead.
+      if (sizeof(T) == 2) {
+        if (n == ROWS) {
+#pragma unroll 32
+          for (int r = 0; r < ROWS; r++) {
+            const float2 f = __half22float2(*(const __half2*)(st + r * kStripBytes));
+            s0 = __fadd_rn(s0, f.x);
+            s1 = __fadd_rn(s1, f.y);
+          }
+        } else {
+          for (int r = 0; r < n; r++) {
+            const float2 f = __half22float2(*(const __half2*)(st + r * kStripBytes));
+            s0 = __fadd_rn(s0, f.x);
+            s1 = __fadd_rn(s1, f.y);
+          }
+        }
+      } else {
+        if (n == ROWS) {
+#pragma unroll 32
+          for (int r = 0; r < ROWS; r++) s0 = __fadd_rn(s0, *(const float*)(st + r * kStripBytes));
+        } else {
+          for (int r = 0; r < n; r++) s0 = __fadd_rn(s0, *(const float*)(st + r * kStripBytes));
+        }
+      }
+    }
+  }
+  if (summing) {
+    const int64_t byte = col0b + tid * 4;
+    if (byte < row_bytes) {
+      if (sizeof(T) == 2) *(__half2*)((unsigned char*)out + byte) = __floats2half2_rn(s0, s1);
+      else *(float*)((unsigned char*)out + byte) = s0;
+    }
+  }
+}
+
+template <typename T, int kStripBytes>
+cudaError_t launch_column_sum_staged(const T* x, T* out, int64_t rows, int64_t cols, cudaStream_t stream) {
+  constexpr size_t smem = 4 * 128 * (size_t)kStripBytes;
+  static bool configured[64] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 64 && !configured[dev]) {
+    cudaError_t e = cudaFuncSetAttribute(column_sum_staged_kernel<T, kStripBytes>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return e;
+    configured[dev] = true;
+  }
+  const int64_t strips = (cols * (int64_t)sizeof(T) + kStripBytes - 1) / kStripBytes;
+  if (strips > 2147483647LL) return cudaErrorInvalidValue;
+  column_sum_staged_kernel<T, kStripBytes><<<(unsigned)strips, 256, smem, stream>>>(x, out, rows, cols);
+  return cudaGetLastError();
+}
+
+template <typename T>
+cudaError_t launch_column_sum_staged_any(const T* x, T* out, int64_t rows, int64_t cols, cudaStream_t stream) {
+  // Strips as wide as a cache line when that still gives every SM two CTAs, narrower otherwise.
+  const int64_t row_bytes = cols * (int64_t)sizeof(T);
+  if (row_bytes >= 128 * 296) return launch_column_sum_staged<T, 128>(x, out, rows, cols, stream);
+  if (row_bytes >= 64 * 296) return launch_column_sum_staged<T, 64>(x, out, rows, cols, stream);
+  return launch_column_sum_staged<T, 32>(x, out, rows, cols, stream);
+}
+
 template <typename TI, typename TO>
 __global__ void cast_kernel(const TI* __restrict__ x, TO* __restrict__ out, int64_t n) {
   for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x)
@@ -106,6 +213,12 @@ int grid_for(int64_t n, int threads) {
 
 cudaError_t launch_column_sum(hc_dtype dtype, const void* x, void* out, int64_t rows, int64_t cols, cudaStream_t stream) {
   if (cols <= 0) return cudaSuccess;
+  // Tall inputs whose rows are 16-byte multiples go through the shared-memory ring.
+  const int64_t eb = dtype == HC_F16 ? 2 : 4;
+  if (rows >= 512 && (cols * eb) % 16 == 0 && ((uintptr_t)x & 15) == 0 && ((uintptr_t)out & 3) == 0) {
+    if (dtype == HC_F16) return launch_column_sum_staged_any<__half>((const __half*)x, (__half*)out, rows, cols, stream);
+    return launch_column_sum_staged_any<float>((const float*)x, (float*)out, rows, cols, stream);
+  }
   const int threads = 128;
   const int64_t blocks = (cols + threads - 1) / threads;
   if (blocks > 2147483647LL) return cudaErrorInvalidValue;

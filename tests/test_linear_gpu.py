@@ -61,7 +61,10 @@ def test_fused_bias_on_the_tensor_core_path(be, rows, n_in, n_out, dtype, tol):
 
 
 @pytest.mark.parametrize("dtype", [np.float32, np.float16])
-@pytest.mark.parametrize("rows,cols", [(1, 7), (9, 1), (33, 130), (4096, 520), (257, 4099)])
+@pytest.mark.parametrize("rows,cols", [(1, 7), (9, 1), (33, 130), (4096, 520), (257, 4099),
+                                       # tall inputs with 16-byte rows stream through shared memory: every strip
+                                       # width (32, 64, 128 bytes), ragged last strip, ragged last row block
+                                       (512, 8), (1000, 72), (777, 1096), (2049, 4104), (600, 16384), (5000, 20000)])
 def test_column_sum_is_bit_identical_to_the_cpu_loop(be, rows, cols, dtype):
     x = np.random.default_rng(rows * cols).standard_normal((rows, cols)).astype(dtype)
     got = be.columnSum(x, rows, cols, dtype).onCPU(dtype)[:cols]
