@@ -35,6 +35,11 @@ struct hc_ctx {
   } slot[2];
   cudaStream_t in_stream = nullptr, out_stream = nullptr;
   int next_slot = 0;
+  // The context's own stream-ordered pool.  It keeps up to 8 GiB (HC_POOL_RETAIN_MB) of freed
+  // memory instead of returning it to the driver at every synchronisation, as the device's
+  // default pool does: a backend that allocates a fresh result for every operation, as the
+  // reference's do (BackendMPS.swift:538-540), would otherwise pay a driver allocation per call.
+  cudaMemPool_t pool = nullptr;
 };
 
 struct hc_event {
@@ -255,6 +260,21 @@ hc_status hc_init(int device, hc_ctx** out) {
     return HC_ERR_CUDA;
   }
   ctx->stream = ctx->own_stream;
+  {
+    cudaMemPoolProps props = {};
+    props.allocType = cudaMemAllocationTypePinned;
+    props.handleTypes = cudaMemHandleTypeNone;
+    props.location.type = cudaMemLocationTypeDevice;
+    props.location.id = device;
+    if (cudaMemPoolCreate(&ctx->pool, &props) == cudaSuccess) {
+      const char* e = getenv("HC_POOL_RETAIN_MB");
+      unsigned long long keep = (e ? strtoull(e, nullptr, 10) : 8192ull) << 20;
+      if (cudaMemPoolSetAttribute(ctx->pool, cudaMemPoolAttrReleaseThreshold, &keep) != cudaSuccess) cudaGetLastError();
+    } else {
+      ctx->pool = nullptr;   // fall back to the device's default pool
+      cudaGetLastError();
+    }
+  }
   *out = ctx;
   return HC_OK;
 }
@@ -278,6 +298,12 @@ void hc_destroy(hc_ctx* ctx) {
   if (ctx->in_stream) cudaStreamDestroy(ctx->in_stream);
   if (ctx->out_stream) cudaStreamDestroy(ctx->out_stream);
   cudaFree(ctx->status_word);
+  if (ctx->pool) {
+    // Buffers the caller has not freed yet stay valid until they are (the pool's memory goes
+    // back to the driver when the last of them has been freed).
+    cudaStreamSynchronize(ctx->own_stream);
+    cudaMemPoolDestroy(ctx->pool);
+  }
   cudaStreamDestroy(ctx->own_stream);
   cudaGetLastError();
   delete ctx;
@@ -306,7 +332,8 @@ hc_status hc_alloc(hc_ctx* ctx, size_t bytes, void** dptr) {
   DeviceGuard g(ctx->device);
   *dptr = nullptr;
   const size_t n = bytes ? bytes : 1;
-  cudaError_t e = cudaMallocAsync(dptr, n, ctx->stream);
+  cudaError_t e = ctx->pool ? cudaMallocFromPoolAsync(dptr, n, ctx->pool, ctx->stream)
+                            : cudaMallocAsync(dptr, n, ctx->stream);
   if (e != cudaSuccess) {
     *dptr = nullptr;
     cudaGetLastError();

@@ -185,6 +185,73 @@ __global__ void add_kernel(const T* __restrict__ a, const T* __restrict__ b, T* 
     out[i] = narrow<T>(__fadd_rn(widen<T>(a[i]), widen<T>(b[i])));
 }
 
+// Eight elements per thread through 16-byte accesses (the scalar kernels above move 2-4 bytes
+// per access and reach a fraction of the HBM bandwidth); same per-element arithmetic.
+template <typename T> struct Vec8;
+template <> struct Vec8<__half> {
+  uint4 raw;
+  __device__ static Vec8 load(const __half* p) { Vec8 v; v.raw = __ldg((const uint4*)p); return v; }
+  __device__ void store(__half* p) const { *(uint4*)p = raw; }
+  __device__ float get(int i) const { return __half2float(((const __half*)&raw)[i]); }
+  __device__ void set(int i, float f) { ((__half*)&raw)[i] = __float2half_rn(f); }
+};
+template <> struct Vec8<float> {
+  alignas(16) float v[8];
+  __device__ static Vec8 load(const float* p) {
+    Vec8 r;
+    *(float4*)&r.v[0] = __ldg((const float4*)p);
+    *(float4*)&r.v[4] = __ldg((const float4*)p + 1);
+    return r;
+  }
+  __device__ void store(float* p) const { *(float4*)p = *(const float4*)&v[0]; *((float4*)p + 1) = *(const float4*)&v[4]; }
+  __device__ float get(int i) const { return v[i]; }
+  __device__ void set(int i, float f) { v[i] = f; }
+};
+
+template <typename TI, typename TO>
+__global__ void __launch_bounds__(256) cast_vec8_kernel(const TI* __restrict__ x, TO* __restrict__ out, int64_t groups) {
+  for (int64_t g = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; g < groups; g += (int64_t)gridDim.x * blockDim.x) {
+    const Vec8<TI> v = Vec8<TI>::load(x + g * 8);
+    Vec8<TO> o;
+#pragma unroll
+    for (int i = 0; i < 8; i++) o.set(i, v.get(i));
+    o.store(out + g * 8);
+  }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256) add_vec8_kernel(const T* __restrict__ a, const T* __restrict__ b, T* __restrict__ out,
+                                                       int64_t groups) {
+  for (int64_t g = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; g < groups; g += (int64_t)gridDim.x * blockDim.x) {
+    const Vec8<T> va = Vec8<T>::load(a + g * 8), vb = Vec8<T>::load(b + g * 8);
+    Vec8<T> o;
+#pragma unroll
+    for (int i = 0; i < 8; i++) o.set(i, __fadd_rn(va.get(i), vb.get(i)));
+    o.store(out + g * 8);
+  }
+}
+
+// 2-byte elements: 64 x 64 tiles moved with 4-byte accesses on both sides (a warp reads and
+// writes 128 contiguous bytes); rows and columns even, buffers 4-byte aligned.
+__global__ void __launch_bounds__(256) transpose_half_kernel(const __half* __restrict__ in, __half* __restrict__ out,
+                                                             int64_t rows, int64_t cols) {
+  __shared__ __half tile[64][66];
+  const int64_t mat = blockIdx.z;
+  in += mat * rows * cols;
+  out += mat * rows * cols;
+  const int64_t c0 = (int64_t)blockIdx.x * 64, r0 = (int64_t)blockIdx.y * 64;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;   // 8 warps
+  for (int j = warp; j < 64; j += 8) {
+    const int64_t r = r0 + j, c = c0 + 2 * lane;
+    if (r < rows && c < cols) *(__half2*)&tile[j][2 * lane] = *(const __half2*)(in + r * cols + c);
+  }
+  __syncthreads();
+  for (int j = warp; j < 64; j += 8) {
+    const int64_t c = c0 + j, r = r0 + 2 * lane;   // out is [cols, rows]
+    if (c < cols && r < rows) *(__half2*)(out + c * rows + r) = __halves2half2(tile[2 * lane][j], tile[2 * lane + 1][j]);
+  }
+}
+
 // Materialised transpose of `batch` dense [rows, cols] matrices through 32 x 33 shared tiles.
 template <typename T>
 __global__ void transpose_kernel(const T* __restrict__ in, T* __restrict__ out, int64_t rows, int64_t cols) {
@@ -237,6 +304,14 @@ cudaError_t launch_transpose(hc_dtype dtype, int64_t batch, const void* in, void
   if (batch <= 0 || rows <= 0 || cols <= 0) return cudaSuccess;
   const int64_t gx = (cols + 31) / 32, gy = (rows + 31) / 32;
   if (gy > 65535 || batch > 65535 || gx > 2147483647LL) return cudaErrorInvalidValue;
+  if (dtype == HC_F16 && rows % 2 == 0 && cols % 2 == 0 && ((((uintptr_t)in | (uintptr_t)out) & 3) == 0)) {
+    const int64_t hx = (cols + 63) / 64, hy = (rows + 63) / 64;
+    if (hy <= 65535) {
+      transpose_half_kernel<<<dim3((unsigned)hx, (unsigned)hy, (unsigned)batch), 256, 0, stream>>>(
+          (const __half*)in, (__half*)out, rows, cols);
+      return cudaGetLastError();
+    }
+  }
   dim3 grid((unsigned)gx, (unsigned)gy, (unsigned)batch), block(32, 8);
   if (dtype == HC_F16)
     transpose_kernel<__half><<<grid, block, 0, stream>>>((const __half*)in, (__half*)out, rows, cols);
@@ -247,7 +322,27 @@ cudaError_t launch_transpose(hc_dtype dtype, int64_t batch, const void* in, void
 
 cudaError_t launch_cast(hc_dtype from, hc_dtype to, const void* x, void* out, int64_t count, cudaStream_t stream) {
   if (count <= 0) return cudaSuccess;
-  const int threads = 256, grid = grid_for(count, threads);
+  const int threads = 256;
+  // Bulk in groups of eight through 16-byte accesses, the remainder through the scalar kernel.
+  const int64_t groups = ((((uintptr_t)x | (uintptr_t)out) & 15) == 0) ? count / 8 : 0;
+  if (groups > 0) {
+    const int vg = grid_for(groups, threads);
+    if (from == HC_F16 && to == HC_F32)
+      cast_vec8_kernel<__half, float><<<vg, threads, 0, stream>>>((const __half*)x, (float*)out, groups);
+    else if (from == HC_F32 && to == HC_F16)
+      cast_vec8_kernel<float, __half><<<vg, threads, 0, stream>>>((const float*)x, (__half*)out, groups);
+    else if (from == HC_F16)
+      cast_vec8_kernel<__half, __half><<<vg, threads, 0, stream>>>((const __half*)x, (__half*)out, groups);
+    else
+      cast_vec8_kernel<float, float><<<vg, threads, 0, stream>>>((const float*)x, (float*)out, groups);
+    const int64_t done = groups * 8;
+    if (done == count) return cudaGetLastError();
+    const size_t in_b = from == HC_F16 ? 2 : 4, out_b = to == HC_F16 ? 2 : 4;
+    x = (const char*)x + done * in_b;
+    out = (char*)out + done * out_b;
+    count -= done;
+  }
+  const int grid = grid_for(count, threads);
   if (from == HC_F16 && to == HC_F32)
     cast_kernel<__half, float><<<grid, threads, 0, stream>>>((const __half*)x, (float*)out, count);
   else if (from == HC_F32 && to == HC_F16)
@@ -261,7 +356,21 @@ cudaError_t launch_cast(hc_dtype from, hc_dtype to, const void* x, void* out, in
 
 cudaError_t launch_add(hc_dtype dtype, const void* a, const void* b, void* out, int64_t count, cudaStream_t stream) {
   if (count <= 0) return cudaSuccess;
-  const int threads = 256, grid = grid_for(count, threads);
+  const int threads = 256;
+  const int64_t groups = ((((uintptr_t)a | (uintptr_t)b | (uintptr_t)out) & 15) == 0) ? count / 8 : 0;
+  if (groups > 0) {
+    const int vg = grid_for(groups, threads);
+    if (dtype == HC_F16)
+      add_vec8_kernel<__half><<<vg, threads, 0, stream>>>((const __half*)a, (const __half*)b, (__half*)out, groups);
+    else
+      add_vec8_kernel<float><<<vg, threads, 0, stream>>>((const float*)a, (const float*)b, (float*)out, groups);
+    const int64_t done = groups * 8;
+    if (done == count) return cudaGetLastError();
+    const size_t eb = dtype == HC_F16 ? 2 : 4;
+    a = (const char*)a + done * eb; b = (const char*)b + done * eb; out = (char*)out + done * eb;
+    count -= done;
+  }
+  const int grid = grid_for(count, threads);
   if (dtype == HC_F16)
     add_kernel<__half><<<grid, threads, 0, stream>>>((const __half*)a, (const __half*)b, (__half*)out, count);
   else

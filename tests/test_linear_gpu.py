@@ -119,7 +119,9 @@ def test_linear_layer_forward_and_backward(be, dtype, tol):
 
 
 @pytest.mark.parametrize("dtype", [np.float32, np.float16])
-@pytest.mark.parametrize("cnt,rows,cols", [(1, 1, 1), (1, 2, 3), (3, 33, 65), (2, 1000, 31), (1, 2048, 512)])
+@pytest.mark.parametrize("cnt,rows,cols", [(1, 1, 1), (1, 2, 3), (3, 33, 65), (2, 1000, 31), (1, 2048, 512),
+                                           # even sides: float16 moves 64 x 64 tiles with 4-byte accesses
+                                           (2, 130, 66), (3, 64, 64), (1, 70, 4098)])
 def test_materialised_transpose(be, cnt, rows, cols, dtype):
     x = np.random.default_rng(cols).standard_normal((cnt, rows, cols)).astype(dtype)
     got = be.transpose(x, cnt, rows, cols, dtype).onCPU(dtype)[: x.size].reshape(cnt, cols, rows)
