@@ -93,7 +93,10 @@ int hc_get_device(hc_ctx* ctx);
 /* Stream-ordered allocation; `bytes == 0` allocates one byte, as the reference's GPU backend
  * does (Sources/Honeycrisp/BackendMPS.swift:538-540).
  * Replaces: MPSBackend.allocateBuf (BackendMPS.swift:500-527), CPUBackend.allocate
- * (BackendCPU.swift:250-253). */
+ * (BackendCPU.swift:250-253).
+ * The memory comes from a pool the context owns, which keeps up to 8 GiB of freed memory for
+ * reuse (environment HC_POOL_RETAIN_MB at hc_init) instead of returning it to the driver at
+ * every synchronisation; buffers still allocated at hc_destroy stay valid until freed. */
 hc_status hc_alloc(hc_ctx* ctx, size_t bytes, void** dptr);
 hc_status hc_free(hc_ctx* ctx, void* dptr);
 
