@@ -96,7 +96,8 @@ int hc_get_device(hc_ctx* ctx);
  * (BackendCPU.swift:250-253).
  * The memory comes from a pool the context owns, which keeps up to 8 GiB of freed memory for
  * reuse (environment HC_POOL_RETAIN_MB at hc_init) instead of returning it to the driver at
- * every synchronisation; buffers still allocated at hc_destroy stay valid until freed. */
+ * every synchronisation.  Free buffers before hc_destroy: what is still allocated then stays
+ * mapped (kernels in flight may use it) and is reclaimed only when the process ends. */
 hc_status hc_alloc(hc_ctx* ctx, size_t bytes, void** dptr);
 hc_status hc_free(hc_ctx* ctx, void* dptr);
 
