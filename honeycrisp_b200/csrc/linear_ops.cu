@@ -219,6 +219,18 @@ __global__ void __launch_bounds__(256) cast_vec8_kernel(const TI* __restrict__ x
   }
 }
 
+// Widening cast: four elements per thread, so that every store instruction of a warp writes 512
+// contiguous bytes (with eight per thread a lane's two 16-byte stores each cover half of a
+// 32-byte sector).
+__global__ void __launch_bounds__(256) cast_h2f_vec4_kernel(const __half* __restrict__ x, float* __restrict__ out,
+                                                            int64_t quads) {
+  for (int64_t g = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; g < quads; g += (int64_t)gridDim.x * blockDim.x) {
+    const uint2 raw = __ldg((const uint2*)(x + g * 4));
+    const float2 a = __half22float2(*(const __half2*)&raw.x), b = __half22float2(*(const __half2*)&raw.y);
+    *(float4*)(out + g * 4) = make_float4(a.x, a.y, b.x, b.y);
+  }
+}
+
 template <typename T>
 __global__ void __launch_bounds__(256) add_vec8_kernel(const T* __restrict__ a, const T* __restrict__ b, T* __restrict__ out,
                                                        int64_t groups) {
@@ -328,7 +340,7 @@ cudaError_t launch_cast(hc_dtype from, hc_dtype to, const void* x, void* out, in
   if (groups > 0) {
     const int vg = grid_for(groups, threads);
     if (from == HC_F16 && to == HC_F32)
-      cast_vec8_kernel<__half, float><<<vg, threads, 0, stream>>>((const __half*)x, (float*)out, groups);
+      cast_h2f_vec4_kernel<<<grid_for(groups * 2, threads), threads, 0, stream>>>((const __half*)x, (float*)out, groups * 2);
     else if (from == HC_F32 && to == HC_F16)
       cast_vec8_kernel<float, __half><<<vg, threads, 0, stream>>>((const float*)x, (__half*)out, groups);
     else if (from == HC_F16)
