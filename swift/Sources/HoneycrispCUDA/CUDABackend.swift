@@ -62,9 +62,13 @@ public final class CUDAData: Tensor.Data, @unchecked Sendable {
     defer { host.deallocate() }
     let (ctx, src, n) = (backend.ctx, pointer, byteCount)
     let backend = self.backend
+    // Read back on the side stream and wait for that copy only: products enqueued after this
+    // tensor keep running (hc_sync would wait for all of them).
     try await backend.offload {
-      try backend.check(hc_d2h(ctx, host, src, n))
-      try backend.check(hc_sync(ctx))
+      var done: OpaquePointer? = nil
+      try backend.check(hc_d2h_async(ctx, host, src, n, &done))
+      defer { hc_event_destroy(done) }
+      try backend.check(hc_event_wait(done))
     }
     return try await fn(UnsafeRawPointer(host))
   }
