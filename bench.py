@@ -557,6 +557,30 @@ def other_configs(be, stream, rank, world):
     o = torch.empty((16384, 16384), device="cuda"); od = be.wrap(o.data_ptr(), o.numel() * 4, o)
     ms = timed(lambda: be.matmul(a, False, b, False, False, 16384, 16384, 16384, np.float32, out=od), 2)
     res["c5_f32_16384_3xtf32"] = {"ms": ms, "tflops_effective": 2 * 16384 ** 3 / ms / 1e9}
+    del a, b, o
+    # The operations either side of a Linear product, each returning a fresh buffer (as the
+    # reference's do), with the bytes they have to move: HBM-bound kernels.
+    n = 8192 * 8192
+    x32 = torch.randn(n, generator=g, device="cuda")
+    x16 = x32.half()
+    y16 = torch.randn(n, generator=g, device="cuda").half()
+    dy = torch.randn((16384, 16384), generator=g, device="cuda").half()
+    ops = {
+        "column_sum_f16_16384x16384": (lambda: be.columnSum(dy, 16384, 16384, np.float16), 16384 * 16384 * 2),
+        "cast_f32_to_f16_64M": (lambda: be.cast(x32, n, np.float32, np.float16), n * 6),
+        "cast_f16_to_f32_64M": (lambda: be.cast(x16, n, np.float16, np.float32), n * 6),
+        "add_f16_64M": (lambda: be.add(x16, y16, n, np.float16), n * 6),
+        "add_f32_64M": (lambda: be.add(x32, x32, n, np.float32), n * 12),
+        "transpose_f16_8192x8192": (lambda: be.transpose(x16, 1, 8192, 8192, np.float16), n * 4),
+        "transpose_f32_8192x8192": (lambda: be.transpose(x32, 1, 8192, 8192, np.float32), n * 8),
+    }
+    lin = {}
+    for name, (fn, nbytes) in ops.items():
+        keep = [fn(), fn()]          # two results alive: the pool has both buffers before timing starts
+        ms = timed(fn, 10)
+        lin[name] = {"ms": ms, "tb_per_s": nbytes / ms / 1e9}
+        del keep
+    res["linear_ops"] = lin
     be.checkDeviceStatus()
     return res
 
