@@ -104,6 +104,26 @@ int main() {
     catch (const BackendError& e) { threw = e.kind == BackendError::Kind::notImplemented; }
     CHECK(threw);
   }
+  {  // asynchronous upload ordered on the device, product, asynchronous read-back
+    std::vector<float> a(256 * 64), b(64 * 128), got(256 * 128, -1.0f);
+    for (size_t i = 0; i < a.size(); i++) a[i] = (float)((i * 5) % 7) - 3;
+    for (size_t i = 0; i < b.size(); i++) b[i] = (float)((i * 11) % 5) - 2;
+    auto ad = std::make_shared<CUDAData>(backend.context(), a.size() * 4);
+    auto bd = std::make_shared<CUDAData>(backend.context(), b.size() * 4);
+    hc_event* ua = ad->writeFrom(a.data(), a.size() * 4);   // later work waits for the copies on the device
+    hc_event* ub = bd->writeFrom(b.data(), b.size() * 4);
+    auto out = std::dynamic_pointer_cast<CUDAData>(be.matmul(ad, false, bd, false, false, 256, 64, 128, DType::float32));
+    CHECK(out != nullptr);
+    hc_event* rd = out->readInto(got.data(), got.size() * 4);
+    CHECK(hc_event_wait(rd) == HC_OK);
+    CHECK(hc_event_wait(ua) == HC_OK && hc_event_wait(ub) == HC_OK);
+    hc_event_destroy(rd); hc_event_destroy(ua); hc_event_destroy(ub);
+    for (int i = 0; i < 256; i += 51) for (int j = 0; j < 128; j += 17) {
+      float want = 0.0f;
+      for (int k = 0; k < 64; k++) want += a[i * 64 + k] * b[k * 128 + j];   // small integers: exact
+      CHECK(got[i * 128 + j] == want);
+    }
+  }
   std::printf("conformance ok\n");
   return 0;
 }
