@@ -94,39 +94,59 @@ SIGNATURES = {
     "hc_launch_count": (_i64, [_vp]),
     "hc_check_device_status": (_int, [_vp]),
     "hc_selftest_bounded_wait": (_int, [_vp, _int]),
+    "hc_inject_allocation_failures": (_int, [_vp, _int]),
+    "hc_set_tracing": (_int, [_vp, _int]),
+    "hc_last_elapsed_ms": (_int, [_vp, ctypes.POINTER(ctypes.c_float)]),
+    "hc_group_unique_id": (_int, [_vp]),
+    "hc_group_init": (_int, [_vp, _int, _int, _vp, ctypes.POINTER(_vp)]),
+    "hc_group_destroy": (None, [_vp]),
+    "hc_group_rank": (_int, [_vp]),
+    "hc_group_world": (_int, [_vp]),
+    "hc_group_set_timeout_ms": (_int, [_vp, _int]),
+    "hc_shard_range": (_int, [_i64, _int, _int, ctypes.POINTER(_i64), ctypes.POINTER(_i64)]),
+    "hc_column_block": (_int, [_i64, _int, _int, ctypes.POINTER(_i64), ctypes.POINTER(_i64)]),
+    "hc_batched_matmul_sharded": (_int, [_vp, _int, _i64, _vp, _int, _vp, _int, _int, _i64, _i64, _i64, _vp, _int]),
+    "hc_matmul_nsplit_allgather": (_int, [_vp, _int, _vp, _int, _vp, _int, _i64, _i64, _i64, _vp, _int]),
+    "hc_group_result_alloc": (_int, [_vp, _sz, ctypes.POINTER(_vp)]),
+    "hc_group_result_free": (_int, [_vp, _vp]),
+    "hc_group_barrier": (_int, [_vp]),
+    "hc_group_selftest_missing_peer": (_int, [_vp, _int]),
     "hc_version": (ctypes.c_char_p, []),
 }
 
-_lib = None
+_libs = {}
 
 
-def lib_path() -> str:
-    return _build.LIB_PATH
+def lib_path(diagnostics: bool = False) -> str:
+    return _build.DIAG_LIB_PATH if diagnostics else _build.LIB_PATH
 
 
-def load() -> ctypes.CDLL:
-    """Load libhccuda.so (building it first if the sources are newer). Raises on failure."""
-    global _lib
-    if _lib is not None:
-        return _lib
-    path = _build.LIB_PATH
+def load(diagnostics: bool = False) -> ctypes.CDLL:
+    """Load libhccuda.so (building it first if the sources are newer). Raises on failure.
+
+    `diagnostics=True` loads the second build of the same sources (libhccuda_diag.so), in which
+    the planner's choices can be forced through HC_TC_* environment variables; the test-suite
+    uses it to reach every tile shape with small products.  Both can live in one process."""
+    if diagnostics in _libs:
+        return _libs[diagnostics]
+    path = lib_path(diagnostics)
     override = os.environ.get("HC_CUDA_LIB")     # a differently built libhccuda.so, for A/B runs
-    if override:
+    if override and not diagnostics:
         path = override
     elif not os.path.exists(path) or os.environ.get("HC_CUDA_REBUILD") == "1":
-        path = _build.build(force=True)
-    elif _build._stale():
+        path = _build.build(force=True, diagnostics=diagnostics)
+    elif _build._stale(path):
         # Sources are newer than the library: rebuild if a compiler is at hand, otherwise say so
         # and use what is there (a copied tree can carry arbitrary file times).
         try:
-            path = _build.build()
+            path = _build.build(diagnostics=diagnostics)
         except Exception as e:  # noqa: BLE001
             import warnings
-            warnings.warn(f"libhccuda.so is older than its sources and could not be rebuilt: {e}")
+            warnings.warn(f"{os.path.basename(path)} is older than its sources and could not be rebuilt: {e}")
     L = ctypes.CDLL(path)
     for name, (res, args) in SIGNATURES.items():
         fn = getattr(L, name)  # AttributeError if the library lacks a declared symbol
         fn.restype = res
         fn.argtypes = args
-    _lib = L
+    _libs[diagnostics] = L
     return L

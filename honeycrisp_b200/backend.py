@@ -75,7 +75,7 @@ class ReadBack:
 
     def wait(self) -> np.ndarray:
         if self._event:
-            lib = L.load()
+            lib = self._source.backend._lib
             st = lib.hc_event_wait(self._event)
             lib.hc_event_destroy(self._event)
             self._event = None
@@ -85,7 +85,7 @@ class ReadBack:
     def __del__(self):
         try:
             if self._event:
-                L.load().hc_event_destroy(self._event)
+                self._source.backend._lib.hc_event_destroy(self._event)
         except Exception:
             pass
 
@@ -111,7 +111,7 @@ class CUDAData:
 
     def _mark(self):
         """Record a completion marker after the work that produces this buffer."""
-        lib = L.load()
+        lib = self.backend._lib
         if self._event:
             lib.hc_event_destroy(self._event)
             self._event = None
@@ -124,7 +124,7 @@ class CUDAData:
         if not self.backend._ctx:
             raise KernelFailed("wait() on a buffer whose backend has been closed")
         if self._event:
-            self.backend._check(L.load().hc_event_wait(self._event))
+            self.backend._check(self.backend._lib.hc_event_wait(self._event))
         else:
             self.backend.sync()
 
@@ -132,11 +132,11 @@ class CUDAData:
         """Tensor.Data.onCPU: the buffer's bytes on the host, viewed as `dtype`."""
         out = np.empty(self.byteCount, dtype=np.uint8)
         if self.byteCount:
-            lib = L.load()
+            lib = self.backend._lib
             self.backend._check(lib.hc_d2h(self.backend._ctx, out.ctypes.data, self.ptr, self.byteCount))
         self.backend.sync()
         if self._event:
-            self.backend._check(L.load().hc_event_wait(self._event))
+            self.backend._check(self.backend._lib.hc_event_wait(self._event))
         return out.view(dtype)
 
     def writeFrom(self, host_array: np.ndarray) -> "Upload":
@@ -146,7 +146,7 @@ class CUDAData:
         if not host_array.flags["C_CONTIGUOUS"] or host_array.nbytes > self.byteCount:
             raise ValueError("writeFrom: need a contiguous host array no larger than the buffer")
         ev = ctypes.c_void_p()
-        self.backend._check(L.load().hc_h2d_async(self.backend._ctx, self.ptr, host_array.ctypes.data,
+        self.backend._check(self.backend._lib.hc_h2d_async(self.backend._ctx, self.ptr, host_array.ctypes.data,
                                                   host_array.nbytes, ctypes.byref(ev)))
         return Upload(self, host_array, ev.value)
 
@@ -157,7 +157,7 @@ class CUDAData:
         if not host_array.flags["C_CONTIGUOUS"] or host_array.nbytes > self.byteCount:
             raise ValueError("readInto: need a contiguous host array no larger than the buffer")
         ev = ctypes.c_void_p()
-        self.backend._check(L.load().hc_d2h_async(self.backend._ctx, host_array.ctypes.data, self.ptr,
+        self.backend._check(self.backend._lib.hc_d2h_async(self.backend._ctx, host_array.ctypes.data, self.ptr,
                                                   host_array.nbytes, ctypes.byref(ev)))
         return ReadBack(self, host_array, ev.value)
 
@@ -179,16 +179,16 @@ class CUDAData:
 
     def free(self) -> None:
         if self._event:
-            L.load().hc_event_destroy(self._event)
+            self.backend._lib.hc_event_destroy(self._event)
             self._event = None
         if self.ptr and self.backend._ctx:
             kind = getattr(self, "_kind", None)
             if kind == "shared":
-                L.load().hc_shared_free(self.backend._ctx, self.ptr)
+                self.backend._lib.hc_shared_free(self.backend._ctx, self.ptr)
             elif kind == "ipc":
-                L.load().hc_ipc_close(self.backend._ctx, self.ptr)
+                self.backend._lib.hc_ipc_close(self.backend._ctx, self.ptr)
             elif self._owns:
-                L.load().hc_free(self.backend._ctx, self.ptr)
+                self.backend._lib.hc_free(self.backend._ctx, self.ptr)
         self.ptr = 0
         self._owner = None
 
@@ -207,8 +207,10 @@ class CUDABackend:
     (Backend.swift: every primitive defaults to `throw BackendError.notImplemented`).
     """
 
-    def __init__(self, device: int = 0):
-        lib = L.load()
+    def __init__(self, device: int = 0, diagnostics: bool = False):
+        """`diagnostics` binds the context to the diagnostics build of the library (planner choices
+        forced through HC_TC_* environment variables); the test-suite's use only."""
+        lib = self._lib = L.load(diagnostics)
         ctx = ctypes.c_void_p()
         st = lib.hc_init(int(device), ctypes.byref(ctx))
         if st != L.HC_OK:
@@ -220,7 +222,7 @@ class CUDABackend:
 
     def close(self):
         if getattr(self, "_ctx", None):
-            L.load().hc_destroy(self._ctx)
+            self._lib.hc_destroy(self._ctx)
             self._ctx = None
 
     def __del__(self):
@@ -232,7 +234,7 @@ class CUDABackend:
     def _check(self, status: int):
         if status == L.HC_OK:
             return
-        lib = L.load()
+        lib = self._lib
         msg = lib.hc_last_error(self._ctx).decode() or lib.hc_status_string(status).decode()
         if status == L.HC_ERR_ALLOCATION_FAILED:
             raise AllocationFailed(msg)
@@ -247,33 +249,33 @@ class CUDABackend:
 
     def useStream(self, cuda_stream_ptr: Optional[int]):
         """Enqueue this backend's work on a stream owned by the caller (None: its own)."""
-        self._check(L.load().hc_set_stream(self._ctx, cuda_stream_ptr or None))
+        self._check(self._lib.hc_set_stream(self._ctx, cuda_stream_ptr or None))
 
     def enqueueWait(self, transfer: "ReadBack"):
         """Work enqueued after this call starts only when `transfer` (an Upload or ReadBack) has
         completed; the host does not block."""
         if transfer._event:
-            self._check(L.load().hc_enqueue_wait(self._ctx, transfer._event))
+            self._check(self._lib.hc_enqueue_wait(self._ctx, transfer._event))
 
     def sync(self):
-        self._check(L.load().hc_sync(self._ctx))
+        self._check(self._lib.hc_sync(self._ctx))
 
     def checkDeviceStatus(self):
-        self._check(L.load().hc_check_device_status(self._ctx))
+        self._check(self._lib.hc_check_device_status(self._ctx))
 
     def launchCount(self) -> int:
-        return int(L.load().hc_launch_count(self._ctx))
+        return int(self._lib.hc_launch_count(self._ctx))
 
     def lastLaunchInfo(self) -> dict:
         info = L.LaunchInfo()
-        self._check(L.load().hc_last_launch_info(self._ctx, ctypes.byref(info)))
+        self._check(self._lib.hc_last_launch_info(self._ctx, ctypes.byref(info)))
         return {name: getattr(info, name) for name, _ in L.LaunchInfo._fields_}
 
     # -- buffers -------------------------------------------------------------------------
 
     def allocate(self, byteCount: int) -> CUDAData:
         ptr = ctypes.c_void_p()
-        self._check(L.load().hc_alloc(self._ctx, int(byteCount), ctypes.byref(ptr)))
+        self._check(self._lib.hc_alloc(self._ctx, int(byteCount), ctypes.byref(ptr)))
         return CUDAData(self, ptr.value, int(byteCount), owns=True)
 
     def collection(self, values, dtype) -> CUDAData:
@@ -282,14 +284,14 @@ class CUDABackend:
         arr = np.ascontiguousarray(np.asarray(values).astype(dt.numpy, copy=False)).reshape(-1)
         data = self.allocate(arr.nbytes)
         if arr.nbytes:
-            self._check(L.load().hc_h2d(self._ctx, data.ptr, arr.ctypes.data, arr.nbytes))
+            self._check(self._lib.hc_h2d(self._ctx, data.ptr, arr.ctypes.data, arr.nbytes))
             self.sync()  # the host array may be a temporary
         return data
 
     def sharedAllocate(self, byteCount: int) -> CUDAData:
         """Memory that the other processes of the box (one per GPU) can map with ipcOpen."""
         ptr = ctypes.c_void_p()
-        self._check(L.load().hc_shared_alloc(self._ctx, int(byteCount), ctypes.byref(ptr)))
+        self._check(self._lib.hc_shared_alloc(self._ctx, int(byteCount), ctypes.byref(ptr)))
         d = CUDAData(self, ptr.value, int(byteCount), owns=False)
         d._kind = "shared"
         return d
@@ -297,13 +299,13 @@ class CUDABackend:
     def ipcExport(self, data: CUDAData) -> bytes:
         """Opaque 64-byte handle of a sharedAllocate buffer, to send to the other processes."""
         buf = ctypes.create_string_buffer(64)
-        self._check(L.load().hc_ipc_export(self._ctx, data.ptr, buf))
+        self._check(self._lib.hc_ipc_export(self._ctx, data.ptr, buf))
         return bytes(buf.raw)
 
     def ipcOpen(self, handle: bytes, byteCount: int) -> CUDAData:
         """Map another process's sharedAllocate buffer into this one (peer access over NVLink)."""
         ptr = ctypes.c_void_p()
-        self._check(L.load().hc_ipc_open(self._ctx, ctypes.c_char_p(handle), ctypes.byref(ptr)))
+        self._check(self._lib.hc_ipc_open(self._ctx, ctypes.c_char_p(handle), ctypes.byref(ptr)))
         d = CUDAData(self, ptr.value, int(byteCount), owns=False)
         d._kind = "ipc"
         return d
@@ -320,7 +322,7 @@ class CUDABackend:
         if out.byteCount < need or any(p.byteCount < need for p in peerOuts):
             raise ValueError("matmulColumnBlockPush: every result must be the full rows x cols buffer")
         arr = (ctypes.c_void_p * max(1, len(peerOuts)))(*[p.ptr for p in peerOuts])
-        st = L.load().hc_matmul_colblock_push(self._ctx, _HC_DTYPE[dt], a_d.ptr, int(bool(transA)), b_d.ptr,
+        st = self._lib.hc_matmul_colblock_push(self._ctx, _HC_DTYPE[dt], a_d.ptr, int(bool(transA)), b_d.ptr,
                                               int(bool(transB)), int(bool(transOut)), int(rows), int(inner),
                                               int(cols), int(colBegin), int(colCount), out.ptr, arr, len(peerOuts))
         self._check(st)
@@ -376,7 +378,7 @@ class CUDABackend:
             out = self.allocate(n_out)
         elif out.byteCount < n_out:
             raise ValueError("matmul: output buffer too small")
-        st = L.load().hc_batched_matmul_ex(self._ctx, int(kernel), _HC_DTYPE[dt], int(matrixCount), a_d.ptr,
+        st = self._lib.hc_batched_matmul_ex(self._ctx, int(kernel), _HC_DTYPE[dt], int(matrixCount), a_d.ptr,
                                            int(bool(transA)), b_d.ptr, int(bool(transB)), int(bool(transOut)),
                                            int(rows), int(inner), int(cols), out.ptr)
         self._check(st)
@@ -397,7 +399,7 @@ class CUDABackend:
         b_d = self._device_operand(b, dt)
         if out.byteCount < rows * cols * dt.byteSize:
             raise ValueError("matmulColumnBlock: output must be the full rows x cols buffer")
-        st = L.load().hc_matmul_colblock(self._ctx, int(kernel), _HC_DTYPE[dt], a_d.ptr, int(bool(transA)), b_d.ptr,
+        st = self._lib.hc_matmul_colblock(self._ctx, int(kernel), _HC_DTYPE[dt], a_d.ptr, int(bool(transA)), b_d.ptr,
                                          int(bool(transB)), int(bool(transOut)), int(rows), int(inner), int(cols),
                                          int(colBegin), int(colCount), out.ptr)
         self._check(st)
@@ -423,7 +425,7 @@ class CUDABackend:
             out = np.empty(matrixCount * rows * cols, dtype=dt.numpy)
         elif out.dtype != dt.numpy or out.size < matrixCount * rows * cols or not out.flags.c_contiguous:
             raise ValueError("bad host output array")
-        fn = L.load().hc_batched_matmul_host_async if asynchronous else L.load().hc_batched_matmul_host
+        fn = self._lib.hc_batched_matmul_host_async if asynchronous else self._lib.hc_batched_matmul_host
         st = fn(self._ctx, _HC_DTYPE[dt], int(matrixCount), a.ctypes.data, int(bool(transA)), b.ctypes.data,
                 int(bool(transB)), int(bool(transOut)), int(rows), int(inner), int(cols), out.ctypes.data)
         self._check(st)
@@ -442,7 +444,7 @@ class CUDABackend:
         b_d = self._device_operand(bias, dt) if bias is not None else None
         if out is None:
             out = self.allocate(rows * outCount * dt.byteSize)
-        self._check(L.load().hc_linear_forward(self._ctx, _HC_DTYPE[dt], x_d.ptr, w_d.ptr, b_d.ptr if b_d else None,
+        self._check(self._lib.hc_linear_forward(self._ctx, _HC_DTYPE[dt], x_d.ptr, w_d.ptr, b_d.ptr if b_d else None,
                                                int(rows), int(inCount), int(outCount), out.ptr))
         out._mark()
         out._inputs = (x_d, w_d, b_d)
@@ -453,7 +455,7 @@ class CUDABackend:
         dt = _as_dtype(dtype)
         x_d = self._device_operand(x, dt)
         out = self.allocate(cols * dt.byteSize)
-        self._check(L.load().hc_column_sum(self._ctx, _HC_DTYPE[dt], x_d.ptr, int(rows), int(cols), out.ptr))
+        self._check(self._lib.hc_column_sum(self._ctx, _HC_DTYPE[dt], x_d.ptr, int(rows), int(cols), out.ptr))
         out._mark()
         out._inputs = (x_d,)
         return out
@@ -465,7 +467,7 @@ class CUDABackend:
             raise NotImplementedByBackend(f"cast {di.value} -> {do.value}")
         x_d = self._device_operand(x, di)
         out = self.allocate(count * do.byteSize)
-        self._check(L.load().hc_cast(self._ctx, _HC_DTYPE[di], _HC_DTYPE[do], x_d.ptr, int(count), out.ptr))
+        self._check(self._lib.hc_cast(self._ctx, _HC_DTYPE[di], _HC_DTYPE[do], x_d.ptr, int(count), out.ptr))
         out._mark()
         out._inputs = (x_d,)
         return out
@@ -475,7 +477,7 @@ class CUDABackend:
         dt = _as_dtype(dtype)
         a_d, b_d = self._device_operand(a, dt), self._device_operand(b, dt)
         out = self.allocate(count * dt.byteSize)
-        self._check(L.load().hc_add(self._ctx, _HC_DTYPE[dt], a_d.ptr, b_d.ptr, int(count), out.ptr))
+        self._check(self._lib.hc_add(self._ctx, _HC_DTYPE[dt], a_d.ptr, b_d.ptr, int(count), out.ptr))
         out._mark()
         out._inputs = (a_d, b_d)
         return out
@@ -485,7 +487,7 @@ class CUDABackend:
         dt = _as_dtype(dtype)
         x_d = self._device_operand(x, dt)
         out = self.allocate(matrixCount * rows * cols * dt.byteSize)
-        self._check(L.load().hc_transpose(self._ctx, _HC_DTYPE[dt], int(matrixCount), x_d.ptr, int(rows), int(cols),
+        self._check(self._lib.hc_transpose(self._ctx, _HC_DTYPE[dt], int(matrixCount), x_d.ptr, int(rows), int(cols),
                                           out.ptr))
         out._mark()
         out._inputs = (x_d,)
@@ -505,7 +507,7 @@ class CUDABackend:
             self.seed(0)
         out = self.allocate(count * dt.byteSize)
         nxt = ctypes.c_uint64()
-        self._check(L.load().hc_random(self._ctx, 1 if dist == "normal" else 0, _HC_DTYPE[dt], self._rng_state[0],
+        self._check(self._lib.hc_random(self._ctx, 1 if dist == "normal" else 0, _HC_DTYPE[dt], self._rng_state[0],
                                        self._rng_state[1], int(count), out.ptr, ctypes.byref(nxt)))
         self._rng_state[1] = nxt.value
         out._mark()
@@ -513,4 +515,4 @@ class CUDABackend:
 
     def hostSync(self):
         """Wait for every asynchronous host-buffer product enqueued so far."""
-        self._check(L.load().hc_host_sync(self._ctx))
+        self._check(self._lib.hc_host_sync(self._ctx))

@@ -13,6 +13,9 @@ import sys
 PKG_DIR = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(PKG_DIR, "csrc")
 LIB_PATH = os.path.join(PKG_DIR, "libhccuda.so")
+# The same sources with -DHC_DIAGNOSTICS: tile shape, cut of the contraction and thresholds of the
+# planner can be forced from the environment.  Only the test-suite loads it.
+DIAG_LIB_PATH = os.path.join(PKG_DIR, "libhccuda_diag.so")
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",
@@ -33,24 +36,30 @@ def sources():
     return sorted(glob.glob(os.path.join(CSRC, "*.cu")))
 
 
-def _stale() -> bool:
-    if not os.path.exists(LIB_PATH):
+def _stale(path: str = LIB_PATH) -> bool:
+    if not os.path.exists(path):
         return True
-    t = os.path.getmtime(LIB_PATH)
+    t = os.path.getmtime(path)
     deps = sources() + glob.glob(os.path.join(CSRC, "*.cuh")) + glob.glob(
         os.path.join(PKG_DIR, "..", "include", "*.h"))
     return any(os.path.getmtime(d) > t for d in deps)
 
 
-def build(force: bool = False, verbose: bool = False) -> str:
-    if not force and not _stale():
-        return LIB_PATH
-    cmd = [_nvcc()] + NVCC_FLAGS + (["-Xptxas", "-v"] if verbose else []) + ["-o", LIB_PATH] + sources()
+def build(force: bool = False, verbose: bool = False, diagnostics: bool = False) -> str:
+    path = DIAG_LIB_PATH if diagnostics else LIB_PATH
+    if not force and not _stale(path):
+        return path
+    cmd = ([_nvcc()] + NVCC_FLAGS + (["-DHC_DIAGNOSTICS"] if diagnostics else []) +
+           (["-Xptxas", "-v"] if verbose else []) + ["-ldl", "-o", path] + sources())
     if verbose:
         print(" ".join(cmd), file=sys.stderr)
     subprocess.check_call(cmd)
-    return LIB_PATH
+    return path
+
+
+def build_all(force: bool = False, verbose: bool = False):
+    return build(force, verbose), build(force, verbose, diagnostics=True)
 
 
 if __name__ == "__main__":
-    print(build(force="--force" in sys.argv, verbose="--verbose" in sys.argv))
+    print(*build_all(force="--force" in sys.argv, verbose="--verbose" in sys.argv))

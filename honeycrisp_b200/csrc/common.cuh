@@ -45,6 +45,7 @@ enum DeviceStatusBits : unsigned int {
   kDevTimeoutMma = 2u,
   kDevTimeoutEpilogue = 4u,
   kDevTimeoutSelfTest = 8u,
+  kDevTimeoutBarrier = 16u,    // a rank of a device group did not arrive at a flag barrier in time
 };
 
 struct LaunchRecord {
@@ -65,9 +66,19 @@ cudaError_t launch_simt(const GemmProblem& p, bool exact, cudaStream_t stream, L
 // operands, repacked float16 operands, partial matrices of a cut contraction).
 // `extra_out`: up to 7 more result buffers of the same shape and pitch as p.C (other devices'
 // copies, mapped into this process); every result tile is stored to each of them as well.
+// `cache` (optional): prepared launches of recent products, owned by the caller's context; a
+// repeat of a product then skips planning and tensor-map encoding.
+// `scratch_needed` (optional) receives the work-area bytes the product needs; when the area given
+// is smaller the call launches nothing and returns cudaErrorInvalidValue, so that the caller can
+// grow the area and call again.
+struct TcCache;
+TcCache* tc_cache_create();
+void tc_cache_destroy(TcCache* c);
+void tc_cache_clear(TcCache* c);
 cudaError_t launch_tc(const GemmProblem& p, cudaStream_t stream, unsigned int* status_word,
                       void* scratch, size_t scratch_bytes, int sm_count, LaunchRecord* rec,
-                      void* const* extra_out = nullptr, int n_extra = 0);
+                      void* const* extra_out = nullptr, int n_extra = 0, TcCache* cache = nullptr,
+                      size_t* scratch_needed = nullptr);
 bool tc_supported(const GemmProblem& p);
 // One-thread kernel whose bounded wait is made to expire after `limit_ns` (self-test).
 cudaError_t launch_wait_probe(cudaStream_t stream, unsigned int* status_word, unsigned long long limit_ns);
@@ -103,4 +114,16 @@ void ctx_note_launch(hc_ctx* ctx, const LaunchRecord& rec, int64_t flops);
 hc_status ctx_build_problem(hc_ctx* ctx, hc_dtype dtype, int64_t count, const void* a, int trans_a, const void* b,
                             int trans_b, int trans_out, int64_t rows, int64_t inner, int64_t cols, void* out,
                             GemmProblem* p);
+// Used by the multi-device code (csrc/hc_group.cu); the caller holds the context's mutex and has
+// made the context's device current.
+hc_status ctx_device_alloc(hc_ctx* ctx, void** ptr, size_t bytes);   // stream-ordered, from the context's pool
+void ctx_device_free(hc_ctx* ctx, void* ptr);
+void ctx_count_launches(hc_ctx* ctx, int n);
+hc_status ctx_run_batched(hc_ctx* ctx, hc_dtype dtype, int64_t count, const void* a, int trans_a, const void* b,
+                          int trans_b, int trans_out, int64_t rows, int64_t inner, int64_t cols, void* out);
+// Columns [col_begin, col_begin + col_count) of op(a)*op(b), tensor-core kernel, written to
+// `block_out` with row pitch `block_ld` (and to `extra[0..n_extra)`, same layout, when given).
+hc_status ctx_run_colblock(hc_ctx* ctx, hc_dtype dtype, const void* a, int trans_a, const void* b, int trans_b,
+                           int64_t rows, int64_t inner, int64_t cols, int64_t col_begin, int64_t col_count,
+                           void* block_out, int64_t block_ld, void* const* extra, int n_extra);
 }  // namespace hc

@@ -88,7 +88,6 @@ struct TcParams {
   int tma_store;      // results leave through shared memory and TMA stores (else direct stores)
   const void* bias;   // optional row vector added to the rounded product (Linear), or null
   int n_out;          // destinations of every result tile: this device's result, then peers' copies
-  int debug;
 };
 
 // ---- PTX wrappers ---------------------------------------------------------------------------
@@ -618,7 +617,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap mapA_hi, const __grid_constan
       KRange kr = k_range(t.mat, p);
       // The ring starts empty: the first kStages slots of the first tile need no wait, and their
       // byte counts can be announced before the previous kernel is waited for.
-      const int free_slots = (tile_first < p.total_tiles && !(p.debug & 8)) ? min(kStages, kr.count) : 0;
+      const int free_slots = (tile_first < p.total_tiles) ? min(kStages, kr.count) : 0;
       if (do_a && rank == 0)
         for (int i = 0; i < free_slots; i++) mbar_expect_tx(bar_full + 8 * i, STAGE_BYTES * kCta);
       pdl_wait();
@@ -636,11 +635,6 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap mapA_hi, const __grid_constan
             break;
           }
           const uint32_t full = full_leader + 8 * s;
-          if (p.debug & 8) {  // timing experiment: no copies
-            if (rank == 0 && do_a) mbar_expect_tx(bar_full + 8 * s, 0);
-            if (++s == kStages) { s = 0; ph ^= 1; }
-            continue;
-          }
           // (copies of B may complete before the bytes are announced: the count goes negative
           // for a moment, and the phase cannot complete before this arrive)
           if (rank == 0 && do_a && kb >= prearmed) mbar_expect_tx(bar_full + 8 * s, STAGE_BYTES * kCta);
@@ -749,7 +743,6 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap mapA_hi, const __grid_constan
               const uint32_t d = tmem_base + (kNSplit == 2 ? h : slot) * kBN;
 #pragma unroll
               for (int k = 0; k < BK / UMMA_K; k++) {
-                if (p.debug & 16) break;  // timing experiment: no MMAs
                 tc_mma<kTf32, kCta>(d, adesc + (uint64_t)((k * a_kstep) >> 4), bdesc + (uint64_t)((k * b_kstep) >> 4),
                                     idesc, (in_win | j | pr | k) ? 1u : 0u);
               }
@@ -1210,8 +1203,10 @@ bool operand_ok(const void* base, int elem_bytes, int64_t ld, int64_t stride_mat
   return true;
 }
 
-// Per-launch diagnostic switches, gathered in one pass over the environment (a getenv per
-// switch costs a scan each, a few microseconds per launch in total).
+// Thresholds of the tile-shape model.  In the shipped library they are constants.  A library
+// built with -DHC_DIAGNOSTICS (the test-suite's second build) can move them, force a tile shape
+// or a cut of the contraction from the environment, read at every launch, so that small test
+// products reach every code path; none of the switches changes what a product computes.
 struct Tunables {
   int wide_min_kb = 32;   // HC_TC_WIDE_MIN_KB: k blocks from which the 256x512 tile is considered
   int shape = 0;          // HC_TC_SHAPE: force a tile shape (1..6)
@@ -1220,6 +1215,7 @@ struct Tunables {
   int group_m = 0;        // HC_TC_GROUP_M: tile rows sharing a sweep over the columns (0: default)
   int wide_epi8 = 1;      // HC_TC_WIDE_EPI8: eight epilogue warps on the 256x512 tile
 };
+#ifdef HC_DIAGNOSTICS
 Tunables read_tunables() {
   Tunables t;
   for (char** e = environ; e && *e; e++) {
@@ -1239,14 +1235,12 @@ Tunables read_tunables() {
   }
   return t;
 }
-
 int env_int(const char* name, int fallback) {
   const char* e = getenv(name);
   return e ? atoi(e) : fallback;
 }
-// Diagnostic switches (HC_TC_DEBUG, not part of the interface): 2 = no accumulation windows,
-// 4 = never pair CTAs, 8 = skip the copies, 16 = skip the MMAs (8 and 16 give wrong results and
-// exist to time the load path and the MMA stream separately), 128 = direct stores, no TMA store.
+// HC_TC_DEBUG bits: 2 = no accumulation windows, 4 = never pair CTAs, 128 = direct stores instead
+// of TMA stores.
 int debug_flags() {
   static int v = env_int("HC_TC_DEBUG", 0);
   return v;
@@ -1256,13 +1250,21 @@ int window_slabs() {
   static int v = env_int("HC_TC_WINDOW_SLABS", 4);
   return v < 1 ? 1 : v;
 }
-
-// Successive kernels of this library in one stream may overlap their prologue with the
-// predecessor's tail (programmatic dependent launch); HC_TC_PDL=0 turns that off.
+// HC_TC_PDL=0 launches without programmatic dependent launch.
 bool overlap_launches() {
   static int v = env_int("HC_TC_PDL", 1);
   return v != 0;
 }
+constexpr bool kPlanCacheEnabled = false;   // the switches are read per launch
+#else
+inline Tunables read_tunables() { return Tunables(); }
+constexpr int debug_flags() { return 0; }
+constexpr int window_slabs() { return 4; }
+// Successive kernels of this library in one stream overlap their prologue with the
+// predecessor's tail (programmatic dependent launch).
+constexpr bool overlap_launches() { return true; }
+constexpr bool kPlanCacheEnabled = true;
+#endif
 
 template <int kElemBytes, int kBN, int kStages, int kEpiWarps, bool kWindowed, int kCta, int kNSplit = 1, int kSlabs = 1,
           bool kPartial = false>
@@ -1534,110 +1536,167 @@ PlanSummary tc_describe_plan(const GemmProblem& p, int sm_count) {
   return r;
 }
 
-cudaError_t launch_tc(const GemmProblem& p, cudaStream_t stream, unsigned int* status_word, void* scratch,
-                      size_t scratch_bytes, int sm_count, LaunchRecord* rec, void* const* extra_out, int n_extra) {
-  if (!tc_supported(p)) return cudaErrorNotSupported;
-  if (n_extra < 0 || n_extra > kMaxOut - 1 || (n_extra > 0 && !extra_out)) return cudaErrorInvalidValue;
+// ---- a product, prepared once and issued many times ------------------------------------------
+// Planning a product (tile shape, cut, tensor maps: four driver calls) costs the host several
+// microseconds, which is as long as the kernel of a small product runs.  A training loop issues
+// the same products - same buffers, same shapes - step after step, so the context keeps the
+// prepared launches of the products it has seen most recently and a repeat costs one lookup.
+namespace {
+
+typedef cudaError_t (*TcLaunchFn)(const CUtensorMap maps[4], const OutMaps& outs, const TcParams& p, int sm_count,
+                                  cudaStream_t stream, LaunchRecord* rec);
+
+struct TcPrepared {
+  int pre = 0;                       // pre-pass: 0 none, 1 repack float16 operands, 2 split float32 operands
+  RepackJob rja, rjb;
+  SplitJob sja, sjb;
+  int pre_blocks_a = 0, pre_blocks_b = 0;
+  CUtensorMap maps[4];
+  OutMaps outs;
+  TcParams tp;
+  TcLaunchFn fn = nullptr;
+  bool cut = false;                  // second kernel sums the parts of a cut contraction
+  bool reduce_half = false;
+  ReduceJob job;
+  int reduce_blocks = 0;
+  size_t scratch_used = 0;           // bytes of the work area this product touches
+};
+
+struct TcKey {
+  int dtype, a_mn, b_mn, no_split, n_extra, may_split;
+  int64_t batch, M, N, K, lda, ldb, ldc, sA, sB, sC, plan_M, plan_N;
+  const void *A, *B, *C, *bias, *scratch, *status;
+  const void* extra[kMaxOut - 1];
+};
+
+TcKey make_key(const GemmProblem& p, const void* scratch, const void* status, void* const* extra_out, int n_extra) {
+  TcKey k;
+  memset(&k, 0, sizeof k);
+  k.dtype = (int)p.dtype; k.a_mn = p.a_mn_major; k.b_mn = p.b_mn_major; k.no_split = p.no_split ? 1 : 0;
+  k.n_extra = n_extra; k.may_split = n_extra == 0;
+  k.batch = p.batch; k.M = p.M; k.N = p.N; k.K = p.K; k.lda = p.lda; k.ldb = p.ldb; k.ldc = p.ldc;
+  k.sA = p.strideA; k.sB = p.strideB; k.sC = p.strideC; k.plan_M = p.plan_M; k.plan_N = p.plan_N;
+  k.A = p.A; k.B = p.B; k.C = p.C; k.bias = p.bias; k.scratch = scratch; k.status = status;
+  for (int i = 0; i < n_extra && i < kMaxOut - 1; i++) k.extra[i] = extra_out[i];
+  return k;
+}
+
+}  // namespace
+
+struct TcCache {
+  static constexpr int kEntries = 32;
+  struct Entry {
+    bool used = false;
+    uint64_t stamp = 0;
+    TcKey key;
+    TcPrepared prep;
+  };
+  Entry e[kEntries];
+  uint64_t clock = 0;
+};
+
+TcCache* tc_cache_create() { return new (std::nothrow) TcCache(); }
+void tc_cache_destroy(TcCache* c) { delete c; }
+void tc_cache_clear(TcCache* c) {
+  if (c) for (auto& x : c->e) x.used = false;
+}
+
+namespace {
+
+cudaError_t launch_elementwise(const void* fn, void** args, int blocks, cudaStream_t stream) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)blocks);
+  cfg.blockDim = dim3(256);
+  cfg.stream = stream;
+  cudaLaunchAttribute attr;
+  attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr.val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = &attr;
+  cfg.numAttrs = overlap_launches() ? 1 : 0;
+  return cudaLaunchKernelExC(&cfg, fn, args);
+}
+
+// Everything about a product that does not depend on the stream: pre-pass jobs, tensor maps,
+// kernel parameters, which kernel.  `*scratch_needed` receives the work-area bytes the product
+// needs; when the area given is smaller, nothing else is filled in and cudaErrorInvalidValue
+// comes back, so that the caller can grow the area and ask again.
+cudaError_t prepare_tc(const GemmProblem& p, unsigned int* status_word, void* scratch, size_t scratch_bytes,
+                       int sm_count, void* const* extra_out, int n_extra, TcPrepared* out, size_t* scratch_needed) {
+  TcPrepared& pp = *out;
   const bool f32 = p.dtype == HC_F32;
   const int eb = f32 ? 4 : 2;
   const int BK = 128 / eb;
-  if (rec) { *rec = LaunchRecord(); rec->kernel = HC_KERNEL_TENSOR; }
+  const Tunables tun = read_tunables();
+  const TcPlan plan = plan_tc(p, sm_count, n_extra == 0, tun);
+  const size_t ops_bytes = operand_scratch_bytes(p);
+  const size_t need = plan.ws_bytes ? ((ops_bytes + 255) & ~(size_t)255) + plan.ws_bytes : ops_bytes;
+  if (scratch_needed) *scratch_needed = need;
+  if (need > 0 && (!scratch || scratch_bytes < need)) return cudaErrorInvalidValue;
+  pp.scratch_used = need;
 
   const void *a_hi = p.A, *a_lo = p.A, *b_hi = p.B, *b_lo = p.B;
   int64_t lda = p.lda, ldb = p.ldb, sa = p.strideA, sb = p.strideB;
+  pp.pre = 0;
   if (!f32) {
     const RepackLayout r = repack_layout(p);
     if (r.a || r.b) {
-      if (!scratch || scratch_bytes < r.a_bytes + r.b_bytes) return cudaErrorInvalidValue;
       __half* ra = (__half*)scratch;
       __half* rb = (__half*)((char*)scratch + r.a_bytes);
-      RepackJob ja{(const __half*)p.A, ra, r.a_rows, r.a_width, p.lda, r.a_ld, p.strideA, r.a_mat, r.a ? p.batch : 0};
-      RepackJob jb{(const __half*)p.B, rb, r.b_rows, r.b_width, p.ldb, r.b_ld, p.strideB, r.b_mat, r.b ? p.batch : 0};
+      pp.rja = RepackJob{(const __half*)p.A, ra, r.a_rows, r.a_width, p.lda, r.a_ld, p.strideA, r.a_mat, r.a ? p.batch : 0};
+      pp.rjb = RepackJob{(const __half*)p.B, rb, r.b_rows, r.b_width, p.ldb, r.b_ld, p.strideB, r.b_mat, r.b ? p.batch : 0};
       auto blocks = [&](const RepackJob& j) {
         const int64_t work = j.batch * j.rows * j.width;
         int64_t b = (work + 255) / 256;
         return (int)(b > 148 * 8 ? 148 * 8 : b);   // zero blocks for an operand that stays in place
       };
-      const int blocks_a = blocks(ja), blocks_b = blocks(jb);
-      cudaLaunchConfig_t rcfg = {};
-      rcfg.gridDim = dim3((unsigned)(blocks_a + blocks_b));
-      rcfg.blockDim = dim3(256);
-      rcfg.stream = stream;
-      cudaLaunchAttribute rattr;
-      rattr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
-      rattr.val.programmaticStreamSerializationAllowed = 1;
-      rcfg.attrs = &rattr;
-      rcfg.numAttrs = overlap_launches() ? 1 : 0;
-      cudaError_t re = cudaLaunchKernelEx(&rcfg, repack_f16_kernel, ja, jb, blocks_a);
-      if (re != cudaSuccess) return re;
-      if (rec) { rec->launches += 1; rec->scratch_bytes = r.a_bytes + r.b_bytes; }
+      pp.pre_blocks_a = blocks(pp.rja); pp.pre_blocks_b = blocks(pp.rjb);
+      pp.pre = 1;
       if (r.a) { a_hi = a_lo = ra; lda = r.a_ld; sa = r.a_mat; }
       if (r.b) { b_hi = b_lo = rb; ldb = r.b_ld; sb = r.b_mat; }
     }
-  }
-  if (f32) {
+  } else {
     const SplitLayout s = split_layout(p);
-    if (!scratch || scratch_bytes < 2 * s.a_bytes + 2 * s.b_bytes) return cudaErrorInvalidValue;
-    float* base = (float*)scratch;
-    float* ah = base; float* al = (float*)((char*)ah + s.a_bytes);
+    float* ah = (float*)scratch; float* al = (float*)((char*)ah + s.a_bytes);
     float* bh = (float*)((char*)al + s.a_bytes); float* bl = (float*)((char*)bh + s.b_bytes);
-    const int threads = 256;
     auto vec_ok4 = [](const void* src, int64_t width, int64_t ld, int64_t stride, int64_t batch) {
       return (int)(width % 4 == 0 && ld % 4 == 0 && ((uintptr_t)src & 15) == 0 && (batch == 1 || stride % 4 == 0));
     };
-    SplitJob ja{(const float*)p.A, ah, al, s.a_rows, s.a_width, p.lda, s.a_ld, p.strideA, s.a_mat, p.batch,
-                vec_ok4(p.A, s.a_width, p.lda, p.strideA, p.batch)};
-    SplitJob jb{(const float*)p.B, bh, bl, s.b_rows, s.b_width, p.ldb, s.b_ld, p.strideB, s.b_mat, p.batch,
-                vec_ok4(p.B, s.b_width, p.ldb, p.strideB, p.batch)};
+    pp.sja = SplitJob{(const float*)p.A, ah, al, s.a_rows, s.a_width, p.lda, s.a_ld, p.strideA, s.a_mat, p.batch,
+                      vec_ok4(p.A, s.a_width, p.lda, p.strideA, p.batch)};
+    pp.sjb = SplitJob{(const float*)p.B, bh, bl, s.b_rows, s.b_width, p.ldb, s.b_ld, p.strideB, s.b_mat, p.batch,
+                      vec_ok4(p.B, s.b_width, p.ldb, p.strideB, p.batch)};
     auto blocks = [&](const SplitJob& j) {
       const int64_t work = j.batch * j.rows * (j.vec4 ? j.width / 4 : j.width);
-      int64_t b = (work + threads - 1) / threads;
+      int64_t b = (work + 255) / 256;
       return (int)(b > 148 * 8 ? 148 * 8 : (b < 1 ? 1 : b));
     };
-    const int blocks_a = blocks(ja), blocks_b = blocks(jb);
-    {
-      cudaLaunchConfig_t scfg = {};
-      scfg.gridDim = dim3((unsigned)(blocks_a + blocks_b));
-      scfg.blockDim = dim3(threads);
-      scfg.stream = stream;
-      cudaLaunchAttribute sattr;
-      sattr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
-      sattr.val.programmaticStreamSerializationAllowed = 1;
-      scfg.attrs = &sattr;
-      scfg.numAttrs = overlap_launches() ? 1 : 0;
-      cudaError_t se = cudaLaunchKernelEx(&scfg, split_tf32_kernel, ja, jb, blocks_a);
-      if (se != cudaSuccess) return se;
-    }
-    if (rec) { rec->launches += 1; rec->scratch_bytes = 2 * s.a_bytes + 2 * s.b_bytes; }
+    pp.pre_blocks_a = blocks(pp.sja); pp.pre_blocks_b = blocks(pp.sjb);
+    pp.pre = 2;
     a_hi = ah; a_lo = al; b_hi = bh; b_lo = bl;
     lda = s.a_ld; ldb = s.b_ld; sa = s.a_mat; sb = s.b_mat;
   }
 
   const int dbg = debug_flags();
   const int kslabs = (int)((p.K + BK - 1) / BK);
-  const Tunables tun = read_tunables();
-  const TcPlan plan = plan_tc(p, sm_count, n_extra == 0, tun);
   const int shape = plan.shape;
   const int bn = (shape == SHAPE_C1_128 || shape == SHAPE_PAIR_128) ? 128 : shape == SHAPE_PAIR_64 ? 64 : 256;
   const int cta = (shape == SHAPE_C1_256 || shape == SHAPE_C1_128) ? 1 : 2;
   const int b_box = bn / cta;
-  CUtensorMap maps[4];
-  OutMaps outs;
-  memset(maps, 0, sizeof maps);
-  memset(&outs, 0, sizeof outs);
-  if (!make_operand_map(&maps[0], a_hi, eb, p.a_mn_major, p.M, p.K, lda, sa, p.batch, BM) ||
-      !make_operand_map(&maps[2], b_hi, eb, p.b_mn_major, p.N, p.K, ldb, sb, p.batch, b_box))
+  memset(pp.maps, 0, sizeof pp.maps);
+  memset(&pp.outs, 0, sizeof pp.outs);
+  if (!make_operand_map(&pp.maps[0], a_hi, eb, p.a_mn_major, p.M, p.K, lda, sa, p.batch, BM) ||
+      !make_operand_map(&pp.maps[2], b_hi, eb, p.b_mn_major, p.N, p.K, ldb, sb, p.batch, b_box))
     return cudaErrorNotSupported;
   if (f32) {
-    if (!make_operand_map(&maps[1], a_lo, eb, p.a_mn_major, p.M, p.K, lda, sa, p.batch, BM) ||
-        !make_operand_map(&maps[3], b_lo, eb, p.b_mn_major, p.N, p.K, ldb, sb, p.batch, b_box))
+    if (!make_operand_map(&pp.maps[1], a_lo, eb, p.a_mn_major, p.M, p.K, lda, sa, p.batch, BM) ||
+        !make_operand_map(&pp.maps[3], b_lo, eb, p.b_mn_major, p.N, p.K, ldb, sb, p.batch, b_box))
       return cudaErrorNotSupported;
   } else {
-    maps[1] = maps[0];   // float16 has no lo parts; the kernel never reads these two
-    maps[3] = maps[2];
+    pp.maps[1] = pp.maps[0];   // float16 has no lo parts; the kernel never reads these two
+    pp.maps[3] = pp.maps[2];
   }
 
-  TcParams tp;
+  TcParams& tp = pp.tp;
   tp.M = p.M; tp.N = p.N;
   // Short contractions are bound by draining results, not by the MMA: they get more epilogue
   // warps (eight up to 8 slabs, sixteen up to 2: each warp's drain is a serial chain of tensor-
@@ -1666,7 +1725,6 @@ cudaError_t launch_tc(const GemmProblem& p, cudaStream_t stream, unsigned int* s
   tp.group_m = tun.group_m > 0 ? tun.group_m : wide ? 16 : 16 / cta;
   tp.a_mn_major = p.a_mn_major; tp.b_mn_major = p.b_mn_major;
   tp.status = status_word;
-  tp.debug = dbg;
   // Where the tiles go: the result itself, or - for a cut contraction - float32 partial matrices
   // in the work area (part z of matrix m at index m * parts + z), which a second kernel sums.
   void* out_base = p.C;
@@ -1674,13 +1732,11 @@ cudaError_t launch_tc(const GemmProblem& p, cudaStream_t stream, unsigned int* s
   int64_t out_ld = p.ldc, out_stride = p.strideC, out_mats = p.batch;
   tp.bias = p.bias;
   if (cut) {
-    const size_t off = (operand_scratch_bytes(p) + 255) & ~(size_t)255;
-    if (!scratch || scratch_bytes < off + plan.ws_bytes) return cudaErrorInvalidValue;
+    const size_t off = (ops_bytes + 255) & ~(size_t)255;
     out_base = (char*)scratch + off;
     out_bytes = 4;
     out_ld = plan.ws_ld; out_stride = p.M * plan.ws_ld; out_mats = p.batch * plan.splits;
     tp.bias = nullptr;
-    if (rec) rec->scratch_bytes = off + plan.ws_bytes;
   }
   tp.C = out_base; tp.ldc = out_ld; tp.strideC = out_stride;
   tp.vec_ok = (((uintptr_t)out_base & 15) == 0 && (out_ld * out_bytes) % 16 == 0 && (out_stride * out_bytes) % 16 == 0) ? 1 : 0;
@@ -1689,74 +1745,130 @@ cudaError_t launch_tc(const GemmProblem& p, cudaStream_t stream, unsigned int* s
   tp.tma_store = 0;
   tp.n_out = 1;
   if (tp.vec_ok && !(dbg & 128) && p.M < (1ll << 31) && p.N < (1ll << 31) && out_ld * out_bytes < (1ll << 40) &&
-      make_output_map(&outs.m[0], out_base, out_bytes, p.N, p.M, out_ld, out_stride, out_mats))
+      make_output_map(&pp.outs.m[0], out_base, out_bytes, p.N, p.M, out_ld, out_stride, out_mats))
     tp.tma_store = 1;
   if (n_extra > 0) {
     // Extra destinations only exist on the TMA-store path.
     if (!tp.tma_store || cut) return cudaErrorNotSupported;
     for (int i = 0; i < n_extra; i++) {
       if (((uintptr_t)extra_out[i] & 15) != 0 ||
-          !make_output_map(&outs.m[1 + i], extra_out[i], eb, p.N, p.M, p.ldc, p.strideC, p.batch))
+          !make_output_map(&pp.outs.m[1 + i], extra_out[i], eb, p.N, p.M, p.ldc, p.strideC, p.batch))
         return cudaErrorNotSupported;
     }
     tp.n_out = 1 + n_extra;
   }
-  if (rec) rec->tiles = tp.total_tiles;
 
-  cudaError_t ge;
+  TcLaunchFn fn = nullptr;
   if (!f32 && cut) {
-    if (shape == SHAPE_PAIR_128) ge = TcConfig<2, 128, 4, 4, false, 2, 1, 2, true>::launch(maps, outs, tp, sm_count, stream, rec);
-    else if (shape == SHAPE_PAIR_64) ge = TcConfig<2, 64, 4, 4, false, 2, 1, 2, true>::launch(maps, outs, tp, sm_count, stream, rec);
-    else if (shape == SHAPE_PAIR) ge = TcConfig<2, 256, 6, 4, false, 2, 1, 1, true>::launch(maps, outs, tp, sm_count, stream, rec);
-    else if (shape == SHAPE_C1_128) ge = TcConfig<2, 128, 3, 4, false, 1, 1, 2, true>::launch(maps, outs, tp, sm_count, stream, rec);
+    if (shape == SHAPE_PAIR_128) fn = TcConfig<2, 128, 4, 4, false, 2, 1, 2, true>::launch;
+    else if (shape == SHAPE_PAIR_64) fn = TcConfig<2, 64, 4, 4, false, 2, 1, 2, true>::launch;
+    else if (shape == SHAPE_PAIR) fn = TcConfig<2, 256, 6, 4, false, 2, 1, 1, true>::launch;
+    else if (shape == SHAPE_C1_128) fn = TcConfig<2, 128, 3, 4, false, 1, 1, 2, true>::launch;
     else return cudaErrorInvalidValue;
   } else if (!f32) {
-    if (wide && tun.wide_epi8) ge = TcConfig<2, 256, 4, 8, false, 2, 2>::launch(maps, outs, tp, sm_count, stream, rec);
-    else if (wide) ge = TcConfig<2, 256, 4, 4, false, 2, 2>::launch(maps, outs, tp, sm_count, stream, rec);
-    else if (shape == SHAPE_PAIR_128) ge = TcConfig<2, 128, 4, 4, false, 2, 1, 2>::launch(maps, outs, tp, sm_count, stream, rec);
-    else if (shape == SHAPE_PAIR_64) ge = TcConfig<2, 64, 4, 4, false, 2, 1, 2>::launch(maps, outs, tp, sm_count, stream, rec);
-    else if (cta == 2 && short_k && kslabs <= 2) ge = TcConfig<2, 256, 4, 16, false, 2>::launch(maps, outs, tp, sm_count, stream, rec);
-    else if (cta == 2 && short_k) ge = TcConfig<2, 256, 4, 8, false, 2>::launch(maps, outs, tp, sm_count, stream, rec);
-    else if (cta == 2) ge = TcConfig<2, 256, 6, 4, false, 2>::launch(maps, outs, tp, sm_count, stream, rec);
-    else if (bn == 256) ge = TcConfig<2, 256, 4, 4, false, 1>::launch(maps, outs, tp, sm_count, stream, rec);
-    else ge = TcConfig<2, 128, 3, 4, false, 1, 1, 2>::launch(maps, outs, tp, sm_count, stream, rec);
+    if (wide && tun.wide_epi8) fn = TcConfig<2, 256, 4, 8, false, 2, 2>::launch;
+    else if (wide) fn = TcConfig<2, 256, 4, 4, false, 2, 2>::launch;
+    else if (shape == SHAPE_PAIR_128) fn = TcConfig<2, 128, 4, 4, false, 2, 1, 2>::launch;
+    else if (shape == SHAPE_PAIR_64) fn = TcConfig<2, 64, 4, 4, false, 2, 1, 2>::launch;
+    else if (cta == 2 && short_k && kslabs <= 2) fn = TcConfig<2, 256, 4, 16, false, 2>::launch;
+    else if (cta == 2 && short_k) fn = TcConfig<2, 256, 4, 8, false, 2>::launch;
+    else if (cta == 2) fn = TcConfig<2, 256, 6, 4, false, 2>::launch;
+    else if (bn == 256) fn = TcConfig<2, 256, 4, 4, false, 1>::launch;
+    else fn = TcConfig<2, 128, 3, 4, false, 1, 1, 2>::launch;
   } else if (windowed) {
-    if (shape == SHAPE_PAIR_128) ge = TcConfig<4, 128, 3, 4, true, 2>::launch(maps, outs, tp, sm_count, stream, rec);
-    else if (shape == SHAPE_PAIR_64) ge = TcConfig<4, 64, 4, 4, true, 2>::launch(maps, outs, tp, sm_count, stream, rec);
-    else if (cta == 2) ge = TcConfig<4, 256, 3, 8, true, 2>::launch(maps, outs, tp, sm_count, stream, rec);
-    else if (bn == 256) ge = TcConfig<4, 256, 2, 8, true, 1>::launch(maps, outs, tp, sm_count, stream, rec);
-    else ge = TcConfig<4, 128, 3, 4, true, 1>::launch(maps, outs, tp, sm_count, stream, rec);
+    if (shape == SHAPE_PAIR_128) fn = TcConfig<4, 128, 3, 4, true, 2>::launch;
+    else if (shape == SHAPE_PAIR_64) fn = TcConfig<4, 64, 4, 4, true, 2>::launch;
+    else if (cta == 2) fn = TcConfig<4, 256, 3, 8, true, 2>::launch;
+    else if (bn == 256) fn = TcConfig<4, 256, 2, 8, true, 1>::launch;
+    else fn = TcConfig<4, 128, 3, 4, true, 1>::launch;
   } else {
-    if (cta == 2) ge = TcConfig<4, 256, 3, 4, false, 2>::launch(maps, outs, tp, sm_count, stream, rec);
-    else if (bn == 256) ge = TcConfig<4, 256, 2, 4, false, 1>::launch(maps, outs, tp, sm_count, stream, rec);
-    else ge = TcConfig<4, 128, 3, 4, false, 1>::launch(maps, outs, tp, sm_count, stream, rec);
+#ifdef HC_DIAGNOSTICS
+    if (cta == 2) fn = TcConfig<4, 256, 3, 4, false, 2>::launch;
+    else if (bn == 256) fn = TcConfig<4, 256, 2, 4, false, 1>::launch;
+    else fn = TcConfig<4, 128, 3, 4, false, 1>::launch;
+#else
+    return cudaErrorInvalidValue;   // float32 always runs windowed in the shipped library
+#endif
   }
-  if (ge != cudaSuccess || !cut) return ge;
+  pp.fn = fn;
+  pp.cut = cut;
+  if (cut) {
+    // Sum the parts in ascending order, add the bias, round once, store the result.
+    ReduceJob& job = pp.job;
+    job.ws = (const float*)out_base; job.C = p.C; job.bias = p.bias;
+    job.M = p.M; job.N = p.N; job.ws_ld = plan.ws_ld; job.batch = p.batch; job.parts = plan.splits;
+    job.ldc = p.ldc; job.strideC = p.strideC;
+    const int out_align = f32 ? 15 : 7;   // four results per thread: 16 bytes of float32, 8 of float16
+    job.vec_ok = (((uintptr_t)p.C & out_align) == 0 && p.ldc % 4 == 0 && p.strideC % 4 == 0) ? 1 : 0;
+    const int64_t work = p.batch * p.M * (plan.ws_ld / 4);
+    int64_t blocks = (work + 255) / 256;
+    if (blocks > 148 * 8) blocks = 148 * 8;
+    pp.reduce_blocks = (int)blocks;
+    pp.reduce_half = !f32;
+  }
+  return cudaSuccess;
+}
 
-  // Sum the parts in ascending order, add the bias, round once, store the result.
-  ReduceJob job;
-  job.ws = (const float*)out_base; job.C = p.C; job.bias = p.bias;
-  job.M = p.M; job.N = p.N; job.ws_ld = plan.ws_ld; job.batch = p.batch; job.parts = plan.splits;
-  job.ldc = p.ldc; job.strideC = p.strideC;
-  const int out_align = f32 ? 15 : 7;   // four results per thread: 16 bytes of float32, 8 of float16
-  job.vec_ok = (((uintptr_t)p.C & out_align) == 0 && p.ldc % 4 == 0 && p.strideC % 4 == 0) ? 1 : 0;
-  const int64_t work = p.batch * p.M * (plan.ws_ld / 4);
-  int64_t blocks = (work + 255) / 256;
-  if (blocks > 148 * 8) blocks = 148 * 8;
-  cudaLaunchConfig_t rcfg = {};
-  rcfg.gridDim = dim3((unsigned)blocks);
-  rcfg.blockDim = dim3(256);
-  rcfg.stream = stream;
-  cudaLaunchAttribute rattr;
-  rattr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
-  rattr.val.programmaticStreamSerializationAllowed = 1;
-  rcfg.attrs = &rattr;
-  rcfg.numAttrs = overlap_launches() ? 1 : 0;
-  cudaError_t re = f32 ? cudaLaunchKernelEx(&rcfg, splitk_reduce_kernel<false>, job)
-                       : cudaLaunchKernelEx(&rcfg, splitk_reduce_kernel<true>, job);
+cudaError_t issue_tc(const TcPrepared& pp, int sm_count, cudaStream_t stream, LaunchRecord* rec) {
+  if (rec) { *rec = LaunchRecord(); rec->kernel = HC_KERNEL_TENSOR; rec->scratch_bytes = pp.scratch_used; }
+  if (pp.pre == 1) {
+    int blocks_a = pp.pre_blocks_a;
+    void* args[3] = {(void*)&pp.rja, (void*)&pp.rjb, (void*)&blocks_a};
+    cudaError_t e = launch_elementwise((const void*)repack_f16_kernel, args, pp.pre_blocks_a + pp.pre_blocks_b, stream);
+    if (e != cudaSuccess) return e;
+    if (rec) rec->launches += 1;
+  } else if (pp.pre == 2) {
+    int blocks_a = pp.pre_blocks_a;
+    void* args[3] = {(void*)&pp.sja, (void*)&pp.sjb, (void*)&blocks_a};
+    cudaError_t e = launch_elementwise((const void*)split_tf32_kernel, args, pp.pre_blocks_a + pp.pre_blocks_b, stream);
+    if (e != cudaSuccess) return e;
+    if (rec) rec->launches += 1;
+  }
+  if (rec) rec->tiles = pp.tp.total_tiles;
+  // cudaLaunchKernelEx reports this launch's own failure; the thread's sticky-less "last error"
+  // may hold another library's earlier error and is not this launch's to report.
+  cudaError_t ge = pp.fn(pp.maps, pp.outs, pp.tp, sm_count, stream, rec);
+  if (ge != cudaSuccess || !pp.cut) return ge;
+  void* args[1] = {(void*)&pp.job};
+  cudaError_t re = launch_elementwise(pp.reduce_half ? (const void*)splitk_reduce_kernel<true>
+                                                     : (const void*)splitk_reduce_kernel<false>,
+                                      args, pp.reduce_blocks, stream);
   if (re != cudaSuccess) return re;
   if (rec) rec->launches += 1;
   return cudaSuccess;
+}
+
+}  // namespace
+
+cudaError_t launch_tc(const GemmProblem& p, cudaStream_t stream, unsigned int* status_word, void* scratch,
+                      size_t scratch_bytes, int sm_count, LaunchRecord* rec, void* const* extra_out, int n_extra,
+                      TcCache* cache, size_t* scratch_needed) {
+  if (scratch_needed) *scratch_needed = 0;
+  if (!tc_supported(p)) return cudaErrorNotSupported;
+  if (n_extra < 0 || n_extra > kMaxOut - 1 || (n_extra > 0 && !extra_out)) return cudaErrorInvalidValue;
+  if (cache && kPlanCacheEnabled) {
+    const TcKey key = make_key(p, scratch, status_word, extra_out, n_extra);
+    TcCache::Entry* victim = &cache->e[0];
+    for (auto& x : cache->e) {
+      if (x.used && memcmp(&x.key, &key, sizeof key) == 0) {
+        x.stamp = ++cache->clock;
+        return issue_tc(x.prep, sm_count, stream, rec);
+      }
+      if (!x.used ? victim->used : (victim->used && x.stamp < victim->stamp)) victim = &x;
+    }
+    victim->used = false;
+    cudaError_t e = prepare_tc(p, status_word, scratch, scratch_bytes, sm_count, extra_out, n_extra, &victim->prep,
+                               scratch_needed);
+    if (e != cudaSuccess) return e;
+    victim->key = key;
+    victim->stamp = ++cache->clock;
+    victim->used = true;
+    return issue_tc(victim->prep, sm_count, stream, rec);
+  }
+  TcPrepared prep;
+  cudaError_t e = prepare_tc(p, status_word, scratch, scratch_bytes, sm_count, extra_out, n_extra, &prep, scratch_needed);
+  if (e != cudaSuccess) return e;
+  return issue_tc(prep, sm_count, stream, rec);
 }
 
 }  // namespace hc

@@ -6,6 +6,8 @@
 #include <new>
 #include <string>
 
+#include <nvtx3/nvToolsExt.h>
+
 #include "common.cuh"
 
 struct hc_ctx {
@@ -40,6 +42,15 @@ struct hc_ctx {
   // default pool does: a backend that allocates a fresh result for every operation, as the
   // reference's do (BackendMPS.swift:538-540), would otherwise pay a driver allocation per call.
   cudaMemPool_t pool = nullptr;
+  // Prepared launches of recent tensor-core products (plan + tensor maps), see gemm_tc.cu.
+  hc::TcCache* cache = nullptr;
+  // Test hook: the next `fail_allocs` device allocations of this context report failure.
+  int fail_allocs = 0;
+  // Tracing (off by default): an NVTX range around every product's launches and a pair of events
+  // from which hc_last_elapsed_ms reads the product's device time.
+  bool tracing = false;
+  cudaEvent_t trace_begin = nullptr, trace_end = nullptr;
+  bool trace_valid = false;
 };
 
 struct hc_event {
@@ -82,25 +93,40 @@ hc_status cuda_fail(hc_ctx* ctx, cudaError_t e, const char* what) {
     if (e__ != cudaSuccess) return cuda_fail(ctx, e__, #expr);   \
   } while (0)
 
-// Grow-only device buffer owned by the context.
-hc_status ensure_buffer(hc_ctx* ctx, void** buf, size_t* have, size_t need) {
-  if (need <= *have && *buf) return HC_OK;
-  if (*buf) {
-    // Earlier work on the stream may still read the old buffer.
-    HC_CUDA_TRY(ctx, cudaStreamSynchronize(ctx->stream));
-    HC_CUDA_TRY(ctx, cudaFree(*buf));
-    *buf = nullptr;
-    *have = 0;
+// Device allocation on behalf of the context: stream-ordered from the context's pool, so that
+// neither growing a work area nor a fresh result synchronises the device.  Every allocation the
+// library makes goes through here, which is also where the allocation-failure test hook sits.
+cudaError_t ctx_malloc(hc_ctx* ctx, void** ptr, size_t bytes, cudaStream_t stream) {
+  *ptr = nullptr;
+  if (ctx->fail_allocs > 0) {
+    ctx->fail_allocs--;
+    return cudaErrorMemoryAllocation;
   }
-  size_t bytes = need ? need : 1;
-  cudaError_t e = cudaMalloc(buf, bytes);
+  cudaError_t e = ctx->pool ? cudaMallocFromPoolAsync(ptr, bytes ? bytes : 1, ctx->pool, stream)
+                            : cudaMallocAsync(ptr, bytes ? bytes : 1, stream);
   if (e != cudaSuccess) {
-    *buf = nullptr;
+    *ptr = nullptr;
     cudaGetLastError();
+  }
+  return e;
+}
+
+// Grow-only device buffer owned by the context and used on `stream` only.  The old buffer is
+// freed in stream order: work already enqueued keeps reading it, nothing waits.
+hc_status ensure_buffer(hc_ctx* ctx, void** buf, size_t* have, size_t need, cudaStream_t stream) {
+  if (need <= *have && *buf) return HC_OK;
+  const size_t bytes = need ? need : 1;
+  void* fresh = nullptr;
+  if (ctx_malloc(ctx, &fresh, bytes, stream) != cudaSuccess) {
+    // The old buffer stays: the context is as usable as before the call.
     char msg[96];
     snprintf(msg, sizeof msg, "allocation of %zu bytes failed", bytes);
     return fail(ctx, HC_ERR_ALLOCATION_FAILED, msg);
   }
+  if (*buf) {
+    if (cudaFreeAsync(*buf, stream) != cudaSuccess) cudaGetLastError();
+  }
+  *buf = fresh;
   *have = bytes;
   return HC_OK;
 }
@@ -156,6 +182,40 @@ hc_status build_problem(hc_ctx* ctx, hc_dtype dtype, int64_t count, const void* 
 // 128 x 128 tensor-core tile would be mostly padding.
 constexpr int64_t kAutoTensorMinWork = 64ll * 64 * 64;
 
+// Launches the tensor-core path, growing the context's work area when the product needs more.
+cudaError_t launch_tensor(hc_ctx* ctx, const hc::GemmProblem& p, void* const* extra, int n_extra, hc_status* st) {
+  *st = HC_OK;
+  size_t need = 0;
+  cudaError_t e = hc::launch_tc(p, ctx->stream, ctx->status_word, ctx->scratch, ctx->scratch_bytes, ctx->sm_count,
+                                &ctx->last, extra, n_extra, ctx->cache, &need);
+  if (e == cudaErrorInvalidValue && need > ctx->scratch_bytes) {
+    *st = ensure_buffer(ctx, &ctx->scratch, &ctx->scratch_bytes, need, ctx->stream);
+    if (*st != HC_OK) return cudaErrorMemoryAllocation;
+    hc::tc_cache_clear(ctx->cache);   // prepared launches point into the old work area
+    e = hc::launch_tc(p, ctx->stream, ctx->status_word, ctx->scratch, ctx->scratch_bytes, ctx->sm_count, &ctx->last,
+                      extra, n_extra, ctx->cache, &need);
+  }
+  return e;
+}
+
+struct TraceScope {
+  hc_ctx* ctx;
+  bool on;
+  TraceScope(hc_ctx* c, const hc::GemmProblem& p) : ctx(c), on(c->tracing) {
+    if (!on) return;
+    char name[96];
+    snprintf(name, sizeof name, "hc_matmul %s %lldx[%lldx%lldx%lld]", p.dtype == HC_F16 ? "f16" : "f32",
+             (long long)p.batch, (long long)p.M, (long long)p.K, (long long)p.N);
+    nvtxRangePushA(name);
+    ctx->trace_valid = cudaEventRecord(ctx->trace_begin, ctx->stream) == cudaSuccess;
+  }
+  ~TraceScope() {
+    if (!on) return;
+    if (cudaEventRecord(ctx->trace_end, ctx->stream) != cudaSuccess) ctx->trace_valid = false;
+    nvtxRangePop();
+  }
+};
+
 hc_status run_problem(hc_ctx* ctx, hc_kernel kernel, const hc::GemmProblem& p, int64_t flops) {
   ctx->last_flops = flops;
   if (p.batch == 0 || p.M == 0 || p.N == 0) {
@@ -173,19 +233,19 @@ hc_status run_problem(hc_ctx* ctx, hc_kernel kernel, const hc::GemmProblem& p, i
   }
   hc_kernel chosen = kernel;
   if (kernel == HC_KERNEL_AUTO) {
+    // Tiny products stay on the CUDA cores, in the reference's own arithmetic (separate multiply
+    // and add, k ascending: bit-identical to BackendCPU.swift:1290-1300 for every flag combination).
     const bool big = (p.M * p.N >= 64 * 64) && (p.M * p.N * p.K >= kAutoTensorMinWork) && p.K >= 32;
-    chosen = (big && hc::tc_supported(p)) ? HC_KERNEL_TENSOR : HC_KERNEL_SIMT;
+    chosen = (big && hc::tc_supported(p)) ? HC_KERNEL_TENSOR : HC_KERNEL_SIMT_EXACT;
   }
+  TraceScope trace(ctx, p);
   cudaError_t e;
   if (chosen == HC_KERNEL_TENSOR) {
     if (!hc::tc_supported(p))
       return fail(ctx, HC_ERR_NOT_IMPLEMENTED, "product too large for the tensor-core kernel's 32-bit tile coordinates");
-    const size_t need = hc::tc_scratch_bytes(p, ctx->sm_count);
-    if (need) {
-      hc_status s = ensure_buffer(ctx, &ctx->scratch, &ctx->scratch_bytes, need);
-      if (s != HC_OK) return s;
-    }
-    e = hc::launch_tc(p, ctx->stream, ctx->status_word, ctx->scratch, ctx->scratch_bytes, ctx->sm_count, &ctx->last);
+    hc_status st;
+    e = launch_tensor(ctx, p, nullptr, 0, &st);
+    if (st != HC_OK) return st;
   } else if (chosen == HC_KERNEL_SIMT || chosen == HC_KERNEL_SIMT_EXACT) {
     e = hc::launch_simt(p, chosen == HC_KERNEL_SIMT_EXACT, ctx->stream, &ctx->last);
   } else {
@@ -222,6 +282,54 @@ hc_status ctx_build_problem(hc_ctx* ctx, hc_dtype dtype, int64_t count, const vo
                             int trans_b, int trans_out, int64_t rows, int64_t inner, int64_t cols, void* out,
                             GemmProblem* p) {
   return build_problem(ctx, dtype, count, a, trans_a, b, trans_b, trans_out, rows, inner, cols, 0, cols, out, p);
+}
+hc_status ctx_device_alloc(hc_ctx* ctx, void** ptr, size_t bytes) {
+  if (ctx_malloc(ctx, ptr, bytes, ctx->stream) != cudaSuccess) {
+    char msg[96];
+    snprintf(msg, sizeof msg, "allocation of %zu bytes failed", bytes);
+    return fail(ctx, HC_ERR_ALLOCATION_FAILED, msg);
+  }
+  return HC_OK;
+}
+void ctx_device_free(hc_ctx* ctx, void* ptr) {
+  if (ptr && cudaFreeAsync(ptr, ctx->stream) != cudaSuccess) cudaGetLastError();
+}
+void ctx_count_launches(hc_ctx* ctx, int n) { ctx->launch_count += n; }
+hc_status ctx_run_batched(hc_ctx* ctx, hc_dtype dtype, int64_t count, const void* a, int trans_a, const void* b,
+                          int trans_b, int trans_out, int64_t rows, int64_t inner, int64_t cols, void* out) {
+  GemmProblem p;
+  hc_status s = build_problem(ctx, dtype, count, a, trans_a, b, trans_b, trans_out, rows, inner, cols, 0, cols, out, &p);
+  if (s != HC_OK) return s;
+  return run_problem(ctx, HC_KERNEL_AUTO, p, flop_count(count, rows, inner, cols));
+}
+hc_status ctx_run_colblock(hc_ctx* ctx, hc_dtype dtype, const void* a, int trans_a, const void* b, int trans_b,
+                           int64_t rows, int64_t inner, int64_t cols, int64_t col_begin, int64_t col_count,
+                           void* block_out, int64_t block_ld, void* const* extra, int n_extra) {
+  GemmProblem p;
+  // Planned as the block of the whole product (so that it is bitwise that block), stored where
+  // the caller wants it: `block_out` is the block's first element, `block_ld` its row pitch.
+  hc_status s = build_problem(ctx, dtype, 1, a, trans_a, b, trans_b, 0, rows, inner, cols, col_begin, col_count,
+                              block_out, &p);
+  if (s != HC_OK) return s;
+  p.C = block_out;
+  p.ldc = block_ld;
+  p.strideC = rows * block_ld;
+  ctx->last_flops = flop_count(1, rows, inner, col_count);
+  if (p.M == 0 || p.N == 0) return HC_OK;
+  if (n_extra == 0) return run_problem(ctx, HC_KERNEL_TENSOR, p, ctx->last_flops);
+  if (p.K == 0) return fail(ctx, HC_ERR_INVALID_ARGUMENT, "pushed column blocks need a non-empty contraction");
+  if (!tc_supported(p)) return fail(ctx, HC_ERR_NOT_IMPLEMENTED, "product too large for the tensor-core kernel");
+  TraceScope trace(ctx, p);
+  cudaError_t e = launch_tensor(ctx, p, extra, n_extra, &s);
+  if (s != HC_OK) return s;
+  ctx->launch_count += ctx->last.launches;
+  if (e == cudaErrorNotSupported)
+    return fail(ctx, HC_ERR_NOT_IMPLEMENTED, "result buffers must be 16-byte aligned with 16-byte row pitch");
+  if (e != cudaSuccess) {
+    cudaGetLastError();
+    return fail(ctx, HC_ERR_KERNEL_FAILED, std::string("kernel launch failed: ") + cudaGetErrorString(e));
+  }
+  return HC_OK;
 }
 }  // namespace hc
 
@@ -275,6 +383,7 @@ hc_status hc_init(int device, hc_ctx** out) {
       cudaGetLastError();
     }
   }
+  ctx->cache = hc::tc_cache_create();
   *out = ctx;
   return HC_OK;
 }
@@ -284,13 +393,16 @@ void hc_destroy(hc_ctx* ctx) {
   DeviceGuard g(ctx->device);
   cudaStreamSynchronize(ctx->stream);
   if (ctx->stream != ctx->own_stream) cudaStreamSynchronize(ctx->own_stream);
-  if (ctx->scratch) cudaFree(ctx->scratch);
+  hc::tc_cache_destroy(ctx->cache);
+  if (ctx->trace_begin) cudaEventDestroy(ctx->trace_begin);
+  if (ctx->trace_end) cudaEventDestroy(ctx->trace_end);
+  if (ctx->scratch) cudaFreeAsync(ctx->scratch, ctx->own_stream);
   for (int i = 0; i < 3; i++)
-    if (ctx->stage[i]) cudaFree(ctx->stage[i]);
+    if (ctx->stage[i]) cudaFreeAsync(ctx->stage[i], ctx->own_stream);
   for (auto& sl : ctx->slot) {
     if (sl.out_done) cudaEventSynchronize(sl.out_done);
     for (int i = 0; i < 3; i++)
-      if (sl.buf[i]) cudaFree(sl.buf[i]);
+      if (sl.buf[i]) cudaFreeAsync(sl.buf[i], ctx->own_stream);
     if (sl.in_done) cudaEventDestroy(sl.in_done);
     if (sl.product_done) cudaEventDestroy(sl.product_done);
     if (sl.out_done) cudaEventDestroy(sl.out_done);
@@ -332,11 +444,7 @@ hc_status hc_alloc(hc_ctx* ctx, size_t bytes, void** dptr) {
   DeviceGuard g(ctx->device);
   *dptr = nullptr;
   const size_t n = bytes ? bytes : 1;
-  cudaError_t e = ctx->pool ? cudaMallocFromPoolAsync(dptr, n, ctx->pool, ctx->stream)
-                            : cudaMallocAsync(dptr, n, ctx->stream);
-  if (e != cudaSuccess) {
-    *dptr = nullptr;
-    cudaGetLastError();
+  if (ctx_malloc(ctx, dptr, n, ctx->stream) != cudaSuccess) {
     char msg[96];
     snprintf(msg, sizeof msg, "allocation of %zu bytes failed", n);
     return fail(ctx, HC_ERR_ALLOCATION_FAILED, msg);
@@ -456,6 +564,7 @@ hc_status hc_event_record(hc_ctx* ctx, hc_event** out) {
   cudaError_t e = cudaEventCreate(&ev->ev);
   if (e == cudaSuccess) e = cudaEventRecord(ev->ev, ctx->stream);
   if (e != cudaSuccess) {
+    if (ev->ev) cudaEventDestroy(ev->ev);
     delete ev;
     return cuda_fail(ctx, e, "event record");
   }
@@ -556,11 +665,6 @@ hc_status hc_matmul_colblock_push(hc_ctx* ctx, hc_dtype dtype, const void* a, in
   if (p.K == 0) return fail(ctx, HC_ERR_INVALID_ARGUMENT, "pushed column blocks need a non-empty contraction");
   if (!hc::tc_supported(p))
     return fail(ctx, HC_ERR_NOT_IMPLEMENTED, "tensor-core kernel needs 16-byte aligned operands and leading dimensions");
-  const size_t need = hc::tc_scratch_bytes(p, ctx->sm_count);
-  if (need) {
-    s = ensure_buffer(ctx, &ctx->scratch, &ctx->scratch_bytes, need);
-    if (s != HC_OK) return s;
-  }
   // The block sits at the same offset in every device's copy of the result.
   const ptrdiff_t offset = (const char*)p.C - (const char*)out;
   void* extra[7];
@@ -568,8 +672,8 @@ hc_status hc_matmul_colblock_push(hc_ctx* ctx, hc_dtype dtype, const void* a, in
     if (!peer_outs[i]) return fail(ctx, HC_ERR_INVALID_ARGUMENT, "null peer result");
     extra[i] = (char*)peer_outs[i] + offset;
   }
-  cudaError_t e = hc::launch_tc(p, ctx->stream, ctx->status_word, ctx->scratch, ctx->scratch_bytes, ctx->sm_count,
-                                &ctx->last, extra, n_peers);
+  cudaError_t e = launch_tensor(ctx, p, extra, n_peers, &s);
+  if (s != HC_OK) return s;
   ctx->launch_count += ctx->last.launches;
   if (e == cudaErrorNotSupported)
     return fail(ctx, HC_ERR_NOT_IMPLEMENTED, "result buffers must be 16-byte aligned with 16-byte row pitch");
@@ -636,31 +740,48 @@ hc_status hc_ipc_close(hc_ctx* ctx, void* dptr) {
   return HC_OK;
 }
 
+namespace {
+// Argument checks of the host-buffer products, made before any copy or allocation: dtype, signs,
+// sizes that fit, pointers.  `bytes` receives the sizes of a, b and the result.
+hc_status host_product_bytes(hc_ctx* ctx, hc_dtype dtype, int64_t matrix_count, const void* a_host,
+                             const void* b_host, const void* out_host, int64_t rows, int64_t inner, int64_t cols,
+                             size_t bytes[3]) {
+  if (dtype != HC_F16 && dtype != HC_F32)
+    return fail(ctx, HC_ERR_NOT_IMPLEMENTED, "matmul: only float16 and float32 are implemented");
+  if (matrix_count < 0 || rows < 0 || inner < 0 || cols < 0)
+    return fail(ctx, HC_ERR_INVALID_ARGUMENT, "negative dimension");
+  const int64_t eb = dtype == HC_F16 ? 2 : 4;
+  int64_t na, nb, nc;
+  if (mul_overflows(rows, inner, &na) || mul_overflows(na, matrix_count, &na) || mul_overflows(na, eb, &na) ||
+      mul_overflows(inner, cols, &nb) || mul_overflows(nb, matrix_count, &nb) || mul_overflows(nb, eb, &nb) ||
+      mul_overflows(rows, cols, &nc) || mul_overflows(nc, matrix_count, &nc) || mul_overflows(nc, eb, &nc))
+    return fail(ctx, HC_ERR_INVALID_ARGUMENT, "operand size overflows int64");
+  bytes[0] = (size_t)na; bytes[1] = (size_t)nb; bytes[2] = (size_t)nc;
+  if ((bytes[0] && !a_host) || (bytes[1] && !b_host) || (bytes[2] && !out_host))
+    return fail(ctx, HC_ERR_INVALID_ARGUMENT, "null operand");
+  return HC_OK;
+}
+}  // namespace
+
 hc_status hc_batched_matmul_host(hc_ctx* ctx, hc_dtype dtype, int64_t matrix_count, const void* a_host, int trans_a,
                                  const void* b_host, int trans_b, int trans_out, int64_t rows, int64_t inner,
                                  int64_t cols, void* out_host) {
   if (!ctx) return HC_ERR_INVALID_ARGUMENT;
   std::lock_guard<std::mutex> lock(ctx->mu);
   DeviceGuard g(ctx->device);
-  if (dtype != HC_F16 && dtype != HC_F32)
-    return fail(ctx, HC_ERR_NOT_IMPLEMENTED, "matmul: only float16 and float32 are implemented");
-  if (matrix_count < 0 || rows < 0 || inner < 0 || cols < 0)
-    return fail(ctx, HC_ERR_INVALID_ARGUMENT, "negative dimension");
-  const size_t eb = dtype == HC_F16 ? 2 : 4;
-  const size_t bytes[3] = {(size_t)(matrix_count * rows * inner) * eb, (size_t)(matrix_count * inner * cols) * eb,
-                           (size_t)(matrix_count * rows * cols) * eb};
-  if ((bytes[0] && !a_host) || (bytes[1] && !b_host) || (bytes[2] && !out_host))
-    return fail(ctx, HC_ERR_INVALID_ARGUMENT, "null operand");
+  size_t bytes[3];
+  hc_status s = host_product_bytes(ctx, dtype, matrix_count, a_host, b_host, out_host, rows, inner, cols, bytes);
+  if (s != HC_OK) return s;
   for (int i = 0; i < 3; i++) {
-    hc_status s = ensure_buffer(ctx, &ctx->stage[i], &ctx->stage_bytes[i], bytes[i]);
+    s = ensure_buffer(ctx, &ctx->stage[i], &ctx->stage_bytes[i], bytes[i], ctx->stream);
     if (s != HC_OK) return s;
   }
+  hc::GemmProblem p;
+  s = build_problem(ctx, dtype, matrix_count, ctx->stage[0], trans_a, ctx->stage[1], trans_b, trans_out, rows, inner,
+                    cols, 0, cols, ctx->stage[2], &p);
+  if (s != HC_OK) return s;
   if (bytes[0]) HC_CUDA_TRY(ctx, cudaMemcpyAsync(ctx->stage[0], a_host, bytes[0], cudaMemcpyHostToDevice, ctx->stream));
   if (bytes[1]) HC_CUDA_TRY(ctx, cudaMemcpyAsync(ctx->stage[1], b_host, bytes[1], cudaMemcpyHostToDevice, ctx->stream));
-  hc::GemmProblem p;
-  hc_status s = build_problem(ctx, dtype, matrix_count, ctx->stage[0], trans_a, ctx->stage[1], trans_b, trans_out,
-                              rows, inner, cols, 0, cols, ctx->stage[2], &p);
-  if (s != HC_OK) return s;
   s = run_problem(ctx, HC_KERNEL_AUTO, p, flop_count(matrix_count, rows, inner, cols));
   if (s != HC_OK) return s;
   if (bytes[2]) HC_CUDA_TRY(ctx, cudaMemcpyAsync(out_host, ctx->stage[2], bytes[2], cudaMemcpyDeviceToHost, ctx->stream));
@@ -674,15 +795,9 @@ hc_status hc_batched_matmul_host_async(hc_ctx* ctx, hc_dtype dtype, int64_t matr
   if (!ctx) return HC_ERR_INVALID_ARGUMENT;
   std::lock_guard<std::mutex> lock(ctx->mu);
   DeviceGuard g(ctx->device);
-  if (dtype != HC_F16 && dtype != HC_F32)
-    return fail(ctx, HC_ERR_NOT_IMPLEMENTED, "matmul: only float16 and float32 are implemented");
-  if (matrix_count < 0 || rows < 0 || inner < 0 || cols < 0)
-    return fail(ctx, HC_ERR_INVALID_ARGUMENT, "negative dimension");
-  const size_t eb = dtype == HC_F16 ? 2 : 4;
-  const size_t bytes[3] = {(size_t)(matrix_count * rows * inner) * eb, (size_t)(matrix_count * inner * cols) * eb,
-                           (size_t)(matrix_count * rows * cols) * eb};
-  if ((bytes[0] && !a_host) || (bytes[1] && !b_host) || (bytes[2] && !out_host))
-    return fail(ctx, HC_ERR_INVALID_ARGUMENT, "null operand");
+  size_t bytes[3];
+  hc_status s = host_product_bytes(ctx, dtype, matrix_count, a_host, b_host, out_host, rows, inner, cols, bytes);
+  if (s != HC_OK) return s;
   if (!ctx->in_stream) {
     HC_CUDA_TRY(ctx, cudaStreamCreateWithFlags(&ctx->in_stream, cudaStreamNonBlocking));
     HC_CUDA_TRY(ctx, cudaStreamCreateWithFlags(&ctx->out_stream, cudaStreamNonBlocking));
@@ -697,28 +812,28 @@ hc_status hc_batched_matmul_host_async(hc_ctx* ctx, hc_dtype dtype, int64_t matr
   // The slot's previous product (two calls ago) must have left its buffers.
   if (sl.busy) HC_CUDA_TRY(ctx, cudaEventSynchronize(sl.out_done));
   sl.busy = false;
+  bool grew = false;
   for (int i = 0; i < 3; i++) {
     if (bytes[i] > sl.bytes[i] || !sl.buf[i]) {
-      if (sl.buf[i]) HC_CUDA_TRY(ctx, cudaFree(sl.buf[i]));
-      sl.buf[i] = nullptr;
-      sl.bytes[i] = 0;
-      cudaError_t e = cudaMalloc(&sl.buf[i], bytes[i] ? bytes[i] : 1);
-      if (e != cudaSuccess) {
-        sl.buf[i] = nullptr;
-        cudaGetLastError();
-        return fail(ctx, HC_ERR_ALLOCATION_FAILED, "staging allocation failed");
-      }
-      sl.bytes[i] = bytes[i] ? bytes[i] : 1;
+      s = ensure_buffer(ctx, &sl.buf[i], &sl.bytes[i], bytes[i], ctx->stream);
+      if (s != HC_OK) return s;
+      grew = true;
     }
   }
+  if (grew) {
+    // The staging memory was allocated in the order of the context's stream; the copy-in stream
+    // may use it only from that point on.
+    HC_CUDA_TRY(ctx, cudaEventRecord(sl.in_done, ctx->stream));
+    HC_CUDA_TRY(ctx, cudaStreamWaitEvent(ctx->in_stream, sl.in_done, 0));
+  }
+  hc::GemmProblem p;
+  s = build_problem(ctx, dtype, matrix_count, sl.buf[0], trans_a, sl.buf[1], trans_b, trans_out, rows, inner, cols, 0,
+                    cols, sl.buf[2], &p);
+  if (s != HC_OK) return s;
   if (bytes[0]) HC_CUDA_TRY(ctx, cudaMemcpyAsync(sl.buf[0], a_host, bytes[0], cudaMemcpyHostToDevice, ctx->in_stream));
   if (bytes[1]) HC_CUDA_TRY(ctx, cudaMemcpyAsync(sl.buf[1], b_host, bytes[1], cudaMemcpyHostToDevice, ctx->in_stream));
   HC_CUDA_TRY(ctx, cudaEventRecord(sl.in_done, ctx->in_stream));
   HC_CUDA_TRY(ctx, cudaStreamWaitEvent(ctx->stream, sl.in_done, 0));
-  hc::GemmProblem p;
-  hc_status s = build_problem(ctx, dtype, matrix_count, sl.buf[0], trans_a, sl.buf[1], trans_b, trans_out, rows, inner,
-                              cols, 0, cols, sl.buf[2], &p);
-  if (s != HC_OK) return s;
   s = run_problem(ctx, HC_KERNEL_AUTO, p, flop_count(matrix_count, rows, inner, cols));
   if (s != HC_OK) return s;
   HC_CUDA_TRY(ctx, cudaEventRecord(sl.product_done, ctx->stream));
@@ -899,6 +1014,37 @@ hc_status hc_selftest_bounded_wait(hc_ctx* ctx, int limit_ms) {
   return HC_OK;
 }
 
-const char* hc_version(void) { return "0.1"; }
+hc_status hc_inject_allocation_failures(hc_ctx* ctx, int count) {
+  if (!ctx || count < 0) return HC_ERR_INVALID_ARGUMENT;
+  std::lock_guard<std::mutex> lock(ctx->mu);
+  ctx->fail_allocs = count;
+  return HC_OK;
+}
+
+hc_status hc_set_tracing(hc_ctx* ctx, int on) {
+  if (!ctx) return HC_ERR_INVALID_ARGUMENT;
+  std::lock_guard<std::mutex> lock(ctx->mu);
+  DeviceGuard g(ctx->device);
+  if (on && !ctx->trace_begin) {
+    HC_CUDA_TRY(ctx, cudaEventCreate(&ctx->trace_begin));
+    HC_CUDA_TRY(ctx, cudaEventCreate(&ctx->trace_end));
+  }
+  ctx->tracing = on != 0;
+  ctx->trace_valid = false;
+  return HC_OK;
+}
+
+hc_status hc_last_elapsed_ms(hc_ctx* ctx, float* ms) {
+  if (!ctx || !ms) return HC_ERR_INVALID_ARGUMENT;
+  std::lock_guard<std::mutex> lock(ctx->mu);
+  DeviceGuard g(ctx->device);
+  if (!ctx->tracing || !ctx->trace_valid)
+    return fail(ctx, HC_ERR_INVALID_ARGUMENT, "no traced product: switch tracing on and run one first");
+  HC_CUDA_TRY(ctx, cudaEventSynchronize(ctx->trace_end));
+  HC_CUDA_TRY(ctx, cudaEventElapsedTime(ms, ctx->trace_begin, ctx->trace_end));
+  return HC_OK;
+}
+
+const char* hc_version(void) { return "0.2"; }
 
 }  // extern "C"

@@ -18,7 +18,7 @@
 //
 // The work area is shared by every call and every context of the process and is never cleared:
 // nothing in it has to start at zero, because each call first overwrites exactly the elements
-// it later reads.  Two calls that overlap on the GPU (different streams, different contexts,
+// it later reads (split operands by the pre-pass, partial sums by the product kernel's tiles).  Two calls that overlap on the GPU (different streams, different contexts,
 // different host threads on one device) would overwrite each other's split operands; callers
 // must order such calls themselves.
 #include <cstdio>
@@ -27,7 +27,8 @@
 #include "common.cuh"
 
 // Capacity of the static work area.  A product needs 8 * (rows*inner + inner*cols) bytes plus
-// alignment padding (two float32 copies of each operand).
+// alignment padding (two float32 copies of each operand), and a long contraction that is cut
+// into parts another parts * rows * cols * 4 bytes for its partial sums.
 #define HC_STATIC_SCRATCH_BYTES (32u * 1024u * 1024u)
 
 static __device__ __align__(256) unsigned char hc_static_scratch[HC_STATIC_SCRATCH_BYTES];
@@ -83,8 +84,14 @@ hc_status hc_matmul_f32_static_scratch(hc_ctx* ctx, const void* a, int trans_a, 
   if (!hc::tc_supported(p))
     return hc::ctx_fail(ctx, HC_ERR_NOT_IMPLEMENTED,
                         "tensor-core kernel needs 16-byte aligned operands and leading dimensions");
-  p.no_split = true;   // the work area is fixed: operands only, no partial matrices
-  const size_t need = hc::tc_scratch_bytes(p, hc::ctx_sm_count(ctx));
+  // Planned like the allocating path - a long contraction over few outputs is cut into parts whose
+  // float32 partial sums also live in the array - so the bits are that path's.  Only when the
+  // operands fit but the partial sums do not is the contraction kept whole.
+  size_t need = hc::tc_scratch_bytes(p, hc::ctx_sm_count(ctx));
+  if (need > (size_t)HC_STATIC_SCRATCH_BYTES) {
+    p.no_split = true;
+    need = hc::tc_scratch_bytes(p, hc::ctx_sm_count(ctx));
+  }
   if (need > (size_t)HC_STATIC_SCRATCH_BYTES) {
     char msg[160];
     snprintf(msg, sizeof msg,

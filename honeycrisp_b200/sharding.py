@@ -1,4 +1,5 @@
-"""Splitting matrix products over the GPUs of one box: one process per GPU.
+"""Splitting matrix products over the GPUs of one box: a thin layer over the group entry points
+of the C ABI (`hc_group_*`, `hc_batched_matmul_sharded`, `hc_matmul_nsplit_allgather`).
 
 The reference has no multi-device code (a `Backend` holds one device,
 Sources/Honeycrisp/BackendMPS.swift:352), so the contract of everything here is "equals the
@@ -6,159 +7,157 @@ single-device result of the same call":
 
 * `batchedMatmul` partitions over `matrixCount` - the matrices are independent
   (Sources/Honeycrisp/BackendCPU.swift:1290 loops over them), so each rank multiplies a
-  contiguous range of them and nothing is exchanged;
+  contiguous range of them and nothing is exchanged unless the caller asks for it;
 * one large `matmul` partitions over the columns of op(a)*op(b); each rank computes its column
-  block with the same tile decomposition of the contraction as the full product, and the
-  blocks are exchanged with one all-gather (NCCL through torch.distributed) only when the
-  caller wants the whole result on every device.
+  block with the tile plan of the whole product, and the blocks are exchanged either by NCCL
+  (all-gather of packed blocks + one unpack kernel) or by the product kernel itself, whose
+  epilogue stores every finished tile into every rank's result over NVLink.
 
-torch supplies device memory and the process group; the arithmetic is libhccuda's.
+Partitioning, the NCCL communicator, the buffers the ranks share and the barriers all live in the
+library; this module converts arguments.  Everything is enqueued on the backend's stream: make
+that the stream your other work uses (`backend.useStream(...)`) or call `backend.sync()` before
+touching a result from elsewhere.  A host channel is needed once, to hand rank 0's 128-byte group
+id to the other ranks; `DeviceGroup.fromTorchDistributed` uses a torch.distributed process group
+for that and for nothing else.
 """
 from __future__ import annotations
 
-from typing import Callable, Optional, Tuple
+import ctypes
+from typing import Optional, Tuple
 
-import torch
-import torch.distributed as dist
-
-from .backend import CUDABackend, DType, _as_dtype
+from . import _lib as L
+from .backend import CUDABackend, CUDAData, DType, NotImplementedByBackend, _HC_DTYPE, _as_dtype
 
 
 def shardBatch(matrixCount: int, rank: int, world: int) -> Tuple[int, int]:
     """Contiguous range (begin, count) of the matrices rank `rank` of `world` multiplies.
     Ranges differ in size by at most one and cover [0, matrixCount) in rank order."""
-    if world < 1 or not (0 <= rank < world) or matrixCount < 0:
+    b, c = ctypes.c_int64(), ctypes.c_int64()
+    if L.load().hc_shard_range(int(matrixCount), int(world), int(rank), ctypes.byref(b), ctypes.byref(c)) != L.HC_OK:
         raise ValueError("bad shard request")
-    base, extra = divmod(matrixCount, world)
-    begin = rank * base + min(rank, extra)
-    return begin, base + (1 if rank < extra else 0)
+    return b.value, c.value
 
 
-def columnBlock(cols: int, rank: int, world: int, align: int = 256) -> Tuple[int, int]:
-    """Column range (begin, count) of rank `rank`.  Boundaries fall on multiples of `align`
-    (the kernel's tile width, which also keeps every block's first element 16-byte aligned
-    for TMA) as long as that leaves every rank a block; otherwise on multiples of 8."""
-    if world < 1 or not (0 <= rank < world) or cols < 0:
+def columnBlock(cols: int, rank: int, world: int) -> Tuple[int, int]:
+    """Column range (begin, count) of rank `rank`.  Boundaries fall on multiples of 256 (the
+    kernel's tile width, which also keeps every block's first element 16-byte aligned) as long
+    as that leaves every rank a block; otherwise on multiples of 8."""
+    b, c = ctypes.c_int64(), ctypes.c_int64()
+    if L.load().hc_column_block(int(cols), int(world), int(rank), ctypes.byref(b), ctypes.byref(c)) != L.HC_OK:
         raise ValueError("bad column-block request")
-    for unit in (align, 8, 1):
-        units = -(-cols // unit)
-        if units >= world or unit == 1:
-            b, c = shardBatch(units, rank, world)
-            begin = min(b * unit, cols)
-            end = min((b + c) * unit, cols)
-            return begin, end - begin
-    raise AssertionError
+    return b.value, c.value
 
 
-def batchedMatmulSharded(backend: Optional[CUDABackend], rank: int, world: int, matrixCount: int,
-                         a: torch.Tensor, transA: bool, b: torch.Tensor, transB: bool, transOut: bool,
-                         rows: int, inner: int, cols: int, dtype, out: Optional[torch.Tensor] = None,
-                         compute: Optional[Callable] = None) -> Tuple[torch.Tensor, Tuple[int, int]]:
-    """This rank's share of a batched product.  `a`, `b` hold ALL matrices (or at least this
-    rank's range at its global position); the result holds only this rank's matrices.
-    No collective.  Returns (out_shard, (begin, count))."""
-    dt = _as_dtype(dtype)
-    begin, count = shardBatch(matrixCount, rank, world)
-    a3 = a.reshape(matrixCount, -1)
-    b3 = b.reshape(matrixCount, -1)
-    a_sh = a3[begin:begin + count]
-    b_sh = b3[begin:begin + count]
-    if out is None:
-        out = torch.empty(count * rows * cols, dtype=a.dtype, device=a.device)
-    if count:
-        if compute is not None:
-            compute(count, a_sh, transA, b_sh, transB, transOut, rows, inner, cols, dt, out)
-        else:
-            od = backend.wrap(out.data_ptr(), out.numel() * out.element_size(), out)
-            backend.batchedMatmul(count, a_sh, transA, b_sh, transB, transOut, rows, inner, cols, dt, out=od,
-                                  mark=False)
-    return out, (begin, count)
+def _ptr(x) -> int:
+    """Device address of a CUDAData, a CUDA torch tensor or a raw integer address."""
+    if isinstance(x, int):
+        return x
+    if isinstance(x, CUDAData):
+        return x.ptr
+    if hasattr(x, "data_ptr"):
+        if not x.is_cuda or not x.is_contiguous():
+            raise ValueError("torch operands must be contiguous CUDA tensors")
+        return x.data_ptr()
+    raise TypeError(f"unsupported operand type {type(x)!r}")
 
 
-def matmulColumnSplit(backend: Optional[CUDABackend], rank: int, world: int, a: torch.Tensor, transA: bool,
-                      b: torch.Tensor, transB: bool, rows: int, inner: int, cols: int, dtype,
-                      gather: bool = True, group=None, compute: Optional[Callable] = None) -> torch.Tensor:
-    """op(a)*op(b) with the columns split over `world` ranks; every rank holds all of `a` and
-    `b` (only its column block of `b` is read).
+class DeviceGroup:
+    """One rank of a group of `world` backends, one per GPU (processes, or threads of one process)."""
 
-    Each rank writes its block in place into a full-size row-major result.  With `gather`, the
-    blocks are then exchanged: packed to a contiguous [rows, block] buffer, all-gathered, and
-    unpacked, so that every rank ends with the complete product.  Returns the [rows, cols]
-    result (complete if `gather`, otherwise valid only in this rank's columns).
-    """
-    dt = _as_dtype(dtype)
-    out = torch.empty((rows, cols), dtype=a.dtype, device=a.device)
-    begin, count = columnBlock(cols, rank, world)
-    if count:
-        if compute is not None:
-            compute(a, transA, b, transB, rows, inner, cols, begin, count, dt, out)
-        else:
-            od = backend.wrap(out.data_ptr(), out.numel() * out.element_size(), out)
-            backend.matmulColumnBlock(a, transA, b, transB, False, rows, inner, cols, begin, count, dt, out=od)
-    if not gather or world == 1:
-        return out
-    if backend is not None:
-        # The product was enqueued on the backend's stream; the collective runs on torch's.
-        backend.sync()
-    widths = [columnBlock(cols, r, world)[1] for r in range(world)]
-    wmax = max(widths)
-    send = torch.zeros((rows, wmax), dtype=a.dtype, device=a.device)
-    send[:, :count] = out[:, begin:begin + count]
-    recv_flat = torch.empty((world * rows, wmax), dtype=a.dtype, device=a.device)
-    dist.all_gather_into_tensor(recv_flat, send, group=group)
-    recv = recv_flat.view(world, rows, wmax)
-    for r in range(world):
-        if r == rank or widths[r] == 0:
-            continue
-        rb = columnBlock(cols, r, world)[0]
-        out[:, rb:rb + widths[r]] = recv[r, :, :widths[r]]
-    return out
+    def __init__(self, backend: CUDABackend, rank: int, world: int, uniqueId: Optional[bytes] = None):
+        self.backend, self.rank, self.world = backend, int(rank), int(world)
+        self._lib = backend._lib
+        g = ctypes.c_void_p()
+        if world > 1 and (uniqueId is None or len(uniqueId) != 128):
+            raise ValueError("a group of more than one rank needs rank 0's 128-byte id")
+        backend._check(self._lib.hc_group_init(backend._ctx, self.world, self.rank,
+                                               ctypes.c_char_p(uniqueId) if uniqueId else None, ctypes.byref(g)))
+        self._g = g.value
 
+    @staticmethod
+    def uniqueId() -> bytes:
+        """Rank 0 calls this and sends the bytes to the other ranks over any host channel."""
+        buf = ctypes.create_string_buffer(128)
+        st = L.load().hc_group_unique_id(buf)
+        if st != L.HC_OK:
+            raise NotImplementedByBackend("no usable NCCL library: " + L.load().hc_status_string(st).decode())
+        return bytes(buf.raw)
 
-class FusedColumnSplit:
-    """A product split over columns whose exchange is fused into the kernel's epilogue.
-
-    Every rank owns a full-size result buffer that the other ranks map (CUDA IPC).  Each rank
-    computes its column block and its epilogue stores every finished tile into all `world`
-    buffers (peer stores over NVLink), so after the ranks have synchronised and passed a
-    barrier each of them holds the complete product - there is no all-gather, no packing, and
-    the transfer overlaps the remaining tiles' arithmetic.  Set up once per shape, reuse per call.
-    """
-
-    def __init__(self, backend: CUDABackend, rank: int, world: int, rows: int, cols: int, dtype, group=None):
-        self.backend, self.rank, self.world, self.group = backend, rank, world, group
-        self.rows, self.cols, self.dtype = rows, cols, _as_dtype(dtype)
-        nbytes = rows * cols * self.dtype.byteSize
-        self.out = backend.sharedAllocate(nbytes)
-        handle = backend.ipcExport(self.out)
-        handles = [None] * world
+    @classmethod
+    def fromTorchDistributed(cls, backend: CUDABackend, group=None) -> "DeviceGroup":
+        """Rank and world size of an initialised torch.distributed group; the id travels through it."""
+        import torch.distributed as dist
+        rank, world = dist.get_rank(group), dist.get_world_size(group)
+        box = [cls.uniqueId() if rank == 0 and world > 1 else None]
         if world > 1:
-            dist.all_gather_object(handles, handle, group=group)
-        self.peers = [backend.ipcOpen(h, nbytes) for r, h in enumerate(handles) if r != rank and h is not None]
+            dist.broadcast_object_list(box, src=dist.get_global_rank(group, 0) if group is not None else 0, group=group)
+        return cls(backend, rank, world, box[0])
 
-    def matmul(self, a, transA: bool, b, transB: bool, inner: int, wait: bool = True):
-        """Enqueue this rank's block (and its pushes).  With `wait`, also synchronise and pass
-        the group barrier, after which `self.out` holds the complete product on every rank."""
-        begin, count = columnBlock(self.cols, self.rank, self.world)
-        if count:
-            self.backend.matmulColumnBlockPush(a, transA, b, transB, False, self.rows, inner, self.cols, begin,
-                                               count, self.dtype, self.out, self.peers)
-        if wait:
-            self.finish()
-        return self.out
-
-    def finish(self):
-        self.backend.sync()
-        if self.world > 1:
-            dist.barrier(group=self.group)
+    # -- plumbing ----------------------------------------------------------------------------
 
     def close(self):
-        self.backend.sync()
-        if self.world > 1:
-            dist.barrier(group=self.group)   # nobody unmaps while a peer may still be storing
-        for p in self.peers:
-            p.free()
-        self.peers = []
-        if self.world > 1:
-            dist.barrier(group=self.group)   # nobody frees while a peer still has it mapped
-        self.out.free()
+        """Collective: every rank's close meets in the communicator's teardown."""
+        if getattr(self, "_g", None):
+            self._lib.hc_group_destroy(self._g)
+            self._g = None
+
+    def __del__(self):
+        # Not closed here: destruction is collective and must not happen at an arbitrary moment.
+        pass
+
+    def setTimeout(self, milliseconds: int):
+        self.backend._check(self._lib.hc_group_set_timeout_ms(self._g, int(milliseconds)))
+
+    def barrier(self):
+        """Enqueue a flag barrier on the backend's stream (returns without waiting)."""
+        self.backend._check(self._lib.hc_group_barrier(self._g))
+
+    def selftestMissingPeer(self, limit_ms: int = 50):
+        self.backend._check(self._lib.hc_group_selftest_missing_peer(self._g, int(limit_ms)))
+
+    def resultAllocate(self, byteCount: int) -> CUDAData:
+        """Collective: a result buffer on every rank that the other ranks can store into."""
+        ptr = ctypes.c_void_p()
+        self.backend._check(self._lib.hc_group_result_alloc(self._g, int(byteCount), ctypes.byref(ptr)))
+        d = CUDAData(self.backend, ptr.value, int(byteCount), owns=False)
+        d._kind = "group"
+        d._group = self
+        return d
+
+    def resultFree(self, data: CUDAData):
+        """Collective."""
+        if data.ptr and self._g:
+            self.backend._check(self._lib.hc_group_result_free(self._g, data.ptr))
+        data.ptr = 0
+
+    # -- the products ------------------------------------------------------------------------
+
+    def shard(self, matrixCount: int) -> Tuple[int, int]:
+        return shardBatch(matrixCount, self.rank, self.world)
+
+    def batchedMatmulSharded(self, matrixCount: int, aShard, transA: bool, bShard, transB: bool, transOut: bool,
+                             rows: int, inner: int, cols: int, dtype, out, gather: bool = False):
+        """This rank's share of `batchedMatmul` over `matrixCount` matrices.  `aShard`/`bShard`
+        hold the matrices of `self.shard(matrixCount)`.  Without `gather`, `out` receives those
+        matrices' results and nothing is exchanged; with it, `out` is the whole batch's result
+        buffer on every rank and the ranges are all-gathered in place (collective)."""
+        dt = dtype if isinstance(dtype, DType) else _as_dtype(dtype)
+        st = self._lib.hc_batched_matmul_sharded(self._g, _HC_DTYPE[dt], matrixCount, _ptr(aShard), 1 if transA else 0,
+                                                 _ptr(bShard), 1 if transB else 0, 1 if transOut else 0, rows, inner,
+                                                 cols, _ptr(out), 1 if gather else 0)
+        if st != L.HC_OK:
+            self.backend._check(st)
+        return out
+
+    def matmulColumnSplit(self, a, transA: bool, b, transB: bool, rows: int, inner: int, cols: int, dtype, out,
+                          fused: bool = False):
+        """op(a)*op(b) with the columns split over the ranks; collective.  Every rank holds all of
+        `a` and `b` and ends with the complete [rows, cols] product in `out`.  `fused` moves the
+        exchange into the product kernel's epilogue (peer stores); `out` must then come from
+        `resultAllocate`."""
+        dt = dtype if isinstance(dtype, DType) else _as_dtype(dtype)
+        st = self._lib.hc_matmul_nsplit_allgather(self._g, _HC_DTYPE[dt], _ptr(a), 1 if transA else 0, _ptr(b),
+                                                  1 if transB else 0, rows, inner, cols, _ptr(out), 1 if fused else 0)
+        if st != L.HC_OK:
+            self.backend._check(st)
+        return out

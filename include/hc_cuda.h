@@ -45,7 +45,8 @@ typedef enum hc_status {
   HC_ERR_NOT_IMPLEMENTED = 3,
   HC_ERR_INVALID_ARGUMENT = 4, /* the reference traps these earlier with #alwaysAssert
                                   (Sources/Honeycrisp/Linalg.swift:52-59,90-104) */
-  HC_ERR_TIMEOUT = 5,          /* a bounded device-side wait gave up; context stays usable */
+  HC_ERR_TIMEOUT = 5,          /* a bounded device-side wait gave up (inside a kernel, or for
+                                  another rank of a device group); context stays usable */
   HC_ERR_CUDA = 6              /* any other CUDA runtime/driver error; see hc_last_error */
 } hc_status;
 
@@ -149,8 +150,15 @@ void hc_event_destroy(hc_event* ev);
  * The products may use the context's work area, a device buffer that only grows (to the
  * largest need seen: float32 operands split into TF32 parts, float16 operands repacked to an
  * aligned pitch, and at most 256 MiB of float32 partial sums when a long contraction over few
- * outputs is cut into parts); growing it is the only allocation a product makes.  Results do
- * not depend on how the work is tiled, cut or scheduled: the same call gives the same bits. */
+ * outputs is cut into parts); growing it is the only allocation a product makes, and it is
+ * stream-ordered from the context's pool (no device-wide synchronisation).  A CUDA graph that
+ * captured products is invalid once a later, larger product has grown the work area: run the
+ * largest product once before capturing.  The context remembers how it prepared its most recent
+ * products (tile plan, tensor maps), so repeating a product on the same buffers costs the host
+ * little more than the launch.  Results do not depend on how the work is tiled, cut or
+ * scheduled: the same call gives the same bits.  Under HC_KERNEL_AUTO products too small for a
+ * tensor-core tile run on the CUDA cores in the reference's own arithmetic (separate multiply and
+ * add, k ascending: bit-identical to BackendCPU.swift:1290-1300). */
 hc_status hc_matmul(hc_ctx* ctx, hc_dtype dtype, const void* a, int trans_a, const void* b,
                     int trans_b, int trans_out, int64_t rows, int64_t inner, int64_t cols,
                     void* out);
@@ -266,6 +274,78 @@ hc_status hc_ipc_export(hc_ctx* ctx, void* dptr, void* handle_out);
 hc_status hc_ipc_open(hc_ctx* ctx, const void* handle, void** dptr);
 hc_status hc_ipc_close(hc_ctx* ctx, void* dptr);
 
+/* ---- products split over the GPUs of one box ------------------------------------------------ */
+/* No counterpart in the reference, which has no multi-device code (a Backend holds one device,
+ * Sources/Honeycrisp/BackendMPS.swift:352); the contract of every entry point is "equals the
+ * single-device result of the same call".  They extend the two primitives of
+ * Sources/Honeycrisp/Backend.swift:650-669.
+ *
+ * A group is one rank's handle on `world` contexts, one per GPU (at most 8).  Ranks are
+ * processes (one per GPU) or threads of one process (one host driving several devices); either
+ * way every rank creates its own context and calls hc_group_init with the same 128-byte id,
+ * which rank 0 makes with hc_group_unique_id and hands to the others over any host channel.
+ * The calls marked "collective" must be made by every rank, in the same order.  NCCL is looked
+ * up at run time (a copy already loaded into the process, else HC_NCCL_LIB, else libnccl.so.2
+ * on the library path); without it groups of one rank still work. */
+typedef struct hc_group hc_group;
+#define HC_GROUP_ID_BYTES 128
+hc_status hc_group_unique_id(void* id_out);
+hc_status hc_group_init(hc_ctx* ctx, int world, int rank, const void* id, hc_group** out); /* collective */
+void hc_group_destroy(hc_group* g);                                                        /* collective */
+int hc_group_rank(hc_group* g);
+int hc_group_world(hc_group* g);
+/* Limit of every device-side wait for another rank (default 10 000 ms).  When it runs out the
+ * waiting kernel returns, and hc_check_device_status / hc_event_wait report HC_ERR_TIMEOUT. */
+hc_status hc_group_set_timeout_ms(hc_group* g, int ms);
+
+/* The partitions, as pure host arithmetic (no device, no group): rank `rank` of `world` owns
+ * matrices [begin, begin+count) of a batch - contiguous ranges that differ by at most one - and
+ * columns [begin, begin+count) of a split product, with block boundaries on multiples of 256
+ * columns (the kernel's tile width) while that leaves every rank a block, else on multiples of 8. */
+hc_status hc_shard_range(int64_t total, int world, int rank, int64_t* begin, int64_t* count);
+hc_status hc_column_block(int64_t cols, int world, int rank, int64_t* begin, int64_t* count);
+
+/* This rank's share of Backend.batchedMatmul over `matrix_count` matrices: `a_shard` and
+ * `b_shard` hold the matrices of hc_shard_range(matrix_count, world, rank), back to back.
+ * gather == 0: `out` receives the results of those matrices; nothing is exchanged.
+ * gather != 0: `out` is the result buffer of the WHOLE batch on every rank; each rank writes its
+ * range in place and the ranges are exchanged with one ncclAllGather (one ncclBroadcast per rank
+ * when the ranges differ in size) - the batch dimension is contiguous, nothing is re-laid.
+ * Collective when gather != 0. */
+hc_status hc_batched_matmul_sharded(hc_group* g, hc_dtype dtype, int64_t matrix_count, const void* a_shard,
+                                    int trans_a, const void* b_shard, int trans_b, int trans_out,
+                                    int64_t rows, int64_t inner, int64_t cols, void* out, int gather);
+
+/* One large Backend.matmul split over the columns of op(a)*op(b); every rank holds all of `a`
+ * and `b` (it reads only its column block of `b`) and ends with the complete [rows, cols]
+ * product in `out`.  Each block is computed with the tile plan of the whole product, so the
+ * result equals hc_batched_matmul_ex(HC_KERNEL_TENSOR) bit for bit.  Collective.
+ * fused == 0: blocks are computed into a packed buffer the group owns (it grows to rows*cols
+ *   elements), exchanged with ncclAllGather, and one kernel moves them into `out`.
+ * fused != 0: there is no collective and no staging: the product kernel's epilogue stores every
+ *   finished tile into `out` on EVERY rank (peer stores over NVLink), so the exchange overlaps
+ *   the remaining tiles.  `out` must come from hc_group_result_alloc.  The call enqueues a flag
+ *   barrier before the product (no rank overwrites a peer's result while work enqueued earlier
+ *   on that peer's context may still read it) and one after it (when it has passed on a rank's
+ *   stream, every rank's tiles have landed there).  Work that reads the result on another
+ *   stream must be ordered against the context's stream by the caller. */
+hc_status hc_matmul_nsplit_allgather(hc_group* g, hc_dtype dtype, const void* a, int trans_a, const void* b,
+                                     int trans_b, int64_t rows, int64_t inner, int64_t cols, void* out,
+                                     int fused);
+/* A result buffer of `bytes` on every rank that the other ranks can store into (mapped through
+ * CUDA IPC between processes, through peer access inside one process).  Collective, as is the
+ * matching free, which waits until no rank can still be storing into the buffer. */
+hc_status hc_group_result_alloc(hc_group* g, size_t bytes, void** dptr);
+hc_status hc_group_result_free(hc_group* g, void* dptr);
+/* Enqueues a flag barrier on the context's stream: work enqueued after it starts when every rank
+ * has completed the work it enqueued before its own call.  Returns without waiting.  Collective. */
+hc_status hc_group_barrier(hc_group* g);
+/* Failure-path self-test that harms nothing: a barrier in which this rank does not announce
+ * itself, which is what a rank sees whose peer never arrives.  After `limit_ms` (1..1000) the
+ * wait gives up; the next hc_check_device_status reports HC_ERR_TIMEOUT, and the group stays
+ * usable.  In a group of more than one rank every rank must call it. */
+hc_status hc_group_selftest_missing_peer(hc_group* g, int limit_ms);
+
 /* float32 `transOut(op(a) * op(b))` on the tensor cores WITHOUT allocating: no counterpart in
  * the reference.  It exists for hosts that must not allocate device memory from inside a
  * library call - a framework whose caching allocator already owns the device, or a loop that
@@ -273,8 +353,11 @@ hc_status hc_ipc_close(hc_ctx* ctx, void* dptr);
  * 3xTF32 split operands is a fixed array inside the library (hc_static_scratch_capacity()
  * bytes, held by every GPU that loads the library); a product needs about
  * 8 * (rows*inner + inner*cols) bytes of it, and a larger one is refused with
- * HC_ERR_INVALID_ARGUMENT (hc_last_error says how much was needed).  Same result, bit for
- * bit, as hc_batched_matmul_ex(ctx, HC_KERNEL_TENSOR, HC_F32, 1, ...).
+ * HC_ERR_INVALID_ARGUMENT (hc_last_error says how much was needed).  The result is, bit for
+ * bit, that of hc_batched_matmul_ex(ctx, HC_KERNEL_TENSOR, HC_F32, 1, ...) whenever that call's
+ * whole work area fits into the array - including the float32 partial sums of a long contraction
+ * over few outputs, which it cuts into parts.  When the operands fit but those partial sums do
+ * not, the contraction runs uncut: same tolerance (1e-5), different summation order.
  * The first call on each device looks up the array's device address; make that call outside
  * stream capture.  All calls in the process share the one array: calls that can overlap on
  * the GPU (other streams or contexts on the same device) must be ordered by the caller. */
@@ -317,6 +400,16 @@ hc_status hc_check_device_status(hc_ctx* ctx);
  * `limit_ms` (1..1000) the wait gives up, sets the status word and the kernel returns; the next
  * hc_check_device_status / hc_event_wait reports HC_ERR_TIMEOUT and the context stays usable. */
 hc_status hc_selftest_bounded_wait(hc_ctx* ctx, int limit_ms);
+/* Test hook for the allocation-failure paths: the next `count` device allocations this context
+ * makes (results of hc_alloc, growth of a work area or staging buffer) fail as if the device were
+ * out of memory.  Whatever the context held before such a failure stays valid. */
+hc_status hc_inject_allocation_failures(hc_ctx* ctx, int count);
+/* Tracing, off by default: while on, every product is wrapped in an NVTX range
+ * ("hc_matmul f16 1x[8192x8192x8192]", visible to Nsight tools; the reference labels its command
+ * buffers the same way, Sources/Honeycrisp/BackendMPS.swift:2698) and in a pair of events, from
+ * which hc_last_elapsed_ms returns the device time of the most recent product (it waits for it). */
+hc_status hc_set_tracing(hc_ctx* ctx, int on);
+hc_status hc_last_elapsed_ms(hc_ctx* ctx, float* ms);
 /* Library version, "major.minor". */
 const char* hc_version(void);
 

@@ -33,6 +33,22 @@ def test_library_exports_every_declared_symbol():
     assert set(L.SIGNATURES) <= set(declared_functions())
 
 
+def test_diagnostics_build_exports_the_same_interface():
+    lib = L.load(diagnostics=True)
+    for name in declared_functions():
+        assert hasattr(lib, name)
+
+
+def test_partitions_are_host_arithmetic():
+    lib = L.load()
+    b, c = ctypes.c_int64(), ctypes.c_int64()
+    assert lib.hc_shard_range(64, 8, 3, ctypes.byref(b), ctypes.byref(c)) == L.HC_OK and (b.value, c.value) == (24, 8)
+    assert lib.hc_column_block(16384, 8, 7, ctypes.byref(b), ctypes.byref(c)) == L.HC_OK and (b.value, c.value) == (14336, 2048)
+    assert lib.hc_shard_range(64, 8, 8, ctypes.byref(b), ctypes.byref(c)) == L.HC_ERR_INVALID_ARGUMENT
+    assert lib.hc_group_init(None, 1, 0, None, None) == L.HC_ERR_INVALID_ARGUMENT
+    assert lib.hc_group_world(None) == 0 and lib.hc_group_rank(None) == -1
+
+
 def test_header_compiles_as_plain_c(tmp_path):
     src = tmp_path / "t.c"
     src.write_text('#include "hc_cuda.h"\nint main(void) { hc_launch_info i; (void)i; return (int)HC_OK; }\n')
@@ -42,7 +58,7 @@ def test_header_compiles_as_plain_c(tmp_path):
 
 def test_status_strings_and_version():
     lib = L.load()
-    assert lib.hc_version().decode() == "0.1"
+    assert lib.hc_version().decode() == "0.2"
     seen = {lib.hc_status_string(i).decode() for i in range(7)}
     assert len(seen) == 7
     assert lib.hc_status_string(99).decode() == "unknown status"

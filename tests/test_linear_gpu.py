@@ -31,8 +31,10 @@ def test_fused_bias_is_bit_identical_to_matmul_then_add_small(be, rows, n_in, n_
     assert np.array_equal(got.view(np.uint8), ref.broadcast_add_rows(h, b, rows, n_out).view(np.uint8))
     want = ref.linear_forward(x, w, b, rows, n_in, n_out)
     from honeycrisp_b200 import _lib
-    if dtype == np.float16 and be.lastLaunchInfo()["kernel"] == _lib.HC_KERNEL_SIMT:
-        assert np.array_equal(got.view(np.uint16), want.view(np.uint16))      # CUDA-core product = CPU loop
+    if dtype == np.float16 and be.lastLaunchInfo()["kernel"] == _lib.HC_KERNEL_SIMT_EXACT:
+        # CUDA-core product in the reference's arithmetic = the CPU loop (float32 without flags is a
+        # library sgemm in the reference, so only float16 is bit-comparable end to end)
+        assert np.array_equal(got.view(np.uint16), want.view(np.uint16))
     else:
         assert ref.rel_frobenius(got, want) < (1e-5 if dtype == np.float32 else 2e-3)
     none = be.linearForward(x, w, None, rows, n_in, n_out, dtype).onCPU(dtype)[: rows * n_out]

@@ -231,7 +231,7 @@ def test_misaligned_operands_are_repacked_for_the_tensor_cores(be):
     # the default dispatch sends tiny products to the CUDA-core kernel, bit-identical to the CPU loop
     A, B = random_operands(4, 1, 30, 17, 29, np.float16)
     res, a_st, b_st = run(be, 1, A, B, False, False, False, np.float16, kernel=0)
-    assert be.lastLaunchInfo()["kernel"] == K().HC_KERNEL_SIMT
+    assert be.lastLaunchInfo()["kernel"] == K().HC_KERNEL_SIMT_EXACT
     assert np.array_equal(res.view(np.uint16), ref.matmul(a_st, False, b_st, False, False, 30, 17, 29).view(np.uint16))
 
 

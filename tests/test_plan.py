@@ -11,9 +11,9 @@ F16, F32 = 0, 1
 SMS = 148
 
 
-def plan(dtype, count, rows, inner, cols, ta=False, tb=False, to=False, sms=SMS):
+def plan(dtype, count, rows, inner, cols, ta=False, tb=False, to=False, sms=SMS, diagnostics=False):
     info = L.PlanInfo()
-    st = L.load().hc_plan_product(dtype, count, int(ta), int(tb), int(to), rows, inner, cols, sms, ctypes.byref(info))
+    st = L.load(diagnostics).hc_plan_product(dtype, count, int(ta), int(tb), int(to), rows, inner, cols, sms, ctypes.byref(info))
     assert st == L.HC_OK, st
     return info
 
@@ -53,17 +53,22 @@ def test_long_contractions_over_few_outputs_are_cut():
 
 
 def test_switches(monkeypatch):
+    """The HC_TC_* switches exist in the diagnostics build only; the shipped library ignores them."""
+    dplan = lambda *a, **k: plan(*a, diagnostics=True, **k)
     monkeypatch.setenv("HC_TC_SPLITS", "1")
-    assert plan(F16, 1, 512, 4096, 512, tb=True).parts == 1
+    assert dplan(F16, 1, 512, 4096, 512, tb=True).parts == 1
+    assert plan(F16, 1, 512, 4096, 512, tb=True).parts >= 2
     monkeypatch.setenv("HC_TC_SPLITS", "5")
-    assert plan(F16, 1, 512, 4096, 512, tb=True).parts == 5
+    assert dplan(F16, 1, 512, 4096, 512, tb=True).parts == 5
     monkeypatch.delenv("HC_TC_SPLITS")
     for forced, tile in {1: (256, 512), 2: (256, 256), 3: (128, 256), 4: (128, 128), 5: (256, 128), 6: (256, 64)}.items():
         monkeypatch.setenv("HC_TC_SHAPE", str(forced))
-        p = plan(F16, 1, 1024, 4096, 2048, tb=True)
+        p = dplan(F16, 1, 1024, 4096, 2048, tb=True)
         assert (p.tile_m, p.tile_n) == tile, forced
     monkeypatch.setenv("HC_TC_SHAPE", "1")
-    assert plan(F16, 1, 1024, 512, 512, tb=True).tile_n != 512    # a shape the product does not admit is ignored
+    assert dplan(F16, 1, 1024, 512, 512, tb=True).tile_n != 512    # a shape the product does not admit is ignored
+    monkeypatch.setenv("HC_TC_SHAPE", "6")
+    assert plan(F16, 1, 8192, 8192, 8192, tb=True).tile_n == 512    # shipped library: no switches
 
 
 def test_every_part_has_work_and_the_parts_cover_the_contraction():

@@ -1,6 +1,11 @@
-"""Host-side sharding logic on CPU: partition arithmetic, and a world_size-2 gloo run in which
-the per-rank arithmetic is done by the CPU oracle (injected; the shipped default is the CUDA
-backend)."""
+"""Host-side sharding logic on CPU.
+
+The partitions are host arithmetic inside the C library (hc_shard_range, hc_column_block), so
+they are checked here without a GPU.  The world_size-2 run uses gloo ranks in which the per-rank
+arithmetic is the CPU oracle's and the exchange is gloo's, laid out exactly as the library lays it
+out on GPUs (blocks packed rank after rank, all-gathered, then moved into the row-major result);
+it pins the claim the GPU path rests on: sharded = single-device result, bit for bit.
+"""
 import os
 import socket
 
@@ -10,7 +15,7 @@ import torch
 import torch.distributed as dist
 import torch.multiprocessing as mp
 
-from honeycrisp_b200.sharding import batchedMatmulSharded, columnBlock, matmulColumnSplit, shardBatch
+from honeycrisp_b200.sharding import columnBlock, shardBatch
 from oracle import reference_cpu as ref
 
 
@@ -40,6 +45,14 @@ def test_column_blocks_cover_and_align(cols, world):
         assert all(columnBlock(cols, r, world)[1] == cols // world for r in range(world))
 
 
+def test_bad_requests_are_rejected():
+    for bad in ((4, 2, 2), (4, -1, 2), (-1, 0, 2), (4, 0, 0)):
+        with pytest.raises(ValueError):
+            shardBatch(*bad)
+        with pytest.raises(ValueError):
+            columnBlock(*bad)
+
+
 def _free_port():
     s = socket.socket()
     s.bind(("127.0.0.1", 0))
@@ -48,39 +61,47 @@ def _free_port():
     return p
 
 
-def _oracle_batched(count, a, ta, b, tb, to, rows, inner, cols, dt, out):
-    res = ref.batched_matmul(count, a.numpy(), ta, b.numpy(), tb, to, rows, inner, cols, library_fast_path=False)
-    out.copy_(torch.from_numpy(res))
-
-
-def _oracle_colblock(a, ta, b, tb, rows, inner, cols, begin, count, dt, out):
-    A, B = ref.logical_operands(1, a.numpy(), ta, b.numpy(), tb, rows, inner, cols)
-    blk = np.ascontiguousarray(B[0][:, begin:begin + count])
-    res = ref.matmul(np.ascontiguousarray(A[0]), False, blk, False, False, rows, inner, count, library_fast_path=False)
-    out[:, begin:begin + count] = torch.from_numpy(res.reshape(rows, count))
-
-
 def _worker(rank, world, port, ret):
     os.environ["MASTER_ADDR"] = "127.0.0.1"
     os.environ["MASTER_PORT"] = str(port)
     dist.init_process_group("gloo", rank=rank, world_size=world)
     try:
         rng = np.random.default_rng(5)
-        # batched: 5 matrices [6,7]x[7,4]^T over 2 ranks, no collective on the data path
-        a = torch.from_numpy(rng.standard_normal((5, 6, 7)).astype(np.float32))
-        b = torch.from_numpy(rng.standard_normal((5, 4, 7)).astype(np.float32))
-        shard, (begin, count) = batchedMatmulSharded(None, rank, world, 5, a, False, b, True, False, 6, 7, 4,
-                                                     np.float32, compute=_oracle_batched)
-        full = ref.batched_matmul(5, a.numpy(), False, b.numpy(), True, False, 6, 7, 4).reshape(5, -1)
-        ok1 = np.array_equal(shard.numpy().reshape(count, -1), full[begin:begin + count])
-        # column split of [9,11]x[11,21] with all-gather
-        a2 = torch.from_numpy(rng.standard_normal((9, 11)).astype(np.float32))
-        b2 = torch.from_numpy(rng.standard_normal((11, 21)).astype(np.float32))
-        c = matmulColumnSplit(None, rank, world, a2, False, b2, False, 9, 11, 21, np.float32, gather=True,
-                              compute=_oracle_colblock)
-        full2 = ref.matmul(a2.numpy(), False, b2.numpy(), False, False, 9, 11, 21, library_fast_path=False)
-        ok2 = np.array_equal(c.numpy().reshape(-1), full2)
-        ret[rank] = (ok1, ok2)
+        # batched: 5 matrices [6,7]x[7,4]^T over 2 ranks; each rank holds only its shard of the
+        # operands; the ranges (3 and 2 matrices) are then exchanged, one broadcast per rank
+        a = rng.standard_normal((5, 6, 7)).astype(np.float32)
+        b = rng.standard_normal((5, 4, 7)).astype(np.float32)
+        begin, count = shardBatch(5, rank, world)
+        mine = ref.batched_matmul(count, a[begin:begin + count], False, b[begin:begin + count], True, False, 6, 7, 4,
+                                  library_fast_path=False).reshape(count, -1)
+        full = ref.batched_matmul(5, a, False, b, True, False, 6, 7, 4).reshape(5, -1)
+        ok1 = np.array_equal(mine, full[begin:begin + count])
+        whole = torch.zeros((5, 24))
+        whole[begin:begin + count] = torch.from_numpy(mine)
+        for r in range(world):
+            rb, rc = shardBatch(5, r, world)
+            part = whole[rb:rb + rc].contiguous()
+            dist.broadcast(part, src=r)
+            whole[rb:rb + rc] = part
+        ok2 = np.array_equal(whole.numpy(), full)
+        # column split of [9,11]x[11,21]: blocks computed on their own, packed rank after rank,
+        # gathered, moved into the row-major result
+        a2 = rng.standard_normal((9, 11)).astype(np.float32)
+        b2 = rng.standard_normal((11, 21)).astype(np.float32)
+        widths = [columnBlock(21, r, world)[1] for r in range(world)]
+        begins = [columnBlock(21, r, world)[0] for r in range(world)]
+        blk = np.ascontiguousarray(b2[:, begins[rank]:begins[rank] + widths[rank]])
+        block = ref.matmul(a2, False, blk, False, False, 9, 11, widths[rank], library_fast_path=False)
+        packed = [torch.zeros(9 * w) for w in widths]
+        packed[rank] = torch.from_numpy(block.reshape(-1).copy())
+        for r in range(world):
+            dist.broadcast(packed[r], src=r)
+        out = np.zeros((9, 21), dtype=np.float32)
+        for r in range(world):
+            out[:, begins[r]:begins[r] + widths[r]] = packed[r].numpy().reshape(9, widths[r])
+        full2 = ref.matmul(a2, False, b2, False, False, 9, 11, 21, library_fast_path=False)
+        ok3 = np.array_equal(out.reshape(-1), full2)
+        ret[rank] = (ok1, ok2, ok3)
     finally:
         dist.destroy_process_group()
 
@@ -91,4 +112,4 @@ def test_two_rank_gloo_sharding_equals_single_device_result():
     mgr = mp.Manager()
     ret = mgr.dict()
     mp.spawn(_worker, args=(world, port, ret), nprocs=world, join=True)
-    assert dict(ret) == {0: (True, True), 1: (True, True)}
+    assert dict(ret) == {0: (True, True, True), 1: (True, True, True)}

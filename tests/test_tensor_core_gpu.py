@@ -22,6 +22,17 @@ def be():
     b.close()
 
 
+@pytest.fixture(scope="module")
+def dbe():
+    """A context on the diagnostics build of the library, where HC_TC_SHAPE / HC_TC_SPLITS force
+    the planner's choices (read at every launch); the shipped library has no such switches."""
+    from honeycrisp_b200 import CUDABackend
+    b = CUDABackend(0, diagnostics=True)
+    yield b
+    b.checkDeviceStatus()
+    b.close()
+
+
 def TENSOR():
     from honeycrisp_b200 import _lib
     return _lib.HC_KERNEL_TENSOR
@@ -65,7 +76,8 @@ TILE_SHAPES = {1: (256, 512), 2: (256, 256), 3: (128, 256), 4: (128, 128), 5: (2
 
 
 @pytest.mark.parametrize("forced", sorted(TILE_SHAPES))
-def test_half_every_tile_shape(be, forced, monkeypatch):
+def test_half_every_tile_shape(dbe, forced, monkeypatch):
+    be = dbe
     monkeypatch.setenv("HC_TC_SHAPE", str(forced))
     M, Kd, N, cnt = 520, 2056, 1096, 2   # ragged in every dimension, long enough for the 512-wide tiles
     used = set()
@@ -80,7 +92,8 @@ def test_half_every_tile_shape(be, forced, monkeypatch):
 
 
 @pytest.mark.parametrize("forced", [2, 3, 4, 5, 6])
-def test_float_every_tile_shape(be, forced, monkeypatch):
+def test_float_every_tile_shape(dbe, forced, monkeypatch):
+    be = dbe
     monkeypatch.setenv("HC_TC_SHAPE", str(forced))
     monkeypatch.setenv("HC_TC_SPLITS", "1")
     M, Kd, N, cnt = 520, 264, 1096, 2
@@ -128,10 +141,11 @@ def test_half_cut_contraction(be, shape):
 
 
 @pytest.mark.parametrize("parts", [1, 2, 5, 16, 64])
-def test_half_forced_cuts_agree(be, parts, monkeypatch):
+def test_half_forced_cuts_agree(dbe, parts, monkeypatch):
     """HC_TC_SPLITS forces the number of parts (1: never cut).  Every cut gives the float64
     product within the float16 tolerance, and a result that float16 represents exactly
     (small integers) is identical whatever the cut."""
+    be = dbe
     monkeypatch.setenv("HC_TC_SPLITS", str(parts))
     M, Kd, N = 264, 2120, 200
     A, B = random_operands(3, 1, M, Kd, N, np.float16, scale=0.25)

@@ -48,6 +48,26 @@ def test_static_scratch_product_matches_allocating_product_twice():
             ref = ref.T if to else ref
             err = np.linalg.norm(got.astype(np.float64) - ref.reshape(-1)) / np.linalg.norm(ref)
             assert err < 1e-5
+        # A long contraction over few outputs: the allocating path cuts it into parts and sums float32
+        # partial matrices; here those live in the static area too, so the bits still agree.
+        rows, inner, cols = 128, 8192, 128
+        plan = _lib.PlanInfo()
+        assert lib.hc_plan_product(_lib.HC_F32, 1, 0, 0, 0, rows, inner, cols, 148, ctypes.byref(plan)) == _lib.HC_OK
+        assert plan.parts > 1 and 8 * (rows * inner + inner * cols) + plan.workspace_bytes <= cap
+        a = (rng.random(rows * inner, dtype=np.float32) * 2 - 1)
+        b = (rng.random(inner * cols, dtype=np.float32) * 2 - 1)
+        a_d, b_d = be.collection(a, np.float32), be.collection(b, np.float32)
+        want = be.matmul(a_d, False, b_d, False, False, rows, inner, cols, np.float32,
+                         kernel=_lib.HC_KERNEL_TENSOR).onCPU(np.float32)
+        assert be.lastLaunchInfo()["tiles"] > 1
+        out = be.allocate(rows * cols * 4)
+        st = lib.hc_matmul_f32_static_scratch(be._ctx, a_d.ptr, 0, b_d.ptr, 0, 0, rows, inner, cols, out.ptr)
+        assert st == _lib.HC_OK, lib.hc_last_error(be._ctx).decode()
+        got = out.onCPU(np.float32)
+        be.checkDeviceStatus()
+        assert np.array_equal(got.view(np.uint32), want.view(np.uint32)), "cut contraction"
+        ref = a.reshape(rows, inner).astype(np.float64) @ b.reshape(inner, cols).astype(np.float64)
+        assert np.linalg.norm(got.astype(np.float64) - ref.reshape(-1)) / np.linalg.norm(ref) < 1e-5
         # A product whose split operands do not fit is refused, with the sizes in the message.
         big = 4096
         st = lib.hc_matmul_f32_static_scratch(be._ctx, a_d.ptr, 0, b_d.ptr, 0, 0, big, big, big, out.ptr)
