@@ -89,6 +89,7 @@ SIGNATURES = {
     "hc_static_scratch_capacity": (_sz, []),
     "hc_status_string": (ctypes.c_char_p, [_int]),
     "hc_last_error": (ctypes.c_char_p, [_vp]),
+    "hc_copy_last_error": (_sz, [_vp, ctypes.c_char_p, _sz]),
     "hc_last_launch_info": (_int, [_vp, ctypes.POINTER(LaunchInfo)]),
     "hc_plan_product": (_int, [_int, _i64, _int, _int, _int, _i64, _i64, _i64, _int, ctypes.POINTER(PlanInfo)]),
     "hc_launch_count": (_i64, [_vp]),

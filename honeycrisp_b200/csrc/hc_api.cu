@@ -871,6 +871,15 @@ const char* hc_status_string(hc_status s) {
 
 const char* hc_last_error(hc_ctx* ctx) { return ctx ? ctx->last_error.c_str() : ""; }
 
+size_t hc_copy_last_error(hc_ctx* ctx, char* buf, size_t capacity) {
+  if (!ctx || !buf || capacity == 0) return 0;
+  std::lock_guard<std::mutex> lock(ctx->mu);
+  const size_t n = ctx->last_error.size() < capacity - 1 ? ctx->last_error.size() : capacity - 1;
+  memcpy(buf, ctx->last_error.data(), n);
+  buf[n] = 0;
+  return n;
+}
+
 hc_status hc_last_launch_info(hc_ctx* ctx, hc_launch_info* out) {
   if (!ctx || !out) return HC_ERR_INVALID_ARGUMENT;
   std::lock_guard<std::mutex> lock(ctx->mu);

@@ -371,6 +371,9 @@ size_t hc_static_scratch_capacity(void);
 const char* hc_status_string(hc_status s);
 /* Text of the last failure on this context (thread-unsafe snapshot; empty if none). */
 const char* hc_last_error(hc_ctx* ctx);
+/* The same text copied into `buf` (NUL-terminated, at most `capacity` bytes) under the context's
+ * lock, for hosts whose threads call into one context concurrently; returns the length copied. */
+size_t hc_copy_last_error(hc_ctx* ctx, char* buf, size_t capacity);
 /* Geometry of the most recent product launched on this context. */
 hc_status hc_last_launch_info(hc_ctx* ctx, hc_launch_info* out);
 /* How the tensor-core path would tile a product on a device with `sm_count` SMs: tile shape,
