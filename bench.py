@@ -6,7 +6,12 @@
 One step = one pass of the headline workload: float16 GEMM M=N=K=8192, fp32 accumulate, over
 all four transA/transB combinations (four products, 4.398 TFLOP).  With N > 1 (launched by
 torchrun, one rank per GPU) every rank runs that step on its own operands - independent
-products, nothing exchanged - and the value is the aggregate over the box.
+products, nothing exchanged - and `value` is the aggregate over the box (replicas: weak scaling).
+The configurations that SHARD are timed in the same run and reported under `sharded`: the
+batched attention-score product split over the batch (no collective) and the float32 16384^3
+product split over columns, exchanged by NCCL all-gather and by the fused epilogue push; each
+with the whole problem timed on rank 0 alone in the same run, the same way, as its 1-GPU time.
+At N = 1 `configs` holds the single-GPU roofline blocks of the other configurations.
 
 Prints ONE JSON line on stdout (rank 0).  `value` is timed with operands resident in HBM;
 `e2e` is the same step from pinned host buffers through the C ABI (inputs copied to the device once
@@ -40,6 +45,8 @@ FLOPS_PER_GEMM = 2.0 * N_DIM ** 3
 # kernel, from the latest ncu capture summarised under profiles/ (931 MB read + 122 MB written).
 # The algorithmic minimum is 3 * 8192^2 * 2 = 403 MB.
 NCU_DRAM_BYTES_PER_LAUNCH = 1.053e9
+NCU_DRAM_SOURCE = ("ncu capture of tc_gemm_kernel<2,256,4,8,false,2,2,1,false> (256x512 pair tile) at 8192^3, "
+                   "profiles/tc_gemm_f16_8192.md; not measured by this run")
 
 
 def load_peaks():
@@ -392,9 +399,21 @@ def run_ours(args):
     launch_ms = statistics.mean(x.elapsed_time(y) for x, y in evs)
     info = be.lastLaunchInfo()
 
-    multi_extra = None
-    if args.all_configs and use_dist:
-        multi_extra = sharded_configs(be, stream, rank, world)   # collective: every rank takes part
+    # Sustained regime: the same step for about a second and a half, so that the power cap has
+    # settled (the default 20-100 steps end within the burst), with the vendor library's product on
+    # the same operands timed the same way right after it.
+    sustained = None
+    if not args.quick:
+        sustained = sustained_leg(be, stream, step, a, b, out, barrier, use_dist, world)
+
+    link = link_probe(stream, use_dist, world)
+
+    sharded = None
+    if not args.quick:
+        sharded = sharded_configs(be, stream, rank, world)   # collective: every rank takes part
+    single = None
+    if world == 1 and not args.quick:
+        single = single_gpu_configs(be, stream)
 
     if rank != 0:
         if use_dist:
@@ -414,7 +433,8 @@ def run_ours(args):
         "frac_of_burst": achieved / peaks["burst"], "frac_of_sustained": achieved / peaks["sustained"],
         "frac_of_nominal_2250": achieved / 2250.0,
         "single_launch_tflops": FLOPS_PER_GEMM / (launch_ms * 1e-3) / 1e12,
-        "traffic": NCU_DRAM_BYTES_PER_LAUNCH,
+        "traffic": NCU_DRAM_BYTES_PER_LAUNCH, "traffic_source": NCU_DRAM_SOURCE,
+        "traffic_algorithmic_bytes": 3 * N_DIM * N_DIM * 2,
         "algorithmic_flops_per_launch": FLOPS_PER_GEMM,
     }
 
@@ -434,7 +454,8 @@ def run_ours(args):
         "warmup": max(args.warmup, 3), "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "f16 in, f32 accumulate", "data": "synthetic",
         "config": {"workload": WORKLOAD, "products_per_step": 4, "l2": "inputs larger than L2 (384 MB per product)",
-                   "kernel": info, "per_rank": "each rank runs the step on its own operands; no collective"},
+                   "kernel": info, "per_rank": "each rank runs the step on its own operands; no collective "
+                   "(replicas - the configurations that shard are under `sharded`)"},
         "clocks": clocks,
         # The step as a Tensor program issues it: the step's inputs (A, B) go from pinned host memory to
         # the device once, the four products use them, all four results are read back to pinned host
@@ -450,8 +471,18 @@ def run_ours(args):
         "cpu_baseline": cpu_baseline,
         "cpu_sgemm_baseline": cpu_sgemm,
     }
-    if args.all_configs:
-        line["extra"] = other_configs(be, stream, rank, world) if world == 1 else multi_extra
+    line["e2e"]["link_probe"] = link
+    line["e2e"]["note"] = ("bound by the host link: the four results are 0.54 GB per step and rank, and every GPU of "
+                           "this box hangs off the same host memory (link_probe: plain pinned-memory copies, all ranks "
+                           "at once)")
+    if sustained:
+        line["sustained"] = sustained
+    if sharded:
+        line["sharded"] = sharded
+    if single:
+        line["configs"] = single
+    if args.all_configs and world == 1:
+        line["extra"] = other_configs(be, stream, rank, world)
     emit(line)
     if use_dist:
         dist.destroy_process_group()
@@ -676,107 +707,238 @@ def probe_one(args, spec):
             "tflops": 2.0 * cnt * M * N * K / ms / 1e9, "kernel": info}
 
 
-def sharded_configs(be, stream, rank, world):
-    """Configurations 3 and 5 split over the ranks (strong scaling): batch-sharded Q.K^T with no
-    collective; float32 16384^3 split over columns, exchanged by NCCL all-gather and by the fused
-    epilogue push.  Device-timed, max over ranks."""
-    import numpy as np
+def _max_over_ranks(x, use_dist):
     import torch
+    if not use_dist:
+        return float(x)
     import torch.distributed as dist
+    t = torch.tensor([x], device="cuda", dtype=torch.float64)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t.item())
 
-    from honeycrisp_b200.sharding import FusedColumnSplit, batchedMatmulSharded, matmulColumnSplit, shardBatch
 
-    def max_ms(ms):
-        t = torch.tensor([ms], device="cuda", dtype=torch.float64)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        return float(t.item())
+def sustained_leg(be, stream, step, a, b, out, barrier, use_dist, world):
+    import torch
+    n = N_DIM
+    steps = 400
+    barrier()
+    e0 = torch.cuda.Event(enable_timing=True); e1 = torch.cuda.Event(enable_timing=True)
+    e0.record(stream)
+    for _ in range(steps):
+        step()
+    e1.record(stream)
+    barrier()
+    ms = _max_over_ranks(e0.elapsed_time(e1), use_dist)
+    res = {"steps": steps, "ms_per_step": ms / steps, "tflops": FLOPS_PER_GEMM * 4 * steps * world / ms / 1e9,
+           "timed_s": ms / 1e3}
+    views = [(a.t() if ta else a, b.t() if tb else b) for ta, tb in COMBOS]
 
-    def timed(fn, iters):
-        fn()
-        torch.cuda.synchronize(); dist.barrier()
+    def lib_step():
+        for x, y in views:
+            torch.matmul(x, y, out=out)
+
+    for _ in range(3):
+        lib_step()
+    barrier()
+    e0.record(stream)
+    for _ in range(steps):
+        lib_step()
+    e1.record(stream)
+    barrier()
+    lms = _max_over_ranks(e0.elapsed_time(e1), use_dist)
+    res["library_same_run"] = {"what": "torch.matmul (cuBLAS) on the same operands, same four layouts, same loop",
+                               "ms_per_step": lms / steps, "tflops": FLOPS_PER_GEMM * 4 * steps * world / lms / 1e9}
+    res["ratio_to_library"] = lms / ms
+    peaks = load_peaks()
+    res["frac_of_sustained_peak"] = res["tflops"] / world / peaks["sustained"]
+    return res
+
+
+def link_probe(stream, use_dist, world):
+    """Plain copies between pinned host memory and the device, every rank at once: what the host
+    side of the box can deliver per GPU, the ceiling of any end-to-end number."""
+    import torch
+    nbytes = 512 << 20
+    host = torch.empty(nbytes, dtype=torch.uint8).pin_memory()
+    dev = torch.empty(nbytes, dtype=torch.uint8, device="cuda")
+    out = {"bytes": nbytes, "concurrent_ranks": world}
+    for name, (dst, src) in (("h2d_gbs_per_gpu", (dev, host)), ("d2h_gbs_per_gpu", (host, dev))):
+        dst.copy_(src, non_blocking=True)
+        torch.cuda.synchronize()
+        if use_dist:
+            import torch.distributed as dist
+            dist.barrier()
         e0 = torch.cuda.Event(enable_timing=True); e1 = torch.cuda.Event(enable_timing=True)
         e0.record(stream)
-        for _ in range(iters):
-            fn()
+        for _ in range(4):
+            dst.copy_(src, non_blocking=True)
         e1.record(stream)
-        torch.cuda.synchronize(); dist.barrier()
-        return max_ms(e0.elapsed_time(e1) / iters)
+        torch.cuda.synchronize()
+        ms = _max_over_ranks(e0.elapsed_time(e1), use_dist)
+        out[name] = 4 * nbytes / ms / 1e6
+    return out
 
-    res = {}
-    g = torch.Generator(device="cuda").manual_seed(2)
-    begin, count = shardBatch(64, rank, world)
-    q = torch.randn((64, 2048, 128), generator=g, device="cuda").half()
-    k = torch.randn((64, 2048, 128), generator=g, device="cuda").half()
-    o = torch.empty(count * 2048 * 2048, device="cuda", dtype=torch.float16)
-    shard = lambda: batchedMatmulSharded(be, rank, world, 64, q, False, k, True, False, 2048, 128, 2048,
-                                         np.float16, out=o)
-    ms = timed(shard, 20)
-    res["c3_batch_sharded"] = {"ms": ms, "box_tflops": 2 * 64 * 2048 * 2048 * 128 / ms / 1e9, "collective": "none"}
-    # The shards are tens of microseconds: replay 20 of them from a CUDA graph so the host's
-    # launch rate is out of the picture.
-    try:
-        graph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(graph, stream=stream):
-            for _ in range(20):
-                shard()
-        ms = timed(graph.replay, 5) / 20
-        res["c3_batch_sharded_graph"] = {"ms": ms, "box_tflops": 2 * 64 * 2048 * 2048 * 128 / ms / 1e9,
-                                         "collective": "none", "launches_per_replay": 20}
-        del graph
-    except Exception as e:  # capture is an optimisation of the measurement, not of the product
-        res["c3_batch_sharded_graph"] = {"error": str(e)[:200]}
-    del o
-    # The whole batch on rank 0 alone, in the same run and measured the same way: the
-    # denominator of the strong-scaling ratio on this box.
-    if world > 1:
-        one_ms = 0.0
-        if rank == 0:
-            try:
-                o1 = torch.empty(64 * 2048 * 2048, device="cuda", dtype=torch.float16)
-                whole = lambda: batchedMatmulSharded(be, 0, 1, 64, q, False, k, True, False, 2048, 128, 2048,
-                                                     np.float16, out=o1)
-                whole()
-                graph = torch.cuda.CUDAGraph()
-                with torch.cuda.graph(graph, stream=stream):
-                    for _ in range(20):
-                        whole()
-                graph.replay()
-                torch.cuda.synchronize()
-                e0 = torch.cuda.Event(enable_timing=True); e1 = torch.cuda.Event(enable_timing=True)
-                e0.record(stream)
-                for _ in range(5):
-                    graph.replay()
-                e1.record(stream)
-                torch.cuda.synchronize()
-                one_ms = e0.elapsed_time(e1) / 100
-                del graph, o1
-            except Exception:
-                one_ms = 0.0
+
+def _device_timed(fn, iters, stream, use_dist, warm=3):
+    import torch
+    for _ in range(warm):
+        fn()
+    torch.cuda.synchronize()
+    if use_dist:
+        import torch.distributed as dist
         dist.barrier()
-        one_ms = max_ms(one_ms)
-        sharded = res.get("c3_batch_sharded_graph", {}).get("ms")
-        if one_ms > 0 and sharded:
-            res["c3_one_gpu_same_run_graph"] = {"ms": one_ms, "speedup_of_sharding": one_ms / sharded}
+    e0 = torch.cuda.Event(enable_timing=True); e1 = torch.cuda.Event(enable_timing=True)
+    e0.record(stream)
+    for _ in range(iters):
+        fn()
+    e1.record(stream)
+    torch.cuda.synchronize()
+    if use_dist:
+        import torch.distributed as dist
+        dist.barrier()
+    return _max_over_ranks(e0.elapsed_time(e1) / iters, use_dist)
+
+
+def sharded_configs(be, stream, rank, world):
+    """The configurations that shard (strong scaling over the ranks), through the group entry points
+    of the C ABI, host-launched, device-timed, max over ranks:
+      c3        float16 batched Q.K^T (64 x [2048,128].[2048,128]^T) split over the batch, no collective;
+      c5_nccl   float32 16384^3 split over columns, blocks exchanged by ncclAllGather + one unpack kernel;
+      c5_fused  the same split with the exchange in the product kernel's epilogue (peer stores).
+    Each comes with the whole problem on rank 0 alone, same run, same loop: the 1-GPU time."""
+    import numpy as np
+    import torch
+
+    from honeycrisp_b200.sharding import DeviceGroup, columnBlock
+
+    use_dist = world > 1
+    grp = DeviceGroup.fromTorchDistributed(be) if use_dist else DeviceGroup(be, 0, 1)
+    one = DeviceGroup(be, 0, 1)                       # the same entry points on one device
+    peaks = load_peaks()
+    res = {"world": world, "how": "host-launched through hc_batched_matmul_sharded / hc_matmul_nsplit_allgather, "
+                                  "CUDA events on the context's stream, max over ranks; one_gpu_ms: the whole problem "
+                                  "on rank 0 alone in this run, the same way"}
+
+    # ---- C3
+    cnt, rows, inner, cols = 64, 2048, 128, 2048
+    begin, count = grp.shard(cnt)
+    g = torch.Generator(device="cuda").manual_seed(2)
+    q = torch.randn((cnt, rows, inner), generator=g, device="cuda").half()
+    k = torch.randn((cnt, cols, inner), generator=g, device="cuda").half()
+    o = torch.empty(max(count, 1) * rows * cols, device="cuda", dtype=torch.float16)
+    qp, kp, op = q[begin:].data_ptr(), k[begin:].data_ptr(), o.data_ptr()
+    shard = lambda: grp.batchedMatmulSharded(cnt, qp, False, kp, True, False, rows, inner, cols, np.float16, op)
+    ms = _device_timed(shard, 200, stream, use_dist, warm=10)
+    flops = 2.0 * cnt * rows * cols * inner
+    algo_bytes = 2 * cnt * rows * inner * 2 + cnt * rows * cols * 2
+    c3 = {"ms": ms, "box_tflops": flops / ms / 1e9, "matrices_per_rank": count, "collective": "none",
+          "box_algorithmic_gbs": algo_bytes / ms / 1e6,
+          "roofline": {"bound": "hbm", "achieved": algo_bytes / world / ms / 1e6, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                       "frac": algo_bytes / world / ms / 1e6 / peaks["hbm_gbs"], "per": "GPU"}}
+    del o
+    one_ms = 0.0
+    if rank == 0:
+        o1 = torch.empty(cnt * rows * cols, device="cuda", dtype=torch.float16)
+        q0, k0, o1p = q.data_ptr(), k.data_ptr(), o1.data_ptr()
+        whole = lambda: one.batchedMatmulSharded(cnt, q0, False, k0, True, False, rows, inner, cols, np.float16, o1p)
+        one_ms = _device_timed(whole, 50, stream, False, warm=5)
+        del o1
+    one_ms = _max_over_ranks(one_ms, use_dist)
+    c3["one_gpu_ms"] = one_ms
+    c3["speedup_over_one_gpu"] = one_ms / ms
+    res["c3"] = c3
     del q, k
+
+    # ---- C5
     n = 16384
     g = torch.Generator(device="cuda").manual_seed(4)
     a = torch.rand((n, n), generator=g, device="cuda") * 2 - 1
     b = torch.rand((n, n), generator=g, device="cuda") * 2 - 1
-    holder = {}
+    flops = 2.0 * n ** 3
+    gathered = (world - 1) / world * n * n * 4           # bytes every GPU receives
+    c = torch.empty((n, n), device="cuda")
+    ap, bp, cp = a.data_ptr(), b.data_ptr(), c.data_ptr()
+    nccl = lambda: grp.matmulColumnSplit(ap, False, bp, False, n, n, n, np.float32, cp)
+    ms = _device_timed(nccl, 5, stream, use_dist, warm=2)
+    res["c5_nccl"] = {"ms": ms, "box_tflops_effective": flops / ms / 1e9, "gathered_bytes_per_gpu": gathered}
+    # this rank's block alone (what the exchange is added to)
+    cb, cw = columnBlock(n, rank, world)
+    be_out = be.wrap(c.data_ptr(), n * n * 4, c)
+    block_only = lambda: be.matmulColumnBlock(a, False, b, False, False, n, n, n, cb, cw, np.float32, out=be_out)
+    bms = _device_timed(block_only, 5, stream, use_dist, warm=2)
+    res["c5_nccl"]["block_product_ms"] = bms
+    res["c5_nccl"]["exchange_ms"] = max(ms - bms, 0.0)
+    if world > 1 and ms > bms:
+        res["c5_nccl"]["nvlink_gbs_in_per_gpu"] = gathered / (ms - bms) / 1e6
+    nccl_result = c
+    fused_out = grp.resultAllocate(n * n * 4)
+    fp = fused_out.ptr
+    fused = lambda: grp.matmulColumnSplit(ap, False, bp, False, n, n, n, np.float32, fp, fused=True)
+    ms = _device_timed(fused, 5, stream, use_dist, warm=2)
+    be.sync()
+    nccl()
+    be.sync()
+    same = bool(torch.equal(fused_out.asTorch((n, n), torch.float32), nccl_result))
+    res["c5_fused"] = {"ms": ms, "box_tflops_effective": flops / ms / 1e9, "gathered_bytes_per_gpu": gathered,
+                       "equals_nccl_result": same,
+                       "includes": "entry and exit flag barriers of every call"}
+    if world > 1:
+        res["c5_fused"]["nvlink_gbs_in_per_gpu_overlapped"] = gathered / ms / 1e6
+    grp.resultFree(fused_out)
+    one_ms = 0.0
+    if rank == 0:
+        whole = lambda: one.matmulColumnSplit(ap, False, bp, False, n, n, n, np.float32, cp)
+        one_ms = _device_timed(whole, 3, stream, False, warm=1)
+    one_ms = _max_over_ranks(one_ms, use_dist)
+    for key in ("c5_nccl", "c5_fused"):
+        res[key]["one_gpu_ms"] = one_ms
+        res[key]["speedup_over_one_gpu"] = one_ms / res[key]["ms"]
+        res[key]["roofline"] = {"bound": "tensor", "achieved": res[key]["box_tflops_effective"] / world,
+                                "peak": peaks["burst"] / 6, "unit": "TFLOP/s (effective; 3xTF32 does 3x the MMA work at half the bf16 rate)",
+                                "frac": res[key]["box_tflops_effective"] / world / (peaks["burst"] / 6), "per": "GPU"}
+    del a, b, c
+    be.checkDeviceStatus()
+    one.close()
+    grp.close()
+    return res
 
-    def nccl_path():
-        holder["c"] = matmulColumnSplit(be, rank, world, a, False, b, False, n, n, n, np.float32, gather=True)
 
-    ms = timed(nccl_path, 2)
-    res["c5_colsplit_nccl_allgather"] = {"ms": ms, "box_tflops_effective": 2 * n ** 3 / ms / 1e9}
-    fused = FusedColumnSplit(be, rank, world, n, n, np.float32)
-    ms = timed(lambda: fused.matmul(a, False, b, False, n, wait=False), 2)
-    fused.finish()
-    same = bool(torch.equal(fused.out.asTorch((n, n), torch.float32), holder["c"]))
-    res["c5_colsplit_fused_push"] = {"ms": ms, "box_tflops_effective": 2 * n ** 3 / ms / 1e9,
-                                     "equals_nccl_result": same}
-    holder.clear()
-    fused.close()
+def single_gpu_configs(be, stream):
+    """Roofline blocks of configurations 1, 3 and 5 on one GPU (host-launched, device-timed)."""
+    import numpy as np
+    import torch
+    peaks = load_peaks()
+    res = {}
+    g = torch.Generator(device="cuda").manual_seed(0)
+    a = torch.rand((1024, 1024), generator=g, device="cuda"); b = torch.rand((1024, 1024), generator=g, device="cuda")
+    o = torch.empty((1024, 1024), device="cuda"); od = be.wrap(o.data_ptr(), o.numel() * 4, o)
+    ms = _device_timed(lambda: be.matmul(a, False, b, False, False, 1024, 1024, 1024, np.float32, out=od, mark=False),
+                       200, stream, False, warm=10)
+    tf = 2 * 1024 ** 3 / ms / 1e9
+    res["c1_f32_1024"] = {"ms": ms, "tflops_effective": tf,
+                          "roofline": {"bound": "latency (64 tiles, one wave); against the 3xTF32 tensor ceiling for scale",
+                                       "achieved": tf, "peak": peaks["burst"] / 6, "unit": "TFLOP/s", "frac": tf / (peaks["burst"] / 6)}}
+    q = torch.randn((64, 2048, 128), generator=g, device="cuda").half(); k = torch.randn((64, 2048, 128), generator=g, device="cuda").half()
+    o = torch.empty((64, 2048, 2048), device="cuda", dtype=torch.float16); od = be.wrap(o.data_ptr(), o.numel() * 2, o)
+    ms = _device_timed(lambda: be.batchedMatmul(64, q, False, k, True, False, 2048, 128, 2048, np.float16, out=od, mark=False),
+                       50, stream, False, warm=5)
+    nbytes = 2 * 64 * 2048 * 128 * 2 + 64 * 2048 * 2048 * 2
+    res["c3_f16_batched_qkT"] = {"ms": ms, "tflops": 2 * 64 * 2048 * 2048 * 128 / ms / 1e9,
+                                 "roofline": {"bound": "hbm", "achieved": nbytes / ms / 1e6, "peak": peaks["hbm_gbs"],
+                                              "unit": "GB/s", "frac": nbytes / ms / 1e6 / peaks["hbm_gbs"],
+                                              "algorithmic_bytes": nbytes}}
+    del q, k, o
+    n = 16384
+    a = torch.rand((n, n), generator=g, device="cuda") * 2 - 1
+    b = torch.rand((n, n), generator=g, device="cuda") * 2 - 1
+    o = torch.empty((n, n), device="cuda"); od = be.wrap(o.data_ptr(), o.numel() * 4, o)
+    ms = _device_timed(lambda: be.matmul(a, False, b, False, False, n, n, n, np.float32, out=od, mark=False), 3, stream, False, warm=1)
+    tf = 2 * n ** 3 / ms / 1e9
+    res["c5_f32_16384_3xtf32"] = {"ms": ms, "tflops_effective": tf,
+                                  "roofline": {"bound": "tensor", "achieved": tf, "peak": peaks["burst"] / 6,
+                                               "unit": "TFLOP/s effective (3xTF32: 3x the MMA work at half the bf16 rate)",
+                                               "frac": tf / (peaks["burst"] / 6)}}
+    del a, b, o
     be.checkDeviceStatus()
     return res
 
@@ -809,6 +971,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--all-configs", action="store_true")
+    ap.add_argument("--quick", action="store_true", help="headline step only: no sustained leg, no sharded/other configurations")
     ap.add_argument("--probe", default=None, help="M,K,N[,count]: run one product a few times (profiler target)")
     ap.add_argument("--dtype", choices=["f16", "f32"], default="f16")
     ap.add_argument("--flags", default="0,1", help="transA,transB for --probe")

@@ -707,6 +707,103 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap mapA_hi, const __grid_constan
         // pipe waits for the issuer: no division, no blocking probe on the usual path.
         int in_win = -1;   // position of this k block in its accumulation window
         const int nkb_t = (p.splits > 1) ? k_range(decode_tile(tile, p).mat, p).count : nkb;
+        if (kNSplit == 2) {
+          // 512-wide tile: both accumulator buffers belong to this tile, half h in buffer h, so
+          // the drain cannot hide behind the next tile as a whole - but it can half by half.  The
+          // last kHead k blocks first run their left-half MMAs, the left half is published, and
+          // its drain overlaps their right-half MMAs; the next tile starts with the left-half MMAs
+          // of its first kHead k blocks, which overlap the drain of the previous right half.
+          // In between, every k block issues both halves.  `win` counts tiles here.
+          constexpr int kHead = 2;
+          static_assert(kNSplit == 1 || kStages >= 2 * kHead, "head and tail each hold kHead slots");
+          const uint32_t tpar = win & 1;
+          const bool staged = nkb_t >= 2 * kHead;
+          auto mma_half = [&](uint32_t slot_s, int h, bool fresh) {
+#pragma unroll
+            for (int j = 0; j < kSlabs; j++) {
+              const uint32_t stage = smem_base + slot_s * STAGE_BYTES + j * SLAB_BYTES;
+              const uint64_t adesc = make_smem_desc(stage, a_lbo, a_sbo, a_mode);
+              const uint64_t bdesc = make_smem_desc(stage + PARTS * A_BYTES + h * B_PART_BYTES, b_lbo, b_sbo, b_mode);
+#pragma unroll
+              for (int k = 0; k < BK / UMMA_K; k++)
+                tc_mma<kTf32, kCta>(tmem_base + h * kBN, adesc + (uint64_t)((k * a_kstep) >> 4),
+                                    bdesc + (uint64_t)((k * b_kstep) >> 4), idesc, (fresh && j == 0 && k == 0) ? 0u : 1u);
+            }
+          };
+          auto release = [&](uint32_t slot_s) {
+            tc_commit<kCta>(bar_empty + 8 * slot_s);
+            if (kCta == 2) tc_commit<kCta>(empty_peer + 8 * slot_s);
+          };
+          auto fail = [&]() {
+            atomicOr(p.status, kDevTimeoutMma);
+            abort_flag = 1;
+            ok = false;
+          };
+          int kb = 0;
+          if (!mbar_wait(bar_tempty, tpar ^ 1, abortp)) { fail(); break; }
+          tc_fence_after();
+          if (staged) {
+            uint32_t hs[kHead];
+#pragma unroll
+            for (int i = 0; i < kHead && ok; i++) {
+              hs[i] = s;
+              if (!mbar_wait(bar_full + 8 * s, ph, abortp)) { fail(); break; }
+              tc_fence_after();
+              mma_half(s, 0, i == 0);
+              if (++s == kStages) { s = 0; ph ^= 1; }
+            }
+            if (!ok) break;
+            if (!mbar_wait(bar_tempty + 8, tpar ^ 1, abortp)) { fail(); break; }
+            tc_fence_after();
+#pragma unroll
+            for (int i = 0; i < kHead; i++) {
+              mma_half(hs[i], 1, i == 0);
+              release(hs[i]);
+            }
+            kb = kHead;
+          } else {
+            if (!mbar_wait(bar_tempty + 8, tpar ^ 1, abortp)) { fail(); break; }
+            tc_fence_after();
+          }
+          const int body_end = staged ? nkb_t - kHead : nkb_t;
+          for (; kb < body_end; kb++) {
+            if (!mbar_wait(bar_full + 8 * s, ph, abortp)) { fail(); break; }
+            tc_fence_after();
+            mma_half(s, 0, kb == 0);
+            mma_half(s, 1, kb == 0);
+            release(s);
+            if (++s == kStages) { s = 0; ph ^= 1; }
+          }
+          if (!ok) break;
+          if (staged) {
+            uint32_t ts[kHead];
+#pragma unroll
+            for (int i = 0; i < kHead && ok; i++) {
+              ts[i] = s;
+              if (!mbar_wait(bar_full + 8 * s, ph, abortp)) { fail(); break; }
+              tc_fence_after();
+              mma_half(s, 0, false);
+              if (++s == kStages) { s = 0; ph ^= 1; }
+            }
+            if (!ok) break;
+            tc_commit<kCta>(bar_tfull);
+            if (kCta == 2) tc_commit<kCta>(tfull_peer);
+#pragma unroll
+            for (int i = 0; i < kHead; i++) {
+              mma_half(ts[i], 1, false);
+              release(ts[i]);
+            }
+            tc_commit<kCta>(bar_tfull + 8);
+            if (kCta == 2) tc_commit<kCta>(tfull_peer + 8);
+          } else {
+            tc_commit<kCta>(bar_tfull);
+            if (kCta == 2) tc_commit<kCta>(tfull_peer);
+            tc_commit<kCta>(bar_tfull + 8);
+            if (kCta == 2) tc_commit<kCta>(tfull_peer + 8);
+          }
+          win++;
+          continue;
+        }
         for (int kb = 0; kb < nkb_t; kb++) {
           if (++in_win == chunk_kb) in_win = 0;
           if (in_win == 0) {
@@ -787,26 +884,35 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap mapA_hi, const __grid_constan
       const int nkb_t = (p.splits > 1) ? k_range(t.mat, p).count : nkb;
       const int nwin = (nkb_t + chunk_kb - 1) / chunk_kb;
       if (!kWindowed) {
-        const uint32_t slot = win % ACC_SLOTS;
-        const bool got = mbar_wait_warp(bar_tfull + 8 * slot, (win / ACC_SLOTS) & 1, abortp, lane);
+        // A 512-wide tile is drained half by half (half h lives in accumulator buffer h and is
+        // published on its own, the left one while the right one's last MMAs still run); every
+        // epilogue warp takes its share of the columns of each half.
+        constexpr int COLS_PER_PART = kBN / COL_SPLIT;
+#pragma unroll 1
+        for (int h = 0; h < kNSplit && ok; h++) {
+        const uint32_t slot = (kNSplit == 2) ? (uint32_t)h : win % ACC_SLOTS;
+        const uint32_t par = (kNSplit == 2) ? (win & 1) : ((win / ACC_SLOTS) & 1);
+        const bool got = mbar_wait_warp(bar_tfull + 8 * slot, par, abortp, lane);
         if (!got) {
           if (lane == 0) { atomicOr(p.status, kDevTimeoutEpilogue); abort_flag = 1; }
           ok = false;
           break;
         }
         tc_fence_after();
-        const uint32_t tbase = tmem_base + lane_base + (kNSplit == 2 ? 0 : slot * kBN) + col0;
+        const int part0 = col_part * COLS_PER_PART;
+        const uint32_t tbase = tmem_base + lane_base + slot * kBN + part0;
+        const int64_t n0h = (int64_t)t.tn * TILE_N + h * kBN + part0;
         if (p.tma_store) {
           // Each warp rounds its 32 rows x 128 bytes into a swizzled staging buffer and one lane
           // sends it with a TMA store (full 128-byte lines); two buffers per warp alternate.
           constexpr int COLS_PER_BUF = kOutHalf ? 64 : 32;   // columns in one 128-byte staging row
           constexpr int LOADS = STG_BUFS * (kOutHalf ? 2 : 1);   // tcgen05.ld.x32 per pass (all staging buffers)
-          static_assert(COLS_PER_THREAD % (STG_BUFS * COLS_PER_BUF) == 0, "a pass fills every staging buffer");
+          static_assert(COLS_PER_PART % (STG_BUFS * COLS_PER_BUF) == 0, "a pass fills every staging buffer");
           const int m_warp = t.tm * (BM * kCta) + (int)rank * BM + quarter * 32;
           const uint32_t row_addr = stg_base + (uint32_t)lane * 128u;
           const uint32_t sw = (uint32_t)(lane & 7);
 #pragma unroll 1
-          for (int c = 0; c < COLS_PER_THREAD; c += STG_BUFS * COLS_PER_BUF) {
+          for (int c = 0; c < COLS_PER_PART; c += STG_BUFS * COLS_PER_BUF) {
             uint32_t r[LOADS][32];
 #pragma unroll
             for (int l = 0; l < LOADS; l++) tmem_ld_x32(tbase + c + 32 * l, r[l]);
@@ -825,14 +931,14 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap mapA_hi, const __grid_constan
                   float x[8];
 #pragma unroll
                   for (int e = 0; e < 8; e++) x[e] = __uint_as_float(r[l][q * 8 + e]);
-                  if (p.bias) add_bias<true, 8>(p.bias, n0 + c + 32 * l + q * 8, p.N, x);
-                  uint32_t h[4];
+                  if (p.bias) add_bias<true, 8>(p.bias, n0h + c + 32 * l + q * 8, p.N, x);
+                  uint32_t hh[4];
 #pragma unroll
                   for (int e = 0; e < 4; e++) {
                     __half2 v2 = __floats2half2_rn(x[2 * e], x[2 * e + 1]);
-                    h[e] = *(uint32_t*)&v2;
+                    hh[e] = *(uint32_t*)&v2;
                   }
-                  st_shared_v4(buf + (((uint32_t)(q + 4 * (l & 1)) ^ sw) << 4), h[0], h[1], h[2], h[3]);
+                  st_shared_v4(buf + (((uint32_t)(q + 4 * (l & 1)) ^ sw) << 4), hh[0], hh[1], hh[2], hh[3]);
                 }
               } else {
                 const uint32_t buf = row_addr + (uint32_t)l * 4096u;
@@ -841,7 +947,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap mapA_hi, const __grid_constan
                   float x[4];
 #pragma unroll
                   for (int e = 0; e < 4; e++) x[e] = __uint_as_float(r[l][q * 4 + e]);
-                  if (p.bias) add_bias<false, 4>(p.bias, n0 + c + 32 * l + q * 4, p.N, x);
+                  if (p.bias) add_bias<false, 4>(p.bias, n0h + c + 32 * l + q * 4, p.N, x);
                   st_shared_v4(buf + (((uint32_t)q ^ sw) << 4), __float_as_uint(x[0]), __float_as_uint(x[1]),
                                __float_as_uint(x[2]), __float_as_uint(x[3]));
                 }
@@ -852,7 +958,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap mapA_hi, const __grid_constan
             if (store_leader && m_warp < p.M) {
 #pragma unroll
               for (int b2 = 0; b2 < STG_BUFS; b2++) {
-                const int64_t col = n0 + c + b2 * COLS_PER_BUF;
+                const int64_t col = n0h + c + b2 * COLS_PER_BUF;
                 if (col < p.N) {
                   for (int d = 0; d < p.n_out; d++)
                     tma_store_3d(&mapC.m[d], stg_base + (uint32_t)b2 * 4096u, (int)col, m_warp, (int)t.mat);
@@ -863,19 +969,20 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap mapA_hi, const __grid_constan
           }
         } else {
 #pragma unroll 1
-          for (int c = 0; c < COLS_PER_THREAD; c += 32) {
+          for (int c = 0; c < COLS_PER_PART; c += 32) {
             uint32_t r[32];
             tmem_ld_x32(tbase + c, r);
             tmem_ld_wait();
             float v[32];
 #pragma unroll
             for (int j = 0; j < 32; j++) v[j] = __uint_as_float(r[j]);
-            if (p.bias) add_bias<kOutHalf, 32>(p.bias, n0 + c, p.N, v);
-            if (gm < p.M && n0 + c < p.N) store_row32<kOutHalf>(cmat, row_off, n0 + c, p.N, v, p.vec_ok != 0);
+            if (p.bias) add_bias<kOutHalf, 32>(p.bias, n0h + c, p.N, v);
+            if (gm < p.M && n0h + c < p.N) store_row32<kOutHalf>(cmat, row_off, n0h + c, p.N, v, p.vec_ok != 0);
           }
         }
         tc_fence_before();
         mbar_arrive_cluster_relaxed(tempty_leader + 8 * slot);
+        }
         win++;
       } else {
         float acc[COLS_PER_THREAD];

@@ -89,35 +89,57 @@ def test_cast_and_add_are_bit_identical(be):
         assert np.array_equal(got.view(np.uint8), ref.add(a, b).reshape(-1).view(np.uint8))
 
 
-@pytest.mark.parametrize("dtype,tol", [(np.float32, 1e-5), (np.float16, 2e-3)])
-def test_linear_layer_forward_and_backward(be, dtype, tol):
+# (weight dtype, castParams, compute dtype): the three ways the reference's Linear is used
+# (Trainable.swift:514-544) - plain float32; float16 weights with the float32 bias cast on use;
+# float32 master weights cast to float16 on every call.
+@pytest.mark.parametrize("wdtype,cast,cdtype,tol", [(np.float32, None, np.float32, 1e-5),
+                                                    (np.float16, np.float16, np.float16, 2e-3),
+                                                    (np.float32, np.float16, np.float16, 2e-3)])
+def test_linear_layer_forward_and_backward(be, wdtype, cast, cdtype, tol):
     """Linear(inCount -> outCount) on a [batch, seq, in] input: output, input gradient, weight
-    gradient and bias gradient against the oracle's products and sums."""
+    gradient and bias gradient against the oracle's products, sums and casts."""
     from honeycrisp_b200 import Linear
-    layer = Linear(be, 256, 384, dtype=dtype, seed=3)
-    w = layer.weight.onCPU(dtype)[: 256 * 384].reshape(256, 384)
+    layer = Linear(be, 256, 384, dtype=wdtype, castParams=cast, seed=3)
+    w = layer.weight.onCPU(wdtype)[: 256 * 384].reshape(256, 384)
     assert np.abs(w.astype(np.float32)).max() <= np.sqrt(3.0) / np.sqrt(256) + 1e-3
+    assert layer.bias.byteCount == 384 * 4                      # the bias is float32 whatever the layer's dtype
+    assert not layer.bias.onCPU(np.float32)[:384].any()
     rng = np.random.default_rng(1)
-    b = rng.standard_normal(384).astype(dtype)
-    layer.bias = be.collection(b, dtype)
-    x = rng.standard_normal((4, 96, 256)).astype(dtype)
+    b32 = rng.standard_normal(384).astype(np.float32)
+    layer.bias = be.collection(b32, np.float32)
+    x = rng.standard_normal((4, 96, 256)).astype(cdtype)
     y, yshape = layer(x, x.shape)
     assert yshape == [4, 96, 384]
     rows = 4 * 96
-    want_y = ref.linear_forward(x.reshape(rows, 256), w, b, rows, 256, 384)
-    assert ref.rel_frobenius(y.onCPU(dtype)[: rows * 384], want_y) < tol
-    g = rng.standard_normal((4, 96, 384)).astype(dtype)
+    wc, bc = ref.cast(w, cdtype).reshape(256, 384), ref.cast(b32, cdtype).reshape(-1)   # weight.cast / bias.cast
+    want_y = ref.linear_forward(x.reshape(rows, 256), wc, bc, rows, 256, 384)
+    assert ref.rel_frobenius(y.onCPU(cdtype)[: rows * 384], want_y) < tol
+    g = rng.standard_normal((4, 96, 384)).astype(cdtype)
     dx = layer.backward(x, x.shape, g)
     (fa, fb) = ref.matmul_grad_calls(False, False, False)
-    want_dx = ref.matmul(g.reshape(rows, 384), fa[0], w, fa[1], fa[2], rows, 384, 256)
+    want_dx = ref.matmul(g.reshape(rows, 384), fa[0], wc, fa[1], fa[2], rows, 384, 256)
     want_dw = ref.matmul(x.reshape(rows, 256), fb[0], g.reshape(rows, 384), fb[1], fb[2], 256, rows, 384)
-    assert ref.rel_frobenius(dx.onCPU(dtype)[: rows * 256], want_dx) < tol
-    assert ref.rel_frobenius(layer.weightGrad.onCPU(dtype)[: 256 * 384], want_dw) < tol
-    want_db = ref.column_sum(g.reshape(rows, 384), rows, 384)
-    assert np.array_equal(layer.biasGrad.onCPU(dtype)[:384].view(np.uint8), want_db.view(np.uint8))
+    assert ref.rel_frobenius(dx.onCPU(cdtype)[: rows * 256], want_dx) < tol
+    # gradients come back in the parameters' own dtypes (the backward of cast)
+    assert layer.weightGrad.byteCount == 256 * 384 * np.dtype(wdtype).itemsize
+    assert ref.rel_frobenius(layer.weightGrad.onCPU(wdtype)[: 256 * 384], ref.cast(want_dw, wdtype).reshape(-1)) < tol
+    want_db = ref.cast(ref.column_sum(g.reshape(rows, 384), rows, 384), np.float32).reshape(-1)
+    assert layer.biasGrad.byteCount == 384 * 4
+    assert np.array_equal(layer.biasGrad.onCPU(np.float32)[:384].view(np.uint8), want_db.view(np.uint8))
     # a second backward accumulates (Param.addGrad)
     layer.backward(x, x.shape, g)
-    assert np.array_equal(layer.biasGrad.onCPU(dtype)[:384].view(np.uint8), ref.add(want_db, want_db).reshape(-1).view(np.uint8))
+    assert np.array_equal(layer.biasGrad.onCPU(np.float32)[:384].view(np.uint8), ref.add(want_db, want_db).reshape(-1).view(np.uint8))
+
+
+def test_linear_layer_refuses_what_the_reference_refuses(be):
+    """float16 weights, float32 bias, no castParams: `h + bias` mixes dtypes, which the reference's
+    binary ops assert against; without a bias the same layer is fine."""
+    from honeycrisp_b200 import Linear
+    x = np.ones((8, 64), dtype=np.float16)
+    with pytest.raises(ValueError):
+        Linear(be, 64, 32, dtype=np.float16)(x, x.shape)
+    out, shape = Linear(be, 64, 32, dtype=np.float16, bias=False)(x, x.shape)
+    assert shape == [8, 32] and out.byteCount == 8 * 32 * 2
 
 
 @pytest.mark.parametrize("dtype", [np.float32, np.float16])
