@@ -255,9 +255,11 @@ def run_ours(args):
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
 
     be = CUDABackend(local)
-    stream = torch.cuda.Stream()
-    torch.cuda.set_stream(stream)
-    be.useStream(stream.cuda_stream)
+    # The backend keeps its own stream, on which nothing but the library launches kernels (it may
+    # then start a product's operand loads before the previous product has finished); torch only
+    # records timing events there.  torch's own work (data generation, the vendor-library legs)
+    # runs on torch's streams, separated from the backend's by device synchronisation.
+    stream = torch.cuda.ExternalStream(be.stream(), device=torch.device("cuda", local))
 
     n = N_DIM
     gen = torch.Generator(device="cuda").manual_seed(1 + rank)
@@ -494,6 +496,7 @@ def other_configs(be, stream, rank, world):
     import torch
 
     def timed(fn, iters):
+        torch.cuda.synchronize()
         for _ in range(3):
             fn()
         e0 = torch.cuda.Event(enable_timing=True); e1 = torch.cuda.Event(enable_timing=True)
@@ -639,19 +642,19 @@ def probe_one(args, spec):
     ta, tb = (bool(int(x)) for x in args.flags.split(","))
     npdt, tdt = (np.float16, torch.float16) if args.dtype == "f16" else (np.float32, torch.float32)
     be = CUDABackend(0)
-    stream = torch.cuda.Stream()
-    torch.cuda.set_stream(stream)
-    be.useStream(stream.cuda_stream)
+    stream = torch.cuda.ExternalStream(be.stream(), device=torch.device("cuda", 0))   # events only; see run_ours
+    lib_stream = torch.cuda.Stream()
     g = torch.Generator(device="cuda").manual_seed(1)
     a = (torch.randn((cnt, K, M) if ta else (cnt, M, K), generator=g, device="cuda") / K ** 0.25).to(tdt)
     b = (torch.randn((cnt, N, K) if tb else (cnt, K, N), generator=g, device="cuda") / K ** 0.25).to(tdt)
     out = torch.empty((cnt, M, N), device="cuda", dtype=tdt)
     od = be.wrap(out.data_ptr(), out.numel() * out.element_size(), out)
+    torch.cuda.synchronize()
     be.batchedMatmul(cnt, a, ta, b, tb, False, M, K, N, npdt, out=od)
     e0 = torch.cuda.Event(enable_timing=True); e1 = torch.cuda.Event(enable_timing=True)
     e0.record(stream)
     for _ in range(args.steps):
-        be.batchedMatmul(cnt, a, ta, b, tb, False, M, K, N, npdt, out=od)
+        be.batchedMatmul(cnt, a, ta, b, tb, False, M, K, N, npdt, out=od, mark=False)
     e1.record(stream)
     torch.cuda.synchronize()
     be.checkDeviceStatus()
@@ -679,27 +682,29 @@ def probe_one(args, spec):
         B = b.transpose(-1, -2) if tb else b
         ref_out = torch.empty_like(out)
         run_lib = lambda: torch.matmul(A, B, out=ref_out)
-        for _ in range(3):
-            run_lib()
-        if args.graph:
-            g2 = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(g2, stream=stream):
+        torch.cuda.synchronize()
+        with torch.cuda.stream(lib_stream):
+            for _ in range(3):
+                run_lib()
+            if args.graph:
+                g2 = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g2, stream=lib_stream):
+                    for _ in range(args.steps):
+                        run_lib()
+                g2.replay()
+                e0.record(lib_stream)
+                for _ in range(5):
+                    g2.replay()
+                e1.record(lib_stream)
+                torch.cuda.synchronize()
+                lib_ms = e0.elapsed_time(e1) / (5 * args.steps)
+            else:
+                e0.record(lib_stream)
                 for _ in range(args.steps):
                     run_lib()
-            g2.replay()
-            e0.record(stream)
-            for _ in range(5):
-                g2.replay()
-            e1.record(stream)
-            torch.cuda.synchronize()
-            lib_ms = e0.elapsed_time(e1) / (5 * args.steps)
-        else:
-            e0.record(stream)
-            for _ in range(args.steps):
-                run_lib()
-            e1.record(stream)
-            torch.cuda.synchronize()
-            lib_ms = e0.elapsed_time(e1) / args.steps
+                e1.record(lib_stream)
+                torch.cuda.synchronize()
+                lib_ms = e0.elapsed_time(e1) / args.steps
     info = be.lastLaunchInfo()
     be.close()
     return {"probe": [M, K, N, cnt], "dtype": args.dtype, "flags": [ta, tb], "ms": ms, "graph": bool(args.graph),
@@ -737,13 +742,15 @@ def sustained_leg(be, stream, step, a, b, out, barrier, use_dist, world):
         for x, y in views:
             torch.matmul(x, y, out=out)
 
-    for _ in range(3):
-        lib_step()
-    barrier()
-    e0.record(stream)
-    for _ in range(steps):
-        lib_step()
-    e1.record(stream)
+    lib_stream = torch.cuda.Stream()
+    with torch.cuda.stream(lib_stream):
+        for _ in range(3):
+            lib_step()
+        barrier()
+        e0.record(lib_stream)
+        for _ in range(steps):
+            lib_step()
+        e1.record(lib_stream)
     barrier()
     lms = _max_over_ranks(e0.elapsed_time(e1), use_dist)
     res["library_same_run"] = {"what": "torch.matmul (cuBLAS) on the same operands, same four layouts, same loop",
@@ -758,6 +765,7 @@ def link_probe(stream, use_dist, world):
     """Plain copies between pinned host memory and the device, every rank at once: what the host
     side of the box can deliver per GPU, the ceiling of any end-to-end number."""
     import torch
+    stream = torch.cuda.current_stream()      # torch's copies run on torch's stream
     nbytes = 512 << 20
     host = torch.empty(nbytes, dtype=torch.uint8).pin_memory()
     dev = torch.empty(nbytes, dtype=torch.uint8, device="cuda")
@@ -781,6 +789,7 @@ def link_probe(stream, use_dist, world):
 
 def _device_timed(fn, iters, stream, use_dist, warm=3):
     import torch
+    torch.cuda.synchronize()                  # operands made on torch's stream are complete
     for _ in range(warm):
         fn()
     torch.cuda.synchronize()
@@ -859,15 +868,20 @@ def sharded_configs(be, stream, rank, world):
     c = torch.empty((n, n), device="cuda")
     ap, bp, cp = a.data_ptr(), b.data_ptr(), c.data_ptr()
     nccl = lambda: grp.matmulColumnSplit(ap, False, bp, False, n, n, n, np.float32, cp)
-    ms = _device_timed(nccl, 5, stream, use_dist, warm=2)
-    res["c5_nccl"] = {"ms": ms, "box_tflops_effective": flops / ms / 1e9, "gathered_bytes_per_gpu": gathered}
-    # this rank's block alone (what the exchange is added to)
     cb, cw = columnBlock(n, rank, world)
     be_out = be.wrap(c.data_ptr(), n * n * 4, c)
     block_only = lambda: be.matmulColumnBlock(a, False, b, False, False, n, n, n, cb, cw, np.float32, out=be_out)
-    bms = _device_timed(block_only, 5, stream, use_dist, warm=2)
-    res["c5_nccl"]["block_product_ms"] = bms
-    res["c5_nccl"]["exchange_ms"] = max(ms - bms, 0.0)
+    # The whole call and this rank's block product alone, alternating (the clock under the power
+    # cap drifts by a few per cent within seconds; alternating keeps the difference honest).
+    whole_ms, block_ms = [], []
+    nccl(); block_only()
+    for _ in range(5):
+        whole_ms.append(_device_timed(nccl, 1, stream, use_dist, warm=0))
+        block_ms.append(_device_timed(block_only, 1, stream, use_dist, warm=0))
+    ms, bms = statistics.median(whole_ms), statistics.median(block_ms)
+    res["c5_nccl"] = {"ms": ms, "box_tflops_effective": flops / ms / 1e9, "gathered_bytes_per_gpu": gathered,
+                      "block_product_ms": bms, "exchange_ms": max(ms - bms, 0.0),
+                      "exchange_is": "ncclAllGather of the packed blocks + the unpack kernel (whole call minus block product)"}
     if world > 1 and ms > bms:
         res["c5_nccl"]["nvlink_gbs_in_per_gpu"] = gathered / (ms - bms) / 1e6
     nccl_result = c

@@ -58,10 +58,22 @@ class DType(enum.Enum):
         return {"float16": np.float16, "float32": np.float32, "int64": np.int64}[self.value]
 
 
+_DTYPE_OF = {}
+
+
 def _as_dtype(dtype) -> DType:
     if isinstance(dtype, DType):
         return dtype
-    return DType(np.dtype(dtype).name)
+    try:
+        return _DTYPE_OF[dtype]
+    except (KeyError, TypeError):
+        pass
+    dt = DType(np.dtype(dtype).name)
+    try:
+        _DTYPE_OF[dtype] = dt
+    except TypeError:
+        pass
+    return dt
 
 
 _HC_DTYPE = {DType.float16: L.HC_F16, DType.float32: L.HC_F32}
@@ -86,6 +98,34 @@ class ReadBack:
         try:
             if self._event:
                 self._source.backend._lib.hc_event_destroy(self._event)
+        except Exception:
+            pass
+
+
+class Marker:
+    """A completion marker on the backend's stream (hc_event_record): wait for it, or measure the
+    device time between two of them."""
+
+    def __init__(self, backend: "CUDABackend"):
+        self.backend = backend
+        ev = ctypes.c_void_p()
+        backend._check(backend._lib.hc_event_record(backend._ctx, ctypes.byref(ev)))
+        self._event = ev.value
+
+    def wait(self):
+        self.backend._check(self.backend._lib.hc_event_wait(self._event))
+
+    def elapsedMs(self, later: "Marker") -> float:
+        """Milliseconds from this marker to `later` (both must have completed)."""
+        ms = ctypes.c_float()
+        self.backend._check(self.backend._lib.hc_event_elapsed_ms(self._event, later._event, ctypes.byref(ms)))
+        return float(ms.value)
+
+    def __del__(self):
+        try:
+            if self._event:
+                self.backend._lib.hc_event_destroy(self._event)
+                self._event = None
         except Exception:
             pass
 
@@ -260,6 +300,14 @@ class CUDABackend:
     def sync(self):
         self._check(self._lib.hc_sync(self._ctx))
 
+    def marker(self) -> Marker:
+        """Record a completion marker after everything enqueued so far."""
+        return Marker(self)
+
+    def stream(self) -> int:
+        """The CUDA stream (a `cudaStream_t` as an integer) this backend enqueues on."""
+        return int(self._lib.hc_get_stream(self._ctx) or 0)
+
     def checkDeviceStatus(self):
         self._check(self._lib.hc_check_device_status(self._ctx))
 
@@ -347,6 +395,19 @@ class CUDABackend:
             return self.wrap(x.data_ptr(), x.numel() * x.element_size(), owner=x)
         raise TypeError(f"unsupported operand type {type(x)!r}")
 
+    def _operand(self, x, dt: DType):
+        """(device address, bytes, object to keep alive) of an operand, without building a handle
+        for device memory that already has an owner: the per-call cost matters for products that
+        run for a few microseconds."""
+        if isinstance(x, CUDAData):
+            return x.ptr, x.byteCount, x
+        if hasattr(x, "data_ptr"):  # a CUDA torch tensor
+            if not x.is_cuda or not x.is_contiguous():
+                raise ValueError("torch operands must be contiguous CUDA tensors")
+            return x.data_ptr(), x.numel() * x.element_size(), x
+        d = self._device_operand(x, dt)
+        return d.ptr, d.byteCount, d
+
     # -- the hot path --------------------------------------------------------------------
 
     def matmul(self, a, transA: bool, b, transB: bool, transOut: bool, rows: int, inner: int, cols: int,
@@ -363,28 +424,30 @@ class CUDABackend:
         `mark=False` skips the per-result completion marker (wait() then synchronises the whole
         stream instead); launch-bound loops and CUDA-graph capture use it."""
         dt = _as_dtype(dtype)
-        if dt not in _HC_DTYPE:
+        hdt = _HC_DTYPE.get(dt)
+        if hdt is None:
             raise NotImplementedByBackend(f"matmul for dtype {dt.value}")
-        a_d = self._device_operand(a, dt)
-        b_d = self._device_operand(b, dt)
-        n_out = matrixCount * rows * cols * dt.byteSize
+        a_p, a_n, a_keep = self._operand(a, dt)
+        b_p, b_n, b_keep = self._operand(b, dt)
+        eb = 2 if hdt == L.HC_F16 else 4
+        n_out = matrixCount * rows * cols * eb
         # Same size checks the reference's GPU backend makes before encoding
         # (Sources/Honeycrisp/BackendMPS.swift:2221-2230).
-        if a_d.byteCount < matrixCount * rows * inner * dt.byteSize:
+        if a_n < matrixCount * rows * inner * eb:
             raise ValueError("matmul: operand a is smaller than matrixCount*rows*inner elements")
-        if b_d.byteCount < matrixCount * inner * cols * dt.byteSize:
+        if b_n < matrixCount * inner * cols * eb:
             raise ValueError("matmul: operand b is smaller than matrixCount*inner*cols elements")
         if out is None:
             out = self.allocate(n_out)
         elif out.byteCount < n_out:
             raise ValueError("matmul: output buffer too small")
-        st = self._lib.hc_batched_matmul_ex(self._ctx, int(kernel), _HC_DTYPE[dt], int(matrixCount), a_d.ptr,
-                                           int(bool(transA)), b_d.ptr, int(bool(transB)), int(bool(transOut)),
-                                           int(rows), int(inner), int(cols), out.ptr)
-        self._check(st)
+        st = self._lib.hc_batched_matmul_ex(self._ctx, kernel, hdt, matrixCount, a_p, 1 if transA else 0, b_p,
+                                            1 if transB else 0, 1 if transOut else 0, rows, inner, cols, out.ptr)
+        if st != L.HC_OK:
+            self._check(st)
         if mark:
             out._mark()
-        out._inputs = (a_d, b_d)  # keep operands alive until the result is collected
+        out._inputs = (a_keep, b_keep)  # keep operands alive until the result is collected
         return out
 
     def matmulColumnBlock(self, a, transA: bool, b, transB: bool, transOut: bool, rows: int, inner: int,

@@ -68,6 +68,9 @@ cudaError_t launch_simt(const GemmProblem& p, bool exact, cudaStream_t stream, L
 // copies, mapped into this process); every result tile is stored to each of them as well.
 // `cache` (optional): prepared launches of recent products, owned by the caller's context; a
 // repeat of a product then skips planning and tensor-map encoding.
+// `private_stream`: the caller vouches that nobody but this library launches kernels on `stream`;
+// the operand loads of a product may then start before the previous product has finished, when
+// that product cannot have written them.
 // `scratch_needed` (optional) receives the work-area bytes the product needs; when the area given
 // is smaller the call launches nothing and returns cudaErrorInvalidValue, so that the caller can
 // grow the area and call again.
@@ -78,7 +81,7 @@ void tc_cache_clear(TcCache* c);
 cudaError_t launch_tc(const GemmProblem& p, cudaStream_t stream, unsigned int* status_word,
                       void* scratch, size_t scratch_bytes, int sm_count, LaunchRecord* rec,
                       void* const* extra_out = nullptr, int n_extra = 0, TcCache* cache = nullptr,
-                      size_t* scratch_needed = nullptr);
+                      size_t* scratch_needed = nullptr, bool private_stream = false);
 bool tc_supported(const GemmProblem& p);
 // One-thread kernel whose bounded wait is made to expire after `limit_ns` (self-test).
 cudaError_t launch_wait_probe(cudaStream_t stream, unsigned int* status_word, unsigned long long limit_ns);

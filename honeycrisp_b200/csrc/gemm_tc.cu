@@ -64,6 +64,10 @@
 
 extern "C" char** environ;
 
+// The 512-wide tile's MMA issuer leaves its tile loop body early (`continue`), which makes the
+// generic k loop behind it unreachable in that one instantiation.
+#pragma nv_diag_suppress 128
+
 namespace hc {
 namespace {
 
@@ -88,6 +92,8 @@ struct TcParams {
   int tma_store;      // results leave through shared memory and TMA stores (else direct stores)
   const void* bias;   // optional row vector added to the rounded product (Linear), or null
   int n_out;          // destinations of every result tile: this device's result, then peers' copies
+  int l2_hints;       // operand loads carry L2 eviction priorities (see tma_load_3d_hint)
+  int skip_input_wait;  // the operands are known not to be written by the kernel launched just before
 };
 
 // ---- PTX wrappers ---------------------------------------------------------------------------
@@ -129,7 +135,13 @@ __device__ __forceinline__ uint32_t map_to_cta(uint32_t addr, uint32_t rank) {
 // start while its predecessor in the stream is still draining.  `pdl_release` lets the successor
 // be scheduled as soon as every CTA of this grid has issued it (or exited); `pdl_wait` blocks
 // until the predecessor has completed and its memory is visible.  Both are no-ops for an
-// ordinary launch.  Everything before pdl_wait must touch no global memory.
+// ordinary launch.  Everything before pdl_wait must touch no global memory - with one exception
+// the host decides: operand loads may run ahead of it when the operands cannot have been written
+// by the predecessor (TcParams::skip_input_wait).
+// Every kernel of this library releases its successor only AFTER its own wait has returned.  A
+// successor therefore never starts before its predecessor's predecessor has completed: at most
+// two kernels of a chain are in flight, and the only kernel a launch can race with is the one
+// enqueued immediately before it.
 __device__ __forceinline__ void pdl_release() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 // Rendezvous without memory ordering: for the teardown, where the CTAs of a pair only have to
@@ -256,6 +268,38 @@ __device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map
         "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes "
         "[%0], [%1, {%3, %4, %5}], [%2];"
         ::"r"(dst), "l"((unsigned long long)map), "r"(bar), "r"(c0), "r"(c1), "r"(c2)
+        : "memory");
+  }
+}
+
+// The same load with an L2 eviction priority.  A wave of tiles shares a band of A rows with the
+// next wave (tiles are walked column by column inside a group of tile rows), while each panel of B
+// columns is read by one wave and never again: A lines are asked to stay (evict_last), B lines to
+// go first (evict_first), so the band survives in L2 instead of being re-read from HBM every wave.
+__device__ __forceinline__ uint64_t l2_policy_evict_last() {
+  uint64_t p;
+  asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(p));
+  return p;
+}
+__device__ __forceinline__ uint64_t l2_policy_evict_first() {
+  uint64_t p;
+  asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(p));
+  return p;
+}
+template <int kCta>
+__device__ __forceinline__ void tma_load_3d_hint(uint32_t dst, const CUtensorMap* map, uint32_t bar,
+                                                 int c0, int c1, int c2, uint64_t policy) {
+  if (kCta == 2) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint "
+        "[%0], [%1, {%3, %4, %5}], [%2], %6;"
+        ::"r"(dst), "l"((unsigned long long)map), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "l"(policy)
+        : "memory");
+  } else {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes.L2::cache_hint "
+        "[%0], [%1, {%3, %4, %5}], [%2], %6;"
+        ::"r"(dst), "l"((unsigned long long)map), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "l"(policy)
         : "memory");
   }
 }
@@ -544,7 +588,6 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap mapA_hi, const __grid_constan
   __shared__ uint32_t tmem_base_slot;
   __shared__ int abort_flag;
 
-  pdl_release();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t rank = (kCta == 2) ? cluster_ctarank() : 0u;
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -611,6 +654,12 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap mapA_hi, const __grid_constan
       }
       // Completion bytes of both CTAs of a pair are counted on the leader's barrier.
       const uint32_t full_leader = (kCta == 2) ? map_to_cta(bar_full, 0) : bar_full;
+      const bool hinted = p.l2_hints != 0;
+      const uint64_t policy = do_a ? l2_policy_evict_last() : l2_policy_evict_first();
+      auto load = [&](uint32_t dst, const CUtensorMap* map, uint32_t bar, int c0, int c1, int c2) {
+        if (hinted) tma_load_3d_hint<kCta>(dst, map, bar, c0, c1, c2, policy);
+        else tma_load_3d<kCta>(dst, map, bar, c0, c1, c2);
+      };
       uint32_t s = 0, ph = 0;
       bool ok = true;
       TileCoord t = decode_tile(tile_first < p.total_tiles ? tile_first : 0, p);
@@ -620,7 +669,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap mapA_hi, const __grid_constan
       const int free_slots = (tile_first < p.total_tiles) ? min(kStages, kr.count) : 0;
       if (do_a && rank == 0)
         for (int i = 0; i < free_slots; i++) mbar_expect_tx(bar_full + 8 * i, STAGE_BYTES * kCta);
-      pdl_wait();
+      if (!p.skip_input_wait) pdl_wait();
       for (int64_t tile = tile_first; ok && tile < p.total_tiles; tile += tile_step) {
         if (tile != tile_first) { t = decode_tile(tile, p); kr = k_range(t.mat, p); }
         const int prearmed = (tile == tile_first) ? free_slots : 0;
@@ -650,10 +699,10 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap mapA_hi, const __grid_constan
             const uint32_t sa = stage + part * A_BYTES, sb = stage + PARTS * A_BYTES + part * B_BYTES;
             if (do_a) {
               if (!p.a_mn_major) {
-                tma_load_3d<kCta>(sa, ma, full, kc, m0, mat);
+                load(sa, ma, full, kc, m0, mat);
               } else {
 #pragma unroll
-                for (int c = 0; c < BM / CH; c++) tma_load_3d<kCta>(sa + c * (BK * 128), ma, full, m0 + c * CH, kc, mat);
+                for (int c = 0; c < BM / CH; c++) load(sa + c * (BK * 128), ma, full, m0 + c * CH, kc, mat);
               }
             }
 #pragma unroll
@@ -661,11 +710,11 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap mapA_hi, const __grid_constan
               const uint32_t sbh = sb + h * B_PART_BYTES;
               const int n0h = n0 + h * kBN;
               if (!p.b_mn_major) {
-                tma_load_3d<kCta>(sbh, mb, full, kc, n0h, mat);
+                load(sbh, mb, full, kc, n0h, mat);
               } else {
 #pragma unroll
                 for (int c = 0; c < BN_LOCAL / CH; c++)
-                  tma_load_3d<kCta>(sbh + c * (BK * 128), mb, full, n0h + c * CH, kc, mat);
+                  load(sbh + c * (BK * 128), mb, full, n0h + c * CH, kc, mat);
               }
             }
           }
@@ -875,6 +924,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap mapA_hi, const __grid_constan
     if (store_leader && p.tma_store) asm volatile("prefetch.tensormap [%0];" ::"l"((unsigned long long)&mapC.m[0]) : "memory");
     TileCoord t = decode_tile(tile_first < p.total_tiles ? tile_first : 0, p);
     pdl_wait();
+    if (warp == 2 && store_leader) pdl_release();   // one thread per CTA is enough
     for (int64_t tile = tile_first; ok && tile < p.total_tiles; tile += tile_step) {
       if (tile != tile_first) t = decode_tile(tile, p);
       const int64_t gm = (int64_t)t.tm * (BM * kCta) + rank * BM + quarter * 32 + lane;
@@ -1117,8 +1167,8 @@ struct ReduceJob {
 
 template <bool kHalf>
 __global__ void __launch_bounds__(256) splitk_reduce_kernel(const ReduceJob j) {
-  pdl_release();
   pdl_wait();
+  pdl_release();
   const int64_t groups = j.ws_ld / 4;
   const int64_t total = j.batch * j.M * groups;
   const int64_t part_stride = j.M * j.ws_ld;
@@ -1171,6 +1221,7 @@ struct SplitJob {
   float *hi, *lo;
   int64_t rows, width, ld_src, ld_dst, stride_src, stride_dst, batch;
   int vec4;   // rows, pitches and bases allow 16-byte accesses
+  int raw;    // diagnostics build only: hi = x unrounded, lo = 0 (how does the MMA read a raw float?)
 };
 
 __device__ __forceinline__ void split_one(float x, float& h, float& l) {
@@ -1191,8 +1242,8 @@ __device__ __forceinline__ void split_one(float x, float& h, float& l) {
 
 // One launch splits both operands: the first `blocks_a` blocks work on A, the rest on B.
 __global__ void __launch_bounds__(256) split_tf32_kernel(const SplitJob ja, const SplitJob jb, int blocks_a) {
-  pdl_release();
   pdl_wait();
+  pdl_release();
   const bool is_a = (int)blockIdx.x < blocks_a;
   const SplitJob& j = is_a ? ja : jb;
   const int64_t bid = is_a ? blockIdx.x : blockIdx.x - blocks_a;
@@ -1204,6 +1255,7 @@ __global__ void __launch_bounds__(256) split_tf32_kernel(const SplitJob ja, cons
       const float4 x = *(const float4*)(j.src + b * j.stride_src + r * j.ld_src + c);
       float4 h, l;
       split_one(x.x, h.x, l.x); split_one(x.y, h.y, l.y); split_one(x.z, h.z, l.z); split_one(x.w, h.w, l.w);
+      if (j.raw) { h = x; l = make_float4(0.f, 0.f, 0.f, 0.f); }
       *(float4*)(j.hi + b * j.stride_dst + r * j.ld_dst + c) = h;
       *(float4*)(j.lo + b * j.stride_dst + r * j.ld_dst + c) = l;
     }
@@ -1213,6 +1265,7 @@ __global__ void __launch_bounds__(256) split_tf32_kernel(const SplitJob ja, cons
       const int64_t c = i % j.width, r = (i / j.width) % j.rows, b = i / (j.width * j.rows);
       float h, l;
       split_one(j.src[b * j.stride_src + r * j.ld_src + c], h, l);
+      if (j.raw) { h = j.src[b * j.stride_src + r * j.ld_src + c]; l = 0.f; }
       j.hi[b * j.stride_dst + r * j.ld_dst + c] = h;
       j.lo[b * j.stride_dst + r * j.ld_dst + c] = l;
     }
@@ -1227,8 +1280,8 @@ struct RepackJob {
   int64_t rows, width, ld_src, ld_dst, stride_src, stride_dst, batch;
 };
 __global__ void __launch_bounds__(256) repack_f16_kernel(const RepackJob ja, const RepackJob jb, int blocks_a) {
-  pdl_release();
   pdl_wait();
+  pdl_release();
   const bool is_a = (int)blockIdx.x < blocks_a;
   const RepackJob& j = is_a ? ja : jb;
   const int64_t bid = is_a ? blockIdx.x : blockIdx.x - blocks_a;
@@ -1321,6 +1374,7 @@ struct Tunables {
   int short_k = 8;        // HC_TC_SHORT_K: slabs up to which the eight-warp epilogue config is used
   int group_m = 0;        // HC_TC_GROUP_M: tile rows sharing a sweep over the columns (0: default)
   int wide_epi8 = 1;      // HC_TC_WIDE_EPI8: eight epilogue warps on the 256x512 tile
+  int l2_hints = 1;       // HC_TC_L2_HINTS: L2 eviction priorities on operand loads of multi-wave products
 };
 #ifdef HC_DIAGNOSTICS
 Tunables read_tunables() {
@@ -1339,6 +1393,7 @@ Tunables read_tunables() {
     else if (n == 7 && !strncmp(k, "SHORT_K", 7)) t.short_k = v;
     else if (n == 7 && !strncmp(k, "GROUP_M", 7)) t.group_m = v;
     else if (n == 9 && !strncmp(k, "WIDE_EPI8", 9)) t.wide_epi8 = v;
+    else if (n == 8 && !strncmp(k, "L2_HINTS", 8)) t.l2_hints = v;
   }
   return t;
 }
@@ -1347,7 +1402,8 @@ int env_int(const char* name, int fallback) {
   return e ? atoi(e) : fallback;
 }
 // HC_TC_DEBUG bits: 2 = no accumulation windows, 4 = never pair CTAs, 128 = direct stores instead
-// of TMA stores.
+// of TMA stores, 32 = feed the float32 operands to the MMA unsplit (an experiment on how the
+// tensor core reads a raw float; results are then plain TF32 products).
 int debug_flags() {
   static int v = env_int("HC_TC_DEBUG", 0);
   return v;
@@ -1667,7 +1723,38 @@ struct TcPrepared {
   ReduceJob job;
   int reduce_blocks = 0;
   size_t scratch_used = 0;           // bytes of the work area this product touches
+  // Address ranges the main kernel reads (operands, bias) and this device's range it writes.
+  uintptr_t in_lo[3] = {0, 0, 0}, in_hi[3] = {0, 0, 0};
+  uintptr_t out_lo = 0, out_hi = 0;
+  bool trackable = false;            // one kernel, no pre-pass, no second kernel: the ranges say it all
 };
+
+// What the tensor-core kernel most recently launched on a stream wrote.  Consulted only for
+// streams the library owns (nobody else enqueues kernels there), where it decides whether the
+// next kernel's operand loads may run ahead of the wait for its predecessor.
+struct StreamTrack {
+  cudaStream_t stream = nullptr;
+  bool used = false, known = false;
+  uintptr_t lo = 0, hi = 0;
+  uint64_t stamp = 0;
+};
+std::mutex g_track_mu;
+StreamTrack g_track[16];
+uint64_t g_track_clock = 0;
+
+StreamTrack* track_entry(cudaStream_t stream, bool create) {
+  StreamTrack* victim = &g_track[0];
+  for (auto& t : g_track) {
+    if (t.used && t.stream == stream) return &t;
+    if (!t.used ? victim->used : (victim->used && t.stamp < victim->stamp)) victim = &t;
+  }
+  if (!create) return nullptr;
+  *victim = StreamTrack();
+  victim->stream = stream;
+  victim->used = true;
+  return victim;
+}
+
 
 struct TcKey {
   int dtype, a_mn, b_mn, no_split, n_extra, may_split;
@@ -1769,9 +1856,9 @@ cudaError_t prepare_tc(const GemmProblem& p, unsigned int* status_word, void* sc
       return (int)(width % 4 == 0 && ld % 4 == 0 && ((uintptr_t)src & 15) == 0 && (batch == 1 || stride % 4 == 0));
     };
     pp.sja = SplitJob{(const float*)p.A, ah, al, s.a_rows, s.a_width, p.lda, s.a_ld, p.strideA, s.a_mat, p.batch,
-                      vec_ok4(p.A, s.a_width, p.lda, p.strideA, p.batch)};
+                      vec_ok4(p.A, s.a_width, p.lda, p.strideA, p.batch), (debug_flags() & 32) ? 1 : 0};
     pp.sjb = SplitJob{(const float*)p.B, bh, bl, s.b_rows, s.b_width, p.ldb, s.b_ld, p.strideB, s.b_mat, p.batch,
-                      vec_ok4(p.B, s.b_width, p.ldb, p.strideB, p.batch)};
+                      vec_ok4(p.B, s.b_width, p.ldb, p.strideB, p.batch), (debug_flags() & 32) ? 1 : 0};
     auto blocks = [&](const SplitJob& j) {
       const int64_t work = j.batch * j.rows * (j.vec4 ? j.width / 4 : j.width);
       int64_t b = (work + 255) / 256;
@@ -1832,6 +1919,10 @@ cudaError_t prepare_tc(const GemmProblem& p, unsigned int* status_word, void* sc
   tp.group_m = tun.group_m > 0 ? tun.group_m : wide ? 16 : 16 / cta;
   tp.a_mn_major = p.a_mn_major; tp.b_mn_major = p.b_mn_major;
   tp.status = status_word;
+  tp.skip_input_wait = 0;
+  // Eviction priorities only matter when a band of A is revisited by later waves: more than one
+  // wave of tiles, and several tile columns to sweep.
+  tp.l2_hints = (tun.l2_hints && tp.tiles_n > 1 && tp.total_tiles > (cta == 2 ? sm_count / 2 : sm_count)) ? 1 : 0;
   // Where the tiles go: the result itself, or - for a cut contraction - float32 partial matrices
   // in the work area (part z of matrix m at index m * parts + z), which a second kernel sums.
   void* out_base = p.C;
@@ -1863,6 +1954,23 @@ cudaError_t prepare_tc(const GemmProblem& p, unsigned int* status_word, void* sc
         return cudaErrorNotSupported;
     }
     tp.n_out = 1 + n_extra;
+  }
+
+  {
+    auto span = [&](const void* base, int64_t rows_, int64_t ld, int64_t stride, int64_t batch, int idx) {
+      const int64_t per = rows_ * ld;
+      const int64_t elems = (batch - 1) * (stride > per ? stride : per) + per;
+      pp.in_lo[idx] = (uintptr_t)base;
+      pp.in_hi[idx] = (uintptr_t)base + (uintptr_t)(elems * eb);
+    };
+    span(p.A, p.a_mn_major ? p.K : p.M, p.lda, p.strideA, p.batch, 0);
+    span(p.B, p.b_mn_major ? p.K : p.N, p.ldb, p.strideB, p.batch, 1);
+    pp.in_lo[2] = (uintptr_t)p.bias;
+    pp.in_hi[2] = p.bias ? (uintptr_t)p.bias + (uintptr_t)(p.N * eb) : 0;
+    const int64_t per_c = p.M * p.ldc;
+    pp.out_lo = (uintptr_t)p.C;
+    pp.out_hi = (uintptr_t)p.C + (uintptr_t)(((p.batch - 1) * (p.strideC > per_c ? p.strideC : per_c) + per_c) * eb);
+    pp.trackable = (pp.pre == 0 && !cut);
   }
 
   TcLaunchFn fn = nullptr;
@@ -1916,7 +2024,7 @@ cudaError_t prepare_tc(const GemmProblem& p, unsigned int* status_word, void* sc
   return cudaSuccess;
 }
 
-cudaError_t issue_tc(const TcPrepared& pp, int sm_count, cudaStream_t stream, LaunchRecord* rec) {
+cudaError_t issue_tc(const TcPrepared& pp, int sm_count, cudaStream_t stream, LaunchRecord* rec, bool private_stream) {
   if (rec) { *rec = LaunchRecord(); rec->kernel = HC_KERNEL_TENSOR; rec->scratch_bytes = pp.scratch_used; }
   if (pp.pre == 1) {
     int blocks_a = pp.pre_blocks_a;
@@ -1932,9 +2040,35 @@ cudaError_t issue_tc(const TcPrepared& pp, int sm_count, cudaStream_t stream, La
     if (rec) rec->launches += 1;
   }
   if (rec) rec->tiles = pp.tp.total_tiles;
+  // May the operand loads run ahead of the wait for the previous kernel?  Only on a stream no one
+  // else launches kernels on, only against a predecessor whose written range is known, and only
+  // when that range and this product's operands are disjoint.  (Anything else enqueued on the
+  // stream in between - copies, ordinary kernels, event waits - completes before this kernel
+  // starts at all.)
+  bool skip = false;
+  if (private_stream && overlap_launches()) {
+    std::lock_guard<std::mutex> lock(g_track_mu);
+    StreamTrack* t = track_entry(stream, true);
+    if (t->known && pp.trackable) {
+      skip = true;
+      for (int i = 0; i < 3; i++)
+        if (pp.in_hi[i] > pp.in_lo[i] && pp.in_lo[i] < t->hi && t->lo < pp.in_hi[i]) skip = false;
+    }
+    t->known = pp.trackable;
+    t->lo = pp.out_lo;
+    t->hi = pp.out_hi;
+    t->stamp = ++g_track_clock;
+  }
   // cudaLaunchKernelEx reports this launch's own failure; the thread's sticky-less "last error"
   // may hold another library's earlier error and is not this launch's to report.
-  cudaError_t ge = pp.fn(pp.maps, pp.outs, pp.tp, sm_count, stream, rec);
+  cudaError_t ge;
+  if (skip) {
+    TcParams tp = pp.tp;
+    tp.skip_input_wait = 1;
+    ge = pp.fn(pp.maps, pp.outs, tp, sm_count, stream, rec);
+  } else {
+    ge = pp.fn(pp.maps, pp.outs, pp.tp, sm_count, stream, rec);
+  }
   if (ge != cudaSuccess || !pp.cut) return ge;
   void* args[1] = {(void*)&pp.job};
   cudaError_t re = launch_elementwise(pp.reduce_half ? (const void*)splitk_reduce_kernel<true>
@@ -1949,7 +2083,7 @@ cudaError_t issue_tc(const TcPrepared& pp, int sm_count, cudaStream_t stream, La
 
 cudaError_t launch_tc(const GemmProblem& p, cudaStream_t stream, unsigned int* status_word, void* scratch,
                       size_t scratch_bytes, int sm_count, LaunchRecord* rec, void* const* extra_out, int n_extra,
-                      TcCache* cache, size_t* scratch_needed) {
+                      TcCache* cache, size_t* scratch_needed, bool private_stream) {
   if (scratch_needed) *scratch_needed = 0;
   if (!tc_supported(p)) return cudaErrorNotSupported;
   if (n_extra < 0 || n_extra > kMaxOut - 1 || (n_extra > 0 && !extra_out)) return cudaErrorInvalidValue;
@@ -1959,7 +2093,7 @@ cudaError_t launch_tc(const GemmProblem& p, cudaStream_t stream, unsigned int* s
     for (auto& x : cache->e) {
       if (x.used && memcmp(&x.key, &key, sizeof key) == 0) {
         x.stamp = ++cache->clock;
-        return issue_tc(x.prep, sm_count, stream, rec);
+        return issue_tc(x.prep, sm_count, stream, rec, private_stream);
       }
       if (!x.used ? victim->used : (victim->used && x.stamp < victim->stamp)) victim = &x;
     }
@@ -1970,12 +2104,12 @@ cudaError_t launch_tc(const GemmProblem& p, cudaStream_t stream, unsigned int* s
     victim->key = key;
     victim->stamp = ++cache->clock;
     victim->used = true;
-    return issue_tc(victim->prep, sm_count, stream, rec);
+    return issue_tc(victim->prep, sm_count, stream, rec, private_stream);
   }
   TcPrepared prep;
   cudaError_t e = prepare_tc(p, status_word, scratch, scratch_bytes, sm_count, extra_out, n_extra, &prep, scratch_needed);
   if (e != cudaSuccess) return e;
-  return issue_tc(prep, sm_count, stream, rec);
+  return issue_tc(prep, sm_count, stream, rec, private_stream);
 }
 
 }  // namespace hc

@@ -186,14 +186,15 @@ constexpr int64_t kAutoTensorMinWork = 64ll * 64 * 64;
 cudaError_t launch_tensor(hc_ctx* ctx, const hc::GemmProblem& p, void* const* extra, int n_extra, hc_status* st) {
   *st = HC_OK;
   size_t need = 0;
+  const bool private_stream = ctx->stream == ctx->own_stream;
   cudaError_t e = hc::launch_tc(p, ctx->stream, ctx->status_word, ctx->scratch, ctx->scratch_bytes, ctx->sm_count,
-                                &ctx->last, extra, n_extra, ctx->cache, &need);
+                                &ctx->last, extra, n_extra, ctx->cache, &need, private_stream);
   if (e == cudaErrorInvalidValue && need > ctx->scratch_bytes) {
     *st = ensure_buffer(ctx, &ctx->scratch, &ctx->scratch_bytes, need, ctx->stream);
     if (*st != HC_OK) return cudaErrorMemoryAllocation;
     hc::tc_cache_clear(ctx->cache);   // prepared launches point into the old work area
     e = hc::launch_tc(p, ctx->stream, ctx->status_word, ctx->scratch, ctx->scratch_bytes, ctx->sm_count, &ctx->last,
-                      extra, n_extra, ctx->cache, &need);
+                      extra, n_extra, ctx->cache, &need, private_stream);
   }
   return e;
 }
