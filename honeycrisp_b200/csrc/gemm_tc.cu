@@ -56,6 +56,7 @@
 // the context's status word, raises a CTA-wide abort flag and the CTA leaves through the
 // normal teardown (tensor memory is freed).  The host reports HC_ERR_TIMEOUT.
 #include <cuda.h>
+#include <cstdio>
 #include <cstdlib>
 #include <cstring>
 #include <mutex>
@@ -550,6 +551,10 @@ __device__ __forceinline__ KRange k_range(int64_t vmat, const TcParams& p) {
 // kSlabs    : 128-byte k slabs per pipeline slot.  Two halve the barrier round trips per k, which
 //             is what bounds the small tile shapes (their MMAs are shorter than the issue loop).
 // kPartial  : float16 operands, float32 results: the partial sums of a contraction cut into parts.
+// One CTA per SM: a kernel that allocates tensor memory (tcgen05.alloc) is never given a second
+// resident CTA on an SM, however little shared memory and however few registers it uses (the
+// occupancy query answers 1 for any such kernel; measured).  Overlap across the end of one launch
+// and the start of the next therefore has to come from programmatic dependent launch alone.
 template <int kElemBytes, int kBN, int kStages, int kEpiWarps, bool kWindowed, int kCta, int kNSplit, int kSlabs,
           bool kPartial>
 __global__ void __launch_bounds__(96 + 32 * kEpiWarps, 1)
@@ -1446,6 +1451,9 @@ struct TcConfig {
     if (dev < 64 && !configured[dev]) {
       cudaError_t e = cudaFuncSetAttribute(kernel(), cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
       if (e != cudaSuccess) return e;
+      // All of the SM's configurable memory as shared memory: nothing here uses the L1 cache.
+      e = cudaFuncSetAttribute(kernel(), cudaFuncAttributePreferredSharedMemoryCarveout, (int)cudaSharedmemCarveoutMaxShared);
+      if (e != cudaSuccess) cudaGetLastError();
       if (kCta == 2) {
         e = cudaFuncSetAttribute(kernel(), cudaFuncAttributeNonPortableClusterSizeAllowed, 0);
         if (e != cudaSuccess) cudaGetLastError();
@@ -1462,8 +1470,9 @@ struct TcConfig {
     int dev = 0;
     cudaGetDevice(&dev);
     if (dev < 64 && cached[dev]) return cached[dev];
+    configure();   // the answer depends on the shared-memory attributes
     cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3((unsigned)(sm_count / 2 * 2));
+    cfg.gridDim = dim3((unsigned)(sm_count * 4));   // more than can be resident: the answer is the limit
     cfg.blockDim = dim3(block);
     cfg.dynamicSmemBytes = smem;
     cudaLaunchAttribute attr;
