@@ -93,7 +93,6 @@ struct TcParams {
   int tma_store;      // results leave through shared memory and TMA stores (else direct stores)
   const void* bias;   // optional row vector added to the rounded product (Linear), or null
   int n_out;          // destinations of every result tile: this device's result, then peers' copies
-  int l2_hints;       // operand loads carry L2 eviction priorities (see tma_load_3d_hint)
   int skip_input_wait;  // the operands are known not to be written by the kernel launched just before
 };
 
@@ -269,38 +268,6 @@ __device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map
         "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes "
         "[%0], [%1, {%3, %4, %5}], [%2];"
         ::"r"(dst), "l"((unsigned long long)map), "r"(bar), "r"(c0), "r"(c1), "r"(c2)
-        : "memory");
-  }
-}
-
-// The same load with an L2 eviction priority.  A wave of tiles shares a band of A rows with the
-// next wave (tiles are walked column by column inside a group of tile rows), while each panel of B
-// columns is read by one wave and never again: A lines are asked to stay (evict_last), B lines to
-// go first (evict_first), so the band survives in L2 instead of being re-read from HBM every wave.
-__device__ __forceinline__ uint64_t l2_policy_evict_last() {
-  uint64_t p;
-  asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(p));
-  return p;
-}
-__device__ __forceinline__ uint64_t l2_policy_evict_first() {
-  uint64_t p;
-  asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(p));
-  return p;
-}
-template <int kCta>
-__device__ __forceinline__ void tma_load_3d_hint(uint32_t dst, const CUtensorMap* map, uint32_t bar,
-                                                 int c0, int c1, int c2, uint64_t policy) {
-  if (kCta == 2) {
-    asm volatile(
-        "cp.async.bulk.tensor.3d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint "
-        "[%0], [%1, {%3, %4, %5}], [%2], %6;"
-        ::"r"(dst), "l"((unsigned long long)map), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "l"(policy)
-        : "memory");
-  } else {
-    asm volatile(
-        "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes.L2::cache_hint "
-        "[%0], [%1, {%3, %4, %5}], [%2], %6;"
-        ::"r"(dst), "l"((unsigned long long)map), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "l"(policy)
         : "memory");
   }
 }
@@ -659,11 +626,11 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap mapA_hi, const __grid_constan
       }
       // Completion bytes of both CTAs of a pair are counted on the leader's barrier.
       const uint32_t full_leader = (kCta == 2) ? map_to_cta(bar_full, 0) : bar_full;
-      const bool hinted = p.l2_hints != 0;
-      const uint64_t policy = do_a ? l2_policy_evict_last() : l2_policy_evict_first();
+      // (L2 eviction priorities on these loads - the band of A a wave shares with the next one
+      // asked to stay, the panels of B to go first - were measured at 8192^3: evict_last changes
+      // nothing (897-913 MB read from DRAM either way), evict_first on B doubles the reads.)
       auto load = [&](uint32_t dst, const CUtensorMap* map, uint32_t bar, int c0, int c1, int c2) {
-        if (hinted) tma_load_3d_hint<kCta>(dst, map, bar, c0, c1, c2, policy);
-        else tma_load_3d<kCta>(dst, map, bar, c0, c1, c2);
+        tma_load_3d<kCta>(dst, map, bar, c0, c1, c2);
       };
       uint32_t s = 0, ph = 0;
       bool ok = true;
@@ -1379,7 +1346,6 @@ struct Tunables {
   int short_k = 8;        // HC_TC_SHORT_K: slabs up to which the eight-warp epilogue config is used
   int group_m = 0;        // HC_TC_GROUP_M: tile rows sharing a sweep over the columns (0: default)
   int wide_epi8 = 1;      // HC_TC_WIDE_EPI8: eight epilogue warps on the 256x512 tile
-  int l2_hints = 1;       // HC_TC_L2_HINTS: L2 eviction priorities on operand loads of multi-wave products
 };
 #ifdef HC_DIAGNOSTICS
 Tunables read_tunables() {
@@ -1398,7 +1364,6 @@ Tunables read_tunables() {
     else if (n == 7 && !strncmp(k, "SHORT_K", 7)) t.short_k = v;
     else if (n == 7 && !strncmp(k, "GROUP_M", 7)) t.group_m = v;
     else if (n == 9 && !strncmp(k, "WIDE_EPI8", 9)) t.wide_epi8 = v;
-    else if (n == 8 && !strncmp(k, "L2_HINTS", 8)) t.l2_hints = v;
   }
   return t;
 }
@@ -1929,9 +1894,6 @@ cudaError_t prepare_tc(const GemmProblem& p, unsigned int* status_word, void* sc
   tp.a_mn_major = p.a_mn_major; tp.b_mn_major = p.b_mn_major;
   tp.status = status_word;
   tp.skip_input_wait = 0;
-  // Eviction priorities only matter when a band of A is revisited by later waves: more than one
-  // wave of tiles, and several tile columns to sweep.
-  tp.l2_hints = (tun.l2_hints && tp.tiles_n > 1 && tp.total_tiles > (cta == 2 ? sm_count / 2 : sm_count)) ? 1 : 0;
   // Where the tiles go: the result itself, or - for a cut contraction - float32 partial matrices
   // in the work area (part z of matrix m at index m * parts + z), which a second kernel sums.
   void* out_base = p.C;
