@@ -1185,31 +1185,25 @@ __global__ void __launch_bounds__(256) splitk_reduce_kernel(const ReduceJob j) {
   }
 }
 
-// Splits float32 into two TF32-representable parts: hi = nearest TF32 of x, lo = nearest TF32
-// of (x - hi).  x - hi is exact in float32.  Non-finite x: hi = x, lo = 0, so infinities and
-// NaNs propagate through the hi*hi product only.
+// float32 as two TF32 operands: x = hi + lo with hi = x truncated to TF32's 10 mantissa bits and
+// lo = nearest TF32 of (x - hi), which is exact in float32.  hi is never computed: kind::tf32
+// reads a float32 operand by dropping its low 13 mantissa bits (measured on both operands: the
+// MMA of 1 + 2^-11 + 2^-12 by 1 gives 1, not the 1 + 2^-10 rounding would give), so the operand
+// itself serves as hi and only lo is written.  Non-finite x: lo = 0, so infinities and NaNs
+// propagate through the hi*hi product only.
 struct SplitJob {
   const float* src;
-  float *hi, *lo;
+  float *hi, *lo;     // hi: null, or where to put a TMA-addressable copy of src
   int64_t rows, width, ld_src, ld_dst, stride_src, stride_dst, batch;
   int vec4;   // rows, pitches and bases allow 16-byte accesses
-  int raw;    // diagnostics build only: hi = x unrounded, lo = 0 (how does the MMA read a raw float?)
 };
 
-__device__ __forceinline__ void split_one(float x, float& h, float& l) {
-  uint32_t hbits;
-  asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(hbits) : "f"(x));
-  h = __uint_as_float(hbits & 0xFFFFE000u);
-  l = 0.0f;
-  if (isfinite(x)) {
-    if (!isfinite(h)) h = __uint_as_float(__float_as_uint(x) & 0xFFFFE000u);
-    const float d = x - h;
-    uint32_t lbits;
-    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(lbits) : "f"(d));
-    l = __uint_as_float(lbits & 0xFFFFE000u);
-  } else {
-    h = x;
-  }
+__device__ __forceinline__ float split_lo(float x) {
+  if (!isfinite(x)) return 0.0f;
+  const float d = x - __uint_as_float(__float_as_uint(x) & 0xFFFFE000u);
+  uint32_t lbits;
+  asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(lbits) : "f"(d));
+  return __uint_as_float(lbits & 0xFFFFE000u);
 }
 
 // One launch splits both operands: the first `blocks_a` blocks work on A, the rest on B.
@@ -1225,21 +1219,17 @@ __global__ void __launch_bounds__(256) split_tf32_kernel(const SplitJob ja, cons
     for (int64_t i = bid * blockDim.x + threadIdx.x; i < total; i += nblk * blockDim.x) {
       const int64_t c = (i % w4) * 4, r = (i / w4) % j.rows, b = i / (w4 * j.rows);
       const float4 x = *(const float4*)(j.src + b * j.stride_src + r * j.ld_src + c);
-      float4 h, l;
-      split_one(x.x, h.x, l.x); split_one(x.y, h.y, l.y); split_one(x.z, h.z, l.z); split_one(x.w, h.w, l.w);
-      if (j.raw) { h = x; l = make_float4(0.f, 0.f, 0.f, 0.f); }
-      *(float4*)(j.hi + b * j.stride_dst + r * j.ld_dst + c) = h;
-      *(float4*)(j.lo + b * j.stride_dst + r * j.ld_dst + c) = l;
+      if (j.hi) *(float4*)(j.hi + b * j.stride_dst + r * j.ld_dst + c) = x;
+      *(float4*)(j.lo + b * j.stride_dst + r * j.ld_dst + c) =
+          make_float4(split_lo(x.x), split_lo(x.y), split_lo(x.z), split_lo(x.w));
     }
   } else {
     const int64_t total = j.batch * j.rows * j.width;
     for (int64_t i = bid * blockDim.x + threadIdx.x; i < total; i += nblk * blockDim.x) {
       const int64_t c = i % j.width, r = (i / j.width) % j.rows, b = i / (j.width * j.rows);
-      float h, l;
-      split_one(j.src[b * j.stride_src + r * j.ld_src + c], h, l);
-      if (j.raw) { h = j.src[b * j.stride_src + r * j.ld_src + c]; l = 0.f; }
-      j.hi[b * j.stride_dst + r * j.ld_dst + c] = h;
-      j.lo[b * j.stride_dst + r * j.ld_dst + c] = l;
+      const float x = j.src[b * j.stride_src + r * j.ld_src + c];
+      if (j.hi) j.hi[b * j.stride_dst + r * j.ld_dst + c] = x;
+      j.lo[b * j.stride_dst + r * j.ld_dst + c] = split_lo(x);
     }
   }
 }
@@ -1372,8 +1362,7 @@ int env_int(const char* name, int fallback) {
   return e ? atoi(e) : fallback;
 }
 // HC_TC_DEBUG bits: 2 = no accumulation windows, 4 = never pair CTAs, 128 = direct stores instead
-// of TMA stores, 32 = feed the float32 operands to the MMA unsplit (an experiment on how the
-// tensor core reads a raw float; results are then plain TF32 products).
+// of TMA stores
 int debug_flags() {
   static int v = env_int("HC_TC_DEBUG", 0);
   return v;
@@ -1501,12 +1490,15 @@ bool tc_supported(const GemmProblem& p) {
   return encode_fn() != nullptr;
 }
 
-// float32 products split both operands into hi and lo copies, stored compactly with the
-// leading dimension rounded up to four elements so TMA can address them.
+// float32 products: the lo halves of both operands are stored compactly, with the leading
+// dimension rounded up to four elements so TMA can address them.  The hi half is the operand
+// where it lies; only an operand TMA cannot address (base or pitches not multiples of 16 bytes)
+// is also copied, into the same compact layout.
 static inline int64_t round4(int64_t x) { return (x + 3) & ~3ll; }
 struct SplitLayout {
   int64_t a_rows, a_width, a_ld, a_mat, b_rows, b_width, b_ld, b_mat;
-  size_t a_bytes, b_bytes;
+  size_t a_bytes, b_bytes;   // of one compact array
+  bool a_copy, b_copy;       // the operand needs a TMA-addressable copy as its hi half
 };
 static SplitLayout split_layout(const GemmProblem& p) {
   SplitLayout s;
@@ -1516,6 +1508,8 @@ static SplitLayout split_layout(const GemmProblem& p) {
   s.a_mat = s.a_rows * s.a_ld; s.b_mat = s.b_rows * s.b_ld;
   s.a_bytes = ((size_t)(s.a_mat * p.batch) * 4 + 255) & ~(size_t)255;
   s.b_bytes = ((size_t)(s.b_mat * p.batch) * 4 + 255) & ~(size_t)255;
+  s.a_copy = !operand_ok(p.A, 4, p.lda, p.strideA, p.batch, p.M, p.K);
+  s.b_copy = !operand_ok(p.B, 4, p.ldb, p.strideB, p.batch, p.N, p.K);
   return s;
 }
 
@@ -1646,7 +1640,7 @@ static size_t operand_scratch_bytes(const GemmProblem& p) {
     return r.a_bytes + r.b_bytes;
   }
   const SplitLayout s = split_layout(p);
-  return 2 * s.a_bytes + 2 * s.b_bytes;
+  return (s.a_copy ? 2 : 1) * s.a_bytes + (s.b_copy ? 2 : 1) * s.b_bytes;
 }
 
 // Work area of one product: re-laid operands (float32 hi/lo parts, repacked float16), then,
@@ -1804,6 +1798,7 @@ cudaError_t prepare_tc(const GemmProblem& p, unsigned int* status_word, void* sc
 
   const void *a_hi = p.A, *a_lo = p.A, *b_hi = p.B, *b_lo = p.B;
   int64_t lda = p.lda, ldb = p.ldb, sa = p.strideA, sb = p.strideB;
+  int64_t lda_lo = 0, ldb_lo = 0, sa_lo = 0, sb_lo = 0;   // float32: layout of the lo arrays
   pp.pre = 0;
   if (!f32) {
     const RepackLayout r = repack_layout(p);
@@ -1824,15 +1819,21 @@ cudaError_t prepare_tc(const GemmProblem& p, unsigned int* status_word, void* sc
     }
   } else {
     const SplitLayout s = split_layout(p);
-    float* ah = (float*)scratch; float* al = (float*)((char*)ah + s.a_bytes);
-    float* bh = (float*)((char*)al + s.a_bytes); float* bl = (float*)((char*)bh + s.b_bytes);
+    // Work area: [A lo][A copy, if needed][B lo][B copy, if needed]
+    char* at = (char*)scratch;
+    float* al = (float*)at; at += s.a_bytes;
+    float* ah = nullptr;
+    if (s.a_copy) { ah = (float*)at; at += s.a_bytes; }
+    float* bl = (float*)at; at += s.b_bytes;
+    float* bh = nullptr;
+    if (s.b_copy) { bh = (float*)at; at += s.b_bytes; }
     auto vec_ok4 = [](const void* src, int64_t width, int64_t ld, int64_t stride, int64_t batch) {
       return (int)(width % 4 == 0 && ld % 4 == 0 && ((uintptr_t)src & 15) == 0 && (batch == 1 || stride % 4 == 0));
     };
     pp.sja = SplitJob{(const float*)p.A, ah, al, s.a_rows, s.a_width, p.lda, s.a_ld, p.strideA, s.a_mat, p.batch,
-                      vec_ok4(p.A, s.a_width, p.lda, p.strideA, p.batch), (debug_flags() & 32) ? 1 : 0};
+                      vec_ok4(p.A, s.a_width, p.lda, p.strideA, p.batch)};
     pp.sjb = SplitJob{(const float*)p.B, bh, bl, s.b_rows, s.b_width, p.ldb, s.b_ld, p.strideB, s.b_mat, p.batch,
-                      vec_ok4(p.B, s.b_width, p.ldb, p.strideB, p.batch), (debug_flags() & 32) ? 1 : 0};
+                      vec_ok4(p.B, s.b_width, p.ldb, p.strideB, p.batch)};
     auto blocks = [&](const SplitJob& j) {
       const int64_t work = j.batch * j.rows * (j.vec4 ? j.width / 4 : j.width);
       int64_t b = (work + 255) / 256;
@@ -1840,8 +1841,10 @@ cudaError_t prepare_tc(const GemmProblem& p, unsigned int* status_word, void* sc
     };
     pp.pre_blocks_a = blocks(pp.sja); pp.pre_blocks_b = blocks(pp.sjb);
     pp.pre = 2;
-    a_hi = ah; a_lo = al; b_hi = bh; b_lo = bl;
-    lda = s.a_ld; ldb = s.b_ld; sa = s.a_mat; sb = s.b_mat;
+    a_lo = al; b_lo = bl;
+    lda_lo = s.a_ld; ldb_lo = s.b_ld; sa_lo = s.a_mat; sb_lo = s.b_mat;
+    if (s.a_copy) { a_hi = ah; lda = s.a_ld; sa = s.a_mat; }
+    if (s.b_copy) { b_hi = bh; ldb = s.b_ld; sb = s.b_mat; }
   }
 
   const int dbg = debug_flags();
@@ -1856,8 +1859,8 @@ cudaError_t prepare_tc(const GemmProblem& p, unsigned int* status_word, void* sc
       !make_operand_map(&pp.maps[2], b_hi, eb, p.b_mn_major, p.N, p.K, ldb, sb, p.batch, b_box))
     return cudaErrorNotSupported;
   if (f32) {
-    if (!make_operand_map(&pp.maps[1], a_lo, eb, p.a_mn_major, p.M, p.K, lda, sa, p.batch, BM) ||
-        !make_operand_map(&pp.maps[3], b_lo, eb, p.b_mn_major, p.N, p.K, ldb, sb, p.batch, b_box))
+    if (!make_operand_map(&pp.maps[1], a_lo, eb, p.a_mn_major, p.M, p.K, lda_lo, sa_lo, p.batch, BM) ||
+        !make_operand_map(&pp.maps[3], b_lo, eb, p.b_mn_major, p.N, p.K, ldb_lo, sb_lo, p.batch, b_box))
       return cudaErrorNotSupported;
   } else {
     pp.maps[1] = pp.maps[0];   // float16 has no lo parts; the kernel never reads these two

@@ -1,8 +1,8 @@
 // hc_matmul_f32_static_scratch: the float32 tensor-core product for callers that must not
 // allocate device memory.
 //
-// The float32 product runs as 3xTF32 and needs a work area for the hi/lo halves of both
-// operands.  hc_matmul obtains that area with cudaMalloc on first use and grows it on demand.
+// The float32 product runs as 3xTF32 and needs a work area for the low halves of both
+// operands (and for a copy of an operand TMA cannot address where it lies).  hc_matmul obtains that area with cudaMalloc on first use and grows it on demand.
 // Some hosts cannot tolerate that: a framework whose own caching allocator has already claimed
 // the whole device (a cudaMalloc from inside a library then fails or fragments its pool), or a
 // latency-critical loop in which the implicit device-wide synchronisation of cudaMalloc/cudaFree
@@ -26,8 +26,8 @@
 
 #include "common.cuh"
 
-// Capacity of the static work area.  A product needs 8 * (rows*inner + inner*cols) bytes plus
-// alignment padding (two float32 copies of each operand), and a long contraction that is cut
+// Capacity of the static work area.  A product needs 4 * (rows*inner + inner*cols) bytes plus
+// alignment padding (one float32 array per operand; two for a misaligned one), and a long contraction that is cut
 // into parts another parts * rows * cols * 4 bytes for its partial sums.
 #define HC_STATIC_SCRATCH_BYTES (32u * 1024u * 1024u)
 

@@ -148,7 +148,7 @@ void hc_event_destroy(hc_event* ev);
  * Replaces: Backend.matmul(a:transA:b:transB:transOut:rows:inner:cols:dtype:)
  * (Sources/Honeycrisp/Backend.swift:650-658; CPU body BackendCPU.swift:1222-1232).
  * The products may use the context's work area, a device buffer that only grows (to the
- * largest need seen: float32 operands split into TF32 parts, float16 operands repacked to an
+ * largest need seen: the low TF32 halves of float32 operands, float16 operands repacked to an
  * aligned pitch, and at most 256 MiB of float32 partial sums when a long contraction over few
  * outputs is cut into parts); growing it is the only allocation a product makes, and it is
  * stream-ordered from the context's pool (no device-wide synchronisation).  A CUDA graph that
@@ -352,7 +352,8 @@ hc_status hc_group_selftest_missing_peer(hc_group* g, int limit_ms);
  * cannot afford the device-wide synchronisation cudaMalloc implies.  The work area of the
  * 3xTF32 split operands is a fixed array inside the library (hc_static_scratch_capacity()
  * bytes, held by every GPU that loads the library); a product needs about
- * 8 * (rows*inner + inner*cols) bytes of it, and a larger one is refused with
+ * 4 * (rows*inner + inner*cols) bytes of it (twice that for an operand whose address or row
+ * pitch is not a multiple of 16 bytes), and a larger one is refused with
  * HC_ERR_INVALID_ARGUMENT (hc_last_error says how much was needed).  The result is, bit for
  * bit, that of hc_batched_matmul_ex(ctx, HC_KERNEL_TENSOR, HC_F32, 1, ...) whenever that call's
  * whole work area fits into the array - including the float32 partial sums of a long contraction

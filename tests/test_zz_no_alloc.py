@@ -68,7 +68,7 @@ def test_static_scratch_product_matches_allocating_product_twice():
         assert np.array_equal(got.view(np.uint32), want.view(np.uint32)), "cut contraction"
         ref = a.reshape(rows, inner).astype(np.float64) @ b.reshape(inner, cols).astype(np.float64)
         assert np.linalg.norm(got.astype(np.float64) - ref.reshape(-1)) / np.linalg.norm(ref) < 1e-5
-        # A product whose split operands do not fit is refused, with the sizes in the message.
+        # A product whose work area does not fit is refused, with the sizes in the message.
         big = 4096
         st = lib.hc_matmul_f32_static_scratch(be._ctx, a_d.ptr, 0, b_d.ptr, 0, 0, big, big, big, out.ptr)
         assert st == _lib.HC_ERR_INVALID_ARGUMENT
