@@ -401,21 +401,35 @@ def run_ours(args):
     launch_ms = statistics.mean(x.elapsed_time(y) for x, y in evs)
     info = be.lastLaunchInfo()
 
-    # Sustained regime: the same step for about a second and a half, so that the power cap has
-    # settled (the default 20-100 steps end within the burst), with the vendor library's product on
-    # the same operands timed the same way right after it.
-    sustained = None
+    # The other configurations, lightest first: products of tens of microseconds are bound by
+    # latencies that scale with the SM clock, and the clock stays low for a while after seconds at
+    # the power cap - so they are timed before the long legs, and a sharded time and its 1-GPU time
+    # are always taken next to each other.
+    sharded, single, sustained = None, None, None
+    groups = None
     if not args.quick:
+        from honeycrisp_b200.sharding import DeviceGroup
+        groups = (DeviceGroup.fromTorchDistributed(be) if use_dist else DeviceGroup(be, 0, 1), DeviceGroup(be, 0, 1))
+        sharded = {"world": world,
+                   "how": "host-launched through hc_batched_matmul_sharded / hc_matmul_nsplit_allgather, CUDA events on "
+                          "the context's stream, max over ranks; one_gpu_ms: the whole problem on rank 0 alone in this "
+                          "run, the same way"}
+        sharded.update(sharded_c3(be, groups, stream, rank, world))
+        if world == 1:
+            single = single_gpu_configs(be, stream, heavy=False)
+        # Sustained regime: the same step for about a second and a half, so that the power cap has
+        # settled (the default 20-100 steps end within the burst), with the vendor library's product
+        # on the same operands timed the same way right after it.
         sustained = sustained_leg(be, stream, step, a, b, out, barrier, use_dist, world)
 
     link = link_probe(stream, use_dist, world)
 
-    sharded = None
     if not args.quick:
-        sharded = sharded_configs(be, stream, rank, world)   # collective: every rank takes part
-    single = None
-    if world == 1 and not args.quick:
-        single = single_gpu_configs(be, stream)
+        sharded.update(sharded_c5(be, groups, stream, rank, world))   # collective: every rank takes part
+        if world == 1:
+            single.update(single_gpu_configs(be, stream, heavy=True))
+        groups[1].close()
+        groups[0].close()
 
     if rank != 0:
         if use_dist:
@@ -808,57 +822,57 @@ def _device_timed(fn, iters, stream, use_dist, warm=3):
     return _max_over_ranks(e0.elapsed_time(e1) / iters, use_dist)
 
 
-def sharded_configs(be, stream, rank, world):
-    """The configurations that shard (strong scaling over the ranks), through the group entry points
-    of the C ABI, host-launched, device-timed, max over ranks:
-      c3        float16 batched Q.K^T (64 x [2048,128].[2048,128]^T) split over the batch, no collective;
-      c5_nccl   float32 16384^3 split over columns, blocks exchanged by ncclAllGather + one unpack kernel;
-      c5_fused  the same split with the exchange in the product kernel's epilogue (peer stores).
-    Each comes with the whole problem on rank 0 alone, same run, same loop: the 1-GPU time."""
+def sharded_c3(be, groups, stream, rank, world):
+    """float16 batched Q.K^T (64 x [2048,128].[2048,128]^T) split over the batch, no collective:
+    host-launched through the group entry point, device-timed, max over ranks; next to it the whole
+    batch on rank 0 alone, same loop, three rounds alternating, medians."""
     import numpy as np
     import torch
 
-    from honeycrisp_b200.sharding import DeviceGroup, columnBlock
-
     use_dist = world > 1
-    grp = DeviceGroup.fromTorchDistributed(be) if use_dist else DeviceGroup(be, 0, 1)
-    one = DeviceGroup(be, 0, 1)                       # the same entry points on one device
+    grp, one = groups
     peaks = load_peaks()
-    res = {"world": world, "how": "host-launched through hc_batched_matmul_sharded / hc_matmul_nsplit_allgather, "
-                                  "CUDA events on the context's stream, max over ranks; one_gpu_ms: the whole problem "
-                                  "on rank 0 alone in this run, the same way"}
-
-    # ---- C3
     cnt, rows, inner, cols = 64, 2048, 128, 2048
     begin, count = grp.shard(cnt)
     g = torch.Generator(device="cuda").manual_seed(2)
     q = torch.randn((cnt, rows, inner), generator=g, device="cuda").half()
     k = torch.randn((cnt, cols, inner), generator=g, device="cuda").half()
-    o = torch.empty(max(count, 1) * rows * cols, device="cuda", dtype=torch.float16)
+    o = torch.empty(cnt * rows * cols, device="cuda", dtype=torch.float16)
     qp, kp, op = q[begin:].data_ptr(), k[begin:].data_ptr(), o.data_ptr()
+    q0, k0 = q.data_ptr(), k.data_ptr()
     shard = lambda: grp.batchedMatmulSharded(cnt, qp, False, kp, True, False, rows, inner, cols, np.float16, op)
-    ms = _device_timed(shard, 200, stream, use_dist, warm=10)
+    whole = lambda: one.batchedMatmulSharded(cnt, q0, False, k0, True, False, rows, inner, cols, np.float16, op)
+    shard_ms, whole_ms = [], []
+    for _ in range(3):
+        shard_ms.append(_device_timed(shard, 200, stream, use_dist, warm=10))
+        t = _device_timed(whole, 50, stream, False, warm=5) if rank == 0 else 0.0
+        whole_ms.append(_max_over_ranks(t, use_dist))
+    ms, one_ms = statistics.median(shard_ms), statistics.median(whole_ms)
     flops = 2.0 * cnt * rows * cols * inner
     algo_bytes = 2 * cnt * rows * inner * 2 + cnt * rows * cols * 2
     c3 = {"ms": ms, "box_tflops": flops / ms / 1e9, "matrices_per_rank": count, "collective": "none",
-          "box_algorithmic_gbs": algo_bytes / ms / 1e6,
+          "box_algorithmic_gbs": algo_bytes / ms / 1e6, "rounds_ms": shard_ms,
+          "one_gpu_ms": one_ms, "one_gpu_rounds_ms": whole_ms, "speedup_over_one_gpu": one_ms / ms,
           "roofline": {"bound": "hbm", "achieved": algo_bytes / world / ms / 1e6, "peak": peaks["hbm_gbs"], "unit": "GB/s",
                        "frac": algo_bytes / world / ms / 1e6 / peaks["hbm_gbs"], "per": "GPU"}}
-    del o
-    one_ms = 0.0
-    if rank == 0:
-        o1 = torch.empty(cnt * rows * cols, device="cuda", dtype=torch.float16)
-        q0, k0, o1p = q.data_ptr(), k.data_ptr(), o1.data_ptr()
-        whole = lambda: one.batchedMatmulSharded(cnt, q0, False, k0, True, False, rows, inner, cols, np.float16, o1p)
-        one_ms = _device_timed(whole, 50, stream, False, warm=5)
-        del o1
-    one_ms = _max_over_ranks(one_ms, use_dist)
-    c3["one_gpu_ms"] = one_ms
-    c3["speedup_over_one_gpu"] = one_ms / ms
-    res["c3"] = c3
-    del q, k
+    del q, k, o
+    be.checkDeviceStatus()
+    return {"c3": c3}
 
-    # ---- C5
+
+def sharded_c5(be, groups, stream, rank, world):
+    """float32 16384^3 split over columns: blocks exchanged by ncclAllGather + one unpack kernel
+    (c5_nccl), or by the product kernel's epilogue with peer stores (c5_fused); and the whole product
+    on rank 0 alone in the same run."""
+    import numpy as np
+    import torch
+
+    from honeycrisp_b200.sharding import columnBlock
+
+    use_dist = world > 1
+    grp, one = groups
+    peaks = load_peaks()
+    res = {}
     n = 16384
     g = torch.Generator(device="cuda").manual_seed(4)
     a = torch.rand((n, n), generator=g, device="cuda") * 2 - 1
@@ -912,47 +926,49 @@ def sharded_configs(be, stream, rank, world):
                                 "frac": res[key]["box_tflops_effective"] / world / (peaks["burst"] / 6), "per": "GPU"}
     del a, b, c
     be.checkDeviceStatus()
-    one.close()
-    grp.close()
     return res
 
 
-def single_gpu_configs(be, stream):
-    """Roofline blocks of configurations 1, 3 and 5 on one GPU (host-launched, device-timed)."""
+def single_gpu_configs(be, stream, heavy):
+    """Roofline blocks on one GPU (host-launched, device-timed): configurations 1 and 3 (light), or
+    configuration 5 (heavy)."""
     import numpy as np
     import torch
     peaks = load_peaks()
     res = {}
     g = torch.Generator(device="cuda").manual_seed(0)
-    a = torch.rand((1024, 1024), generator=g, device="cuda"); b = torch.rand((1024, 1024), generator=g, device="cuda")
-    o = torch.empty((1024, 1024), device="cuda"); od = be.wrap(o.data_ptr(), o.numel() * 4, o)
-    ms = _device_timed(lambda: be.matmul(a, False, b, False, False, 1024, 1024, 1024, np.float32, out=od, mark=False),
-                       200, stream, False, warm=10)
-    tf = 2 * 1024 ** 3 / ms / 1e9
-    res["c1_f32_1024"] = {"ms": ms, "tflops_effective": tf,
-                          "roofline": {"bound": "latency (64 tiles, one wave); against the 3xTF32 tensor ceiling for scale",
-                                       "achieved": tf, "peak": peaks["burst"] / 6, "unit": "TFLOP/s", "frac": tf / (peaks["burst"] / 6)}}
-    q = torch.randn((64, 2048, 128), generator=g, device="cuda").half(); k = torch.randn((64, 2048, 128), generator=g, device="cuda").half()
-    o = torch.empty((64, 2048, 2048), device="cuda", dtype=torch.float16); od = be.wrap(o.data_ptr(), o.numel() * 2, o)
-    ms = _device_timed(lambda: be.batchedMatmul(64, q, False, k, True, False, 2048, 128, 2048, np.float16, out=od, mark=False),
-                       50, stream, False, warm=5)
-    nbytes = 2 * 64 * 2048 * 128 * 2 + 64 * 2048 * 2048 * 2
-    res["c3_f16_batched_qkT"] = {"ms": ms, "tflops": 2 * 64 * 2048 * 2048 * 128 / ms / 1e9,
-                                 "roofline": {"bound": "hbm", "achieved": nbytes / ms / 1e6, "peak": peaks["hbm_gbs"],
-                                              "unit": "GB/s", "frac": nbytes / ms / 1e6 / peaks["hbm_gbs"],
-                                              "algorithmic_bytes": nbytes}}
-    del q, k, o
-    n = 16384
-    a = torch.rand((n, n), generator=g, device="cuda") * 2 - 1
-    b = torch.rand((n, n), generator=g, device="cuda") * 2 - 1
-    o = torch.empty((n, n), device="cuda"); od = be.wrap(o.data_ptr(), o.numel() * 4, o)
-    ms = _device_timed(lambda: be.matmul(a, False, b, False, False, n, n, n, np.float32, out=od, mark=False), 3, stream, False, warm=1)
-    tf = 2 * n ** 3 / ms / 1e9
-    res["c5_f32_16384_3xtf32"] = {"ms": ms, "tflops_effective": tf,
-                                  "roofline": {"bound": "tensor", "achieved": tf, "peak": peaks["burst"] / 6,
-                                               "unit": "TFLOP/s effective (3xTF32: 3x the MMA work at half the bf16 rate)",
-                                               "frac": tf / (peaks["burst"] / 6)}}
-    del a, b, o
+    if not heavy:
+        a = torch.rand((1024, 1024), generator=g, device="cuda"); b = torch.rand((1024, 1024), generator=g, device="cuda")
+        o = torch.empty((1024, 1024), device="cuda"); od = be.wrap(o.data_ptr(), o.numel() * 4, o)
+        ms = _device_timed(lambda: be.matmul(a, False, b, False, False, 1024, 1024, 1024, np.float32, out=od, mark=False),
+                           200, stream, False, warm=10)
+        tf = 2 * 1024 ** 3 / ms / 1e9
+        res["c1_f32_1024"] = {"ms": ms, "tflops_effective": tf,
+                              "roofline": {"bound": "latency (64 tiles, one wave); against the 3xTF32 tensor ceiling for scale",
+                                           "achieved": tf, "peak": peaks["burst"] / 6, "unit": "TFLOP/s", "frac": tf / (peaks["burst"] / 6)}}
+        q = torch.randn((64, 2048, 128), generator=g, device="cuda").half(); k = torch.randn((64, 2048, 128), generator=g, device="cuda").half()
+        o = torch.empty((64, 2048, 2048), device="cuda", dtype=torch.float16); od = be.wrap(o.data_ptr(), o.numel() * 2, o)
+        ms = _device_timed(lambda: be.batchedMatmul(64, q, False, k, True, False, 2048, 128, 2048, np.float16, out=od, mark=False),
+                           50, stream, False, warm=5)
+        nbytes = 2 * 64 * 2048 * 128 * 2 + 64 * 2048 * 2048 * 2
+        res["c3_f16_batched_qkT"] = {"ms": ms, "tflops": 2 * 64 * 2048 * 2048 * 128 / ms / 1e9,
+                                     "roofline": {"bound": "hbm", "achieved": nbytes / ms / 1e6, "peak": peaks["hbm_gbs"],
+                                                  "unit": "GB/s", "frac": nbytes / ms / 1e6 / peaks["hbm_gbs"],
+                                                  "algorithmic_bytes": nbytes}}
+        del q, k, o
+    else:
+        n = 16384
+        a = torch.rand((n, n), generator=g, device="cuda") * 2 - 1
+        b = torch.rand((n, n), generator=g, device="cuda") * 2 - 1
+        o = torch.empty((n, n), device="cuda"); od = be.wrap(o.data_ptr(), o.numel() * 4, o)
+        ms = _device_timed(lambda: be.matmul(a, False, b, False, False, n, n, n, np.float32, out=od, mark=False), 3, stream, False, warm=1)
+        tf = 2 * n ** 3 / ms / 1e9
+        res["c5_f32_16384_3xtf32"] = {"ms": ms, "tflops_effective": tf,
+                                      "roofline": {"bound": "tensor", "achieved": tf, "peak": peaks["burst"] / 6,
+                                                   "unit": "TFLOP/s effective (3xTF32: 3x the MMA work at half the bf16 rate)",
+                                                   "frac": tf / (peaks["burst"] / 6),
+                                                   "frac_of_sustained": tf / (peaks["sustained"] / 6)}}
+        del a, b, o
     be.checkDeviceStatus()
     return res
 
