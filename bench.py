@@ -537,7 +537,10 @@ def other_configs(be, stream, rank, world):
         with torch.cuda.graph(graph, stream=stream):
             for _ in range(20):
                 be.batchedMatmul(64, q, False, k, True, False, 2048, 128, 2048, np.float16, out=od, mark=False)
-        ms = timed(graph.replay, 5) / 20
+        def replay():
+            with torch.cuda.stream(stream):     # a replay goes to torch's current stream
+                graph.replay()
+        ms = timed(replay, 5) / 20
         res["c3_f16_batched_qkT_graph"] = {"ms": ms, "tflops": 2 * 64 * 2048 * 2048 * 128 / ms / 1e9}
         del graph
     except Exception as e:
@@ -679,11 +682,12 @@ def probe_one(args, spec):
         with torch.cuda.graph(graph, stream=stream):
             for _ in range(args.steps):
                 be.batchedMatmul(cnt, a, ta, b, tb, False, M, K, N, npdt, out=od, mark=False)
-        graph.replay()
-        e0.record(stream)
-        for _ in range(5):
+        with torch.cuda.stream(stream):         # a replay goes to torch's current stream
             graph.replay()
-        e1.record(stream)
+            e0.record(stream)
+            for _ in range(5):
+                graph.replay()
+            e1.record(stream)
         torch.cuda.synchronize()
         be.checkDeviceStatus()
         ms = e0.elapsed_time(e1) / (5 * args.steps)
