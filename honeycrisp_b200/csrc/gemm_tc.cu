@@ -138,10 +138,12 @@ __device__ __forceinline__ uint32_t map_to_cta(uint32_t addr, uint32_t rank) {
 // ordinary launch.  Everything before pdl_wait must touch no global memory - with one exception
 // the host decides: operand loads may run ahead of it when the operands cannot have been written
 // by the predecessor (TcParams::skip_input_wait).
-// Every kernel of this library releases its successor only AFTER its own wait has returned.  A
-// successor therefore never starts before its predecessor's predecessor has completed: at most
-// two kernels of a chain are in flight, and the only kernel a launch can race with is the one
-// enqueued immediately before it.
+// The product kernel releases its successor only AFTER its own wait has returned.  Its successor
+// therefore never starts before the product kernel's predecessor has completed, and the only
+// kernel a product can race with when it skips its operand wait is the one enqueued immediately
+// before it.  The small elementwise kernels around it (operand split, repack, sum of a cut
+// contraction's parts) release at entry, so that the kernel behind them is already launched and
+// parked at its wait when they finish; a product that follows one of them never skips its wait.
 __device__ __forceinline__ void pdl_release() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 // Rendezvous without memory ordering: for the teardown, where the CTAs of a pair only have to
@@ -1139,8 +1141,8 @@ struct ReduceJob {
 
 template <bool kHalf>
 __global__ void __launch_bounds__(256) splitk_reduce_kernel(const ReduceJob j) {
-  pdl_wait();
   pdl_release();
+  pdl_wait();
   const int64_t groups = j.ws_ld / 4;
   const int64_t total = j.batch * j.M * groups;
   const int64_t part_stride = j.M * j.ws_ld;
@@ -1208,8 +1210,8 @@ __device__ __forceinline__ float split_lo(float x) {
 
 // One launch splits both operands: the first `blocks_a` blocks work on A, the rest on B.
 __global__ void __launch_bounds__(256) split_tf32_kernel(const SplitJob ja, const SplitJob jb, int blocks_a) {
-  pdl_wait();
   pdl_release();
+  pdl_wait();
   const bool is_a = (int)blockIdx.x < blocks_a;
   const SplitJob& j = is_a ? ja : jb;
   const int64_t bid = is_a ? blockIdx.x : blockIdx.x - blocks_a;
@@ -1242,8 +1244,8 @@ struct RepackJob {
   int64_t rows, width, ld_src, ld_dst, stride_src, stride_dst, batch;
 };
 __global__ void __launch_bounds__(256) repack_f16_kernel(const RepackJob ja, const RepackJob jb, int blocks_a) {
-  pdl_wait();
   pdl_release();
+  pdl_wait();
   const bool is_a = (int)blockIdx.x < blocks_a;
   const RepackJob& j = is_a ? ja : jb;
   const int64_t bid = is_a ? blockIdx.x : blockIdx.x - blocks_a;
