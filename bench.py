@@ -973,6 +973,26 @@ def single_gpu_configs(be, stream, heavy):
                                                    "frac": tf / (peaks["burst"] / 6),
                                                    "frac_of_sustained": tf / (peaks["sustained"] / 6)}}
         del a, b, o
+        # Configuration 4: the three products of a Linear layer's forward and backward pass as the
+        # reference's autodiff issues them (Y = X.W^T, dX = dY.W, dW = dY^T.X through transOut).
+        x = torch.randn((16384, 4096), generator=g, device="cuda").half()
+        w = ((torch.rand((16384, 4096), generator=g, device="cuda") - 0.5) / 32).half()
+        dy = torch.randn((16384, 16384), generator=g, device="cuda").half()
+        y = torch.empty((16384, 16384), device="cuda", dtype=torch.float16); yd = be.wrap(y.data_ptr(), y.numel() * 2, y)
+        dx = torch.empty((16384, 4096), device="cuda", dtype=torch.float16); dxd = be.wrap(dx.data_ptr(), dx.numel() * 2, dx)
+        dw = torch.empty((16384, 4096), device="cuda", dtype=torch.float16); dwd = be.wrap(dw.data_ptr(), dw.numel() * 2, dw)
+
+        def triple():
+            be.matmul(x, False, w, True, False, 16384, 4096, 16384, np.float16, out=yd, mark=False)
+            be.matmul(dy, False, w, False, False, 16384, 16384, 4096, np.float16, out=dxd, mark=False)
+            be.matmul(x, True, dy, False, True, 4096, 16384, 16384, np.float16, out=dwd, mark=False)
+
+        ms = _device_timed(triple, 5, stream, False, warm=2)
+        tf = 3 * 2 * 16384 * 16384 * 4096 / ms / 1e9
+        res["c4_f16_linear_triple"] = {"ms": ms, "tflops": tf,
+                                       "roofline": {"bound": "tensor", "achieved": tf, "peak": peaks["burst"], "unit": "TFLOP/s",
+                                                    "frac": tf / peaks["burst"], "frac_of_sustained": tf / peaks["sustained"]}}
+        del x, w, dy, y, dx, dw
     be.checkDeviceStatus()
     return res
 

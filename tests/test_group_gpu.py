@@ -169,3 +169,22 @@ def test_tiny_products_take_the_reference_arithmetic_under_auto(be):
     assert be.lastLaunchInfo()["kernel"] == _lib.HC_KERNEL_SIMT_EXACT
     want = ref.batched_matmul(2, a, False, b, True, False, 9, 33, 7, library_fast_path=False)
     assert np.array_equal(got.view(np.uint32), np.asarray(want).reshape(-1).view(np.uint32))
+
+
+def test_group_creation_rejects_bad_requests_without_waiting_for_anyone(be):
+    """Misuse is answered on the spot with a status code: nothing is sent to NCCL, nobody is
+    waited for, the context keeps working."""
+    from honeycrisp_b200 import _lib
+    lib = be._lib
+    g = ctypes.c_void_p()
+    ident = ctypes.create_string_buffer(128)
+    assert lib.hc_group_init(be._ctx, 9, 0, ident, ctypes.byref(g)) == _lib.HC_ERR_INVALID_ARGUMENT     # more than 8 ranks
+    assert lib.hc_group_init(be._ctx, 2, 2, ident, ctypes.byref(g)) == _lib.HC_ERR_INVALID_ARGUMENT     # rank outside the group
+    assert lib.hc_group_init(be._ctx, 2, 0, None, ctypes.byref(g)) == _lib.HC_ERR_INVALID_ARGUMENT      # no id for a real group
+    assert lib.hc_group_init(be._ctx, 0, 0, None, ctypes.byref(g)) == _lib.HC_ERR_INVALID_ARGUMENT
+    assert not g.value
+    assert lib.hc_group_barrier(None) == _lib.HC_ERR_INVALID_ARGUMENT
+    assert lib.hc_matmul_nsplit_allgather(None, 0, None, 0, None, 0, 1, 1, 1, None, 0) == _lib.HC_ERR_INVALID_ARGUMENT
+    out = be.matmul(np.ones((64, 64), np.float32), False, np.ones((64, 64), np.float32), False, False, 64, 64, 64,
+                    np.float32).onCPU(np.float32)
+    assert np.all(out == 64.0)
