@@ -347,7 +347,10 @@ def run_ours(args):
     # Two sets of device operands: the inputs of step i+1 are uploaded (side stream) while the
     # results of step i are still being read back; host links are full duplex.
     dab = [(be.allocate(n * n * 2), be.allocate(n * n * 2)) for _ in range(2)]
-    douts = [be.allocate(n * n * 2) for _ in range(4)]
+    # Two sets of result buffers, on the device and (pinned) on the host: the products of step i+1
+    # run while the results of step i are still on their way to the host, so the link never idles.
+    douts = [[be.allocate(n * n * 2) for _ in range(4)] for _ in range(2)]
+    houts2 = [houts, [torch.empty((n, n), dtype=torch.float16).pin_memory().numpy().reshape(-1) for _ in range(4)]]
 
     def upload(step):
         da, db = dab[step % 2]
@@ -355,20 +358,24 @@ def run_ours(args):
 
     def staged_steps(count):
         pending = upload(0)
+        in_flight = []                              # read-backs of the previous step
         for step in range(count):
             da, db = dab[step % 2]
             for u in pending:
                 be.enqueueWait(u)                   # the products wait on the device, not the host
             reads = []
-            for (ta, tb), do, ho in zip(COMBOS, douts, houts):
+            for (ta, tb), do, ho in zip(COMBOS, douts[step % 2], houts2[step % 2]):
                 be.batchedMatmul(1, da, ta, db, tb, False, n, n, n, np.float16, out=do, mark=False)
                 reads.append(do.readInto(ho))       # side stream: the next product runs meanwhile
             nxt = upload(step + 1) if step + 1 < count else []
-            for r in reads:
-                r.wait()                            # the step ends when all four results are in host memory
+            for r in in_flight:
+                r.wait()                            # step i-1 has ended: its four results are in host memory,
+            in_flight = reads                       # and its buffers are free for step i+1
             for u in pending:
                 u.wait()
             pending = nxt
+        for r in in_flight:
+            r.wait()
 
     staged_steps(1)
     barrier()
@@ -385,8 +392,9 @@ def run_ours(args):
                   "bytes_are": "whole job (all ranks), like value",
                   "what": ("A and B uploaded once per step (hc_h2d_async, the next step's while this step's results "
                            "are read back), four products on them, each result read back with hc_d2h_async while the "
-                           "next product runs; a step ends when its four results are in host memory")}
-    for d in [x for pair in dab for x in pair] + douts:
+                           "next product runs; a step has ended when its four results are in host memory, and the products "
+                           "of the next step run meanwhile (two sets of result buffers)")}
+    for d in [x for pair in dab for x in pair] + [x for four in douts for x in four]:
         d.free()
 
     # ---- per-launch timing of the dominant kernel for the roofline (events around each launch)
