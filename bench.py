@@ -42,11 +42,11 @@ COMBOS = [(False, False), (False, True), (True, False), (True, True)]  # (transA
 WORKLOAD = "float16 GEMM M=N=K=8192, fp32 accumulate, float16 out, all four transA/transB, N(0,1)/sqrt(K), seed 1"
 FLOPS_PER_GEMM = 2.0 * N_DIM ** 3
 # DRAM bytes (dram__bytes_read.sum + dram__bytes_write.sum) of one 8192^3 launch of the tensor-core
-# kernel, from the latest ncu capture summarised under profiles/ (931 MB read + 122 MB written).
+# kernel, from the latest ncu capture summarised under profiles/ (865 MB read + 120 MB written).
 # The algorithmic minimum is 3 * 8192^2 * 2 = 403 MB.
-NCU_DRAM_BYTES_PER_LAUNCH = 1.053e9
-NCU_DRAM_SOURCE = ("ncu capture of tc_gemm_kernel<2,256,4,8,false,2,2,1,false> (256x512 pair tile) at 8192^3, "
-                   "profiles/tc_gemm_f16_8192.md; not measured by this run")
+NCU_DRAM_BYTES_PER_LAUNCH = 0.985e9
+NCU_DRAM_SOURCE = ("ncu capture of tc_gemm_kernel<2, 256, 4, 8, 0, 2, 2, 1, 0> (256x512 pair tile, half-by-half drain) "
+                   "at 8192^3, profiles/tc_gemm_f16_8192.md; not measured by this run")
 
 
 def load_peaks():
