@@ -1110,368 +1110,6 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap mapA_hi, const __grid_constan
   }
 }
 
-__device__ __forceinline__ float split_lo(float x);
-
-// ---- float32 with the operand split done in shared memory ---------------------------------------
-// The same 3xTF32 product as tc_gemm_kernel<4, ...>, without the pre-pass and without a work area:
-// TMA brings the raw float32 slabs of both operands, a warp group of converters writes each slab's
-// low half (lo = nearest TF32 of x minus x truncated to TF32) next to it in shared memory, and the
-// issuer runs A_lo*B_hi, A_hi*B_lo, A_hi*B_hi from the four slabs, the raw slab serving as hi (the
-// tensor core drops its low 13 mantissa bits itself).  Accumulation windows and their sum in the
-// epilogue's registers are as in the other kernel.
-//
-// 512 threads in four warp groups, so that registers can be moved between the roles
-// (setmaxnreg works on whole warp groups): the windowed epilogue holds 128 running sums per thread
-// and gets 216 registers, producers, issuer and converters 40 each (40 + 216 + 216 + 40 = 4 x 128).
-//   warps 0-3   : TMA producer of A (warp 0), MMA issuer (warp 1), TMA producer of B (warp 2)
-//   warps 4-11  : epilogue
-//   warps 12-15 : converters
-// Per pipeline slot: the producers wait for `empty`, each CTA's copies complete on its OWN `full`
-// barrier, that CTA's converters wait for it, write the low halves, make them visible to the async
-// proxy and arrive on the leader's `conv` barrier, which is what the issuer waits for.
-template <int kBN, int kStages, int kCta>
-__global__ void __launch_bounds__(512, 1)
-tc_gemm_f32_fused_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapB,
-                         const __grid_constant__ OutMaps mapC, const TcParams p) {
-  constexpr int BK = 32, UMMA_K = 8, CH = 32;
-  constexpr int BN_LOCAL = kBN / kCta;
-  constexpr uint32_t MN_SBO = 512u, MN_MODE = 1u;
-  constexpr uint32_t A_BYTES = BM * 128, B_BYTES = BN_LOCAL * 128, STAGE_BYTES = 2 * (A_BYTES + B_BYTES);
-  constexpr int kEpiWarps = 8, kConvWarps = 4;
-  constexpr int COL_SPLIT = kEpiWarps / 4;
-  constexpr int COLS_PER_THREAD = kBN / COL_SPLIT;
-  constexpr int TMEM_COLS = (2 * kBN <= 32) ? 32 : 2 * kBN;
-  static_assert(COLS_PER_THREAD % 32 == 0, "the epilogue drains 32 columns at a time");
-  static_assert(B_BYTES % 2048 == 0 && A_BYTES % 2048 == 0, "128 converters, 16 bytes each, whole passes");
-
-  extern __shared__ uint8_t smem_raw[];
-  __shared__ __align__(8) uint64_t bars[3 * kStages + 4];
-  __shared__ uint32_t tmem_base_slot;
-  __shared__ int abort_flag;
-
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const uint32_t rank = (kCta == 2) ? cluster_ctarank() : 0u;
-  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
-  const uint32_t bar_full = smem_u32(&bars[0]);
-  const uint32_t bar_empty = smem_u32(&bars[kStages]);
-  const uint32_t bar_conv = smem_u32(&bars[2 * kStages]);
-  const uint32_t bar_tfull = smem_u32(&bars[3 * kStages]);
-  const uint32_t bar_tempty = smem_u32(&bars[3 * kStages + 2]);
-
-  if (threadIdx.x == 0) {
-    abort_flag = 0;
-    for (int s = 0; s < kStages; s++) {
-      mbar_init(bar_full + 8 * s, 1);
-      mbar_init(bar_empty + 8 * s, 1);
-      mbar_init(bar_conv + 8 * s, 32 * kConvWarps * kCta);
-    }
-    for (int s = 0; s < 2; s++) {
-      mbar_init(bar_tfull + 8 * s, 1);
-      mbar_init(bar_tempty + 8 * s, 32 * kEpiWarps * kCta);
-    }
-    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-  }
-  if (warp == 1) {
-    if (kCta == 2) {
-      asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_slot)),
-                   "r"((uint32_t)TMEM_COLS)
-                   : "memory");
-      asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
-    } else {
-      asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_slot)),
-                   "r"((uint32_t)TMEM_COLS)
-                   : "memory");
-      asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
-    }
-  }
-  tc_fence_before();
-  __syncthreads();
-  if (kCta == 2) cluster_sync_after_barrier_init();
-  tc_fence_after();
-  const uint32_t tmem_base = tmem_base_slot;
-  volatile int* abortp = &abort_flag;
-
-  const int nkb = p.num_k_blocks;
-  const int chunk_kb = p.chunk_kb;
-  const int64_t tile_first = blockIdx.x / kCta, tile_step = gridDim.x / kCta;
-
-  if (warp < 4) {
-    asm volatile("setmaxnreg.dec.sync.aligned.u32 40;");
-    if (warp == 0 || warp == 2) {
-      // ---------------------------------------------------------------- TMA producers (raw slabs only)
-      const bool do_a = (warp == 0);
-      if (elect_one()) {
-        asm volatile("prefetch.tensormap [%0];" ::"l"((unsigned long long)(do_a ? &mapA : &mapB)) : "memory");
-        uint32_t s = 0, ph = 0;
-        bool ok = true;
-        TileCoord t = decode_tile(tile_first < p.total_tiles ? tile_first : 0, p);
-        const int free_slots = (tile_first < p.total_tiles) ? min(kStages, nkb) : 0;
-        if (do_a)
-          for (int i = 0; i < free_slots; i++) mbar_expect_tx(bar_full + 8 * i, A_BYTES + B_BYTES);
-        if (!p.skip_input_wait) pdl_wait();
-        for (int64_t tile = tile_first; ok && tile < p.total_tiles; tile += tile_step) {
-          if (tile != tile_first) t = decode_tile(tile, p);
-          const int prearmed = (tile == tile_first) ? free_slots : 0;
-          const int m0 = t.tm * (BM * kCta) + (int)rank * BM;
-          const int n0 = t.tn * kBN + (int)rank * BN_LOCAL;
-          const int mat = (int)t.mat;
-          for (int kb = 0; kb < nkb; kb++) {
-            if (kb >= prearmed && !mbar_wait(bar_empty + 8 * s, ph ^ 1, abortp)) {
-              atomicOr(p.status, kDevTimeoutProducer);
-              abort_flag = 1;
-              ok = false;
-              break;
-            }
-            const uint32_t full = bar_full + 8 * s;       // this CTA's own barrier
-            if (do_a && kb >= prearmed) mbar_expect_tx(full, A_BYTES + B_BYTES);
-            const int kc = kb * BK;
-            const uint32_t stage = smem_base + s * STAGE_BYTES;
-            if (do_a) {
-              if (!p.a_mn_major) {
-                tma_load_3d<1>(stage, &mapA, full, kc, m0, mat);
-              } else {
-#pragma unroll
-                for (int c = 0; c < BM / CH; c++) tma_load_3d<1>(stage + c * (BK * 128), &mapA, full, m0 + c * CH, kc, mat);
-              }
-            } else {
-              const uint32_t sb = stage + 2 * A_BYTES;
-              if (!p.b_mn_major) {
-                tma_load_3d<1>(sb, &mapB, full, kc, n0, mat);
-              } else {
-#pragma unroll
-                for (int c = 0; c < BN_LOCAL / CH; c++) tma_load_3d<1>(sb + c * (BK * 128), &mapB, full, n0 + c * CH, kc, mat);
-              }
-            }
-            if (++s == kStages) { s = 0; ph ^= 1; }
-          }
-        }
-        if (kCta == 2 && ok && do_a) {
-          // Every slot's release (an asynchronous arrive from the leader's commits) must have landed
-          // in this CTA's barriers before the CTA may exit.
-          for (int i = 0; i < kStages; i++) {
-            if (!mbar_wait(bar_empty + 8 * s, ph ^ 1, abortp)) {
-              atomicOr(p.status, kDevTimeoutProducer);
-              abort_flag = 1;
-              break;
-            }
-            if (++s == kStages) { s = 0; ph ^= 1; }
-          }
-        }
-      }
-    } else if (warp == 1) {
-      // ---------------------------------------------------------------- MMA issuer (leader CTA)
-      if (elect_one() && rank == 0) {
-        const uint32_t idesc = make_idesc(true, p.a_mn_major, p.b_mn_major, BM * kCta, kBN);
-        const uint32_t a_lbo = p.a_mn_major ? (uint32_t)(BK * 128) : 16u, a_sbo = p.a_mn_major ? MN_SBO : 1024u;
-        const uint32_t b_lbo = p.b_mn_major ? (uint32_t)(BK * 128) : 16u, b_sbo = p.b_mn_major ? MN_SBO : 1024u;
-        const uint32_t a_mode = p.a_mn_major ? MN_MODE : 2u, b_mode = p.b_mn_major ? MN_MODE : 2u;
-        const uint32_t a_kstep = p.a_mn_major ? (uint32_t)(UMMA_K * 128) : 32u;
-        const uint32_t b_kstep = p.b_mn_major ? (uint32_t)(UMMA_K * 128) : 32u;
-        const uint32_t empty_peer = (kCta == 2) ? map_to_cta(bar_empty, 1) : 0u;
-        const uint32_t tfull_peer = (kCta == 2) ? map_to_cta(bar_tfull, 1) : 0u;
-        uint32_t s = 0, ph = 0, win = 0, slot = 0;
-        bool ok = true;
-        for (int64_t tile = tile_first; ok && tile < p.total_tiles; tile += tile_step) {
-          int in_win = -1;
-          for (int kb = 0; kb < nkb; kb++) {
-            if (++in_win == chunk_kb) in_win = 0;
-            if (in_win == 0) {
-              slot = win & 1;
-              if (!mbar_wait(bar_tempty + 8 * slot, ((win >> 1) & 1) ^ 1, abortp)) {
-                atomicOr(p.status, kDevTimeoutMma);
-                abort_flag = 1;
-                ok = false;
-                break;
-              }
-              tc_fence_after();
-            }
-            if (!mbar_wait(bar_conv + 8 * s, ph, abortp)) {
-              atomicOr(p.status, kDevTimeoutMma);
-              abort_flag = 1;
-              ok = false;
-              break;
-            }
-            tc_fence_after();
-            const uint32_t stage = smem_base + s * STAGE_BYTES;
-            const uint32_t d = tmem_base + slot * kBN;
-#pragma unroll
-            for (int pr = 0; pr < 3; pr++) {   // A_lo*B_hi, A_hi*B_lo, A_hi*B_hi
-              const uint32_t sa = stage + (pr == 0 ? A_BYTES : 0u);
-              const uint32_t sb = stage + 2 * A_BYTES + (pr == 1 ? B_BYTES : 0u);
-              const uint64_t adesc = make_smem_desc(sa, a_lbo, a_sbo, a_mode);
-              const uint64_t bdesc = make_smem_desc(sb, b_lbo, b_sbo, b_mode);
-#pragma unroll
-              for (int k = 0; k < BK / UMMA_K; k++)
-                tc_mma<true, kCta>(d, adesc + (uint64_t)((k * a_kstep) >> 4), bdesc + (uint64_t)((k * b_kstep) >> 4), idesc,
-                                   (in_win | pr | k) ? 1u : 0u);
-            }
-            tc_commit<kCta>(bar_empty + 8 * s);
-            if (kCta == 2) tc_commit<kCta>(empty_peer + 8 * s);
-            if (in_win == chunk_kb - 1 || kb == nkb - 1) {
-              tc_commit<kCta>(bar_tfull + 8 * slot);
-              if (kCta == 2) tc_commit<kCta>(tfull_peer + 8 * slot);
-              win++;
-            }
-            if (++s == kStages) { s = 0; ph ^= 1; }
-          }
-        }
-      }
-    }
-  } else if (warp >= 4 + kEpiWarps) {
-    // ------------------------------------------------------------------ converters
-    asm volatile("setmaxnreg.dec.sync.aligned.u32 40;");
-    const int ct = threadIdx.x - 32 * (4 + kEpiWarps);          // 0..127
-    const uint32_t conv_leader = (kCta == 2) ? map_to_cta(bar_conv, 0) : bar_conv;
-    uint32_t s = 0, ph = 0;
-    bool ok = true;
-    for (int64_t tile = tile_first; ok && tile < p.total_tiles; tile += tile_step) {
-      for (int kb = 0; kb < nkb; kb++) {
-        if (!mbar_wait(bar_full + 8 * s, ph, abortp)) {
-          if (lane == 0) { atomicOr(p.status, kDevTimeoutProducer); abort_flag = 1; }
-          ok = false;
-          break;
-        }
-        const uint32_t stage = smem_base + s * STAGE_BYTES;
-        // lo sits at the same offset of the neighbouring buffer, so whatever swizzle the copy
-        // applied to the raw slab applies to its low half as well.
-#pragma unroll
-        for (int i = 0; i < (int)(A_BYTES / 2048); i++) {
-          const uint32_t off = (uint32_t)(i * 128 + ct) * 16u;
-          float4 x;
-          asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(x.x), "=f"(x.y), "=f"(x.z), "=f"(x.w) : "r"(stage + off));
-          st_shared_v4(stage + A_BYTES + off, __float_as_uint(split_lo(x.x)), __float_as_uint(split_lo(x.y)),
-                       __float_as_uint(split_lo(x.z)), __float_as_uint(split_lo(x.w)));
-        }
-#pragma unroll
-        for (int i = 0; i < (int)(B_BYTES / 2048); i++) {
-          const uint32_t off = 2 * A_BYTES + (uint32_t)(i * 128 + ct) * 16u;
-          float4 x;
-          asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(x.x), "=f"(x.y), "=f"(x.z), "=f"(x.w) : "r"(stage + off));
-          st_shared_v4(stage + B_BYTES + off, __float_as_uint(split_lo(x.x)), __float_as_uint(split_lo(x.y)),
-                       __float_as_uint(split_lo(x.z)), __float_as_uint(split_lo(x.w)));
-        }
-        fence_proxy_async_smem();
-        asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(conv_leader + 8 * s) : "memory");
-        if (++s == kStages) { s = 0; ph ^= 1; }
-      }
-    }
-  } else {
-    // ------------------------------------------------------------------ epilogue (windows summed in registers)
-    asm volatile("setmaxnreg.inc.sync.aligned.u32 216;");
-    const int ew = warp - 4;
-    const int quarter = warp & 3;
-    const int col_part = ew / 4;
-    const int col0 = col_part * COLS_PER_THREAD;
-    const uint32_t lane_base = (uint32_t)(quarter * 32) << 16;
-    const uint32_t tempty_leader = (kCta == 2) ? map_to_cta(bar_tempty, 0) : bar_tempty;
-    const uint32_t stg_base = smem_base + kStages * STAGE_BYTES + (uint32_t)ew * 4096u;
-    const bool store_leader = elect_one();
-    uint32_t win = 0;
-    bool ok = true;
-    if (store_leader && p.tma_store) asm volatile("prefetch.tensormap [%0];" ::"l"((unsigned long long)&mapC.m[0]) : "memory");
-    TileCoord t = decode_tile(tile_first < p.total_tiles ? tile_first : 0, p);
-    pdl_wait();
-    if (warp == 4 && store_leader) pdl_release();
-    const int nwin = (nkb + chunk_kb - 1) / chunk_kb;
-    for (int64_t tile = tile_first; ok && tile < p.total_tiles; tile += tile_step) {
-      if (tile != tile_first) t = decode_tile(tile, p);
-      const int64_t gm = (int64_t)t.tm * (BM * kCta) + rank * BM + quarter * 32 + lane;
-      const int64_t n0 = (int64_t)t.tn * kBN + col0;
-      void* cmat = (void*)((float*)p.C + t.mat * p.strideC);
-      const int64_t row_off = gm * p.ldc;
-      float acc[COLS_PER_THREAD];
-      for (int w = 0; w < nwin && ok; w++) {
-        const uint32_t slot = win & 1;
-        const bool got = mbar_wait_warp(bar_tfull + 8 * slot, (win >> 1) & 1, abortp, lane);
-        if (!got) {
-          if (lane == 0) { atomicOr(p.status, kDevTimeoutEpilogue); abort_flag = 1; }
-          ok = false;
-          break;
-        }
-        tc_fence_after();
-        const uint32_t tbase = tmem_base + lane_base + slot * kBN + col0;
-#pragma unroll
-        for (int c = 0; c < COLS_PER_THREAD; c += 32) {
-          uint32_t r[32];
-          tmem_ld_x32(tbase + c, r);
-          tmem_ld_wait();
-          if (w == 0) {
-#pragma unroll
-            for (int j = 0; j < 32; j++) acc[c + j] = __uint_as_float(r[j]);
-          } else {
-#pragma unroll
-            for (int j = 0; j < 32; j++) acc[c + j] = __fadd_rn(acc[c + j], __uint_as_float(r[j]));
-          }
-        }
-        tc_fence_before();
-        mbar_arrive_cluster_relaxed(tempty_leader + 8 * slot);
-        win++;
-      }
-      if (ok && p.tma_store) {
-        const int m_warp = t.tm * (BM * kCta) + (int)rank * BM + quarter * 32;
-        const uint32_t row_addr = stg_base + (uint32_t)lane * 128u;
-        const uint32_t sw = (uint32_t)(lane & 7);
-#pragma unroll
-        for (int c = 0; c < COLS_PER_THREAD; c += 32) {
-          if (store_leader) bulk_wait_read<0>();
-          __syncwarp();
-#pragma unroll
-          for (int q = 0; q < 8; q++) {
-            float x[4];
-#pragma unroll
-            for (int e = 0; e < 4; e++) x[e] = acc[c + q * 4 + e];
-            if (p.bias) add_bias<false, 4>(p.bias, n0 + c + q * 4, p.N, x);
-            st_shared_v4(row_addr + (((uint32_t)q ^ sw) << 4), __float_as_uint(x[0]), __float_as_uint(x[1]),
-                         __float_as_uint(x[2]), __float_as_uint(x[3]));
-          }
-          fence_proxy_async_smem();
-          __syncwarp();
-          if (store_leader && m_warp < p.M && n0 + c < p.N) {
-            for (int d = 0; d < p.n_out; d++) tma_store_3d(&mapC.m[d], stg_base, (int)(n0 + c), m_warp, (int)t.mat);
-            bulk_commit();
-          }
-        }
-      } else if (ok && gm < p.M) {
-#pragma unroll
-        for (int c = 0; c < COLS_PER_THREAD; c += 32) {
-          float v[32];
-#pragma unroll
-          for (int j = 0; j < 32; j++) v[j] = acc[c + j];
-          if (p.bias) add_bias<false, 32>(p.bias, n0 + c, p.N, v);
-          if (n0 + c < p.N) store_row32<false>(cmat, row_off, n0 + c, p.N, v, p.vec_ok != 0);
-        }
-      }
-    }
-    __syncwarp();
-    if (elect_one()) {
-      if (p.n_out > 1) bulk_wait_all();
-      else bulk_wait_read<0>();
-    }
-  }
-
-  // ---------------------------------------------------------------- teardown
-  __syncwarp();
-  tc_fence_before();
-  __syncthreads();
-  if (kCta == 2) cluster_rendezvous();
-  tc_fence_after();
-  if (abort_flag) {
-    const unsigned long long t0 = globaltimer_ns();
-    while (globaltimer_ns() - t0 < 200000ull) { __nanosleep(1000); }
-    __syncthreads();
-  }
-  if (warp == 1) {
-    if (kCta == 2) {
-      asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)TMEM_COLS)
-                   : "memory");
-    } else {
-      asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)TMEM_COLS)
-                   : "memory");
-    }
-  }
-}
-
 // Self-test of the bounded wait: one thread waits on a barrier that nothing will ever arrive
 // on, with a short limit, through the same wait routine the GEMM kernel uses.  The wait gives
 // up, the status word gets its bit, and the kernel returns normally.
@@ -1700,7 +1338,6 @@ struct Tunables {
   int short_k = 8;        // HC_TC_SHORT_K: slabs up to which the eight-warp epilogue config is used
   int group_m = 0;        // HC_TC_GROUP_M: tile rows sharing a sweep over the columns (0: default)
   int wide_epi8 = 1;      // HC_TC_WIDE_EPI8: eight epilogue warps on the 256x512 tile
-  int f32_fused = 1;      // HC_TC_F32_FUSED: float32 operands are split in shared memory (0: by the pre-pass)
 };
 #ifdef HC_DIAGNOSTICS
 Tunables read_tunables() {
@@ -1719,7 +1356,6 @@ Tunables read_tunables() {
     else if (n == 7 && !strncmp(k, "SHORT_K", 7)) t.short_k = v;
     else if (n == 7 && !strncmp(k, "GROUP_M", 7)) t.group_m = v;
     else if (n == 9 && !strncmp(k, "WIDE_EPI8", 9)) t.wide_epi8 = v;
-    else if (n == 9 && !strncmp(k, "F32_FUSED", 9)) t.f32_fused = v;
   }
   return t;
 }
@@ -1835,84 +1471,6 @@ struct TcConfig {
     }
     // cudaLaunchKernelEx reports this launch's own failure; the thread's sticky-less "last error"
     // may hold another library's earlier error and is not this launch's to report.
-    return e;
-  }
-};
-
-// Launch configuration of the float32 kernel that splits its operands in shared memory.
-template <int kBN, int kStages, int kCta>
-struct TcFusedConfig {
-  static constexpr size_t smem = (size_t)kStages * 2 * (BM * 128 + (kBN / kCta) * 128) + 8 * 4096 + 1024;
-  static_assert(smem <= 232448, "more shared memory than one CTA can have on sm_100");
-  static constexpr int block = 512;
-  static auto kernel() { return tc_gemm_f32_fused_kernel<kBN, kStages, kCta>; }
-
-  static cudaError_t configure() {
-    static bool configured[64] = {};
-    int dev = 0;
-    cudaGetDevice(&dev);
-    if (dev < 64 && !configured[dev]) {
-      cudaError_t e = cudaFuncSetAttribute(kernel(), cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-      if (e != cudaSuccess) return e;
-      e = cudaFuncSetAttribute(kernel(), cudaFuncAttributePreferredSharedMemoryCarveout, (int)cudaSharedmemCarveoutMaxShared);
-      if (e != cudaSuccess) cudaGetLastError();
-      if (kCta == 2) {
-        e = cudaFuncSetAttribute(kernel(), cudaFuncAttributeNonPortableClusterSizeAllowed, 0);
-        if (e != cudaSuccess) cudaGetLastError();
-      }
-      configured[dev] = true;
-    }
-    return cudaSuccess;
-  }
-
-  static int max_pairs(int sm_count) {
-    static int cached[64] = {};
-    int dev = 0;
-    cudaGetDevice(&dev);
-    if (dev < 64 && cached[dev]) return cached[dev];
-    configure();
-    cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3((unsigned)(sm_count * 4));
-    cfg.blockDim = dim3(block);
-    cfg.dynamicSmemBytes = smem;
-    cudaLaunchAttribute attr;
-    attr.id = cudaLaunchAttributeClusterDimension;
-    attr.val.clusterDim.x = 2; attr.val.clusterDim.y = 1; attr.val.clusterDim.z = 1;
-    cfg.attrs = &attr;
-    cfg.numAttrs = 1;
-    int n = 0;
-    if (cudaOccupancyMaxActiveClusters(&n, kernel(), &cfg) != cudaSuccess || n <= 0) {
-      cudaGetLastError();
-      n = sm_count / 2;
-    }
-    if (dev < 64) cached[dev] = n;
-    return n;
-  }
-
-  static cudaError_t launch(const CUtensorMap maps[4], const OutMaps& outs, const TcParams& p, int sm_count,
-                            cudaStream_t stream, LaunchRecord* rec) {
-    cudaError_t e = configure();
-    if (e != cudaSuccess) return e;
-    int64_t groups = (kCta == 2) ? max_pairs(sm_count) : sm_count;
-    if (p.total_tiles < groups) groups = p.total_tiles;
-    const int grid = (int)groups * kCta;
-    cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3((unsigned)grid);
-    cfg.blockDim = dim3(block);
-    cfg.dynamicSmemBytes = smem;
-    cfg.stream = stream;
-    cudaLaunchAttribute attr[2];
-    attr[0].id = cudaLaunchAttributeClusterDimension;
-    attr[0].val.clusterDim.x = kCta; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
-    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr[1].val.programmaticStreamSerializationAllowed = 1;
-    cfg.attrs = attr;
-    cfg.numAttrs = overlap_launches() ? 2 : 1;
-    e = cudaLaunchKernelEx(&cfg, kernel(), maps[0], maps[2], outs, p);   // the operands themselves: no lo arrays
-    if (rec) {
-      rec->tile_m = BM * kCta; rec->tile_n = kBN; rec->tile_k = 32; rec->stages = kStages;
-      rec->grid = grid; rec->block = block; rec->launches++;
-    }
     return e;
   }
 };
@@ -2078,32 +1636,20 @@ TcPlan plan_tc(const GemmProblem& p, int sm_count, bool may_split, const Tunable
   return best;
 }
 
-// A float32 product takes the kernel that splits its operands in shared memory - no pre-pass, no
-// work area - when TMA can address both operands where they lie and the contraction is not cut
-// (a cut one has few tiles and a long K: its pre-pass is small change, and it needs the kernel
-// that writes partial matrices).
-static bool f32_split_in_kernel(const GemmProblem& p, const TcPlan& plan, const Tunables& tun) {
-  if (p.dtype != HC_F32 || !tun.f32_fused || plan.splits > 1 || (debug_flags() & 2)) return false;
-  const SplitLayout s = split_layout(p);
-  return !s.a_copy && !s.b_copy;
-}
-
-static size_t operand_scratch_bytes(const GemmProblem& p, const TcPlan& plan, const Tunables& tun) {
+static size_t operand_scratch_bytes(const GemmProblem& p) {
   if (p.dtype != HC_F32) {
     const RepackLayout r = repack_layout(p);
     return r.a_bytes + r.b_bytes;
   }
-  if (f32_split_in_kernel(p, plan, tun)) return 0;
   const SplitLayout s = split_layout(p);
   return (s.a_copy ? 2 : 1) * s.a_bytes + (s.b_copy ? 2 : 1) * s.b_bytes;
 }
 
-// Work area of one product: re-laid operands (low halves of float32 operands, repacked float16),
-// then, 256-byte aligned, the partial matrices of a cut contraction.
+// Work area of one product: re-laid operands (float32 hi/lo parts, repacked float16), then,
+// 256-byte aligned, the partial matrices of a cut contraction.
 size_t tc_scratch_bytes(const GemmProblem& p, int sm_count) {
-  const Tunables tun = read_tunables();
-  const TcPlan plan = plan_tc(p, sm_count, true, tun);
-  const size_t ops = operand_scratch_bytes(p, plan, tun);
+  const size_t ops = operand_scratch_bytes(p);
+  const TcPlan plan = plan_tc(p, sm_count, true, read_tunables());
   return plan.ws_bytes ? ((ops + 255) & ~(size_t)255) + plan.ws_bytes : ops;
 }
 
@@ -2246,8 +1792,7 @@ cudaError_t prepare_tc(const GemmProblem& p, unsigned int* status_word, void* sc
   const int BK = 128 / eb;
   const Tunables tun = read_tunables();
   const TcPlan plan = plan_tc(p, sm_count, n_extra == 0, tun);
-  const bool in_kernel_split = f32_split_in_kernel(p, plan, tun);
-  const size_t ops_bytes = operand_scratch_bytes(p, plan, tun);
+  const size_t ops_bytes = operand_scratch_bytes(p);
   const size_t need = plan.ws_bytes ? ((ops_bytes + 255) & ~(size_t)255) + plan.ws_bytes : ops_bytes;
   if (scratch_needed) *scratch_needed = need;
   if (need > 0 && (!scratch || scratch_bytes < need)) return cudaErrorInvalidValue;
@@ -2274,7 +1819,7 @@ cudaError_t prepare_tc(const GemmProblem& p, unsigned int* status_word, void* sc
       if (r.a) { a_hi = a_lo = ra; lda = r.a_ld; sa = r.a_mat; }
       if (r.b) { b_hi = b_lo = rb; ldb = r.b_ld; sb = r.b_mat; }
     }
-  } else if (!in_kernel_split) {
+  } else {
     const SplitLayout s = split_layout(p);
     // Work area: [A lo][A copy, if needed][B lo][B copy, if needed]
     char* at = (char*)scratch;
@@ -2315,7 +1860,7 @@ cudaError_t prepare_tc(const GemmProblem& p, unsigned int* status_word, void* sc
   if (!make_operand_map(&pp.maps[0], a_hi, eb, p.a_mn_major, p.M, p.K, lda, sa, p.batch, BM) ||
       !make_operand_map(&pp.maps[2], b_hi, eb, p.b_mn_major, p.N, p.K, ldb, sb, p.batch, b_box))
     return cudaErrorNotSupported;
-  if (f32 && !in_kernel_split) {
+  if (f32) {
     if (!make_operand_map(&pp.maps[1], a_lo, eb, p.a_mn_major, p.M, p.K, lda_lo, sa_lo, p.batch, BM) ||
         !make_operand_map(&pp.maps[3], b_lo, eb, p.b_mn_major, p.N, p.K, ldb_lo, sb_lo, p.batch, b_box))
       return cudaErrorNotSupported;
@@ -2421,12 +1966,6 @@ cudaError_t prepare_tc(const GemmProblem& p, unsigned int* status_word, void* sc
     else if (cta == 2) fn = TcConfig<2, 256, 6, 4, false, 2>::launch;
     else if (bn == 256) fn = TcConfig<2, 256, 4, 4, false, 1>::launch;
     else fn = TcConfig<2, 128, 3, 4, false, 1, 1, 2>::launch;
-  } else if (in_kernel_split) {
-    if (shape == SHAPE_PAIR_128) fn = TcFusedConfig<128, 3, 2>::launch;
-    else if (shape == SHAPE_PAIR_64) fn = TcFusedConfig<64, 4, 2>::launch;
-    else if (cta == 2) fn = TcFusedConfig<256, 3, 2>::launch;
-    else if (bn == 256) fn = TcFusedConfig<256, 2, 1>::launch;
-    else fn = TcFusedConfig<128, 3, 1>::launch;
   } else if (windowed) {
     if (shape == SHAPE_PAIR_128) fn = TcConfig<4, 128, 3, 4, true, 2>::launch;
     else if (shape == SHAPE_PAIR_64) fn = TcConfig<4, 64, 4, 4, true, 2>::launch;

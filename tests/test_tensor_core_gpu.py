@@ -393,24 +393,3 @@ def test_config5_float32_16384_against_cuda_core_kernel(be):
     be.sync()
     assert torch.equal(blk[:, 4096:6144], c_tc[:, 4096:6144])
     assert float(blk[:, :4096].abs().max()) == 0.0 and float(blk[:, 6144:].abs().max()) == 0.0
-
-
-@pytest.mark.parametrize("shape", [(520, 264, 776, 1), (256, 4096, 512, 1), (1032, 96, 136, 3), (128, 520, 1000, 2)])
-def test_float_split_in_the_kernel_equals_the_pre_pass(dbe, shape, monkeypatch):
-    """float32 operands are split into TF32 halves either by a pre-pass into the work area or, for
-    operands TMA can address in place, by converter warps in shared memory.  Both feed the tensor
-    cores the same bits, so the results are equal bit for bit, whatever the flags."""
-    M, Kd, N, cnt = shape
-    monkeypatch.setenv("HC_TC_SPLITS", "1")
-    for (ta, tb, to) in FLAG_COMBOS:
-        A, B = random_operands(M + Kd, cnt, M, Kd, N, np.float32, dist="uniform11")
-        monkeypatch.setenv("HC_TC_F32_FUSED", "1")
-        fused, a_st, b_st = run(dbe, cnt, A, B, ta, tb, to, np.float32, TENSOR())
-        assert dbe.lastLaunchInfo()["scratch_bytes"] == 0, (shape, ta, tb, to)
-        assert dbe._lib.hc_launch_count(dbe._ctx) >= 1
-        monkeypatch.setenv("HC_TC_F32_FUSED", "0")
-        prepass, _, _ = run(dbe, cnt, A, B, ta, tb, to, np.float32, TENSOR())
-        assert dbe.lastLaunchInfo()["scratch_bytes"] > 0
-        assert np.array_equal(fused.view(np.uint32), prepass.view(np.uint32)), (shape, ta, tb, to)
-        f64 = ref.batched_matmul_f64(cnt, a_st, ta, b_st, tb, to, M, Kd, N)
-        assert ref.rel_frobenius(fused, f64) < TOL_F32, (shape, ta, tb, to)
