@@ -86,7 +86,12 @@ hc_status hc_init(int device, hc_ctx** out);
 void hc_destroy(hc_ctx* ctx);
 
 /* Run this context's work on a stream the caller owns (a `cudaStream_t` passed as void*);
- * NULL returns to the context's own stream.  The caller keeps the stream alive. */
+ * NULL returns to the context's own stream.  The caller keeps the stream alive.
+ * The context's OWN stream is private to the library: record events on it, make other streams
+ * wait for it, but launch your own kernels on a stream you pass here.  On its own stream the
+ * library lets a product's operand loads start while the product enqueued just before it is
+ * still finishing, when that product cannot have written them - which it can only know about
+ * kernels it launched itself.  On a caller's stream every product waits for all earlier work. */
 hc_status hc_set_stream(hc_ctx* ctx, void* cuda_stream);
 void* hc_get_stream(hc_ctx* ctx);
 int hc_get_device(hc_ctx* ctx);

@@ -62,6 +62,9 @@ def _checks(be, grp, rank, world):
     out = grp.resultAllocate(M * N * 4)
     view = out.asTorch((M, N), torch.float32)
     keep = torch.empty((M, N), device=dev)
+    be.sync()
+    shared_stream = torch.cuda.Stream(device=dev)       # a stream of the host's, lent to the backend
+    be.useStream(shared_stream.cuda_stream)
     for trial in range(2):
         a = torch.rand((M, K), generator=g, device=dev) * 2 - 1
         b = torch.rand((K, N), generator=g, device=dev) * 2 - 1
@@ -70,13 +73,14 @@ def _checks(be, grp, rank, world):
         be.matmul(a, False, b, False, False, M, K, N, np.float32, out=be.wrap(one.data_ptr(), one.numel() * 4, one),
                   kernel=_lib.HC_KERNEL_TENSOR)
         grp.matmulColumnSplit(a, False, b, False, M, K, N, np.float32, out, fused=True)
-        # the consumer of this result, enqueued on the backend's stream before the next call
-        be.useStream(None)
-        with torch.cuda.stream(torch.cuda.ExternalStream(be._lib.hc_get_stream(be._ctx), device=dev)):
+        # the consumer of this result, enqueued on the stream the backend works on before the next call
+        with torch.cuda.stream(shared_stream):
             keep.copy_(view)
         be.sync()
         res.append(bool(torch.equal(keep, one)))
     grp.resultFree(out)
+    be.sync()
+    be.useStream(None)
     # float16, transposed B, fused
     ah = torch.randn((768, 320), generator=g, device=dev).half()
     bh = torch.randn((1536, 320), generator=g, device=dev).half()     # stored [cols, inner]
