@@ -76,6 +76,7 @@ SIGNATURES = {
     "hc_column_sum": (_int, [_vp, _int, _vp, _i64, _i64, _vp]),
     "hc_cast": (_int, [_vp, _int, _int, _vp, _i64, _vp]),
     "hc_add": (_int, [_vp, _int, _vp, _vp, _i64, _vp]),
+    "hc_constant": (_int, [_vp, _int, ctypes.c_float, _i64, _vp]),
     "hc_transpose": (_int, [_vp, _int, _i64, _vp, _i64, _i64, _vp]),
     "hc_random": (_int, [_vp, _int, _int, ctypes.c_uint64, ctypes.c_uint64, _i64, _vp, ctypes.POINTER(ctypes.c_uint64)]),
     "hc_matmul_colblock_push": (_int, [_vp, _int, _vp, _int, _vp, _int, _int, _i64, _i64, _i64, _i64, _i64, _vp,

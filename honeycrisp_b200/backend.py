@@ -545,6 +545,16 @@ class CUDABackend:
         out._inputs = (a_d, b_d)
         return out
 
+    def constant(self, value: float, count: int, dtype) -> CUDAData:
+        """Backend.constant (Backend.swift:787-791): `count` elements equal to `value`."""
+        dt = _as_dtype(dtype)
+        if dt not in _HC_DTYPE:
+            raise NotImplementedByBackend(f"constant for dtype {dt.value}")
+        out = self.allocate(count * dt.byteSize)
+        self._check(self._lib.hc_constant(self._ctx, _HC_DTYPE[dt], float(value), int(count), out.ptr))
+        out._mark()
+        return out
+
     def transpose(self, x, matrixCount: int, rows: int, cols: int, dtype) -> CUDAData:
         """The materialised `t()` of the last two axes (Index.swift:359-362)."""
         dt = _as_dtype(dtype)

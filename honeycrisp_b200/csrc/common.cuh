@@ -97,6 +97,7 @@ namespace hc {
 cudaError_t launch_column_sum(hc_dtype dtype, const void* x, void* out, int64_t rows, int64_t cols, cudaStream_t stream);
 cudaError_t launch_cast(hc_dtype from, hc_dtype to, const void* x, void* out, int64_t count, cudaStream_t stream);
 cudaError_t launch_add(hc_dtype dtype, const void* a, const void* b, void* out, int64_t count, cudaStream_t stream);
+cudaError_t launch_constant(hc_dtype dtype, float value, void* out, int64_t count, cudaStream_t stream);
 cudaError_t launch_transpose(hc_dtype dtype, int64_t batch, const void* in, void* out, int64_t rows, int64_t cols,
                              cudaStream_t stream);
 // Philox-4x32-10 samples as Honeycrisp's CPU generator produces them (csrc/random.cu).

@@ -987,6 +987,18 @@ hc_status hc_add(hc_ctx* ctx, hc_dtype dtype, const void* a, const void* b, int6
   return HC_OK;
 }
 
+hc_status hc_constant(hc_ctx* ctx, hc_dtype dtype, float value, int64_t count, void* out) {
+  if (!ctx || count < 0 || (count > 0 && !out)) return HC_ERR_INVALID_ARGUMENT;
+  if (dtype != HC_F16 && dtype != HC_F32) return HC_ERR_NOT_IMPLEMENTED;
+  if (((uintptr_t)out & (dtype == HC_F16 ? 1 : 3)) != 0) return HC_ERR_INVALID_ARGUMENT;
+  std::lock_guard<std::mutex> lock(ctx->mu);
+  DeviceGuard g(ctx->device);
+  cudaError_t e = hc::launch_constant(dtype, value, out, count, ctx->stream);
+  ctx->launch_count += count > 0 ? 1 : 0;
+  if (e != cudaSuccess) return cuda_fail(ctx, e, "constant");
+  return HC_OK;
+}
+
 hc_status hc_transpose(hc_ctx* ctx, hc_dtype dtype, int64_t matrix_count, const void* in, int64_t rows, int64_t cols,
                        void* out) {
   if (!ctx || matrix_count < 0 || rows < 0 || cols < 0) return HC_ERR_INVALID_ARGUMENT;

@@ -390,4 +390,45 @@ cudaError_t launch_add(hc_dtype dtype, const void* a, const void* b, void* out, 
   return cudaGetLastError();
 }
 
+// Backend.constant: every element = the float value narrowed once to the element type.  Whole
+// 16-byte groups are written with one store each; the ragged ends (a misaligned start, a count that
+// is not a multiple of the group) one element at a time.
+template <typename T>
+__global__ void fill_kernel(T* __restrict__ out, T value, uint4 pattern, int64_t head, int64_t groups, int64_t n) {
+  constexpr int kPer = 16 / (int)sizeof(T);
+  const int64_t tid = blockIdx.x * (int64_t)blockDim.x + threadIdx.x, step = (int64_t)gridDim.x * blockDim.x;
+  uint4* body = (uint4*)(out + head);
+  for (int64_t i = tid; i < groups; i += step) body[i] = pattern;
+  for (int64_t i = tid; i < head; i += step) out[i] = value;
+  for (int64_t i = head + groups * kPer + tid; i < n; i += step) out[i] = value;
+}
+
+template <typename T>
+static cudaError_t fill_typed(T* out, T value, int64_t count, cudaStream_t stream) {
+  constexpr int64_t kPer = 16 / (int64_t)sizeof(T);
+  uint32_t word = 0;
+  if (sizeof(T) == 2) {
+    uint16_t bits;
+    memcpy(&bits, &value, 2);
+    word = (uint32_t)bits | ((uint32_t)bits << 16);
+  } else {
+    memcpy(&word, &value, 4);
+  }
+  const uint4 pattern = make_uint4(word, word, word, word);
+  // elements before the first 16-byte boundary (the pointer is at least element-aligned)
+  int64_t head = (int64_t)(((16 - ((uintptr_t)out & 15)) & 15) / sizeof(T));
+  if (head > count) head = count;
+  const int64_t groups = (count - head) / kPer;
+  const int threads = 256;
+  const int grid = grid_for(groups > 0 ? groups : count, threads);
+  fill_kernel<T><<<grid, threads, 0, stream>>>(out, value, pattern, head, groups, count);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_constant(hc_dtype dtype, float value, void* out, int64_t count, cudaStream_t stream) {
+  if (count <= 0) return cudaSuccess;
+  if (dtype == HC_F16) return fill_typed<__half>((__half*)out, __float2half_rn(value), count, stream);
+  return fill_typed<float>((float*)out, value, count, stream);
+}
+
 }  // namespace hc

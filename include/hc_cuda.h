@@ -239,6 +239,12 @@ hc_status hc_cast(hc_ctx* ctx, hc_dtype from, hc_dtype to, const void* x, int64_
  * Trainable.swift:258-266). */
 hc_status hc_add(hc_ctx* ctx, hc_dtype dtype, const void* a, const void* b, int64_t count, void* out);
 
+/* out[0..count) = `value`, narrowed once to `dtype` (round to nearest even for float16): a tensor
+ * filled with a constant, created on the device.
+ * Replaces: Backend.constant (Backend.swift:787-791; CPU body BackendCPU.swift:1796-1815, which
+ * also goes through Float for the float types). */
+hc_status hc_constant(hc_ctx* ctx, hc_dtype dtype, float value, int64_t count, void* out);
+
 /* out[cols,rows] = in[rows,cols]^T for `matrix_count` matrices: the materialising `t()` of the
  * reference (a gather through axisPermutation, Sources/Honeycrisp/Index.swift:238-266,359-362;
  * Backend.swift:609-616,803-805).  A backend that keeps its tensors' layouts would instead pass

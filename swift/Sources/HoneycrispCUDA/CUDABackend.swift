@@ -5,8 +5,9 @@
 //
 // It is a `BackendWrapper` (Sources/Honeycrisp/BackendWrapper.swift:9) around the CPU backend:
 // the two hot-path primitives, `matmul` (Backend.swift:650-658) and `batchedMatmul` (:661-669),
-// are overridden and run on the GPU; every other primitive - collection, constant, random
-// sampling, elementwise and reduction ops - falls through to the wrapped backend, so that
+// are overridden and run on the GPU, and so are `cast` between the float types and `constant`;
+// every other primitive - collection, random sampling, elementwise and reduction ops - falls
+// through to the wrapped backend, so that
 // `Backend.defaultBackend = try CUDABackend()` is a drop-in: tensors can be created, a Linear
 // layer runs forward and backward, and the reference's own tests pass through it.  Operands that
 // arrive as another backend's `Tensor.Data` are staged to the device through `onCPU`, as
@@ -222,6 +223,20 @@ open class CUDABackend: BackendWrapper, @unchecked Sendable {
         ctx, dt, Int64(matrixCount), aBuf.pointer, transA ? 1 : 0, bBuf.pointer, transB ? 1 : 0,
         transOut ? 1 : 0, Int64(rows), Int64(inner), Int64(cols), out.pointer))
     try out.produced(by: [aBuf, bBuf])
+    return out
+  }
+
+  /// `Backend.constant` (Backend.swift:787-791) for the float types is a fill on the device, so that
+  /// `Tensor(zeros:)`/`Tensor(ones:)` operands of a product never cross the host link.
+  override open func constant<T: TensorElement>(_ value: T, count: Int, dtype: Tensor.DType)
+    async throws -> Tensor.Data
+  {
+    guard let dt = hcDType(dtype) else {
+      return try await wrapped.constant(value, count: count, dtype: dtype)
+    }
+    let out = try CUDAData(backend: self, byteCount: count * dtype.byteSize)
+    try check(hc_constant(ctx, dt, value.toFloat(), Int64(count), out.pointer))
+    try out.produced(by: [])
     return out
   }
 

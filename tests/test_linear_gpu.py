@@ -89,6 +89,31 @@ def test_cast_and_add_are_bit_identical(be):
         assert np.array_equal(got.view(np.uint8), ref.add(a, b).reshape(-1).view(np.uint8))
 
 
+def test_constant_is_the_value_narrowed_once(be):
+    """Backend.constant (Backend.swift:787-791): the CPU backend writes Float(value) through the
+    element type (BackendCPU.swift:1796-1815); every count, including the ragged ends around the
+    16-byte groups, and a start that is not 16-byte aligned."""
+    from honeycrisp_b200 import _lib
+    for dt in (np.float32, np.float16):
+        for value in (0.1, 3.0, -0.0, 65520.0, 1e-8, -7.25):
+            for count in (0, 1, 7, 8, 9, 4099):
+                got = be.constant(value, count, dt).onCPU(dt)[:count]
+                with np.errstate(over="ignore"):   # 65520 is infinity in float16, as in the reference
+                    want = np.full(count, np.float32(value)).astype(dt)
+                assert np.array_equal(got.view(np.uint8), want.view(np.uint8)), (dt, value, count)
+        eb = np.dtype(dt).itemsize
+        buf = be.constant(1.0, 64, dt)
+        for first, count in ((1, 37), (3, 5), (5, 59)):
+            assert be._lib.hc_constant(be._ctx, 0 if dt == np.float16 else 1, 2.5, count, buf.ptr + first * eb) == _lib.HC_OK
+            got = buf.onCPU(dt)[:64]
+            want = np.ones(64, dt)
+            want[first:first + count] = 2.5
+            assert np.array_equal(got, want), (dt, first, count)
+            assert be._lib.hc_constant(be._ctx, 0 if dt == np.float16 else 1, 1.0, 64, buf.ptr) == _lib.HC_OK
+    assert be._lib.hc_constant(be._ctx, 1, 0.0, -1, None) == _lib.HC_ERR_INVALID_ARGUMENT
+    assert be._lib.hc_constant(be._ctx, 7, 0.0, 4, buf.ptr) == _lib.HC_ERR_NOT_IMPLEMENTED
+
+
 # (weight dtype, castParams, compute dtype): the three ways the reference's Linear is used
 # (Trainable.swift:514-544) - plain float32; float16 weights with the float32 bias cast on use;
 # float32 master weights cast to float16 on every call.
