@@ -119,40 +119,29 @@ SIGNATURES = {
 _libs = {}
 
 
-def lib_path(diagnostics: bool = False, multicast: bool = False) -> str:
-    return _build.MC_LIB_PATH if multicast else _build.DIAG_LIB_PATH if diagnostics else _build.LIB_PATH
+def lib_path(diagnostics: bool = False) -> str:
+    return _build.DIAG_LIB_PATH if diagnostics else _build.LIB_PATH
 
 
-def multicast_available() -> bool:
-    """Whether the cluster-multicast build (libhccuda_mc.so) is in this tree or can be made here.
-    It is left out of trees that run on several GPUs; everything works without it."""
-    return os.path.exists(_build.MC_LIB_PATH) or _build.multicast_sources_present()
-
-
-def load(diagnostics: bool = False, multicast: bool = False) -> ctypes.CDLL:
+def load(diagnostics: bool = False) -> ctypes.CDLL:
     """Load libhccuda.so (building it first if the sources are newer). Raises on failure.
 
     `diagnostics=True` loads the second build of the same sources (libhccuda_diag.so), in which
     the planner's choices can be forced through HC_TC_* environment variables; the test-suite
-    uses it to reach every tile shape with small products.  `multicast=True` loads the build in
-    which large float16 products run on clusters of two CTA pairs that share operand loads
-    (libhccuda_mc.so; single-GPU hosts, operands in the GPU's own memory).  All can live in one
-    process."""
-    variant = "mc" if multicast else "diag" if diagnostics else ""
-    if variant in _libs:
-        return _libs[variant]
-    path = lib_path(diagnostics, multicast)
-    kw = dict(multicast=True) if multicast else dict(diagnostics=diagnostics)
+    uses it to reach every tile shape with small products.  Both can live in one process."""
+    if diagnostics in _libs:
+        return _libs[diagnostics]
+    path = lib_path(diagnostics)
     override = os.environ.get("HC_CUDA_LIB")     # a differently built libhccuda.so, for A/B runs
-    if override and not variant:
+    if override and not diagnostics:
         path = override
     elif not os.path.exists(path) or os.environ.get("HC_CUDA_REBUILD") == "1":
-        path = _build.build(force=True, **kw)
+        path = _build.build(force=True, diagnostics=diagnostics)
     elif _build._stale(path):
         # Sources are newer than the library: rebuild if a compiler is at hand, otherwise say so
         # and use what is there (a copied tree can carry arbitrary file times).
         try:
-            path = _build.build(**kw)
+            path = _build.build(diagnostics=diagnostics)
         except Exception as e:  # noqa: BLE001
             import warnings
             warnings.warn(f"{os.path.basename(path)} is older than its sources and could not be rebuilt: {e}")
@@ -161,5 +150,5 @@ def load(diagnostics: bool = False, multicast: bool = False) -> ctypes.CDLL:
         fn = getattr(L, name)  # AttributeError if the library lacks a declared symbol
         fn.restype = res
         fn.argtypes = args
-    _libs[variant] = L
+    _libs[diagnostics] = L
     return L

@@ -247,13 +247,10 @@ class CUDABackend:
     (Backend.swift: every primitive defaults to `throw BackendError.notImplemented`).
     """
 
-    def __init__(self, device: int = 0, diagnostics: bool = False, multicast: bool = False):
+    def __init__(self, device: int = 0, diagnostics: bool = False):
         """`diagnostics` binds the context to the diagnostics build of the library (planner choices
-        forced through HC_TC_* environment variables); the test-suite's use only.  `multicast` binds
-        it to the build whose large float16 products share operand loads within clusters of two CTA
-        pairs: for a process that drives this one GPU on operands in its own memory (the library
-        checks that per product); `_lib.multicast_available()` says whether the tree has it."""
-        lib = self._lib = L.load(diagnostics, multicast)
+        forced through HC_TC_* environment variables); the test-suite's use only."""
+        lib = self._lib = L.load(diagnostics)
         ctx = ctypes.c_void_p()
         st = lib.hc_init(int(device), ctypes.byref(ctx))
         if st != L.HC_OK:

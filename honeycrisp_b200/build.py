@@ -16,12 +16,6 @@ LIB_PATH = os.path.join(PKG_DIR, "libhccuda.so")
 # The same sources with -DHC_DIAGNOSTICS: tile shape, cut of the contraction and thresholds of the
 # planner can be forced from the environment.  Only the test-suite loads it.
 DIAG_LIB_PATH = os.path.join(PKG_DIR, "libhccuda_diag.so")
-# The same sources with -DHC_CLUSTER_MULTICAST: the 512-wide float16 tiles run on clusters of two
-# CTA pairs that share their B operand loads.  For hosts that drive one GPU per process on that
-# GPU's own memory; its extra source (csrc/mc/) and this library are left out of multi-GPU runs,
-# and everything works without them.
-MC_DIR = os.path.join(CSRC, "mc")
-MC_LIB_PATH = os.path.join(PKG_DIR, "libhccuda_mc.so")
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",
@@ -48,23 +42,14 @@ def _stale(path: str = LIB_PATH) -> bool:
     t = os.path.getmtime(path)
     deps = sources() + glob.glob(os.path.join(CSRC, "*.cuh")) + glob.glob(
         os.path.join(PKG_DIR, "..", "include", "*.h"))
-    if path == MC_LIB_PATH:
-        deps += glob.glob(os.path.join(MC_DIR, "*.cuh"))
     return any(os.path.getmtime(d) > t for d in deps)
 
 
-def multicast_sources_present() -> bool:
-    return os.path.exists(os.path.join(MC_DIR, "cluster_multicast.cuh"))
-
-
-def build(force: bool = False, verbose: bool = False, diagnostics: bool = False, multicast: bool = False) -> str:
-    path = MC_LIB_PATH if multicast else DIAG_LIB_PATH if diagnostics else LIB_PATH
-    if multicast and not multicast_sources_present():
-        raise RuntimeError("csrc/mc/ is not in this tree: the cluster-multicast build cannot be made here")
+def build(force: bool = False, verbose: bool = False, diagnostics: bool = False) -> str:
+    path = DIAG_LIB_PATH if diagnostics else LIB_PATH
     if not force and not _stale(path):
         return path
-    cmd = ([_nvcc()] + NVCC_FLAGS + (["-DHC_DIAGNOSTICS"] if diagnostics and not multicast else []) +
-           (["-DHC_CLUSTER_MULTICAST"] if multicast else []) +
+    cmd = ([_nvcc()] + NVCC_FLAGS + (["-DHC_DIAGNOSTICS"] if diagnostics else []) +
            (["-Xptxas", "-v"] if verbose else []) + ["-ldl", "-o", path] + sources())
     if verbose:
         print(" ".join(cmd), file=sys.stderr)
@@ -73,10 +58,7 @@ def build(force: bool = False, verbose: bool = False, diagnostics: bool = False,
 
 
 def build_all(force: bool = False, verbose: bool = False):
-    out = [build(force, verbose), build(force, verbose, diagnostics=True)]
-    if multicast_sources_present():
-        out.append(build(force, verbose, multicast=True))
-    return tuple(out)
+    return build(force, verbose), build(force, verbose, diagnostics=True)
 
 
 if __name__ == "__main__":

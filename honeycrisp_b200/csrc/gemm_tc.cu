@@ -62,19 +62,6 @@
 #include <mutex>
 
 #include "common.cuh"
-#ifdef HC_CLUSTER_MULTICAST
-#include "mc/cluster_multicast.cuh"
-#else
-// The build without loads that deliver to several CTAs: the kernels that would use them (kQuad)
-// are not instantiated, and these stand-ins only let the template parse.
-namespace hc {
-namespace {
-constexpr bool kClusterMulticastBuilt = false;
-__device__ __forceinline__ void tma_load_3d_shared(uint32_t, const CUtensorMap*, uint32_t, int, int, int, uint16_t) {}
-__device__ __forceinline__ void tc_commit_shared(uint32_t, uint16_t) {}
-}  // namespace
-}  // namespace hc
-#endif
 
 extern "C" char** environ;
 
@@ -538,7 +525,7 @@ __device__ __forceinline__ KRange k_range(int64_t vmat, const TcParams& p) {
 // occupancy query answers 1 for any such kernel; measured).  Overlap across the end of one launch
 // and the start of the next therefore has to come from programmatic dependent launch alone.
 template <int kElemBytes, int kBN, int kStages, int kEpiWarps, bool kWindowed, int kCta, int kNSplit, int kSlabs,
-          bool kPartial, bool kQuad>
+          bool kPartial>
 __global__ void __launch_bounds__(96 + 32 * kEpiWarps, 1)
 tc_gemm_kernel(const __grid_constant__ CUtensorMap mapA_hi, const __grid_constant__ CUtensorMap mapA_lo,
                const __grid_constant__ CUtensorMap mapB_hi, const __grid_constant__ CUtensorMap mapB_lo,
@@ -569,15 +556,6 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap mapA_hi, const __grid_constan
   static_assert(kEpiWarps == 4 || kEpiWarps == 8 || kEpiWarps == 16, "epilogue warps come in groups of four");
   static_assert(TMEM_COLS == 64 || TMEM_COLS == 128 || TMEM_COLS == 256 || TMEM_COLS == 512, "power of two");
   static_assert(kCta == 1 || kCta == 2, "one CTA or a pair");
-  static_assert(!kQuad || (kCta == 2 && kNSplit == 2 && !kTf32 && !kPartial), "pairs of pairs: 512-wide float16 tiles only");
-  // kQuad: a cluster of two CTA pairs, stacked in M, works on a 512 x 512 block: both pairs need
-  // the same 512 columns of B, so every CTA fetches only one of its two 128-column parts of a k
-  // block and the copy also lands in the CTA of the same pair rank in the other pair (a third less
-  // operand traffic from L2 per flop than two independent pairs).  The pairs then advance through
-  // the ring in step: a slot is refilled once both pairs' MMAs have consumed it.
-  constexpr int PAIRS = kQuad ? 2 : 1;
-  constexpr int CLUSTER = kCta * PAIRS;
-  constexpr int TILE_M = BM * CLUSTER;
 
   extern __shared__ uint8_t smem_raw[];
   __shared__ __align__(8) uint64_t bars[2 * kStages + 4];
@@ -585,10 +563,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap mapA_hi, const __grid_constan
   __shared__ int abort_flag;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const uint32_t crank = (kCta == 2) ? cluster_ctarank() : 0u;
-  const uint32_t rank = crank & 1u;                // within the pair
-  const uint32_t pair = kQuad ? (crank >> 1) : 0u; // which pair of the cluster
-  const uint32_t lead = crank & ~1u;               // cluster rank of this pair's leader
+  const uint32_t rank = (kCta == 2) ? cluster_ctarank() : 0u;
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   const uint32_t bar_full = smem_u32(&bars[0]);
   const uint32_t bar_empty = smem_u32(&bars[kStages]);
@@ -599,7 +574,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap mapA_hi, const __grid_constan
     abort_flag = 0;
     for (int s = 0; s < kStages; s++) {
       mbar_init(bar_full + 8 * s, 1);
-      mbar_init(bar_empty + 8 * s, PAIRS);   // one release per pair that reads or fills the slot
+      mbar_init(bar_empty + 8 * s, 1);
     }
     for (int s = 0; s < 2; s++) {
       mbar_init(bar_tfull + 8 * s, 1);
@@ -634,7 +609,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap mapA_hi, const __grid_constan
 
   const int nkb = p.num_k_blocks;
   const int chunk_kb = p.chunk_kb;
-  const int64_t tile_first = blockIdx.x / CLUSTER, tile_step = gridDim.x / CLUSTER;
+  const int64_t tile_first = blockIdx.x / kCta, tile_step = gridDim.x / kCta;
 
   constexpr int kWarpProducerB = 2 + kEpiWarps;
   if (warp == 0 || warp == kWarpProducerB) {
@@ -652,8 +627,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap mapA_hi, const __grid_constan
         if (do_b) asm volatile("prefetch.tensormap [%0];" ::"l"((unsigned long long)&mapB_lo) : "memory");
       }
       // Completion bytes of both CTAs of a pair are counted on the leader's barrier.
-      const uint32_t full_leader = (kCta == 2) ? map_to_cta(bar_full, lead) : bar_full;
-      const uint16_t same_rank_mask = (uint16_t)(0x5u << rank);   // this CTA and its counterpart in the other pair
+      const uint32_t full_leader = (kCta == 2) ? map_to_cta(bar_full, 0) : bar_full;
       // (L2 eviction priorities on these loads - the band of A a wave shares with the next one
       // asked to stay, the panels of B to go first - were measured at 8192^3: evict_last changes
       // nothing (897-913 MB read from DRAM either way), evict_first on B doubles the reads.)
@@ -673,7 +647,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap mapA_hi, const __grid_constan
       for (int64_t tile = tile_first; ok && tile < p.total_tiles; tile += tile_step) {
         if (tile != tile_first) { t = decode_tile(tile, p); kr = k_range(t.mat, p); }
         const int prearmed = (tile == tile_first) ? free_slots : 0;
-        const int m0 = t.tm * TILE_M + (int)pair * (BM * kCta) + (int)rank * BM;
+        const int m0 = t.tm * (BM * kCta) + (int)rank * BM;
         const int n0 = t.tn * TILE_N + (int)rank * BN_LOCAL;
         const int mat = kr.mat;
         for (int kb = 0; kb < kr.count; kb++) {
@@ -709,17 +683,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap mapA_hi, const __grid_constan
             for (int h = 0; do_b && h < kNSplit; h++) {
               const uint32_t sbh = sb + h * B_PART_BYTES;
               const int n0h = n0 + h * kBN;
-              if (kQuad) {
-                // part h of this CTA's columns comes from pair h's CTA of the same rank
-                if (h != (int)pair) continue;
-                if (!p.b_mn_major) {
-                  tma_load_3d_shared(sbh, mb, full, kc, n0h, mat, same_rank_mask);
-                } else {
-#pragma unroll
-                  for (int c = 0; c < BN_LOCAL / CH; c++)
-                    tma_load_3d_shared(sbh + c * (BK * 128), mb, full, n0h + c * CH, kc, mat, same_rank_mask);
-                }
-              } else if (!p.b_mn_major) {
+              if (!p.b_mn_major) {
                 load(sbh, mb, full, kc, n0h, mat);
               } else {
 #pragma unroll
@@ -756,8 +720,8 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap mapA_hi, const __grid_constan
       const uint32_t a_mode = p.a_mn_major ? MN_MODE : 2u, b_mode = p.b_mn_major ? MN_MODE : 2u;
       const uint32_t a_kstep = p.a_mn_major ? (uint32_t)(UMMA_K * 128) : 32u;
       const uint32_t b_kstep = p.b_mn_major ? (uint32_t)(UMMA_K * 128) : 32u;
-      const uint32_t empty_peer = (kCta == 2) ? map_to_cta(bar_empty, lead | 1u) : 0u;
-      const uint32_t tfull_peer = (kCta == 2) ? map_to_cta(bar_tfull, lead | 1u) : 0u;
+      const uint32_t empty_peer = (kCta == 2) ? map_to_cta(bar_empty, 1) : 0u;
+      const uint32_t tfull_peer = (kCta == 2) ? map_to_cta(bar_tfull, 1) : 0u;
       uint32_t s = 0, ph = 0, win = 0, slot = 0;
       bool ok = true;
       for (int64_t tile = tile_first; ok && tile < p.total_tiles; tile += tile_step) {
@@ -790,13 +754,8 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap mapA_hi, const __grid_constan
             }
           };
           auto release = [&](uint32_t slot_s) {
-            if (kQuad) {
-              // every CTA of the cluster either holds operands this pair's MMAs read or fills them
-              tc_commit_shared(bar_empty + 8 * slot_s, (uint16_t)0xF);
-            } else {
-              tc_commit<kCta>(bar_empty + 8 * slot_s);
-              if (kCta == 2) tc_commit<kCta>(empty_peer + 8 * slot_s);
-            }
+            tc_commit<kCta>(bar_empty + 8 * slot_s);
+            if (kCta == 2) tc_commit<kCta>(empty_peer + 8 * slot_s);
           };
           auto fail = [&]() {
             atomicOr(p.status, kDevTimeoutMma);
@@ -929,7 +888,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap mapA_hi, const __grid_constan
     const int col0 = col_part * COLS_PER_THREAD;
     const uint32_t lane_base = (uint32_t)(quarter * 32) << 16;
     // Buffers are handed back to the leader's MMA issuer.
-    const uint32_t tempty_leader = (kCta == 2) ? map_to_cta(bar_tempty, lead) : bar_tempty;
+    const uint32_t tempty_leader = (kCta == 2) ? map_to_cta(bar_tempty, 0) : bar_tempty;
     // Staging for TMA stores behind the operand ring: per epilogue warp two 4 KB buffers, or one
     // for the windowed epilogue (which stores once per tile).
     const uint32_t stg_base = smem_base + kStages * STAGE_BYTES + (uint32_t)ew * STG_BYTES_PER_WARP;
@@ -942,7 +901,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap mapA_hi, const __grid_constan
     if (warp == 2 && store_leader) pdl_release();   // one thread per CTA is enough
     for (int64_t tile = tile_first; ok && tile < p.total_tiles; tile += tile_step) {
       if (tile != tile_first) t = decode_tile(tile, p);
-      const int64_t gm = (int64_t)t.tm * TILE_M + pair * (BM * kCta) + rank * BM + quarter * 32 + lane;
+      const int64_t gm = (int64_t)t.tm * (BM * kCta) + rank * BM + quarter * 32 + lane;
       const int64_t n0 = (int64_t)t.tn * TILE_N + col0;
       void* cmat = kOutHalf ? (void*)((__half*)p.C + t.mat * p.strideC) : (void*)((float*)p.C + t.mat * p.strideC);
       const int64_t row_off = gm * p.ldc;
@@ -973,7 +932,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap mapA_hi, const __grid_constan
           constexpr int COLS_PER_BUF = kOutHalf ? 64 : 32;   // columns in one 128-byte staging row
           constexpr int LOADS = STG_BUFS * (kOutHalf ? 2 : 1);   // tcgen05.ld.x32 per pass (all staging buffers)
           static_assert(COLS_PER_PART % (STG_BUFS * COLS_PER_BUF) == 0, "a pass fills every staging buffer");
-          const int m_warp = t.tm * TILE_M + (int)pair * (BM * kCta) + (int)rank * BM + quarter * 32;
+          const int m_warp = t.tm * (BM * kCta) + (int)rank * BM + quarter * 32;
           const uint32_t row_addr = stg_base + (uint32_t)lane * 128u;
           const uint32_t sw = (uint32_t)(lane & 7);
 #pragma unroll 1
@@ -1080,7 +1039,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap mapA_hi, const __grid_constan
         }
         if (ok && p.tma_store) {
           // Same staging as above, fed from the register accumulators: one buffer, 32 columns per pass.
-          const int m_warp = t.tm * TILE_M + (int)pair * (BM * kCta) + (int)rank * BM + quarter * 32;
+          const int m_warp = t.tm * (BM * kCta) + (int)rank * BM + quarter * 32;
           const uint32_t row_addr = stg_base + (uint32_t)lane * 128u;
           const uint32_t sw = (uint32_t)(lane & 7);
 #pragma unroll
@@ -1432,15 +1391,14 @@ constexpr bool kPlanCacheEnabled = true;
 #endif
 
 template <int kElemBytes, int kBN, int kStages, int kEpiWarps, bool kWindowed, int kCta, int kNSplit = 1, int kSlabs = 1,
-          bool kPartial = false, bool kQuad = false>
+          bool kPartial = false>
 struct TcConfig {
-  static constexpr int cluster = kCta * (kQuad ? 2 : 1);   // CTAs that are scheduled together
   // operand ring (float32 slots also hold the lo slabs) + store staging + alignment slack
   static constexpr size_t smem = (size_t)kStages * kSlabs * (kElemBytes == 4 ? 2 : 1) * (BM * 128 + kNSplit * (kBN / kCta) * 128) +
                                  (size_t)kEpiWarps * staging_bufs((kElemBytes == 2 && !kPartial) ? 2 : 4, kBN, kEpiWarps, kWindowed, kNSplit) * 4096 + 1024;
   static_assert(smem <= 232448, "more shared memory than one CTA can have on sm_100");
   static constexpr int block = 96 + 32 * kEpiWarps;   // producers A and B, MMA issuer, epilogue warps
-  static auto kernel() { return tc_gemm_kernel<kElemBytes, kBN, kStages, kEpiWarps, kWindowed, kCta, kNSplit, kSlabs, kPartial, kQuad>; }
+  static auto kernel() { return tc_gemm_kernel<kElemBytes, kBN, kStages, kEpiWarps, kWindowed, kCta, kNSplit, kSlabs, kPartial>; }
 
   static cudaError_t configure() {
     static bool configured[64] = {};
@@ -1461,8 +1419,8 @@ struct TcConfig {
     return cudaSuccess;
   }
 
-  // Clusters (CTA pairs, or pairs of pairs) that can be resident at once: a cluster needs its SMs
-  // free in one cluster-capable group, which on some parts leaves a few SMs unused.
+  // CTA pairs that can be resident at once (pairs need two free SMs of one cluster-capable
+  // group; on some parts that leaves a few SMs unpaired).
   static int max_pairs(int sm_count) {
     static int cached[64] = {};
     int dev = 0;
@@ -1475,13 +1433,13 @@ struct TcConfig {
     cfg.dynamicSmemBytes = smem;
     cudaLaunchAttribute attr;
     attr.id = cudaLaunchAttributeClusterDimension;
-    attr.val.clusterDim.x = cluster; attr.val.clusterDim.y = 1; attr.val.clusterDim.z = 1;
+    attr.val.clusterDim.x = 2; attr.val.clusterDim.y = 1; attr.val.clusterDim.z = 1;
     cfg.attrs = &attr;
     cfg.numAttrs = 1;
     int n = 0;
     if (cudaOccupancyMaxActiveClusters(&n, kernel(), &cfg) != cudaSuccess || n <= 0) {
       cudaGetLastError();
-      n = sm_count / cluster;
+      n = sm_count / 2;
     }
     if (dev < 64) cached[dev] = n;
     return n;
@@ -1493,7 +1451,7 @@ struct TcConfig {
     if (e != cudaSuccess) return e;
     int64_t groups = (kCta == 2) ? max_pairs(sm_count) : sm_count;
     if (p.total_tiles < groups) groups = p.total_tiles;
-    const int grid = (int)groups * cluster;
+    const int grid = (int)groups * kCta;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((unsigned)grid);
     cfg.blockDim = dim3(block);
@@ -1501,14 +1459,14 @@ struct TcConfig {
     cfg.stream = stream;
     cudaLaunchAttribute attr[2];
     attr[0].id = cudaLaunchAttributeClusterDimension;
-    attr[0].val.clusterDim.x = cluster; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+    attr[0].val.clusterDim.x = kCta; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
     attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = overlap_launches() ? 2 : 1;
     e = cudaLaunchKernelEx(&cfg, kernel(), maps[0], maps[1], maps[2], maps[3], outs, p);
     if (rec) {
-      rec->tile_m = BM * cluster; rec->tile_n = kBN * kNSplit; rec->tile_k = kSlabs * 128 / kElemBytes; rec->stages = kStages;
+      rec->tile_m = BM * kCta; rec->tile_n = kBN * kNSplit; rec->tile_k = kSlabs * 128 / kElemBytes; rec->stages = kStages;
       rec->grid = grid; rec->block = block; rec->launches++;
     }
     // cudaLaunchKernelEx reports this launch's own failure; the thread's sticky-less "last error"
@@ -1822,19 +1780,6 @@ cudaError_t launch_elementwise(const void* fn, void** args, int blocks, cudaStre
   return cudaLaunchKernelExC(&cfg, fn, args);
 }
 
-// Device memory of the current device (not another device's memory mapped here, not host or
-// managed memory).
-static bool on_this_device(const void* ptr) {
-  cudaPointerAttributes at;
-  if (cudaPointerGetAttributes(&at, ptr) != cudaSuccess) {
-    cudaGetLastError();
-    return false;
-  }
-  int dev = -1;
-  if (cudaGetDevice(&dev) != cudaSuccess) return false;
-  return at.type == cudaMemoryTypeDevice && at.device == dev;
-}
-
 // Everything about a product that does not depend on the stream: pre-pass jobs, tensor maps,
 // kernel parameters, which kernel.  `*scratch_needed` receives the work-area bytes the product
 // needs; when the area given is smaller, nothing else is filled in and cudaErrorInvalidValue
@@ -1943,19 +1888,14 @@ cudaError_t prepare_tc(const GemmProblem& p, unsigned int* status_word, void* sc
   if (tp.chunk_kb > tp.num_k_blocks) tp.chunk_kb = tp.num_k_blocks;
   const bool wide = shape == SHAPE_WIDE;
   const int tile_n = wide ? 2 * bn : bn;
-  // Pairs of pairs (the build with loads shared by a cluster only): 512-wide tiles of a product
-  // whose operands lie in this device's own memory, checked here for every product - such a load
-  // must never read another device's memory.
-  const bool quad = kClusterMulticastBuilt && wide && n_extra == 0 && !cut && p.M >= 2 * BM * cta &&
-                    on_this_device(a_hi) && on_this_device(b_hi);
-  tp.tile_rows = BM * cta * (quad ? 2 : 1);
+  tp.tile_rows = BM * cta;
   tp.tiles_m = (int)((p.M + tp.tile_rows - 1) / tp.tile_rows);
   tp.tiles_n = (int)((p.N + tile_n - 1) / tile_n);
   tp.total_tiles = (int64_t)tp.tiles_m * tp.tiles_n * p.batch * plan.splits;
   // Tile rows that share a sweep over the columns.  A wave of CTA pairs then touches g tile rows
   // of A and (pairs / g) tile columns of B; the bytes are least near g = sqrt(pairs x tile_n / tile_m):
   // 8 for 256x256 pairs, 12-16 for 256x512 (measured at 16384^3: 6.51 ms with 8, 6.35 with 16).
-  tp.group_m = tun.group_m > 0 ? tun.group_m : quad ? 8 : wide ? 16 : 16 / cta;
+  tp.group_m = tun.group_m > 0 ? tun.group_m : wide ? 16 : 16 / cta;
   tp.a_mn_major = p.a_mn_major; tp.b_mn_major = p.b_mn_major;
   tp.status = status_word;
   tp.skip_input_wait = 0;
@@ -2017,13 +1957,7 @@ cudaError_t prepare_tc(const GemmProblem& p, unsigned int* status_word, void* sc
     else if (shape == SHAPE_C1_128) fn = TcConfig<2, 128, 3, 4, false, 1, 1, 2, true>::launch;
     else return cudaErrorInvalidValue;
   } else if (!f32) {
-    if (quad) {
-#ifdef HC_CLUSTER_MULTICAST
-      fn = TcConfig<2, 256, 4, 4, false, 2, 2, 1, false, true>::launch;
-#else
-      return cudaErrorInvalidValue;
-#endif
-    } else if (wide && tun.wide_epi8) fn = TcConfig<2, 256, 4, 8, false, 2, 2>::launch;
+    if (wide && tun.wide_epi8) fn = TcConfig<2, 256, 4, 8, false, 2, 2>::launch;
     else if (wide) fn = TcConfig<2, 256, 4, 4, false, 2, 2>::launch;
     else if (shape == SHAPE_PAIR_128) fn = TcConfig<2, 128, 4, 4, false, 2, 1, 2>::launch;
     else if (shape == SHAPE_PAIR_64) fn = TcConfig<2, 64, 4, 4, false, 2, 1, 2>::launch;
