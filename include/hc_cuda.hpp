@@ -4,6 +4,10 @@
 // The reference's host language is Swift; where no Swift toolchain exists this is the compiled
 // host side.  Names and argument meaning follow the reference:
 //   Backend::matmul / batchedMatmul          Sources/Honeycrisp/Backend.swift:650-669
+//   Backend::constant, cast                  Backend.swift:787-791, 489-494
+//   add, columnSum, transpose, linear        what a Linear layer needs either side of its product
+//                                            (Trainable.swift:530-546; Backend.swift:178-209, 524-531;
+//                                            Index.swift:359-362), in the shapes it needs them
 //   TensorData (byteCount, wait, onCPU)      Sources/Honeycrisp/Tensor.swift:69-85
 //   BackendError (allocationFailed, kernelFailed, notImplemented)   Backend.swift:6-16
 // A primitive a backend does not override throws BackendError::notImplemented, the reference's
@@ -66,6 +70,43 @@ class Backend {
     (void)cols; (void)dtype;
     throw BackendError::notImplemented("batchedMatmul");
   }
+  /// `count` elements equal to `value` (Backend.swift:787-791).
+  virtual std::shared_ptr<TensorData> constant(float value, size_t count, DType dtype) {
+    (void)value; (void)count; (void)dtype;
+    throw BackendError::notImplemented("constant");
+  }
+  /// Elementwise conversion between element types (Backend.swift:489-494).
+  virtual std::shared_ptr<TensorData> cast(const std::shared_ptr<TensorData>& a, size_t count, DType inType,
+                                           DType outType) {
+    (void)a; (void)count; (void)inType; (void)outType;
+    throw BackendError::notImplemented("cast");
+  }
+  /// binaryOp(.add) on two buffers of equal shape (Backend.swift:178-209): gradient accumulation.
+  virtual std::shared_ptr<TensorData> add(const std::shared_ptr<TensorData>& a, const std::shared_ptr<TensorData>& b,
+                                          size_t count, DType dtype) {
+    (void)a; (void)b; (void)count; (void)dtype;
+    throw BackendError::notImplemented("add");
+  }
+  /// reduce(.sum) over the leading axis of a [rows, cols] buffer (Backend.swift:524-531): a bias gradient.
+  virtual std::shared_ptr<TensorData> columnSum(const std::shared_ptr<TensorData>& a, int64_t rows, int64_t cols,
+                                                DType dtype) {
+    (void)a; (void)rows; (void)cols; (void)dtype;
+    throw BackendError::notImplemented("columnSum");
+  }
+  /// The materialised `t()` of the last two axes (Index.swift:359-362).
+  virtual std::shared_ptr<TensorData> transpose(const std::shared_ptr<TensorData>& a, int64_t matrixCount, int64_t rows,
+                                                int64_t cols, DType dtype) {
+    (void)a; (void)matrixCount; (void)rows; (void)cols; (void)dtype;
+    throw BackendError::notImplemented("transpose");
+  }
+  /// x[rows, inCount] * weight[inCount, outCount] + bias[outCount]; `bias` may be null
+  /// (Linear.callAsFunction, Trainable.swift:530-546).
+  virtual std::shared_ptr<TensorData> linear(const std::shared_ptr<TensorData>& x, const std::shared_ptr<TensorData>& weight,
+                                             const std::shared_ptr<TensorData>& bias, int64_t rows, int64_t inCount,
+                                             int64_t outCount, DType dtype) {
+    (void)x; (void)weight; (void)bias; (void)rows; (void)inCount; (void)outCount; (void)dtype;
+    throw BackendError::notImplemented("linear");
+  }
 };
 
 class CUDABackend;
@@ -116,7 +157,9 @@ class CUDAData : public TensorData {
       throw BackendError(BackendError::Kind::kernelFailed, hc_last_error(ctx_));
     return done;
   }
-  void keep(std::shared_ptr<TensorData> a, std::shared_ptr<TensorData> b) { inputs_ = {std::move(a), std::move(b)}; }
+  void keep(std::shared_ptr<TensorData> a, std::shared_ptr<TensorData> b = nullptr, std::shared_ptr<TensorData> c = nullptr) {
+    inputs_ = {std::move(a), std::move(b), std::move(c)};
+  }
 
  private:
   hc_ctx* ctx_;
@@ -170,9 +213,90 @@ class CUDABackend : public Backend {
     return out;
   }
 
+  std::shared_ptr<TensorData> constant(float value, size_t count, DType dtype) override {
+    auto out = std::make_shared<CUDAData>(ctx_, count * byteSize(dtype));
+    check(hc_constant(ctx_, hcType(dtype, "constant"), value, (int64_t)count, out->pointer()));
+    out->mark();
+    return out;
+  }
+
+  std::shared_ptr<TensorData> cast(const std::shared_ptr<TensorData>& a, size_t count, DType inType,
+                                   DType outType) override {
+    const hc_dtype from = hcType(inType, "cast"), to = hcType(outType, "cast");
+    auto da = onDevice(a, count, inType);
+    auto out = std::make_shared<CUDAData>(ctx_, count * byteSize(outType));
+    check(hc_cast(ctx_, from, to, da->pointer(), (int64_t)count, out->pointer()));
+    out->mark();
+    out->keep(da);
+    return out;
+  }
+
+  std::shared_ptr<TensorData> add(const std::shared_ptr<TensorData>& a, const std::shared_ptr<TensorData>& b, size_t count,
+                                  DType dtype) override {
+    const hc_dtype dt = hcType(dtype, "add");
+    auto da = onDevice(a, count, dtype), db = onDevice(b, count, dtype);
+    auto out = std::make_shared<CUDAData>(ctx_, count * byteSize(dtype));
+    check(hc_add(ctx_, dt, da->pointer(), db->pointer(), (int64_t)count, out->pointer()));
+    out->mark();
+    out->keep(da, db);
+    return out;
+  }
+
+  std::shared_ptr<TensorData> columnSum(const std::shared_ptr<TensorData>& a, int64_t rows, int64_t cols,
+                                        DType dtype) override {
+    const hc_dtype dt = hcType(dtype, "columnSum");
+    auto da = onDevice(a, (size_t)(rows * cols), dtype);
+    auto out = std::make_shared<CUDAData>(ctx_, (size_t)cols * byteSize(dtype));
+    check(hc_column_sum(ctx_, dt, da->pointer(), rows, cols, out->pointer()));
+    out->mark();
+    out->keep(da);
+    return out;
+  }
+
+  std::shared_ptr<TensorData> transpose(const std::shared_ptr<TensorData>& a, int64_t matrixCount, int64_t rows,
+                                        int64_t cols, DType dtype) override {
+    const hc_dtype dt = hcType(dtype, "transpose");
+    auto da = onDevice(a, (size_t)(matrixCount * rows * cols), dtype);
+    auto out = std::make_shared<CUDAData>(ctx_, (size_t)(matrixCount * rows * cols) * byteSize(dtype));
+    check(hc_transpose(ctx_, dt, matrixCount, da->pointer(), rows, cols, out->pointer()));
+    out->mark();
+    out->keep(da);
+    return out;
+  }
+
+  std::shared_ptr<TensorData> linear(const std::shared_ptr<TensorData>& x, const std::shared_ptr<TensorData>& weight,
+                                     const std::shared_ptr<TensorData>& bias, int64_t rows, int64_t inCount,
+                                     int64_t outCount, DType dtype) override {
+    const hc_dtype dt = hcType(dtype, "linear");
+    auto dx = onDevice(x, (size_t)(rows * inCount), dtype), dw = onDevice(weight, (size_t)(inCount * outCount), dtype);
+    std::shared_ptr<CUDAData> db = bias ? onDevice(bias, (size_t)outCount, dtype) : nullptr;
+    auto out = std::make_shared<CUDAData>(ctx_, (size_t)(rows * outCount) * byteSize(dtype));
+    check(hc_linear_forward(ctx_, dt, dx->pointer(), dw->pointer(), db ? db->pointer() : nullptr, rows, inCount, outCount,
+                            out->pointer()));
+    out->mark();
+    out->keep(dx, dw, db);
+    return out;
+  }
+
   hc_ctx* context() const { return ctx_; }
 
  private:
+  static hc_dtype hcType(DType t, const char* op) {
+    if (t == DType::float16) return HC_F16;
+    if (t == DType::float32) return HC_F32;
+    throw BackendError::notImplemented(std::string(op) + " for int64");
+  }
+  /// The operand as a buffer of this backend holding at least `count` elements; another backend's
+  /// data is staged through onCPU (Sources/Honeycrisp/BackendMPS.swift:585-620).
+  std::shared_ptr<CUDAData> onDevice(const std::shared_ptr<TensorData>& a, size_t count, DType dtype) {
+    auto d = std::dynamic_pointer_cast<CUDAData>(a);
+    if (!d) {
+      auto h = a->onCPU();
+      d = std::static_pointer_cast<CUDAData>(collection(h.data(), h.size() / byteSize(dtype), dtype));
+    }
+    if (d->byteCount() < count * byteSize(dtype)) throw std::invalid_argument("operand smaller than its stated shape");
+    return d;
+  }
   void check(hc_status st) {
     if (st == HC_OK) return;
     const std::string msg = hc_last_error(ctx_);

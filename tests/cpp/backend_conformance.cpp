@@ -1,5 +1,6 @@
 // The reference's matrix-product known-answer tests (Sources/HCTestUtils/BackendTests.swift:
-// 684-725, 769-783) replayed through the C++ mirror of the Backend interface.  Prints
+// 684-725, 769-783) replayed through the C++ mirror of the Backend interface, followed by the
+// operations either side of a Linear product on the same small exact values.  Prints
 // "conformance ok" and exits 0 when every check holds.
 #include <cmath>
 #include <cstdio>
@@ -123,6 +124,32 @@ int main() {
       for (int k = 0; k < 64; k++) want += a[i * 64 + k] * b[k * 128 + j];   // small integers: exact
       CHECK(got[i * 128 + j] == want);
     }
+  }
+  {  // either side of a Linear product: constant, cast, linear = product + broadcast add, the bias
+     // gradient (column sum), gradient accumulation (add), the materialised transpose
+    for (DType dt : {DType::float32, DType::float16}) {
+      auto ones = download(be.constant(1.0f, 37, dt), dt);
+      CHECK(ones.size() == 37);
+      for (float v : ones) CHECK(v == 1.0f);
+      auto w = upload(be, y, dt);                       // [3,4]
+      auto xd = upload(be, x, dt);                      // [2,3]
+      auto bias = upload(be, {10, 20, 30, 40}, dt);
+      auto h = download(be.linear(xd, w, bias, 2, 3, 4, dt), dt);
+      for (int i = 0; i < 2; i++) for (int j = 0; j < 4; j++) CHECK(h[i * 4 + j] == expect[i * 4 + j] + 10.0f * (j + 1));
+      CHECK(download(be.linear(xd, w, nullptr, 2, 3, 4, dt), dt) == expect);
+      auto g = upload(be, {8, 7, 6, 5, 4, 3, 2, 1}, dt);   // upstream gradient [2,4]
+      CHECK(download(be.columnSum(g, 2, 4, dt), dt) == (std::vector<float>{12, 10, 8, 6}));
+      CHECK(download(be.add(g, g, 8, dt), dt) == (std::vector<float>{16, 14, 12, 10, 8, 6, 4, 2}));
+      CHECK(download(be.transpose(g, 1, 2, 4, dt), dt) == transposed({8, 7, 6, 5, 4, 3, 2, 1}, 2, 4));
+    }
+    auto half = be.cast(upload(be, {1.5f, -2.0f, 65520.0f}, DType::float32), 3, DType::float32, DType::float16);
+    auto hv = download(half, DType::float16);
+    CHECK(hv[0] == 1.5f && hv[1] == -2.0f && std::isinf(hv[2]));
+    CHECK(download(be.cast(half, 2, DType::float16, DType::float32), DType::float32)[0] == 1.5f);
+    bool threw = false;
+    try { be.constant(0.0f, 4, DType::int64); }
+    catch (const BackendError& e) { threw = e.kind == BackendError::Kind::notImplemented; }
+    CHECK(threw);
   }
   std::printf("conformance ok\n");
   return 0;
