@@ -60,18 +60,60 @@ def load_peaks():
 
 
 class ClockSampler:
-    """Samples nvidia-smi clocks and throttle reasons of one GPU while the timed region runs."""
+    """SM clock, power and throttle reasons of one GPU, sampled while the timed region runs.
+
+    Read through NVML inside this process every few milliseconds (reading only; nothing is set), so
+    that even a timed region of tens of milliseconds gets samples that lie inside it; where NVML
+    cannot be loaded, an `nvidia-smi --query-gpu ... -lms` child process is used instead, whose
+    start-up alone can outlast a short region."""
 
     FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
               "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
               "clocks_event_reasons.sw_power_cap")
+    NAMES = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
 
     def __init__(self, index: int):
         self.index = index
         self.proc = None
         self.lines = []
+        self.nvml = None
+        self.handle = None
+        self.samples = []      # (sm MHz, power W, reasons bit mask) from NVML
+        self.running = False
+        self.max_mhz = None
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            handle = None
+            try:
+                import torch
+                props = torch.cuda.get_device_properties(index)
+                bus = "%08x:%02x:%02x.0" % (props.pci_domain_id, props.pci_bus_id, props.pci_device_id)
+                handle = pynvml.nvmlDeviceGetHandleByPciBusId(bus.encode())
+            except Exception:  # noqa: BLE001
+                handle = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = float(pynvml.nvmlDeviceGetMaxClockInfo(handle, pynvml.NVML_CLOCK_SM))
+            self.nvml, self.handle = pynvml, handle
+        except Exception:  # noqa: BLE001
+            self.nvml = None
+
+    def _poll(self):
+        n, h = self.nvml, self.handle
+        reasons_fn = getattr(n, "nvmlDeviceGetCurrentClocksEventReasons", None) or n.nvmlDeviceGetCurrentClocksThrottleReasons
+        while self.running:
+            try:
+                self.samples.append((float(n.nvmlDeviceGetClockInfo(h, n.NVML_CLOCK_SM)),
+                                     n.nvmlDeviceGetPowerUsage(h) / 1000.0, int(reasons_fn(h))))
+            except Exception:  # noqa: BLE001
+                break
+            time.sleep(0.003)
 
     def start(self):
+        if self.nvml:
+            self.running = True
+            self.thread = threading.Thread(target=self._poll, daemon=True)
+            self.thread.start()
+            return
         try:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", "-i", str(self.index), f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
@@ -85,7 +127,26 @@ class ClockSampler:
         for line in self.proc.stdout:
             self.lines.append(line.strip())
 
+    def _stop_nvml(self):
+        self.running = False
+        self.thread.join(timeout=2)
+        n = self.nvml
+        bits = {"hw_slowdown": getattr(n, "nvmlClocksEventReasonHwSlowdown", 0x8),
+                "hw_thermal_slowdown": getattr(n, "nvmlClocksEventReasonHwThermalSlowdown", 0x40),
+                "sw_thermal_slowdown": getattr(n, "nvmlClocksEventReasonSwThermalSlowdown", 0x20),
+                "sw_power_cap": getattr(n, "nvmlClocksEventReasonSwPowerCap", 0x4)}
+        if not self.samples:
+            return {"sm_mhz": None, "sm_max_mhz": self.max_mhz, "reasons": ["no samples"]}
+        sm = [x[0] for x in self.samples]
+        power = [x[1] for x in self.samples]
+        reasons = sorted(name for name, bit in bits.items() if any(x[2] & bit for x in self.samples))
+        return {"sm_mhz": statistics.median(sm), "sm_min_mhz": min(sm), "sm_max_mhz": self.max_mhz,
+                "power_w_max": max(power), "samples": len(sm), "reasons": reasons,
+                "source": "NVML, every 3 ms inside the timed region"}
+
     def stop(self):
+        if self.nvml and self.running:
+            return self._stop_nvml()
         if not self.proc:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
         time.sleep(0.15)
@@ -95,7 +156,6 @@ class ClockSampler:
         except subprocess.TimeoutExpired:
             self.proc.kill()
         sm, mx, power, reasons = [], [], [], set()
-        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
         for line in self.lines:
             parts = [x.strip() for x in line.split(",")]
             if len(parts) < 7:
@@ -104,7 +164,7 @@ class ClockSampler:
                 sm.append(float(parts[0])); mx.append(float(parts[1])); power.append(float(parts[2]))
             except ValueError:
                 continue
-            for name, val in zip(names, parts[3:7]):
+            for name, val in zip(self.NAMES, parts[3:7]):
                 if val == "Active":
                     reasons.add(name)
         if not sm:
@@ -113,7 +173,7 @@ class ClockSampler:
         cut = (max(power) + min(power)) / 2
         loaded = [s for s, p in zip(sm, power) if p >= cut] or sm
         return {"sm_mhz": statistics.median(loaded), "sm_max_mhz": max(mx), "power_w_max": max(power),
-                "samples": len(sm), "reasons": sorted(reasons)}
+                "samples": len(sm), "reasons": sorted(reasons), "source": "nvidia-smi -lms 50"}
 
 
 def bind_near_gpu(local):
