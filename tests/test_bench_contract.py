@@ -34,3 +34,46 @@ def test_reference_arm_under_a_multi_rank_launch_runs_on_rank_zero_only():
                           "--steps", "1", "--warmup", "0"], capture_output=True, text=True, timeout=120, cwd=ROOT, env=env)
     assert out.returncode == 0, out.stderr[-2000:]
     assert out.stdout.strip() == ""        # the other ranks exit without work and without output
+
+
+def _load_bench():
+    import importlib.util
+    spec = importlib.util.spec_from_file_location("hc_bench", os.path.join(ROOT, "bench.py"))
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    return mod
+
+
+def test_clock_sampler_summarises_what_a_fake_nvml_reports():
+    """The sampler only reads; here against a fake NVML: samples taken while it runs, the power-cap
+    bit named, the median and the minimum clock reported."""
+    import time
+    import types
+    bench = _load_bench()
+    clocks = iter([1965, 1800, 1500, 1500, 1500] + [1400] * 10000)
+    fake = types.SimpleNamespace(NVML_CLOCK_SM=1, nvmlDeviceGetClockInfo=lambda h, c: next(clocks),
+                                 nvmlDeviceGetPowerUsage=lambda h: 987000,
+                                 nvmlDeviceGetCurrentClocksEventReasons=lambda h: 0x4,
+                                 nvmlClocksEventReasonSwPowerCap=0x4)
+    s = bench.ClockSampler(0)
+    s.nvml, s.handle, s.max_mhz = fake, object(), 1965.0
+    s.start()
+    time.sleep(0.06)
+    out = s.stop()
+    assert out["samples"] >= 5 and out["sm_max_mhz"] == 1965.0 and out["sm_min_mhz"] == 1400.0
+    assert 1400.0 <= out["sm_mhz"] <= 1965.0
+    assert out["reasons"] == ["sw_power_cap"] and abs(out["power_w_max"] - 987.0) < 1e-6
+
+
+def test_clock_sampler_without_nvml_or_nvidia_smi_says_so():
+    bench = _load_bench()
+    s = bench.ClockSampler(0)
+    if s.nvml is None:     # no GPU here: NVML does not initialise
+        old = os.environ.get("PATH", "")
+        os.environ["PATH"] = ""
+        try:
+            s.start()
+            out = s.stop()
+        finally:
+            os.environ["PATH"] = old
+        assert out["sm_mhz"] is None and out["reasons"]
