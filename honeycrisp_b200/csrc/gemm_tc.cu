@@ -29,7 +29,9 @@
 //                                        spans both SMs; two accumulator buffers alternate;
 //   256 x 512 on a CTA pair              long float16 contractions: two MMAs per k-step share the
 //                                        A slab and fill both accumulator buffers - least operand
-//                                        traffic per flop, no epilogue overlap.
+//                                        traffic per flop; the drain overlaps only half by half
+//                                        (the left half under the last k-steps' right-half MMAs,
+//                                        the right half under the next tile's first left-half ones).
 // Every copy is an ordinary per-CTA TMA load into the CTA's own shared memory.
 // The shape is chosen per launch by a cost model (plan_tc: waves of tiles x clocks per tile).
 // When even the smallest shape fills less than one wave and the contraction is long, the
@@ -41,7 +43,8 @@
 // bit of the instruction descriptor.
 //
 // float32 runs as 3xTF32: x = hi + lo with hi, lo representable in TF32, and
-// A*B ~= A_lo*B_hi + A_hi*B_lo + A_hi*B_hi.  The split operands live in a scratch area; every
+// A*B ~= A_lo*B_hi + A_hi*B_lo + A_hi*B_hi.  hi is the operand itself (the tensor core reads a
+// float32 operand truncated to TF32), lo is written to a scratch area by a pre-pass; every
 // pipeline slot holds the hi and lo slabs of both operands, loaded once, and the issuer runs
 // the three products of the slab from them into the same accumulator.  Tensor-core accumulation
 // truncates instead of rounding, so a long contraction is cut into windows: every window
