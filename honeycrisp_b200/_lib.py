@@ -135,8 +135,10 @@ def load(diagnostics: bool = False) -> ctypes.CDLL:
     override = os.environ.get("HC_CUDA_LIB")     # a differently built libhccuda.so, for A/B runs
     if override and not diagnostics:
         path = override
-    elif not os.path.exists(path) or os.environ.get("HC_CUDA_REBUILD") == "1":
+    elif os.environ.get("HC_CUDA_REBUILD") == "1":
         path = _build.build(force=True, diagnostics=diagnostics)
+    elif not os.path.exists(path):
+        path = _build.build(diagnostics=diagnostics)   # a missing library counts as stale
     elif _build._stale(path):
         # Sources are newer than the library: rebuild if a compiler is at hand, otherwise say so
         # and use what is there (a copied tree can carry arbitrary file times).

@@ -49,11 +49,25 @@ def build(force: bool = False, verbose: bool = False, diagnostics: bool = False)
     path = DIAG_LIB_PATH if diagnostics else LIB_PATH
     if not force and not _stale(path):
         return path
-    cmd = ([_nvcc()] + NVCC_FLAGS + (["-DHC_DIAGNOSTICS"] if diagnostics else []) +
-           (["-Xptxas", "-v"] if verbose else []) + ["-ldl", "-o", path] + sources())
-    if verbose:
-        print(" ".join(cmd), file=sys.stderr)
-    subprocess.check_call(cmd)
+    # Several processes may get here at once (one rank per GPU, all finding the library missing):
+    # one builds, into a file of its own that replaces the library in one step; the others wait
+    # and find it up to date.
+    import fcntl
+    with open(path + ".lock", "w") as lock:
+        fcntl.flock(lock, fcntl.LOCK_EX)
+        if not force and not _stale(path):
+            return path
+        tmp = f"{path}.tmp.{os.getpid()}"
+        cmd = ([_nvcc()] + NVCC_FLAGS + (["-DHC_DIAGNOSTICS"] if diagnostics else []) +
+               (["-Xptxas", "-v"] if verbose else []) + ["-ldl", "-o", tmp] + sources())
+        if verbose:
+            print(" ".join(cmd), file=sys.stderr)
+        try:
+            subprocess.check_call(cmd)
+            os.replace(tmp, path)
+        finally:
+            if os.path.exists(tmp):
+                os.remove(tmp)
     return path
 
 
